@@ -1,0 +1,184 @@
+// Row-wise kernels of the decoder step: embedding gather, RMSNorm, rotary position
+// encoding fused with the cache write, and the standalone SiLU-gate.
+//
+// The residual stream is float32 in both precisions; `T` is the activation/storage
+// type (float or bf16).  Statistics, rotation and SiLU are computed in float32.
+#include "common.cuh"
+
+using namespace ri;
+
+// ----------------------------------------------------------------------------
+// embedding: out[t, :] = table[ids[t], :]        (transformer.rs:74-75)
+// ----------------------------------------------------------------------------
+template <typename T>
+__global__ void embed_gather_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+                                    float* __restrict__ out, int hidden) {
+    const int t = blockIdx.x;
+    const T* row = table + (size_t)ids[t] * hidden;
+    float* o = out + (size_t)t * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_f32<T>(row[i]);
+}
+
+RI_API int ri_embed_gather(const void* table, int dtype, const int* ids, float* out, int n_tokens,
+                           int hidden, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (dtype == RI_F32)
+        embed_gather_kernel<float><<<n_tokens, 256, 0, stream>>>((const float*)table, ids, out, hidden);
+    else if (dtype == RI_BF16)
+        embed_gather_kernel<__nv_bfloat16><<<n_tokens, 256, 0, stream>>>((const __nv_bfloat16*)table, ids, out, hidden);
+    else
+        return fail("embed_gather: unknown dtype %d", dtype);
+    return check_launch("embed_gather");
+}
+
+// ----------------------------------------------------------------------------
+// RMSNorm (math.rs:237-256): ss = sum x^2; rms = sqrt(ss/n + eps); y = x * (1/rms) * w.
+// `rows` (may be null) picks the input row of each output row, so the final norm
+// runs on the wanted positions only.
+// ----------------------------------------------------------------------------
+template <typename T>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                               const int* __restrict__ rows, T* __restrict__ out, int n, float eps) {
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    const float* xr = x + (size_t)(rows ? rows[r] : r) * n;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        float v = xr[i];
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float rms = sqrtf(ss / (float)n + eps);
+    const float scale = 1.0f / rms;
+    T* o = out + (size_t)r * n;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) o[i] = from_f32<T>(xr[i] * scale * w[i]);
+}
+
+RI_API int ri_rmsnorm(const float* x, const float* w, const int* rows, void* out, int out_dtype,
+                      int n_rows, int n, float eps, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    const int threads = n >= 1024 ? 256 : 128;
+    if (out_dtype == RI_F32)
+        rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(x, w, rows, (float*)out, n, eps);
+    else if (out_dtype == RI_BF16)
+        rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(x, w, rows, (__nv_bfloat16*)out, n, eps);
+    else
+        return fail("rmsnorm: unknown dtype %d", out_dtype);
+    return check_launch("rmsnorm");
+}
+
+// ----------------------------------------------------------------------------
+// Rotary position encoding + cache write.
+//
+// qkv is [n_tokens, ld] with q at column 0 (n_heads*hd), k at q_dim, v at q_dim + kv_dim.
+// Every q head and every k head is rotated with the table row of the token's position
+// (attention.rs:78-87, rope.rs:88-97); q is rotated in place, rotated k and plain v go
+// to the token's cache position (attention.rs:89-90, kv_cache.rs:52-75).
+//
+// style 0: pairs (i, i + hd/2); style 1: pairs (2i, 2i+1), the reference's.
+// Cache layer layout: [page][kv head][page_size][hd]; page of position p of sequence b is
+// page_table[slot(b) * max_pages + p / page_size].
+// ----------------------------------------------------------------------------
+template <typename T>
+__global__ void rope_cache_write_kernel(T* __restrict__ qkv, int ld, const float* __restrict__ cos_t,
+                                        const float* __restrict__ sin_t, const int* __restrict__ token_pos,
+                                        const int* __restrict__ token_seq, const int* __restrict__ seq_slot,
+                                        const int* __restrict__ page_table, int max_pages,
+                                        T* __restrict__ kcache, T* __restrict__ vcache,
+                                        int n_heads, int n_kv_heads, int hd, int page_size, int style,
+                                        int write_kv) {
+    const int t = blockIdx.x;
+    const int pos = token_pos[t];
+    const int half = hd >> 1;
+    T* row = qkv + (size_t)t * ld;
+    const float* c = cos_t + (size_t)pos * half;
+    const float* s = sin_t + (size_t)pos * half;
+    const int q_dim = n_heads * hd, kv_dim = n_kv_heads * hd;
+
+    size_t cache_base = 0;
+    if (write_kv) {
+        const int slot = seq_slot[token_seq[t]];
+        const int page = page_table[(size_t)slot * max_pages + pos / page_size];
+        cache_base = ((size_t)page * n_kv_heads * page_size + (pos % page_size)) * hd;
+    }
+    const size_t head_stride = (size_t)page_size * hd;
+
+    // q heads: rotate in place
+    for (int idx = threadIdx.x; idx < n_heads * half; idx += blockDim.x) {
+        const int h = idx / half, i = idx % half;
+        const int i0 = style == 0 ? i : 2 * i;
+        const int i1 = style == 0 ? i + half : 2 * i + 1;
+        T* v = row + h * hd;
+        const float x0 = to_f32<T>(v[i0]), x1 = to_f32<T>(v[i1]);
+        v[i0] = from_f32<T>(x0 * c[i] - x1 * s[i]);
+        v[i1] = from_f32<T>(x0 * s[i] + x1 * c[i]);
+    }
+    if (!write_kv) return;
+    // k heads: rotate into the cache
+    for (int idx = threadIdx.x; idx < n_kv_heads * half; idx += blockDim.x) {
+        const int h = idx / half, i = idx % half;
+        const int i0 = style == 0 ? i : 2 * i;
+        const int i1 = style == 0 ? i + half : 2 * i + 1;
+        const T* v = row + q_dim + h * hd;
+        const float x0 = to_f32<T>(v[i0]), x1 = to_f32<T>(v[i1]);
+        T* dst = kcache + cache_base + h * head_stride;
+        dst[i0] = from_f32<T>(x0 * c[i] - x1 * s[i]);
+        dst[i1] = from_f32<T>(x0 * s[i] + x1 * c[i]);
+    }
+    // v heads: copy
+    for (int idx = threadIdx.x; idx < kv_dim; idx += blockDim.x) {
+        const int h = idx / hd, d = idx % hd;
+        vcache[cache_base + h * head_stride + d] = row[q_dim + kv_dim + idx];
+    }
+}
+
+RI_API int ri_rope_cache_write(void* qkv, int dtype, int ld, const float* cos_t, const float* sin_t,
+                               const int* token_pos, const int* token_seq, const int* seq_slot,
+                               const int* page_table, int max_pages, void* kcache, void* vcache,
+                               int n_tokens, int n_heads, int n_kv_heads, int hd, int page_size,
+                               int style, int write_kv, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (hd % 2) return fail("rope_cache_write: head_dim %d is odd", hd);
+    if (style != 0 && style != 1) return fail("rope_cache_write: unknown style %d", style);
+    const int work = n_heads * hd / 2;
+    const int threads = work >= 256 ? 256 : (work >= 128 ? 128 : 64);
+    if (dtype == RI_F32)
+        rope_cache_write_kernel<float><<<n_tokens, threads, 0, stream>>>(
+            (float*)qkv, ld, cos_t, sin_t, token_pos, token_seq, seq_slot, page_table, max_pages,
+            (float*)kcache, (float*)vcache, n_heads, n_kv_heads, hd, page_size, style, write_kv);
+    else if (dtype == RI_BF16)
+        rope_cache_write_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(
+            (__nv_bfloat16*)qkv, ld, cos_t, sin_t, token_pos, token_seq, seq_slot, page_table, max_pages,
+            (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, n_heads, n_kv_heads, hd, page_size, style, write_kv);
+    else
+        return fail("rope_cache_write: unknown dtype %d", dtype);
+    return check_launch("rope_cache_write");
+}
+
+// ----------------------------------------------------------------------------
+// SiLU-gate: out[t, i] = silu(gu[t, i]) * gu[t, inter + i]      (mlp.rs:35-43)
+// ----------------------------------------------------------------------------
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, size_t total) {
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const size_t t = idx / inter;
+    const int i = (int)(idx % inter);
+    const T* row = gu + t * 2 * (size_t)inter;
+    out[idx] = from_f32<T>(silu_f32(to_f32<T>(row[i])) * to_f32<T>(row[inter + i]));
+}
+
+RI_API int ri_silu_mul(const void* gu, void* out, int dtype, int n_tokens, int inter, cudaStream_t stream) {
+    const size_t total = (size_t)n_tokens * inter;
+    if (total == 0) return 0;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (dtype == RI_F32)
+        silu_mul_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gu, (float*)out, inter, total);
+    else if (dtype == RI_BF16)
+        silu_mul_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter, total);
+    else
+        return fail("silu_mul: unknown dtype %d", dtype);
+    return check_launch("silu_mul");
+}
+
+RI_DEFINE_LAST_ERROR()

@@ -1,0 +1,115 @@
+"""What one step knows about its batch, and the scratch buffers kernels write into."""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+
+
+class Workspace:
+    """Named scratch buffers that live across steps, so a step allocates nothing once its
+    shapes have been seen (and their addresses stay put for CUDA graphs).  A buffer is
+    reused by every layer that asks for the same name: the stream orders the uses."""
+
+    def __init__(self, device):
+        self.device = torch.device(device)
+        self._flat: dict = {}
+
+    def get(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= int(s)
+        key = (name, dtype)
+        flat = self._flat.get(key)
+        if flat is None or flat.numel() < n:
+            flat = torch.empty(max(n, 1), dtype=dtype, device=self.device)
+            self._flat[key] = flat
+        return flat[:n].view(*shape)
+
+    def bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in self._flat.values())
+
+
+@dataclass
+class StepContext:
+    """A packed batch: T tokens of B sequences, sequence after sequence, no padding.
+
+    token_ids[t], token_pos[t] (absolute position in its sequence), token_seq[t] (which of
+    the B sequences), seq_slot[b] (cache slot), seq_start[b] (cached positions before the
+    step), seq_len[b] (after it), cu_seqlens[b] (first token of sequence b; [B+1]),
+    logit_rows[r] (tokens whose logits are wanted).  All int32 on the device."""
+    n_tokens: int
+    n_seqs: int
+    token_ids: torch.Tensor
+    token_pos: torch.Tensor
+    token_seq: torch.Tensor
+    seq_slot: torch.Tensor
+    seq_start: torch.Tensor
+    seq_len: torch.Tensor
+    cu_seqlens: torch.Tensor
+    logit_rows: torch.Tensor
+    n_logit_rows: int
+    max_new: int                  # most tokens any sequence brings in this step
+    max_len: int                  # longest sequence after the step
+    all_single: bool              # every sequence brings exactly one token (a decode step)
+    page_table: torch.Tensor
+    page_size: int
+    dtype: torch.dtype
+    device: torch.device
+    workspace: Workspace
+    extras: dict = field(default_factory=dict)
+
+    def buffer(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
+        return self.workspace.get(name, shape, dtype)
+
+
+def pack_step(starts: list, tokens: list, wants: list) -> tuple:
+    """Host side of a step: flatten B token lists into the int32 arrays of StepContext.
+
+    starts[b]  positions already cached for sequence b
+    tokens[b]  its new tokens
+    wants[b]   indices into tokens[b] whose logits are wanted
+    Returns (meta: np.int32 array, layout: dict name -> (offset, count), scalars: dict)."""
+    n_seqs = len(tokens)
+    counts = [len(t) for t in tokens]
+    n_tokens = sum(counts)
+    cu = np.zeros(n_seqs + 1, dtype=np.int64)
+    np.cumsum(counts, out=cu[1:])
+    n_rows = sum(len(w) for w in wants)
+    sizes = [("token_ids", n_tokens), ("token_pos", n_tokens), ("token_seq", n_tokens),
+             ("seq_slot", n_seqs), ("seq_start", n_seqs), ("seq_len", n_seqs),
+             ("cu_seqlens", n_seqs + 1), ("logit_rows", n_rows)]
+    layout, off = {}, 0
+    for name, cnt in sizes:
+        layout[name] = (off, cnt)
+        off += cnt
+    meta = np.zeros(max(off, 1), dtype=np.int32)
+
+    def view(name):
+        o, c = layout[name]
+        return meta[o:o + c]
+
+    ids, pos, seq = view("token_ids"), view("token_pos"), view("token_seq")
+    rows = view("logit_rows")
+    r = 0
+    for b in range(n_seqs):
+        lo, hi = int(cu[b]), int(cu[b + 1])
+        ids[lo:hi] = tokens[b]
+        pos[lo:hi] = np.arange(starts[b], starts[b] + counts[b], dtype=np.int32)
+        seq[lo:hi] = b
+        for w in wants[b]:
+            if not (0 <= w < counts[b]):
+                raise ValueError(f"sequence {b}: wanted place {w} is outside its {counts[b]} tokens")
+            rows[r] = lo + w
+            r += 1
+    view("seq_start")[:] = starts
+    view("seq_len")[:] = [s + c for s, c in zip(starts, counts)]
+    view("cu_seqlens")[:] = cu
+    scalars = {
+        "n_tokens": n_tokens, "n_seqs": n_seqs, "n_logit_rows": n_rows,
+        "max_new": max(counts) if counts else 0,
+        "max_len": max((s + c for s, c in zip(starts, counts)), default=0),
+        "all_single": bool(counts) and all(c == 1 for c in counts),
+    }
+    return meta, layout, scalars

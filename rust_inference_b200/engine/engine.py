@@ -1,0 +1,178 @@
+"""The engine: a model, its cache, and ONE step function.
+
+`step` takes a batch of sequences with their next tokens (whole prompts of unequal
+length, or one token each, or any continuation in between), runs exactly those tokens
+as one packed batch against what earlier steps left in the cache, and returns float32
+logits at the wanted places.  The reference's step is `Transformer::forward(token_id,
+position, ...)` for one token of one sequence (transformer.rs:63-98), with the position
+passed by the caller (model.rs:361-363); here the position comes from the slot's length.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from ..cache.sequence_cache import SequenceCache
+from ..config.registry import get_architecture, load_config
+from ..weights.loader import random_tensors, read_model_tensors
+from .context import StepContext, Workspace, pack_step
+from .model import DecoderModel
+
+_DTYPES = {"float32": torch.float32, "fp32": torch.float32, "bfloat16": torch.bfloat16, "bf16": torch.bfloat16}
+
+
+def resolve_dtype(dtype) -> torch.dtype:
+    if isinstance(dtype, torch.dtype):
+        return dtype
+    try:
+        return _DTYPES[str(dtype)]
+    except KeyError:
+        raise ValueError(f"dtype must be one of {sorted(_DTYPES)}, found {dtype!r}") from None
+
+
+def require_cuda(device) -> torch.device:
+    device = torch.device(device)
+    if device.type != "cuda":
+        raise RuntimeError(f"the engine runs on a CUDA device only; {device} was asked for")
+    if not torch.cuda.is_available():
+        raise RuntimeError("no CUDA device is available; this library has no CPU path")
+    return device
+
+
+class _PinnedRing:
+    """Pinned host buffers for the per-step int32 arrays, reused round-robin; a buffer is
+    rewritten only after the copy that read it has finished."""
+
+    def __init__(self, n: int = 4):
+        self.bufs = [None] * n
+        self.events = [None] * n
+        self.i = 0
+
+    def stage(self, meta: np.ndarray, device) -> torch.Tensor:
+        i = self.i
+        self.i = (i + 1) % len(self.bufs)
+        if self.events[i] is not None:
+            self.events[i].synchronize()
+        buf = self.bufs[i]
+        if buf is None or buf.numel() < meta.size:
+            buf = torch.empty(max(1024, 2 * meta.size), dtype=torch.int32).pin_memory()
+            self.bufs[i] = buf
+        buf[:meta.size].copy_(torch.from_numpy(meta))
+        dev = buf[:meta.size].to(device, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self.events[i] = ev
+        return dev
+
+
+class Engine:
+    def __init__(self, model: DecoderModel, *, max_tokens: int, max_seq_len: int | None = None,
+                 n_slots: int | None = None):
+        self.model = model
+        self.device = require_cuda(model.device)
+        self.dtype = model.dtype
+        limit = model.spec.max_positions
+        max_seq_len = min(max_seq_len or limit, limit)
+        self.cache = SequenceCache(model.cache_requests(), max_tokens=max_tokens, max_seq_len=max_seq_len,
+                                   dtype=model.dtype, device=self.device, n_slots=n_slots)
+        self.max_seq_len = self.cache.max_seq_len
+        model.prepare(self.max_seq_len)
+        self.workspace = Workspace(self.device)
+        self._ring = _PinnedRing()
+        self.h2d_bytes = 0          # bytes of step inputs copied to the device so far
+
+    # ---- construction ----------------------------------------------------------
+    @classmethod
+    def from_pretrained(cls, model_dir: str, *, dtype="bfloat16", device="cuda", max_tokens: int = 8192,
+                        max_seq_len: int | None = None, n_slots: int | None = None) -> "Engine":
+        """Load a model folder (config.json + safetensors); the model class comes from
+        config.json's architecture name."""
+        device = require_cuda(device)
+        config = load_config(model_dir)
+        spec = get_architecture(config.architecture).build_spec(config)
+        model = DecoderModel(spec, dtype=resolve_dtype(dtype), device=device)
+        model.load(read_model_tensors(model_dir, model.declared_tensors()))
+        eng = cls(model, max_tokens=max_tokens, max_seq_len=max_seq_len, n_slots=n_slots)
+        eng.config = config
+        return eng
+
+    @classmethod
+    def from_random(cls, config, *, seed: int = 0, std: float = 0.02, dtype="bfloat16", device="cuda",
+                    max_tokens: int = 8192, max_seq_len: int | None = None,
+                    n_slots: int | None = None) -> "Engine":
+        """Random weights made on the device, without a folder (benchmarks)."""
+        device = require_cuda(device)
+        dtype = resolve_dtype(dtype)
+        spec = get_architecture(config.architecture).build_spec(config)
+        model = DecoderModel(spec, dtype=dtype, device=device)
+        model.load(random_tensors(model.declared_tensors(), seed, std=std, matrix_dtype=dtype, device=device))
+        eng = cls(model, max_tokens=max_tokens, max_seq_len=max_seq_len, n_slots=n_slots)
+        eng.config = config
+        return eng
+
+    # ---- slots -------------------------------------------------------------------
+    def alloc_slot(self) -> int:
+        return self.cache.alloc_slot()
+
+    def free_slot(self, slot: int) -> None:
+        self.cache.free_slot(slot)
+
+    # ---- the step ------------------------------------------------------------------
+    def _check_batch(self, slots, tokens, wants):
+        if len(slots) != len(tokens) or len(wants) != len(tokens):
+            raise ValueError("step: slots, tokens and wants must have one entry per sequence")
+        if not tokens:
+            raise ValueError("step: an empty batch")
+        if len(set(slots)) != len(slots):
+            raise ValueError("step: a slot appears twice in one batch")
+        vocab = self.model.spec.vocab_size
+        for b, toks in enumerate(tokens):
+            if len(toks) == 0:
+                raise ValueError(f"step: sequence {b} brings no tokens")
+            lo, hi = min(toks), max(toks)
+            if lo < 0 or hi >= vocab:
+                raise ValueError(f"step: sequence {b} has a token id outside [0, {vocab}): {lo if lo < 0 else hi}")
+
+    def make_context(self, slots, tokens, wants) -> StepContext:
+        """Reserve cache room for the step and put its arrays on the device."""
+        self._check_batch(slots, tokens, wants)
+        starts = [self.cache.length(s) for s in slots]
+        self.cache.reserve([(s, st + len(t)) for s, st, t in zip(slots, starts, tokens)])
+        meta, layout, sc = pack_step(starts, tokens, wants)
+        o, c = layout["seq_slot"]
+        meta[o:o + c] = slots
+        dev = self._ring.stage(meta, self.device)
+        self.h2d_bytes += meta.nbytes
+
+        def view(name):
+            o, c = layout[name]
+            return dev[o:o + c]
+
+        return StepContext(
+            n_tokens=sc["n_tokens"], n_seqs=sc["n_seqs"], token_ids=view("token_ids"),
+            token_pos=view("token_pos"), token_seq=view("token_seq"), seq_slot=view("seq_slot"),
+            seq_start=view("seq_start"), seq_len=view("seq_len"), cu_seqlens=view("cu_seqlens"),
+            logit_rows=view("logit_rows"), n_logit_rows=sc["n_logit_rows"], max_new=sc["max_new"],
+            max_len=sc["max_len"], all_single=sc["all_single"], page_table=self.cache.page_table,
+            page_size=self.cache.page_size, dtype=self.dtype, device=self.device, workspace=self.workspace)
+
+    def step(self, slots: list, tokens: list, wants="last"):
+        """Run one step.
+
+        slots[b]   cache slot of sequence b (from `alloc_slot`)
+        tokens[b]  its next tokens (the whole prompt, or one token, or any run of tokens)
+        wants      "last", "all", "none", or per sequence a list of places among its tokens
+        Returns float32 logits [wanted places, vocab] on the device, in the order of the
+        sequences and of their places; None if nothing is wanted."""
+        if wants == "last":
+            wants = [[len(t) - 1] for t in tokens]
+        elif wants == "all":
+            wants = [list(range(len(t))) for t in tokens]
+        elif wants == "none" or wants is None:
+            wants = [[] for _ in tokens]
+        ctx = self.make_context(slots, tokens, wants)
+        with torch.cuda.device(self.device):
+            logits = self.model.forward(ctx, self.cache)
+        for s, t in zip(slots, tokens):
+            self.cache.commit(s, self.cache.length(s) + len(t))
+        return logits

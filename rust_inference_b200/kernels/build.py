@@ -1,0 +1,151 @@
+"""Compiling the CUDA sources for sm_100a and loading them.
+
+Each file under `csrc/` becomes one shared library with a plain C ABI, compiled by nvcc
+the first time something needs it and kept beside the sources (`csrc/_build/`), so a
+model only compiles the kernels it runs.  There is no other implementation behind these
+libraries: if one cannot be built or loaded, the caller gets the error.
+"""
+from __future__ import annotations
+
+import ctypes
+import fcntl
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+CSRC = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "csrc")
+
+MODULES = {
+    "elementwise": "elementwise.cu",
+    "gemm_simt": "gemm_simt.cu",
+    "attention_generic": "attention_generic.cu",
+    "sampling": "sampling.cu",
+    "gemm_tcgen05": "gemm_tcgen05.cu",
+    "attention_mma": "attention_mma.cu",
+}
+
+NVCC_FLAGS = [
+    "-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
+    "-shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
+]
+
+
+class KernelBuildError(RuntimeError):
+    pass
+
+
+_loaded: dict[str, ctypes.CDLL] = {}
+_lock = threading.Lock()
+
+
+def _nvcc() -> str:
+    for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and os.path.isfile(cand):
+            return cand
+    raise KernelBuildError("nvcc not found: the sm_100a kernels cannot be compiled (set NVCC or PATH)")
+
+
+def _build_dir() -> str:
+    d = os.environ.get("RI_B200_BUILD_DIR") or os.path.join(CSRC, "_build")
+    try:
+        os.makedirs(d, exist_ok=True)
+        probe = os.path.join(d, f".w{os.getpid()}")
+        with open(probe, "w"):
+            pass
+        os.remove(probe)
+        return d
+    except OSError:
+        d = os.path.join(tempfile.gettempdir(), f"ri_b200_build_{os.getuid()}")
+        os.makedirs(d, exist_ok=True)
+        return d
+
+
+def _source_digest(src: str) -> str:
+    h = hashlib.sha256()
+    h.update(" ".join(NVCC_FLAGS).encode())
+    for name in [src] + sorted(f for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))):
+        with open(os.path.join(CSRC, name), "rb") as f:
+            h.update(name.encode())
+            h.update(f.read())
+    return h.hexdigest()
+
+
+def _say(msg: str) -> None:
+    print(f"[rust_inference_b200] {msg}", file=sys.stderr, flush=True)
+
+
+def library_path(module: str) -> str:
+    return os.path.join(_build_dir(), f"libri_{module}.so")
+
+
+def build(module: str, *, force: bool = False, verbose: bool = True) -> str:
+    """Compile one module if its library is missing or older than its sources."""
+    if module not in MODULES:
+        raise KernelBuildError(f"unknown kernel module {module!r}")
+    src = MODULES[module]
+    src_path = os.path.join(CSRC, src)
+    if not os.path.isfile(src_path):
+        raise KernelBuildError(f"kernel source {src_path} is missing")
+    out = library_path(module)
+    stamp = out + ".sha256"
+    digest = _source_digest(src)
+    lock_path = os.path.join(os.path.dirname(out), f".{module}.lock")
+    with open(lock_path, "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not force and os.path.isfile(out) and os.path.isfile(stamp):
+                with open(stamp) as f:
+                    if f.read().strip() == digest:
+                        return out
+            nvcc = _nvcc()
+            tmp = out + f".{os.getpid()}.tmp"
+            cmd = [nvcc] + NVCC_FLAGS + ["-I", CSRC, "-o", tmp, src_path]
+            if verbose:
+                _say(f"compiling {src} for sm_100a ...")
+            t0 = time.time()
+            proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+            last = t0
+            while True:
+                try:
+                    output, _ = proc.communicate(timeout=5)
+                    break
+                except subprocess.TimeoutExpired:
+                    if verbose and time.time() - last >= 15:
+                        last = time.time()
+                        _say(f"  still compiling {src} ({int(last - t0)} s)")
+            if proc.returncode != 0:
+                if os.path.exists(tmp):
+                    os.remove(tmp)
+                raise KernelBuildError(f"nvcc failed on {src}:\n{' '.join(cmd)}\n{output}")
+            os.replace(tmp, out)
+            with open(stamp, "w") as f:
+                f.write(digest)
+            if verbose:
+                _say(f"  built {os.path.basename(out)} in {time.time() - t0:.1f} s")
+            return out
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+
+
+def load(module: str) -> ctypes.CDLL:
+    """The module's library, built first if need be.  Raises if it cannot be had."""
+    with _lock:
+        lib = _loaded.get(module)
+        if lib is None:
+            path = build(module)
+            try:
+                lib = ctypes.CDLL(path, mode=ctypes.RTLD_LOCAL)
+            except OSError as e:
+                raise KernelBuildError(f"cannot load {path}: {e}") from None
+            lib.ri_last_error.restype = ctypes.c_char_p
+            _loaded[module] = lib
+        return lib
+
+
+def build_all(verbose: bool = True) -> list[str]:
+    return [build(m, verbose=verbose) for m in MODULES if os.path.isfile(os.path.join(CSRC, MODULES[m]))]

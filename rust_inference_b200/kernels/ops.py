@@ -1,0 +1,156 @@
+"""Python faces of the CUDA kernels: they check the tensors they are given, pass raw
+pointers and the current CUDA stream to the C ABI, and raise on any error.
+
+There is no other implementation behind them.  A tensor that is not on a CUDA device,
+a missing compiler or a library that does not load is an error, never a detour.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_int, c_float, c_void_p, c_longlong, c_ulonglong
+
+import torch
+
+from .build import load
+
+RI_F32, RI_BF16 = 0, 1
+_DTYPE_CODE = {torch.float32: RI_F32, torch.bfloat16: RI_BF16}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPE_CODE[dtype]
+    except KeyError:
+        raise KernelError(f"kernels take float32 or bfloat16, not {dtype}") from None
+
+
+def _p(t) -> c_void_p:
+    return c_void_p(t.data_ptr()) if t is not None else c_void_p(0)
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need_cuda(*tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("kernel called with a tensor that is not on a CUDA device; "
+                              "this library has no CPU path")
+
+
+def _need(cond: bool, msg: str) -> None:
+    if not cond:
+        raise KernelError(msg)
+
+
+def _call(module: str, fn: str, *args) -> None:
+    lib = load(module)
+    rc = getattr(lib, fn)(*args)
+    if rc != 0:
+        raise KernelError(f"{fn}: {lib.ri_last_error().decode()}")
+
+
+# ----------------------------------------------------------------------------
+def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t, :] = table[ids[t], :] widened to float32.  ids: int32 [T]; out: float32 [T, H]."""
+    _need_cuda(table, ids, out)
+    n, hidden = out.shape
+    _need(ids.dtype == torch.int32 and ids.numel() == n, "embed_gather: ids must be int32 [T]")
+    _need(out.dtype == torch.float32 and out.is_contiguous() and table.is_contiguous()
+          and table.shape[1] == hidden, "embed_gather: bad out/table")
+    _call("elementwise", "ri_embed_gather", _p(table), c_int(dtype_code(table.dtype)), _p(ids), _p(out),
+          c_int(n), c_int(hidden), _stream())
+    return out
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+            rows: torch.Tensor | None = None) -> torch.Tensor:
+    """out[r, :] = rmsnorm(x[rows[r] or r, :]) * weight.  x, weight float32; out float32 or bfloat16."""
+    _need_cuda(x, weight, out, rows)
+    n_rows, n = out.shape
+    _need(x.dtype == torch.float32 and weight.dtype == torch.float32, "rmsnorm: x and weight must be float32")
+    _need(x.is_contiguous() and out.is_contiguous() and x.shape[-1] == n and weight.numel() == n,
+          "rmsnorm: bad shapes")
+    if rows is not None:
+        _need(rows.dtype == torch.int32 and rows.numel() == n_rows, "rmsnorm: rows must be int32 [R]")
+    else:
+        _need(x.shape[0] >= n_rows, "rmsnorm: x has fewer rows than out")
+    _call("elementwise", "ri_rmsnorm", _p(x), _p(weight), _p(rows), _p(out), c_int(dtype_code(out.dtype)),
+          c_int(n_rows), c_int(n), c_float(eps), _stream())
+    return out
+
+
+def rope_cache_write(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, token_pos, token_seq,
+                     seq_slot, page_table: torch.Tensor, kcache, vcache, *, n_heads: int,
+                     n_kv_heads: int, head_dim: int, page_size: int, style: int, write_kv: bool) -> None:
+    """Rotate q (in place) and k by the table rows of each token's position; store rotated k and v
+    at the token's cache position.  kcache/vcache: one layer, [pages, kv heads, page_size, head_dim]."""
+    _need_cuda(qkv, cos, sin, token_pos, token_seq, seq_slot, page_table, kcache, vcache)
+    n = qkv.shape[0]
+    _need(qkv.is_contiguous() and qkv.shape[1] == (n_heads + 2 * n_kv_heads) * head_dim,
+          "rope_cache_write: qkv must be [T, (heads + 2 kv heads) * head_dim]")
+    _need(cos.dtype == torch.float32 and sin.dtype == torch.float32 and cos.shape[1] == head_dim // 2,
+          "rope_cache_write: tables must be float32 [positions, head_dim/2]")
+    if write_kv:
+        _need(kcache.dtype == qkv.dtype and vcache.dtype == qkv.dtype and kcache.is_contiguous()
+              and vcache.is_contiguous(), "rope_cache_write: cache dtype/layout")
+        _need(tuple(kcache.shape[1:]) == (n_kv_heads, page_size, head_dim), "rope_cache_write: cache shape")
+    _call("elementwise", "ri_rope_cache_write", _p(qkv), c_int(dtype_code(qkv.dtype)), c_int(qkv.shape[1]),
+          _p(cos), _p(sin), _p(token_pos), _p(token_seq), _p(seq_slot), _p(page_table),
+          c_int(page_table.shape[1]), _p(kcache), _p(vcache), c_int(n), c_int(n_heads), c_int(n_kv_heads),
+          c_int(head_dim), c_int(page_size), c_int(style), c_int(1 if write_kv else 0), _stream())
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
+    _need_cuda(gate_up, out)
+    n, inter = out.shape
+    _need(gate_up.shape == (n, 2 * inter) and gate_up.dtype == out.dtype and gate_up.is_contiguous()
+          and out.is_contiguous(), "silu_mul: bad shapes")
+    _call("elementwise", "ri_silu_mul", _p(gate_up), _p(out), c_int(dtype_code(out.dtype)), c_int(n),
+          c_int(inter), _stream())
+    return out
+
+
+# epilogues of the contractions
+EPI_STORE, EPI_STORE_F32, EPI_RESIDUAL, EPI_SILU_MUL = 0, 1, 2, 3
+
+
+def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, *,
+              bias: torch.Tensor | None = None, w2: torch.Tensor | None = None) -> torch.Tensor:
+    """out = x @ w.T with the chosen epilogue, on the FFMA pipe (float32 accumulate)."""
+    _need_cuda(x, w, out, bias, w2)
+    m, k = x.shape
+    n = w.shape[0]
+    _need(w.shape[1] == k and x.dtype == w.dtype and x.is_contiguous() and w.is_contiguous()
+          and out.is_contiguous() and out.shape == (m, n), "gemm: bad shapes")
+    want_out = torch.float32 if mode in (EPI_STORE_F32, EPI_RESIDUAL) else x.dtype
+    _need(out.dtype == want_out, f"gemm: epilogue {mode} writes {want_out}, out is {out.dtype}")
+    if bias is not None:
+        _need(bias.dtype == torch.float32 and bias.numel() == n, "gemm: bias must be float32 [N]")
+    if w2 is not None:
+        _need(w2.shape == w.shape and w2.dtype == w.dtype and w2.is_contiguous(), "gemm: second matrix")
+    _call("gemm_simt", "ri_gemm_simt", _p(x), _p(w), _p(w2), _p(bias), _p(out), c_int(dtype_code(x.dtype)),
+          c_int(mode), c_int(m), c_int(n), c_int(k), _stream())
+    return out
+
+
+def attention_generic(q: torch.Tensor, q_ld: int, kcache, vcache, page_table, token_pos, token_seq,
+                      seq_slot, out: torch.Tensor, *, n_tokens: int, n_heads: int, n_kv_heads: int,
+                      head_dim: int, page_size: int, scale: float, window: int = 0) -> torch.Tensor:
+    """Attention of every given token over its slot's cached keys 0..position (any sizes)."""
+    _need_cuda(q, kcache, vcache, page_table, token_pos, token_seq, seq_slot, out)
+    _need(q.dtype == kcache.dtype == vcache.dtype == out.dtype, "attention: dtypes differ")
+    _need(out.is_contiguous() and out.shape == (n_tokens, n_heads * head_dim), "attention: out shape")
+    rows = kcache.shape[0] * kcache.shape[1] * kcache.shape[2]
+    _call("attention_generic", "ri_attention_generic", _p(q), c_int(q_ld), _p(kcache), _p(vcache),
+          _p(page_table), c_int(page_table.shape[1]), _p(token_pos), _p(token_seq), _p(seq_slot), _p(out),
+          c_int(out.shape[1]), c_int(dtype_code(q.dtype)), c_int(n_tokens), c_int(n_heads),
+          c_int(n_kv_heads), c_int(head_dim), c_int(page_size), c_longlong(rows), c_float(scale),
+          c_int(window), _stream())
+    return out

@@ -1,0 +1,120 @@
+"""Fetching a model's tensors from its folder by name, and the random-weights mode.
+
+The reference reads every tensor into a map and then takes them out by name, failing
+on the first missing one (model.rs:157-203) and never checking a shape against the
+config (model.rs:205, :246-249).  Here the model declares every tensor it wants with
+its shape; the folder is compared with that declaration as a whole, and ONE error lists
+all missing tensors, all unexpected ones, every wrong shape and every unsupported dtype.
+"""
+from __future__ import annotations
+
+import json
+import os
+import zlib
+from typing import Iterator, Mapping
+
+import torch
+
+from ..parts.spec import TensorSpec
+from .safetensors_io import ModelFiles, write_safetensors
+
+
+class WeightError(ValueError):
+    """The folder's tensors do not match what the model declares."""
+
+    def __init__(self, model_dir, missing, unexpected, wrong_shape, bad_dtype):
+        self.missing = list(missing)
+        self.unexpected = list(unexpected)
+        self.wrong_shape = list(wrong_shape)      # (name, expected, found)
+        self.bad_dtype = list(bad_dtype)          # (name, dtype name)
+        lines = [f"weights in {model_dir!r} do not match the model:"]
+        if self.missing:
+            lines.append(f"  missing ({len(self.missing)}): " + ", ".join(self.missing))
+        if self.unexpected:
+            lines.append(f"  unexpected ({len(self.unexpected)}): " + ", ".join(self.unexpected))
+        for name, want, got in self.wrong_shape:
+            lines.append(f"  wrong shape: {name}: expected {list(want)}, found {list(got)}")
+        for name, dt in self.bad_dtype:
+            lines.append(f"  unsupported dtype: {name}: {dt}")
+        super().__init__("\n".join(lines))
+
+
+def check_tensors(files: ModelFiles, expected: Mapping[str, TensorSpec]) -> None:
+    have = set(files.names())
+    want = set(expected)
+    missing = sorted(want - have)
+    unexpected = sorted(have - want)
+    wrong_shape, bad_dtype = [], []
+    for name in sorted(want & have):
+        if tuple(files.shape(name)) != tuple(expected[name].shape):
+            wrong_shape.append((name, expected[name].shape, files.shape(name)))
+        if not files.supported(name):
+            bad_dtype.append((name, files.dtype_name(name)))
+        elif expected[name].role != "table" and files.dtype_name(name) in ("I32", "I64"):
+            bad_dtype.append((name, files.dtype_name(name)))
+    if missing or unexpected or wrong_shape or bad_dtype:
+        raise WeightError(files.model_dir, missing, unexpected, wrong_shape, bad_dtype)
+
+
+def read_model_tensors(model_dir: str, expected: Mapping[str, TensorSpec]) -> Iterator[tuple]:
+    """Check the folder against `expected`, then yield (name, tensor) one at a time, each in
+    the precision it was stored in (bfloat16 stays bfloat16, 32-bit stays 32-bit, integer
+    tables int32)."""
+    files = ModelFiles(model_dir)
+    try:
+        check_tensors(files, expected)
+        for name in expected:
+            yield name, files.tensor(name)
+    finally:
+        files.close()
+
+
+# ----------------------------------------------------------------------------
+# random weights
+# ----------------------------------------------------------------------------
+
+def _tensor_seed(seed: int, name: str) -> int:
+    # keyed by name, so the numbers do not depend on the order tensors are made in
+    return (int(seed) * 1_000_003 + zlib.crc32(name.encode("utf-8"))) % (2 ** 63 - 1)
+
+
+def random_tensors(expected: Mapping[str, TensorSpec], seed: int, *, std: float = 0.02,
+                   matrix_dtype: torch.dtype = torch.bfloat16, device="cpu") -> Iterator[tuple]:
+    """Yield (name, tensor): matrices ~ N(0, std) in `matrix_dtype`, biases ~ N(0, std) and
+    norm weights 1.0 in float32, integer tables zero."""
+    device = torch.device(device)
+    for name, spec in expected.items():
+        gen = torch.Generator(device=device)
+        gen.manual_seed(_tensor_seed(seed, name))
+        if spec.role == "table":
+            t = torch.zeros(spec.shape, dtype=torch.int32, device=device)
+        elif spec.init == "ones":
+            t = torch.ones(spec.shape, dtype=torch.float32, device=device)
+        elif spec.init == "zeros":
+            t = torch.zeros(spec.shape, dtype=torch.float32, device=device)
+        elif spec.init == "normal":
+            t = torch.empty(spec.shape, dtype=torch.float32, device=device).normal_(0.0, std, generator=gen)
+        else:
+            raise ValueError(f"{name}: unknown init {spec.init!r}")
+        if spec.role == "matrix":
+            t = t.to(matrix_dtype)
+        yield name, t
+
+
+def write_random_model(model_dir: str, config, seed: int, *, std: float = 0.02,
+                       matrix_dtype: torch.dtype = torch.bfloat16) -> str:
+    """Random-weights mode: make a model folder (config.json, model.safetensors) from a
+    typed config and a seed.  Returns the folder."""
+    from ..config.registry import get_architecture
+    from ..engine.model import declared_tensors
+
+    arch = get_architecture(config.architecture)
+    spec = arch.build_spec(config)
+    expected = declared_tensors(spec)
+    os.makedirs(model_dir, exist_ok=True)
+    tensors = dict(random_tensors(expected, seed, std=std, matrix_dtype=matrix_dtype))
+    write_safetensors(os.path.join(model_dir, "model.safetensors"), tensors,
+                      metadata={"format": "pt", "seed": seed})
+    with open(os.path.join(model_dir, "config.json"), "w", encoding="utf-8") as f:
+        json.dump(config.to_dict(), f, indent=2)
+    return model_dir
