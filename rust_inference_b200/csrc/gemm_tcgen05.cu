@@ -1,0 +1,423 @@
+// out[tokens, features] = X[tokens, K] * W[features, K]^T for bf16 operands on the
+// 5th-generation tensor cores: tcgen05.mma with the accumulator in tensor memory,
+// operands brought to shared memory by TMA (128-byte swizzle), float32 accumulation.
+//
+// The product is computed transposed: the MMA's M dimension runs over 128 *features*
+// (rows of W, the A operand), its N dimension over TN *tokens* (rows of X, the B
+// operand), TN in {16, 32, 64, 128, 256}.  So a decode step with a handful of tokens
+// still fills the 128-row MMA with weights, and a prefill step uses 128 x 256 tiles.
+// Both operands are K-major, which is how the reference lays its matrices out
+// ([out, in] row-major, quant.rs:45-50) and how activations are packed.
+//
+// One output tile per CTA.  Warp 0 issues the TMA loads, warp 1 allocates tensor
+// memory and issues the MMAs (one elected thread), warps 2-5 run the epilogue: each
+// reads its 32 lanes of the accumulator with tcgen05.ld and writes the result.
+// blockIdx.z splits K; the split pieces are combined with float32 atomic adds, which
+// only the residual epilogue allows.
+//
+// Epilogues (float32 arithmetic):
+//   0  out<bf16> = acc + bias                         (q/k/v projection, attention.rs:66-76)
+//   1  out<f32>  = acc + bias                         (logits, transformer.rs:97)
+//   2  out<f32> += acc                                (o / down projection onto the residual
+//                                                      stream, transformer.rs:38-39, :47)
+//   3  out<bf16> = silu(acc) * acc2, acc2 = X W2^T    (SwiGLU, mlp.rs:35-43): two accumulators
+//                                                      fed by the same X tile
+//
+// Every wait on an mbarrier is bounded.  A wait that runs out stores a code in the
+// host-visible status word, the CTA stops issuing work, waits (bounded) for its own
+// copies in flight, frees its tensor memory and returns.
+//
+// TMA needs 16-byte row strides: K must be a multiple of 8.  Everything else (tokens,
+// features, K not a multiple of the tile) is handled by TMA's zero fill and by bounds
+// checks in the epilogue.
+#include "common.cuh"
+
+#include <cuda.h>
+
+using namespace ri;
+
+namespace {
+
+constexpr int BLOCK_F = 128;                       // features per tile (MMA M)
+constexpr int BLOCK_K = 64;                        // bf16 per k-block: one 128-byte swizzled row
+constexpr int A_BYTES = BLOCK_F * BLOCK_K * 2;     // 16 KiB
+constexpr int MAX_STAGES = 8;
+constexpr int THREADS = 192;
+constexpr uint32_t WAIT_LIMIT = 4u << 20;
+constexpr int SMEM_BUDGET = 200 * 1024;
+
+enum Status { ST_OK = 0, ST_PRODUCER_TIMEOUT = 1, ST_MMA_TIMEOUT = 2, ST_EPILOGUE_TIMEOUT = 3, ST_DRAIN_TIMEOUT = 4 };
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: false when the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (i > 128) __nanosleep(64);
+    }
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+        : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bf16),
+// written by TMA with 128-byte swizzle: 8-row groups are 1024 bytes apart (stride byte
+// offset), the leading byte offset is unused for swizzled K-major tiles, version 1
+// (Blackwell), layout type 2 (128-byte swizzle).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFF) >> 4);          // start address, bits [0, 14)
+    d |= (uint64_t)1 << 16;                          // leading byte offset (ignored), bits [16, 30)
+    d |= (uint64_t)(1024 >> 4) << 32;                // stride byte offset, bits [32, 46)
+    d |= (uint64_t)1 << 46;                          // descriptor version, bits [46, 48)
+    d |= (uint64_t)2 << 61;                          // SWIZZLE_128B, bits [61, 64)
+    return d;
+}
+
+// Instruction descriptor of kind::f16: D float32, A and B bf16, both K-major, M = 128, N = TN.
+template <int TN>
+__host__ __device__ constexpr uint32_t make_idesc() {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(BLOCK_F >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, bool accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"((uint32_t)accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void report(int* status, int code) {
+    if (status) {
+        *reinterpret_cast<volatile int*>(status) = code;
+        __threadfence_system();
+    }
+}
+
+__host__ __device__ constexpr int tmem_cols(int need) { return need <= 32 ? 32 : need <= 64 ? 64 : need <= 128 ? 128 : need <= 256 ? 256 : 512; }
+
+template <int TN, bool DUAL, int MODE>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_w2,
+               const __grid_constant__ CUtensorMap map_x, const float* __restrict__ bias, void* __restrict__ out_,
+               int n_tok, int n_feat, int K, int kb_per_split, int stages, int* status) {
+    constexpr int B_BYTES = TN * BLOCK_K * 2;
+    constexpr int STAGE_BYTES = (DUAL ? 2 : 1) * A_BYTES + B_BYTES;
+    constexpr int TMEM_COLS = tmem_cols(DUAL ? 2 * TN : TN);
+    constexpr uint32_t IDESC = make_idesc<TN>();
+
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[MAX_STAGES];
+    __shared__ __align__(8) uint64_t empty_bar[MAX_STAGES];
+    __shared__ __align__(8) uint64_t accum_bar;
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ volatile int abort_flag;
+
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;     // swizzled tiles want 1024-byte alignment
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int f0 = blockIdx.x * BLOCK_F, t0 = blockIdx.y * TN;
+    const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
+    const int kb_begin = blockIdx.z * kb_per_split;
+    const int n_kb = min(total_kb, kb_begin + kb_per_split) - kb_begin;    // >= 1 by construction of the grid
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; ++s) {
+            mbar_init(smem_u32(&full_bar[s]), 1);
+            mbar_init(smem_u32(&empty_bar[s]), 1);
+        }
+        mbar_init(smem_u32(&accum_bar), 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
+                     "r"((uint32_t)TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            int issued = 0;
+            for (int i = 0; i < n_kb; ++i) {
+                const int s = i % stages;
+                const uint32_t ph = (uint32_t)(i / stages) & 1u;
+                if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1u)) {
+                    report(status, ST_PRODUCER_TIMEOUT);
+                    abort_flag = 1;
+                    break;
+                }
+                if (abort_flag) break;
+                const uint32_t bar = smem_u32(&full_bar[s]);
+                const uint32_t stage = smem_base + (uint32_t)s * STAGE_BYTES;
+                const int kx = (kb_begin + i) * BLOCK_K;
+                mbar_expect_tx(bar, STAGE_BYTES);
+                tma_load_2d(stage, &map_w, bar, kx, f0);
+                if (DUAL) tma_load_2d(stage + A_BYTES, &map_w2, bar, kx, f0);
+                tma_load_2d(stage + (DUAL ? 2 : 1) * A_BYTES, &map_x, bar, kx, t0);
+                issued = i + 1;
+            }
+            // Do not leave while a copy into this CTA's shared memory may still be in flight:
+            // the last `stages` loads issued must have landed (immediate on the normal path).
+            for (int i = max(0, issued - stages); i < issued; ++i) {
+                const int s = i % stages;
+                const uint32_t ph = (uint32_t)(i / stages) & 1u;
+                if (!mbar_wait(smem_u32(&full_bar[s]), ph)) {
+                    report(status, ST_DRAIN_TIMEOUT);
+                    break;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            bool ok = true;
+            for (int i = 0; i < n_kb && ok; ++i) {
+                const int s = i % stages;
+                const uint32_t ph = (uint32_t)(i / stages) & 1u;
+                if (!mbar_wait(smem_u32(&full_bar[s]), ph)) {
+                    report(status, ST_MMA_TIMEOUT);
+                    abort_flag = 1;
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t stage = smem_base + (uint32_t)s * STAGE_BYTES;
+#pragma unroll
+                for (int k = 0; k < BLOCK_K / 16; ++k) {
+                    // 16 bf16 = 32 bytes further along K inside the swizzled row
+                    const uint64_t a = make_smem_desc(stage + k * 32);
+                    const uint64_t b = make_smem_desc(stage + (DUAL ? 2 : 1) * A_BYTES + k * 32);
+                    umma(tmem_base, a, b, IDESC, i > 0 || k > 0);
+                    if (DUAL) {
+                        const uint64_t a2 = make_smem_desc(stage + A_BYTES + k * 32);
+                        umma(tmem_base + TN, a2, b, IDESC, i > 0 || k > 0);
+                    }
+                }
+                umma_commit(smem_u32(&empty_bar[s]));      // frees the stage once these MMAs have read it
+            }
+            umma_commit(smem_u32(&accum_bar));            // accumulator complete (or aborted: flag says which)
+        }
+    } else {
+        // ---------------- epilogue: warps 2..5 ----------------
+        const bool landed = mbar_wait(smem_u32(&accum_bar), 0);
+        if (!landed && lane == 0) {
+            report(status, ST_EPILOGUE_TIMEOUT);
+            abort_flag = 1;
+        }
+        tc_fence_after();
+        if (landed && !abort_flag) {
+            const int lane_base = (warp & 3) * 32;             // the TMEM lanes this warp may read
+            const int f = f0 + lane_base + lane;
+            const bool f_ok = f < n_feat;
+            const float b = (bias != nullptr && f_ok) ? bias[f] : 0.f;
+            const uint32_t trow = tmem_base + ((uint32_t)lane_base << 16);
+#pragma unroll 1
+            for (int c0 = 0; c0 < TN; c0 += 16) {
+                if (t0 + c0 >= n_tok) break;                   // uniform over the warp
+                uint32_t v[16], u[16];
+                tmem_ld16(trow + c0, v);
+                if (DUAL) tmem_ld16(trow + TN + c0, u);
+                tmem_wait_ld();
+                if (f_ok) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int t = t0 + c0 + j;
+                        if (t < n_tok) {
+                            const size_t o = (size_t)t * n_feat + f;
+                            const float acc = __uint_as_float(v[j]);
+                            if (MODE == 0) {
+                                reinterpret_cast<__nv_bfloat16*>(out_)[o] = __float2bfloat16_rn(acc + b);
+                            } else if (MODE == 1) {
+                                reinterpret_cast<float*>(out_)[o] = acc + b;
+                            } else if (MODE == 2) {
+                                // one add per element and split: a reduction without a return value,
+                                // so the epilogue never waits on a load
+                                atomicAdd(reinterpret_cast<float*>(out_) + o, acc);
+                            } else {
+                                reinterpret_cast<__nv_bfloat16*>(out_)[o] =
+                                    __float2bfloat16_rn(silu_f32(acc) * __uint_as_float(u[j]));
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS)
+                     : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// A bf16 matrix [rows, K] row-major as a 2-D tensor map with a {64, box_rows} box, 128-byte swizzle,
+// zero fill outside the tensor.
+int make_map(CUtensorMap* map, const void* ptr, long long rows, long long K, int box_rows, const char* what) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return fail("gemm_tcgen05: cuTensorMapEncodeTiled is not available from the driver");
+    if ((uintptr_t)ptr % 16) return fail("gemm_tcgen05: %s is not 16-byte aligned", what);
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BLOCK_K, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail("gemm_tcgen05: cuTensorMapEncodeTiled failed for %s (code %d)", what, (int)r);
+    return 0;
+}
+
+template <int TN, bool DUAL, int MODE>
+int launch(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx, const float* bias, void* out,
+           int n_tok, int n_feat, int K, int split_k, int* status, cudaStream_t stream) {
+    constexpr int STAGE_BYTES = (DUAL ? 2 : 1) * A_BYTES + TN * BLOCK_K * 2;
+    const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
+    int stages = SMEM_BUDGET / STAGE_BYTES;
+    if (stages > MAX_STAGES) stages = MAX_STAGES;
+    if (stages > total_kb) stages = total_kb;
+    if (stages < 1) stages = 1;
+    const size_t smem = (size_t)stages * STAGE_BYTES + 1024;
+    if (split_k < 1) split_k = 1;
+    if (split_k > total_kb) split_k = total_kb;
+    int kb_per_split = (total_kb + split_k - 1) / split_k;
+    split_k = (total_kb + kb_per_split - 1) / kb_per_split;          // no empty split
+    auto kernel = gemm_tc_kernel<TN, DUAL, MODE>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BUDGET + 1024);
+        if (e != cudaSuccess) return fail("gemm_tcgen05: cannot raise dynamic shared memory: %s", cudaGetErrorString(e));
+        configured = true;
+    }
+    dim3 grid((n_feat + BLOCK_F - 1) / BLOCK_F, (n_tok + TN - 1) / TN, split_k);
+    kernel<<<grid, THREADS, smem, stream>>>(mw, mw2, mx, bias, out, n_tok, n_feat, K, kb_per_split, stages, status);
+    return check_launch("gemm_tcgen05");
+}
+
+template <bool DUAL, int MODE>
+int pick_tile(int tn, const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx, const float* bias,
+              void* out, int n_tok, int n_feat, int K, int split_k, int* status, cudaStream_t stream) {
+    switch (tn) {
+        case 16: return launch<16, DUAL, MODE>(mw, mw2, mx, bias, out, n_tok, n_feat, K, split_k, status, stream);
+        case 32: return launch<32, DUAL, MODE>(mw, mw2, mx, bias, out, n_tok, n_feat, K, split_k, status, stream);
+        case 64: return launch<64, DUAL, MODE>(mw, mw2, mx, bias, out, n_tok, n_feat, K, split_k, status, stream);
+        case 128: return launch<128, DUAL, MODE>(mw, mw2, mx, bias, out, n_tok, n_feat, K, split_k, status, stream);
+        case 256:
+            if constexpr (!DUAL)
+                return launch<256, DUAL, MODE>(mw, mw2, mx, bias, out, n_tok, n_feat, K, split_k, status, stream);
+    }
+    return fail("gemm_tcgen05: no tile of %d tokens", tn);
+}
+
+}  // namespace
+
+// The token tile a call with n_tok tokens uses.
+RI_API int ri_gemm_tcgen05_tile(int n_tok, int dual) {
+    if (n_tok <= 16) return 16;
+    if (n_tok <= 32) return 32;
+    if (n_tok <= 64) return 64;
+    if (n_tok <= 128 || dual) return 128;
+    return 256;
+}
+
+// Encode the tensor map of a bf16 matrix [rows, K] (row-major, 16-byte aligned, K a multiple of 8)
+// into the 128 bytes at `map_out` (64-byte aligned).  box_rows is 128 for a weight matrix and the
+// token tile (ri_gemm_tcgen05_tile) for activations.  Maps only depend on pointer and shape, so the
+// caller keeps them: weights encode once, activation buffers once per shape.
+RI_API int ri_gemm_tcgen05_encode(void* map_out, const void* ptr, long long rows, long long K, int box_rows) {
+    if ((uintptr_t)map_out % 64) return fail("gemm_tcgen05: tensor map storage must be 64-byte aligned");
+    if (K <= 0 || K % 8) return fail("gemm_tcgen05: K = %lld must be a positive multiple of 8 (16-byte rows for TMA)", K);
+    if (box_rows < 8 || box_rows > 256) return fail("gemm_tcgen05: box of %d rows", box_rows);
+    return make_map(reinterpret_cast<CUtensorMap*>(map_out), ptr, rows, K, box_rows, "matrix");
+}
+
+// X [n_tok, K] with map_x (box rows = the token tile), W (and W2) [n_feat, K] with map_w / map_w2 (box
+// rows 128).  `status` (may be null) is a host-visible int that receives a non-zero code if a wait ran out.
+RI_API int ri_gemm_tcgen05(const void* map_x, const void* map_w, const void* map_w2, const float* bias, void* out,
+                           int mode, int n_tok, int n_feat, int K, int split_k, int* status, cudaStream_t stream) {
+    if (n_tok <= 0 || n_feat <= 0) return 0;
+    if (K <= 0 || K % 8) return fail("gemm_tcgen05: K = %d must be a positive multiple of 8 (16-byte rows for TMA)", K);
+    if (mode < 0 || mode > 3) return fail("gemm_tcgen05: unknown epilogue mode %d", mode);
+    if (mode == 3 && map_w2 == nullptr) return fail("gemm_tcgen05: the SiLU-gate epilogue needs a second matrix");
+    if (mode == 2 && bias != nullptr) return fail("gemm_tcgen05: the residual epilogue takes no bias");
+    if (mode != 2 && split_k > 1) return fail("gemm_tcgen05: only the residual epilogue can split K");
+    const bool dual = mode == 3;
+    const int tn = ri_gemm_tcgen05_tile(n_tok, dual);
+    const CUtensorMap& mw = *reinterpret_cast<const CUtensorMap*>(map_w);
+    const CUtensorMap& mw2 = dual ? *reinterpret_cast<const CUtensorMap*>(map_w2) : mw;
+    const CUtensorMap& mx = *reinterpret_cast<const CUtensorMap*>(map_x);
+    switch (mode) {
+        case 0: return pick_tile<false, 0>(tn, mw, mw2, mx, bias, out, n_tok, n_feat, K, split_k, status, stream);
+        case 1: return pick_tile<false, 1>(tn, mw, mw2, mx, bias, out, n_tok, n_feat, K, split_k, status, stream);
+        case 2: return pick_tile<false, 2>(tn, mw, mw2, mx, bias, out, n_tok, n_feat, K, split_k, status, stream);
+        default: return pick_tile<true, 3>(tn, mw, mw2, mx, bias, out, n_tok, n_feat, K, split_k, status, stream);
+    }
+}
+
+RI_DEFINE_LAST_ERROR()

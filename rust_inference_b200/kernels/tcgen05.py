@@ -1,10 +1,103 @@
 """Python face of the tcgen05 + TMA contraction kernel (bf16 operands, float32 accumulate)."""
 from __future__ import annotations
 
+from ctypes import c_int, c_longlong, c_void_p
 
-def supports(x, w) -> bool:
-    return False
+import torch
+
+from . import ops
+from .ops import KernelError, _call, _need, _need_cuda, _p, _stream
+
+N_SMS = 148
+_status = None     # host-visible word a kernel writes when one of its bounded waits ran out
+_x_maps: dict = {}  # tensor maps of activation buffers, by (pointer, rows, K, token tile)
+
+STATUS_TEXT = {
+    1: "the TMA producer waited too long for a free stage",
+    2: "the MMA issuer waited too long for a TMA load",
+    3: "the epilogue waited too long for the accumulator",
+    4: "a TMA load did not land before the CTA had to leave",
+}
 
 
-def gemm(x, w, out, mode, ctx, bias=None, w2=None):
-    raise NotImplementedError
+def status_word() -> torch.Tensor:
+    global _status
+    if _status is None:
+        _status = torch.zeros(1, dtype=torch.int32).pin_memory()
+    return _status
+
+
+def check_status() -> None:
+    """Raise if any tensor-core kernel since the last check gave up on a wait.  Call after a
+    synchronisation point (the word lives in pinned host memory the device writes to)."""
+    if _status is not None and int(_status[0]) != 0:
+        code = int(_status[0])
+        _status[0] = 0
+        raise KernelError(f"gemm_tcgen05 gave up: {STATUS_TEXT.get(code, f'code {code}')}")
+
+
+def supports(x: torch.Tensor, w) -> bool:
+    """The kernel's alignment rule: bf16, K a multiple of 8 (16-byte rows for TMA)."""
+    return x.dtype == torch.bfloat16 and w.t.dtype == torch.bfloat16 and w.k % 8 == 0 and w.k >= 8
+
+
+def token_tile(n_tok: int, dual: bool) -> int:
+    return 16 if n_tok <= 16 else 32 if n_tok <= 32 else 64 if n_tok <= 64 else 128 if (n_tok <= 128 or dual) else 256
+
+
+def pick_split(n_tok: int, n_feat: int, k: int, dual: bool) -> int:
+    """K splits for the residual epilogue: enough CTAs to keep every SM streaming weights."""
+    tiles = -(-n_feat // 128) * -(-n_tok // token_tile(n_tok, dual))
+    kb = -(-k // 64)
+    if tiles >= N_SMS:
+        return 1
+    return max(1, min(N_SMS // tiles, kb // 8))
+
+
+def _encode(t: torch.Tensor, rows: int, k: int, box_rows: int) -> torch.Tensor:
+    m = torch.empty(128, dtype=torch.uint8)           # CPU allocations are 64-byte aligned
+    _call("gemm_tcgen05", "ri_gemm_tcgen05_encode", c_void_p(m.data_ptr()), _p(t), c_longlong(rows),
+          c_longlong(k), c_int(box_rows))
+    return m
+
+
+def weight_map(w) -> torch.Tensor:
+    if w.tc is None:
+        w.tc = _encode(w.t, w.n, w.k, 128)
+    return w.tc
+
+
+def _x_map(x: torch.Tensor, tn: int) -> torch.Tensor:
+    key = (x.data_ptr(), x.shape[0], x.shape[1], tn)
+    m = _x_maps.get(key)
+    if m is None:
+        if len(_x_maps) > 8192:
+            _x_maps.clear()
+        m = _x_maps[key] = _encode(x, x.shape[0], x.shape[1], tn)
+    return m
+
+
+def gemm(x: torch.Tensor, w, out: torch.Tensor, mode: int, ctx=None, bias=None, w2=None, split_k: int | None = None):
+    _need_cuda(x, w.t, out, bias)
+    m, k = x.shape
+    n = w.n
+    _need(w.k == k and x.dtype == torch.bfloat16 and w.t.dtype == torch.bfloat16 and x.is_contiguous()
+          and out.is_contiguous() and out.shape == (m, n), "gemm_tcgen05: bad shapes or dtypes")
+    want_out = torch.float32 if mode in (ops.EPI_STORE_F32, ops.EPI_RESIDUAL) else torch.bfloat16
+    _need(out.dtype == want_out, f"gemm_tcgen05: epilogue {mode} writes {want_out}, out is {out.dtype}")
+    if bias is not None:
+        _need(bias.dtype == torch.float32 and bias.numel() == n, "gemm_tcgen05: bias must be float32 [N]")
+    map_w2 = None
+    if w2 is not None:
+        _need((w2.n, w2.k) == (n, k) and w2.t.dtype == torch.bfloat16, "gemm_tcgen05: second matrix")
+        map_w2 = weight_map(w2)
+    if split_k is None:
+        split_k = pick_split(m, n, k, w2 is not None) if mode == ops.EPI_RESIDUAL else 1
+    if m == 0:
+        return out
+    map_x = _x_map(x, token_tile(m, w2 is not None))
+    st = status_word()
+    _call("gemm_tcgen05", "ri_gemm_tcgen05", c_void_p(map_x.data_ptr()), c_void_p(weight_map(w).data_ptr()),
+          c_void_p(map_w2.data_ptr() if map_w2 is not None else 0), _p(bias), _p(out), c_int(mode), c_int(m),
+          c_int(n), c_int(k), c_int(split_k), c_void_p(st.data_ptr()), _stream())
+    return out
