@@ -1,0 +1,59 @@
+"""The Python entry point: load a model folder, generate from token ids."""
+from __future__ import annotations
+
+from .engine.engine import Engine
+from .engine.generate import GenerationResult, Generator
+from .sampling.params import SamplerConfig
+from .sampling.sampler import Sampler
+
+
+class Model:
+    """`Model.load` and `Model.generate`, as the reference names them (model.rs:136, :332)."""
+
+    def __init__(self, engine: Engine):
+        self.engine = engine
+        self.config = getattr(engine, "config", None)
+        self.last_stats: dict = {}
+
+    @classmethod
+    def load(cls, path: str, max_seq_len: int | None = None, *, dtype: str = "bfloat16",
+             device: str = "cuda", max_tokens_in_cache: int | None = None, n_slots: int | None = None) -> "Model":
+        """path: a folder with config.json and model.safetensors (or shards with an index).
+        max_seq_len overrides the model's context length, as `--max-seq-len` does in the
+        reference (model.rs:142-144): it caps the cache and the rotary table.
+        max_tokens_in_cache: positions all live sequences may hold together (default: 8 sequences
+        of max_seq_len, at most 65,536 positions)."""
+        from .config.registry import load_config
+        cfg = load_config(path)
+        limit = getattr(cfg, "max_position_embeddings", None) or 32768
+        seq = min(max_seq_len or limit, limit)
+        if max_tokens_in_cache is None:
+            max_tokens_in_cache = min(8 * seq, max(seq, 65536))
+        return cls(Engine.from_pretrained(path, dtype=dtype, device=device, max_tokens=max_tokens_in_cache,
+                                          max_seq_len=seq, n_slots=n_slots))
+
+    @classmethod
+    def random(cls, config, *, seed: int = 0, std: float = 0.02, dtype: str = "bfloat16", device: str = "cuda",
+               max_seq_len: int | None = None, max_tokens_in_cache: int = 65536, n_slots: int | None = None) -> "Model":
+        """A model with random weights made on the device from a typed config and a seed."""
+        return cls(Engine.from_random(config, seed=seed, std=std, dtype=dtype, device=device,
+                                      max_tokens=max_tokens_in_cache, max_seq_len=max_seq_len, n_slots=n_slots))
+
+    def generate(self, prompts, max_tokens: int = 512, sampler_config: SamplerConfig | None = None,
+                 stop_ids=None, max_batch: int | None = None) -> list:
+        """prompts: a list of token-id lists (or one list of ints).  Returns one
+        `GenerationResult` per prompt.  stop_ids defaults to the model's eos ids
+        (config.json `eos_token_id`); a sampled stop id ends its sequence and is not returned
+        (model.rs:383-387).  Defaults follow the reference: max_tokens 512 (main.rs:65),
+        `SamplerConfig()` (sampler.rs:37-48)."""
+        single = len(prompts) > 0 and isinstance(prompts[0], int)
+        batch = [list(prompts)] if single else [list(p) for p in prompts]
+        cfg = sampler_config or SamplerConfig()
+        if stop_ids is None:
+            stop_ids = self.engine.model.spec.stop_ids
+        gen = Generator(self.engine, Sampler(cfg, self.engine.device), stop_ids=stop_ids, max_batch=max_batch)
+        h2d0 = self.engine.h2d_bytes
+        results = gen.generate(batch, max_tokens)
+        self.last_stats = {"steps": gen.steps, "h2d_bytes": self.engine.h2d_bytes - h2d0,
+                           "d2h_bytes": gen.d2h_bytes}
+        return results[0] if single else results

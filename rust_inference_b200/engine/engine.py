@@ -117,6 +117,13 @@ class Engine:
     def free_slot(self, slot: int) -> None:
         self.cache.free_slot(slot)
 
+    def check_device_status(self) -> None:
+        """Raise if a kernel gave up on a bounded wait since the last check.  Meaningful after a
+        synchronisation point (a device-to-host read of the step's result)."""
+        if self.dtype == torch.bfloat16:
+            from ..kernels import tcgen05
+            tcgen05.check_status()
+
     # ---- the step ------------------------------------------------------------------
     def _check_batch(self, slots, tokens, wants):
         if len(slots) != len(tokens) or len(wants) != len(tokens):

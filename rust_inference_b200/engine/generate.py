@@ -1,0 +1,136 @@
+"""The generation loop above the step function.
+
+The reference's loop (model.rs:332-478) serves one prompt: prefill token by token, then
+sample, stop check, emit, forward, up to max_tokens times.  This one serves a list of
+prompts of unequal length: as many as fit the cache start together as one batch (their
+prompts in one step), then each live sequence gets one token per step; a sequence that
+ends gives its slot back at once and the batch shrinks; when a batch is done the next
+requests start, until all are served.
+
+Kept from the reference: a sampled stop token ends the sequence and is not emitted
+(model.rs:383-387); at most max_tokens tokens are generated (model.rs:373).  Changed: a
+sequence that reaches the cache's max_seq_len ends with reason "length" instead of the
+reference's panic (kv_cache.rs:54-59), and no forward pass is run for a token that
+nothing will follow (the reference runs one, model.rs:431-438).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+
+@dataclass
+class GenerationResult:
+    tokens: list
+    finish_reason: str            # "stop" (a stop token was sampled) or "length"
+    prompt_length: int
+
+
+@dataclass
+class _Live:
+    index: int                    # which request
+    slot: int
+    prompt_length: int
+    tokens: list = field(default_factory=list)
+    history: list = field(default_factory=list)
+
+
+class Generator:
+    """engine: alloc_slot(), free_slot(slot), step(slots, tokens, "last") -> logits,
+               max_seq_len, cache.pager (for admission)
+       sampler: sample(logits, streams, counters, histories) -> int tokens (device or host)"""
+
+    def __init__(self, engine, sampler, *, stop_ids=(), max_batch: int | None = None):
+        self.engine = engine
+        self.sampler = sampler
+        self.stop_ids = frozenset(int(s) for s in stop_ids)
+        self.max_batch = max_batch
+        self.steps = 0                # model steps run (prefill and decode)
+        self.d2h_bytes = 0            # bytes of sampled tokens read back
+
+    # ---- admission: which requests start together ---------------------------------
+    def _admit(self, prompts, first: int, max_tokens: int) -> int:
+        """How many requests, starting at `first`, fit the cache together.  Every admitted
+        request has pages for its prompt plus all the tokens it may generate, so a batch
+        never runs out of room half way."""
+        pager = self.engine.cache.pager
+        page = pager.page_size
+        free_pages, free_slots = pager.free_page_count(), pager.free_slot_count()
+        n = 0
+        while first + n < len(prompts):
+            if self.max_batch is not None and n >= self.max_batch:
+                break
+            length = min(len(prompts[first + n]) + max_tokens, self.engine.max_seq_len)
+            need = -(-length // page)
+            if need > free_pages or free_slots == 0:
+                break
+            free_pages -= need
+            free_slots -= 1
+            n += 1
+        if n == 0:
+            raise RuntimeError(
+                f"request {first} (prompt of {len(prompts[first])} tokens, up to {max_tokens} more) "
+                f"does not fit the cache even alone")
+        return n
+
+    def _to_host(self, tokens) -> list:
+        if hasattr(tokens, "cpu"):
+            tokens = tokens.cpu()
+            self.d2h_bytes += tokens.numel() * tokens.element_size()
+        return [int(t) for t in (tokens.tolist() if hasattr(tokens, "tolist") else tokens)]
+
+    # ---- the loop ---------------------------------------------------------------------
+    def generate(self, prompts: list, max_tokens: int) -> list:
+        for i, p in enumerate(prompts):
+            if len(p) == 0:
+                raise ValueError(f"request {i}: empty prompt")
+            if len(p) > self.engine.max_seq_len:
+                raise ValueError(f"request {i}: prompt of {len(p)} tokens exceeds max_seq_len "
+                                 f"{self.engine.max_seq_len}")
+        results: list = [None] * len(prompts)
+        if max_tokens <= 0:
+            return [GenerationResult([], "length", len(p)) for p in prompts]
+        uses_history = getattr(getattr(self.sampler, "params", None), "uses_history", False)
+        nxt = 0
+        while nxt < len(prompts):
+            count = self._admit(prompts, nxt, max_tokens)
+            live = []
+            for i in range(nxt, nxt + count):
+                live.append(_Live(index=i, slot=self.engine.alloc_slot(), prompt_length=len(prompts[i]),
+                                  history=list(prompts[i]) if uses_history else []))
+            nxt += count
+            feed = [list(prompts[s.index]) for s in live]          # first step: whole prompts
+            try:
+                while live:
+                    logits = self.engine.step([s.slot for s in live], feed, "last")
+                    self.steps += 1
+                    sampled = self._to_host(self.sampler.sample(
+                        logits, [s.index for s in live], [len(s.tokens) for s in live],
+                        [s.history for s in live] if uses_history else None))
+                    if hasattr(self.engine, "check_device_status"):
+                        self.engine.check_device_status()
+                    still, feed = [], []
+                    for s, tok in zip(live, sampled):
+                        reason = None
+                        if tok in self.stop_ids:
+                            reason = "stop"                         # not emitted, not fed back
+                        else:
+                            s.tokens.append(tok)
+                            if uses_history:
+                                s.history.append(tok)
+                            if len(s.tokens) >= max_tokens:
+                                reason = "length"
+                            elif s.prompt_length + len(s.tokens) > self.engine.max_seq_len:
+                                reason = "length"                   # no position left to feed it at
+                        if reason is None:
+                            still.append(s)
+                            feed.append([tok])
+                        else:
+                            results[s.index] = GenerationResult(s.tokens, reason, s.prompt_length)
+                            self.engine.free_slot(s.slot)           # the slot is free for the next batch
+                            s.slot = -1
+                    live = still
+            finally:
+                for s in live:                                       # only on an exception
+                    if s.slot >= 0:
+                        self.engine.free_slot(s.slot)
+        return results

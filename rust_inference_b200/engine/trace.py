@@ -54,6 +54,7 @@ def main(argv=None) -> int:
             logits = engine.step(batch_slots, tokens, wants)
             if logits is not None:
                 arr = logits.detach().to("cpu").numpy().astype("<f4", copy=False)
+                engine.check_device_status()
                 arr.tofile(os.path.join(args.out, f"{step_no}.f32"))
         for rid in rec.get("end", []):
             if rid in slots:

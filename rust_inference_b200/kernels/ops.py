@@ -154,3 +154,22 @@ def attention_generic(q: torch.Tensor, q_ld: int, kcache, vcache, page_table, to
           c_int(n_kv_heads), c_int(head_dim), c_int(page_size), c_longlong(rows), c_float(scale),
           c_int(window), _stream())
     return out
+
+
+def sample(logits: torch.Tensor, out: torch.Tensor, *, temperature: float, top_k: int = 0, top_p: float = 1.0,
+           penalty: float = 1.0, recent: torch.Tensor | None = None, recent_count: torch.Tensor | None = None,
+           seed: int = 0, row_stream: torch.Tensor | None = None,
+           row_counter: torch.Tensor | None = None) -> torch.Tensor:
+    """One token per row of float32 logits [R, V] (overwritten).  out: int32 [R]."""
+    _need_cuda(logits, out, recent, recent_count, row_stream, row_counter)
+    rows, vocab = logits.shape
+    _need(logits.dtype == torch.float32 and logits.is_contiguous(), "sample: logits must be contiguous float32")
+    _need(out.dtype == torch.int32 and out.numel() >= rows, "sample: out must be int32 [R]")
+    for t in (recent, recent_count, row_stream, row_counter):
+        _need(t is None or (t.dtype == torch.int32 and t.is_contiguous()), "sample: index tensors must be int32")
+    _need((recent is None) == (recent_count is None), "sample: recent and recent_count go together")
+    _call("sampling", "ri_sample", _p(logits), c_int(rows), c_int(vocab), _p(out), c_float(temperature),
+          c_int(top_k), c_float(top_p), c_float(penalty), _p(recent),
+          c_int(recent.shape[1] if recent is not None else 0), _p(recent_count),
+          c_ulonglong(seed & 0xFFFFFFFFFFFFFFFF), _p(row_stream), _p(row_counter), _stream())
+    return out
