@@ -1,0 +1,275 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the library on one B200, with rooflines.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Default run: a Qwen2.5-7B-sized dense decoder (28 layers, hidden 3584, 28 heads, 4 kv
+heads, head_dim 128, intermediate 18944, vocabulary 152064, q/k/v biases, untied head)
+with random bf16 weights, a batch of 8 sequences whose prompts have seeded random lengths
+in 128..2048, in a cache of 8,192 positions per sequence.  A step is one decode step.
+
+  value     decoded tokens per second over K timed decode steps, timed on the device
+            (sampling on the device, each token fed to the next step without a host trip)
+  e2e       the same through the Python entry point (`Model.generate`): host token ids in,
+            host token ids out, every step with its host-to-device copy of the step's arrays
+            from pinned memory and a device-to-host read of the sampled tokens
+  prefill   one 2,048-token prompt in one step
+  roofline  bytes the decode step must read (every weight once, the cache of the live
+            sequences) / step time, against the measured copy bandwidth
+  points    decode tokens per second at batch 1 and batch 64
+
+Prints ONE JSON line.  Only one GPU is used: for --gpus > 1 it says so and exits with 2.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import random
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# BASELINE configs[2]: the benchmark model (sizes of the model under test, not library constants)
+MODEL = {
+    "architectures": ["Qwen2ForCausalLM"], "hidden_size": 3584, "num_hidden_layers": 28,
+    "num_attention_heads": 28, "num_key_value_heads": 4, "head_dim": 128, "intermediate_size": 18944,
+    "vocab_size": 152064, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "attention_bias": True,
+    "tie_word_embeddings": False, "max_position_embeddings": 32768,
+}
+CONTEXT = 8192
+PROMPT_MIN, PROMPT_MAX = 128, 2048
+PREFILL_TOKENS = 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                d = json.load(f)
+            return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                    "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"]))}, "measured"
+        except (KeyError, ValueError, OSError):
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons, sampled every 200 ms while the timed regions run."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.proc = None
+        self.path = os.path.join(ROOT, "gpurun_out", "bench_clocks.csv")
+
+    def start(self):
+        try:
+            os.makedirs(os.path.dirname(self.path), exist_ok=True)
+            self.out = open(self.path, "w")
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200"],
+                stdout=self.out, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.out.close()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        with open(self.path) as f:
+            for line in f:
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 7:
+                    continue
+                try:
+                    sm.append(float(parts[0]))
+                    mx.append(float(parts[1]))
+                except ValueError:
+                    continue
+                for name, val in zip(names, parts[3:7]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the model has (recorded)")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--skip-points", action="store_true", help="skip the batch-1 and batch-64 points")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "yudono/rust-inference is a Rust crate (Cargo.toml, no Python packaging): pip cannot "
+                          "install it, no Rust toolchain exists here, and its only GPU path is wgpu/WGSL, "
+                          "which needs a graphics stack: unavailable on this box"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    warmup = max(3, args.warmup)
+    steps = max(1, args.steps)
+
+    import torch
+    from rust_inference_b200 import SamplerConfig, config_from_dict
+    from rust_inference_b200.api import Model
+    from rust_inference_b200.kernels import ops
+
+    peaks, peak_source = load_peaks()
+    model_cfg = dict(MODEL)
+    layers_full = model_cfg["num_hidden_layers"]
+    if args.layers:
+        model_cfg["num_hidden_layers"] = args.layers
+    cfg = config_from_dict(model_cfg)
+    n_layers = cfg.num_hidden_layers
+
+    total_steps = warmup + steps + 2
+    biggest = 64 if not args.skip_points else args.batch
+    cache_tokens = biggest * (-(-(PROMPT_MAX + total_steps) // 64) * 64) + 4096
+    torch.cuda.set_device(0)
+    t0 = time.time()
+    model = Model.random(cfg, seed=0, dtype="bfloat16", device="cuda:0", max_seq_len=CONTEXT,
+                         max_tokens_in_cache=cache_tokens)
+    engine = model.engine
+    print(f"[bench] model ready in {time.time() - t0:.1f} s; cache {engine.cache.bytes() / 1e9:.2f} GB",
+          file=sys.stderr, flush=True)
+
+    weight_bytes = engine.model.weight_bytes(include_embedding=False)
+    kv_bytes_per_token = n_layers * 2 * cfg.kv_dim * 2
+    greedy = SamplerConfig.plain(temperature=0.0)
+
+    def make_prompts(batch, seed):
+        rng = random.Random(seed)
+        lens = [rng.randint(PROMPT_MIN, PROMPT_MAX) for _ in range(batch)]
+        return [[rng.randrange(cfg.vocab_size) for _ in range(n)] for n in lens]
+
+    def device_decode(batch, seed):
+        """Prefill `batch` prompts, then time `steps` decode steps on the device."""
+        prompts = make_prompts(batch, seed)
+        slots = [engine.alloc_slot() for _ in prompts]
+        for i in range(0, batch, 8):                       # prompts in groups, to bound scratch memory
+            engine.step(slots[i:i + 8], prompts[i:i + 8], "none")
+        first = [p[-1] for p in prompts]
+        toks = engine.decode_steps(slots, first, warmup, greedy)
+        torch.cuda.synchronize()
+        launches0 = ops.launch_count()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        toks = engine.decode_steps(slots, toks[-1].tolist(), steps, greedy)
+        e1.record()
+        torch.cuda.synchronize()
+        engine.check_device_status()
+        ms = e0.elapsed_time(e1)
+        graph = engine._graphs[batch]
+        launches = steps * (graph.launches + 1)            # the captured kernels plus the sampler
+        ctx_tokens = sum(engine.cache.length(s) for s in slots) - batch * steps / 2.0
+        for s in slots:
+            engine.free_slot(s)
+        return {"tok_s": batch * steps / (ms * 1e-3), "ms_per_step": ms / steps, "launches": launches,
+                "mean_ctx_tokens": ctx_tokens}
+
+    clocks = ClockSampler()
+    clocks.start()
+
+    main_run = device_decode(args.batch, seed=1)
+    step_s = main_run["ms_per_step"] * 1e-3
+    step_bytes = weight_bytes + main_run["mean_ctx_tokens"] * kv_bytes_per_token
+    achieved_gbs = step_bytes / step_s / 1e9
+
+    # ---- end to end through the Python entry point ----
+    prompts = make_prompts(args.batch, seed=1)
+    results = model.generate(prompts, max_tokens=warmup + steps + 1, sampler_config=greedy, stop_ids=(),
+                             record_step_times=True)
+    times = model.last_stats["step_times"]
+    # times[0] is the prefill step; times[i] the i-th decode step's tokens on the host
+    e2e_s = times[warmup + steps] - times[warmup]
+    e2e_tok_s = args.batch * steps / e2e_s
+    from rust_inference_b200.engine.context import pack_step
+    step_arrays = pack_step([0] * args.batch, [[0]] * args.batch, [[0]] * args.batch)[0]
+    h2d_per_step = step_arrays.nbytes + args.batch * 3 * 4      # the step's arrays + the sampler's rows
+    d2h_per_step = args.batch * 4                               # the sampled tokens
+    assert all(len(r.tokens) == warmup + steps + 1 for r in results)
+
+    # ---- prefill of 2,048 tokens ----
+    rng = random.Random(7)
+    prompt = [rng.randrange(cfg.vocab_size) for _ in range(PREFILL_TOKENS)]
+    pre_ms = []
+    for i in range(3 + 5):
+        slot = engine.alloc_slot()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        engine.step([slot], [prompt], "last")
+        e1.record()
+        torch.cuda.synchronize()
+        engine.free_slot(slot)
+        if i >= 3:
+            pre_ms.append(e0.elapsed_time(e1))
+    pre_ms.sort()
+    pre = pre_ms[len(pre_ms) // 2]
+    t = PREFILL_TOKENS
+    per_layer = (cfg.q_dim + 2 * cfg.kv_dim) * cfg.hidden_size + cfg.hidden_size * cfg.q_dim \
+        + 3 * cfg.intermediate_size * cfg.hidden_size
+    flops = 2.0 * t * per_layer * n_layers + n_layers * 4.0 * t * t * cfg.q_dim / 2.0 \
+        + 2.0 * cfg.vocab_size * cfg.hidden_size
+    prefill = {"value": t / (pre * 1e-3), "tokens": t, "ms": pre,
+               "frac": flops / (pre * 1e-3) / (peaks["bf16_tflops"] * 1e12)}
+
+    points = {}
+    if not args.skip_points:
+        for b in (1, 64):
+            r = device_decode(b, seed=100 + b)
+            points[f"decode_b{b}"] = r["tok_s"]
+    engine.check_device_status()
+    clock_info = clocks.stop()
+
+    line = {
+        "metric": "decode tok/s @ batch 8 (Qwen2.5-7B-sized dense decoder, random bf16 weights, 8,192-position cache)",
+        "value": main_run["tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": main_run["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random weights N(0, 0.02), seeded random token ids)",
+        "impl": "ours",
+        "config": {
+            "model": "Qwen2.5-7B-sized dense decoder", "layers": n_layers, "layers_of_model": layers_full,
+            "hidden_size": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+            "head_dim": cfg.head_dim, "intermediate_size": cfg.intermediate_size, "vocab_size": cfg.vocab_size,
+            "qkv_bias": cfg.attention_bias, "tied_embeddings": cfg.tie_word_embeddings,
+            "global_batch": args.batch, "seq_len": CONTEXT, "prompt_lengths": f"uniform {PROMPT_MIN}-{PROMPT_MAX}",
+            "mean_context": round(main_run["mean_ctx_tokens"] / args.batch, 1), "parallelism": "single GPU",
+            "l2": "inputs larger than L2 (weights read once per step)", "peaks": peak_source,
+        },
+        "e2e": {"value": e2e_tok_s, "unit": "tok/s", "h2d_bytes_per_step": round(h2d_per_step, 1),
+                "d2h_bytes_per_step": d2h_per_step},
+        "gpu_launches": main_run["launches"],
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": achieved_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved_gbs / peaks["hbm_gbs"]},
+        "points": points,
+        "clocks": clock_info,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

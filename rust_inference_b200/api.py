@@ -40,7 +40,7 @@ class Model:
                                       max_tokens=max_tokens_in_cache, max_seq_len=max_seq_len, n_slots=n_slots))
 
     def generate(self, prompts, max_tokens: int = 512, sampler_config: SamplerConfig | None = None,
-                 stop_ids=None, max_batch: int | None = None) -> list:
+                 stop_ids=None, max_batch: int | None = None, record_step_times: bool = False) -> list:
         """prompts: a list of token-id lists (or one list of ints).  Returns one
         `GenerationResult` per prompt.  stop_ids defaults to the model's eos ids
         (config.json `eos_token_id`); a sampled stop id ends its sequence and is not returned
@@ -52,8 +52,10 @@ class Model:
         if stop_ids is None:
             stop_ids = self.engine.model.spec.stop_ids
         gen = Generator(self.engine, Sampler(cfg, self.engine.device), stop_ids=stop_ids, max_batch=max_batch)
+        if record_step_times:
+            gen.step_times = []
         h2d0 = self.engine.h2d_bytes
         results = gen.generate(batch, max_tokens)
         self.last_stats = {"steps": gen.steps, "h2d_bytes": self.engine.h2d_bytes - h2d0,
-                           "d2h_bytes": gen.d2h_bytes}
+                           "d2h_bytes": gen.d2h_bytes, "step_times": gen.step_times}
         return results[0] if single else results

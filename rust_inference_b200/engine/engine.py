@@ -67,8 +67,10 @@ class _PinnedRing:
 
 class Engine:
     def __init__(self, model: DecoderModel, *, max_tokens: int, max_seq_len: int | None = None,
-                 n_slots: int | None = None):
+                 n_slots: int | None = None, use_graphs: bool = True):
         self.model = model
+        self.use_graphs = use_graphs
+        self._graphs: dict = {}
         self.device = require_cuda(model.device)
         self.dtype = model.dtype
         limit = model.spec.max_positions
@@ -84,7 +86,8 @@ class Engine:
     # ---- construction ----------------------------------------------------------
     @classmethod
     def from_pretrained(cls, model_dir: str, *, dtype="bfloat16", device="cuda", max_tokens: int = 8192,
-                        max_seq_len: int | None = None, n_slots: int | None = None) -> "Engine":
+                        max_seq_len: int | None = None, n_slots: int | None = None,
+                        use_graphs: bool = True) -> "Engine":
         """Load a model folder (config.json + safetensors); the model class comes from
         config.json's architecture name."""
         device = require_cuda(device)
@@ -92,21 +95,21 @@ class Engine:
         spec = get_architecture(config.architecture).build_spec(config)
         model = DecoderModel(spec, dtype=resolve_dtype(dtype), device=device)
         model.load(read_model_tensors(model_dir, model.declared_tensors()))
-        eng = cls(model, max_tokens=max_tokens, max_seq_len=max_seq_len, n_slots=n_slots)
+        eng = cls(model, max_tokens=max_tokens, max_seq_len=max_seq_len, n_slots=n_slots, use_graphs=use_graphs)
         eng.config = config
         return eng
 
     @classmethod
     def from_random(cls, config, *, seed: int = 0, std: float = 0.02, dtype="bfloat16", device="cuda",
                     max_tokens: int = 8192, max_seq_len: int | None = None,
-                    n_slots: int | None = None) -> "Engine":
+                    n_slots: int | None = None, use_graphs: bool = True) -> "Engine":
         """Random weights made on the device, without a folder (benchmarks)."""
         device = require_cuda(device)
         dtype = resolve_dtype(dtype)
         spec = get_architecture(config.architecture).build_spec(config)
         model = DecoderModel(spec, dtype=dtype, device=device)
         model.load(random_tensors(model.declared_tensors(), seed, std=std, matrix_dtype=dtype, device=device))
-        eng = cls(model, max_tokens=max_tokens, max_seq_len=max_seq_len, n_slots=n_slots)
+        eng = cls(model, max_tokens=max_tokens, max_seq_len=max_seq_len, n_slots=n_slots, use_graphs=use_graphs)
         eng.config = config
         return eng
 
@@ -140,8 +143,8 @@ class Engine:
             if lo < 0 or hi >= vocab:
                 raise ValueError(f"step: sequence {b} has a token id outside [0, {vocab}): {lo if lo < 0 else hi}")
 
-    def make_context(self, slots, tokens, wants) -> StepContext:
-        """Reserve cache room for the step and put its arrays on the device."""
+    def _stage(self, slots, tokens, wants):
+        """Reserve cache room for the step and put its int32 arrays on the device."""
         self._check_batch(slots, tokens, wants)
         starts = [self.cache.length(s) for s in slots]
         self.cache.reserve([(s, st + len(t)) for s, st, t in zip(slots, starts, tokens)])
@@ -150,6 +153,10 @@ class Engine:
         meta[o:o + c] = slots
         dev = self._ring.stage(meta, self.device)
         self.h2d_bytes += meta.nbytes
+        return dev, layout, sc
+
+    def make_context(self, slots, tokens, wants) -> StepContext:
+        dev, layout, sc = self._stage(slots, tokens, wants)
 
         def view(name):
             o, c = layout[name]
@@ -163,23 +170,73 @@ class Engine:
             max_len=sc["max_len"], all_single=sc["all_single"], page_table=self.cache.page_table,
             page_size=self.cache.page_size, dtype=self.dtype, device=self.device, workspace=self.workspace)
 
-    def step(self, slots: list, tokens: list, wants="last"):
+    def step(self, slots: list, tokens: list, wants="last", borrow: bool = False):
         """Run one step.
 
         slots[b]   cache slot of sequence b (from `alloc_slot`)
         tokens[b]  its next tokens (the whole prompt, or one token, or any run of tokens)
         wants      "last", "all", "none", or per sequence a list of places among its tokens
         Returns float32 logits [wanted places, vocab] on the device, in the order of the
-        sequences and of their places; None if nothing is wanted."""
+        sequences and of their places; None if nothing is wanted.  With borrow=True the result
+        may be a buffer that the next step overwrites (the generation loop consumes it at once)."""
         if wants == "last":
             wants = [[len(t) - 1] for t in tokens]
         elif wants == "all":
             wants = [list(range(len(t))) for t in tokens]
         elif wants == "none" or wants is None:
             wants = [[] for _ in tokens]
-        ctx = self.make_context(slots, tokens, wants)
+        decode = all(len(t) == 1 for t in tokens) and all(w == [0] for w in wants)
         with torch.cuda.device(self.device):
-            logits = self.model.forward(ctx, self.cache)
+            if decode and self.use_graphs:
+                # one token per sequence, logits for each: the captured step of this batch size
+                dev, _, _ = self._stage(slots, tokens, wants)
+                graph = self._graphs.get(len(slots))
+                if graph is None:
+                    from .graphs import DecodeGraph
+                    graph = self._graphs[len(slots)] = DecodeGraph(self, len(slots))
+                logits = graph.run(dev)
+                if not borrow:
+                    logits = logits.clone()
+            else:
+                ctx = self.make_context(slots, tokens, wants)
+                logits = self.model.forward(ctx, self.cache)
         for s, t in zip(slots, tokens):
             self.cache.commit(s, self.cache.length(s) + len(t))
         return logits
+
+    def decode_steps(self, slots: list, first_tokens: list, n_steps: int, sampler_config=None) -> torch.Tensor:
+        """Device-resident decoding: n_steps steps of one token per sequence in which each
+        sampled token is fed to the next step on the device, with no host round trip and no
+        stop check in between.  Returns the sampled tokens, int32 [n_steps, B], on the device.
+        The first step is fed `first_tokens`."""
+        from ..sampling.params import SamplerConfig
+        from ..kernels import ops
+        from .graphs import DecodeGraph
+        cfg = sampler_config or SamplerConfig.plain(temperature=0.0)
+        if cfg.uses_history:
+            raise ValueError("decode_steps keeps no token history: use it without a repetition penalty")
+        n = len(slots)
+        self._check_batch(slots, [[t] for t in first_tokens], [[0]] * n)
+        starts = [self.cache.length(s) for s in slots]
+        self.cache.reserve([(s, st + n_steps) for s, st in zip(slots, starts)])
+        with torch.cuda.device(self.device):
+            graph = self._graphs.get(n)
+            if graph is None:
+                graph = self._graphs[n] = DecodeGraph(self, n)
+            out = torch.empty((n_steps, n), dtype=torch.int32, device=self.device)
+            streams = torch.arange(n, dtype=torch.int32, device=self.device)
+            counters = torch.arange(n_steps, dtype=torch.int32, device=self.device).repeat_interleave(n).view(n_steps, n)
+            for i in range(n_steps):
+                meta, layout, _ = pack_step([st + i for st in starts], [[t] for t in first_tokens], [[0]] * n)
+                o, c = layout["seq_slot"]
+                meta[o:o + c] = slots
+                dev = self._ring.stage(meta, self.device)
+                self.h2d_bytes += meta.nbytes
+                graph.load_meta(dev, keep_tokens=i > 0)
+                logits = graph.launch()
+                ops.sample(logits, graph.ctx.token_ids, temperature=cfg.temperature, top_k=cfg.top_k,
+                           top_p=cfg.top_p, seed=cfg.seed, row_stream=streams, row_counter=counters[i])
+                out[i].copy_(graph.ctx.token_ids, non_blocking=True)
+        for s, st in zip(slots, starts):
+            self.cache.commit(s, st + n_steps)
+        return out

@@ -15,6 +15,7 @@ nothing will follow (the reference runs one, model.rs:431-438).
 """
 from __future__ import annotations
 
+import time
 from dataclasses import dataclass, field
 
 
@@ -44,6 +45,7 @@ class Generator:
         self.sampler = sampler
         self.stop_ids = frozenset(int(s) for s in stop_ids)
         self.max_batch = max_batch
+        self.step_times = None        # set to a list to record when each step's tokens reached the host
         self.steps = 0                # model steps run (prefill and decode)
         self.d2h_bytes = 0            # bytes of sampled tokens read back
 
@@ -101,13 +103,15 @@ class Generator:
             feed = [list(prompts[s.index]) for s in live]          # first step: whole prompts
             try:
                 while live:
-                    logits = self.engine.step([s.slot for s in live], feed, "last")
+                    logits = self.engine.step([s.slot for s in live], feed, "last", borrow=True)
                     self.steps += 1
                     sampled = self._to_host(self.sampler.sample(
                         logits, [s.index for s in live], [len(s.tokens) for s in live],
                         [s.history for s in live] if uses_history else None))
                     if hasattr(self.engine, "check_device_status"):
                         self.engine.check_device_status()
+                    if self.step_times is not None:
+                        self.step_times.append(time.perf_counter())
                     still, feed = [], []
                     for s, tok in zip(live, sampled):
                         reason = None

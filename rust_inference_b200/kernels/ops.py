@@ -48,11 +48,21 @@ def _need(cond: bool, msg: str) -> None:
         raise KernelError(msg)
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """How many kernel entry points have been called (each launches one kernel)."""
+    return _launches
+
+
 def _call(module: str, fn: str, *args) -> None:
+    global _launches
     lib = load(module)
     rc = getattr(lib, fn)(*args)
     if rc != 0:
         raise KernelError(f"{fn}: {lib.ri_last_error().decode()}")
+    _launches += 1
 
 
 # ----------------------------------------------------------------------------

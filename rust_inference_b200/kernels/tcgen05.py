@@ -58,6 +58,7 @@ def _encode(t: torch.Tensor, rows: int, k: int, box_rows: int) -> torch.Tensor:
     m = torch.empty(128, dtype=torch.uint8)           # CPU allocations are 64-byte aligned
     _call("gemm_tcgen05", "ri_gemm_tcgen05_encode", c_void_p(m.data_ptr()), _p(t), c_longlong(rows),
           c_longlong(k), c_int(box_rows))
+    ops._launches -= 1                                # encoding a map launches nothing
     return m
 
 
