@@ -1,0 +1,520 @@
+// bf16 attention over the paged cache on the tensor cores, head sizes 64 and 128.
+//
+// What it computes is attention.rs:95-121: for query head h (kv head h / n_rep),
+// scores = dot(q, k) * scale over the keys 0..position of the token's slot, softmax with
+// the maximum subtracted (math.rs:104-118), weighted sum of the values; all statistics
+// and accumulators in float32, here with an online softmax over pages of 64 keys.
+//
+// Two kernels share the building blocks (cp.async into XOR-swizzled shared tiles,
+// ldmatrix, mma.sync m16n8k16 with float32 accumulation):
+//
+//  attn_decode   one token per sequence.  A CTA serves one (sequence, kv head, split): the
+//                n_rep (<= 16) query heads that share the kv head are the 16 rows of the
+//                MMA, so each key and value is read once for all of them.  The keys of the
+//                sequence are cut into `n_splits` runs of pages so that a small batch still
+//                fills the GPU; inside a CTA the 4 warps take 16 keys of each page each.
+//                Every split writes an un-normalised partial result and its (max, sum) to
+//                scratch memory; attn_combine merges them by log-sum-exp.
+//  attn_prefill  any number of new tokens per sequence (whole prompts, or a continuation).
+//                A CTA serves 64 consecutive query tokens of one head; the warps take 16
+//                query rows each and walk the key pages up to the causal limit: the token
+//                at position p sees keys 0..p (window > 0: p-window+1..p).
+//
+// Keys and values are only ever read from the cache: the step's new tokens were written
+// there (after rotation) before attention runs, so prefill, continuation and decode use
+// one convention.
+#include "common.cuh"
+
+using namespace ri;
+
+namespace {
+
+constexpr int PAGE = 64;            // keys per cache page (fixed by the tile shapes below)
+constexpr int THREADS = 128;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// A [rows][HD] bf16 tile in shared memory; the 16-byte chunk c of row r lives at chunk
+// (c & ~7) | ((c ^ r) & 7), so that the 8 rows an ldmatrix reads hit 8 different bank groups.
+template <int HD>
+__device__ __forceinline__ uint32_t tile_off(int r, int c) {
+    return (uint32_t)(r * (HD * 2) + (((c & ~7) | ((c ^ r) & 7)) << 4));
+}
+
+// Copy `rows` rows of HD bf16 (consecutive in global memory) into a swizzled tile; all threads call.
+template <int HD>
+__device__ __forceinline__ void load_tile_async(uint32_t tile, const __nv_bfloat16* src, int rows) {
+    constexpr int CPR = HD / 8;                       // 16-byte chunks per row
+    for (int idx = threadIdx.x; idx < rows * CPR; idx += THREADS) {
+        const int r = idx / CPR, c = idx % CPR;
+        cp_async16(tile + tile_off<HD>(r, c), src + (size_t)r * HD + c * 8);
+    }
+}
+
+// S[16 x 16 keys] (+)= Q[16 x HD] * K[keys kbase .. kbase+15]^T for one warp; q: A fragments of all k-steps.
+template <int HD>
+__device__ __forceinline__ void qk_16keys(const uint32_t (*q)[4], uint32_t ktile, int kbase, float (*s)[4]) {
+    const int lane = threadIdx.x & 31;
+    const int mi = lane >> 3, rr = lane & 7;
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks) {
+        // matrices: (keys 0-7, k 0-7), (keys 0-7, k 8-15), (keys 8-15, k 0-7), (keys 8-15, k 8-15)
+        const int row = kbase + (mi >> 1) * 8 + rr;
+        const int chunk = ks * 2 + (mi & 1);
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4(ktile + tile_off<HD>(row, chunk), b0, b1, b2, b3);
+        mma_bf16(s[0], q[ks], b0, b1);
+        mma_bf16(s[1], q[ks], b2, b3);
+    }
+}
+
+// O[16 x HD] += P[16 x 16 keys] * V[keys kbase .. kbase+15]; p: one A fragment.
+template <int HD>
+__device__ __forceinline__ void pv_16keys(const uint32_t* p, uint32_t vtile, int kbase, float (*o)[4]) {
+    const int lane = threadIdx.x & 31;
+    const int mi = lane >> 3, rr = lane & 7;
+#pragma unroll
+    for (int dp = 0; dp < HD / 16; ++dp) {
+        // transposed loads: (keys 0-7, d 0-7), (keys 8-15, d 0-7), (keys 0-7, d 8-15), (keys 8-15, d 8-15)
+        const int row = kbase + (mi & 1) * 8 + rr;
+        const int chunk = dp * 2 + (mi >> 1);
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4_trans(vtile + tile_off<HD>(row, chunk), b0, b1, b2, b3);
+        mma_bf16(o[2 * dp], p, b0, b1);
+        mma_bf16(o[2 * dp + 1], p, b2, b3);
+    }
+}
+
+// Online-softmax update of one warp's 16 rows with a fresh S[16 x (NT*8)] tile (already scaled and
+// masked with -inf).  Rows g and g+8 of the thread; statistics are shared by the 4 threads of a quad.
+template <int NT, int ONT>
+__device__ __forceinline__ void softmax_update(float (*s)[4], float* m, float* l, float (*o)[4]) {
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        float mx = -INFINITY;
+#pragma unroll
+        for (int t = 0; t < NT; ++t) mx = fmaxf(mx, fmaxf(s[t][2 * half], s[t][2 * half + 1]));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m[half], mx);
+        const float base = (m_new == -INFINITY) ? 0.f : m_new;      // nothing visible yet: exp(-inf - 0) = 0
+        const float alpha = expf(m[half] - base);                    // m = -inf gives 0
+        float sum = 0.f;
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+            const float p0 = expf(s[t][2 * half] - base), p1 = expf(s[t][2 * half + 1] - base);
+            s[t][2 * half] = p0;
+            s[t][2 * half + 1] = p1;
+            sum += p0 + p1;
+        }
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        l[half] = l[half] * alpha + sum;
+        m[half] = m_new;
+#pragma unroll
+        for (int t = 0; t < ONT; ++t) {
+            o[t][2 * half] *= alpha;
+            o[t][2 * half + 1] *= alpha;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// decode: one token per sequence, split over runs of pages
+// ---------------------------------------------------------------------------------------------
+template <int HD>
+__global__ void __launch_bounds__(THREADS)
+attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_ld, const __nv_bfloat16* __restrict__ kcache,
+                   const __nv_bfloat16* __restrict__ vcache, const int* __restrict__ page_table, int max_pages,
+                   const int* __restrict__ seq_slot, const int* __restrict__ seq_len,
+                   const int* __restrict__ cu_seqlens, int n_heads, int n_kv_heads, float scale, int window,
+                   int n_splits, float* __restrict__ part_o, float* __restrict__ part_ml,
+                   __nv_bfloat16* __restrict__ out, int out_ld) {
+    constexpr int TILE = PAGE * HD * 2;                 // bytes of one K or V page tile
+    extern __shared__ __align__(128) uint8_t smem[];
+    // [2 buffers][K tile, V tile], then the Q tile [16][HD]
+    const uint32_t kv_base = smem_u32(smem);
+    const uint32_t q_tile = kv_base + 4 * TILE;
+
+    const int b = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    const int n_rep = n_heads / n_kv_heads;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
+    const int n_keys = seq_len[b];                       // the new token's key is in the cache already
+    const int token = cu_seqlens[b];
+    const int first_key = (window > 0 && n_keys - window > 0) ? n_keys - window : 0;
+    const int* pages = page_table + (size_t)seq_slot[b] * max_pages;
+
+    const int pg_lo = first_key / PAGE, pg_hi = (n_keys + PAGE - 1) / PAGE;    // pages [pg_lo, pg_hi)
+    const int per = (pg_hi - pg_lo + n_splits - 1) / n_splits;
+    const int pg_begin = pg_lo + split * per, pg_end = min(pg_hi, pg_begin + per);
+
+    // Q rows: head kvh*n_rep + r for r < n_rep, zero above
+    for (int idx = threadIdx.x; idx < 16 * (HD / 8); idx += THREADS) {
+        const int r = idx / (HD / 8), c = idx % (HD / 8);
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < n_rep) v = *reinterpret_cast<const uint4*>(q + (size_t)token * q_ld + (size_t)(kvh * n_rep + r) * HD + c * 8);
+        *reinterpret_cast<uint4*>(smem + 4 * TILE + tile_off<HD>(r, c)) = v;
+    }
+    auto issue = [&](int pg, int buf) {
+        const size_t base = ((size_t)pages[pg] * n_kv_heads + kvh) * PAGE * HD;
+        load_tile_async<HD>(kv_base + (2 * buf) * TILE, kcache + base, PAGE);
+        load_tile_async<HD>(kv_base + (2 * buf + 1) * TILE, vcache + base, PAGE);
+        cp_async_commit();
+    };
+    if (pg_begin < pg_end) issue(pg_begin, 0);
+    __syncthreads();                                      // Q tile written
+
+    uint32_t qf[HD / 16][4];
+    {
+        const int row = lane & 15, half = lane >> 4;
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks)
+            ldmatrix_x4(q_tile + tile_off<HD>(row, ks * 2 + half), qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
+    }
+
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float o[HD / 8][4];
+#pragma unroll
+    for (int t = 0; t < HD / 8; ++t) o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.f;
+
+    for (int pg = pg_begin; pg < pg_end; ++pg) {
+        const int buf = (pg - pg_begin) & 1;
+        if (pg + 1 < pg_end) {
+            issue(pg + 1, buf ^ 1);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();                                  // this page's tiles have landed for everyone
+        const uint32_t ktile = kv_base + (2 * buf) * TILE, vtile = ktile + TILE;
+        const int kbase = warp * 16;                      // this warp's 16 keys of the page
+        const int key0 = pg * PAGE + kbase;
+        if (key0 < n_keys && key0 + 16 > first_key) {
+            float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+            qk_16keys<HD>(qf, ktile, kbase, s);
+#pragma unroll
+            for (int t = 0; t < 2; ++t)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int key = key0 + t * 8 + 2 * tq + (e & 1);
+                    s[t][e] = (key < n_keys && key >= first_key) ? s[t][e] * scale : -INFINITY;
+                }
+            softmax_update<2, HD / 8>(s, m, l, o);
+            uint32_t pf[4] = {pack_bf16(s[0][0], s[0][1]), pack_bf16(s[0][2], s[0][3]),
+                              pack_bf16(s[1][0], s[1][1]), pack_bf16(s[1][2], s[1][3])};
+            pv_16keys<HD>(pf, vtile, kbase, o);
+        }
+        __syncthreads();                                  // everyone is done with this buffer
+    }
+
+    // ---- merge the 4 warps (each saw a quarter of the keys) through shared memory ----
+    float* so = reinterpret_cast<float*>(smem);           // [4][16][HD]
+    float* sml = so + 4 * 16 * HD;                        // [4][16][2]
+#pragma unroll
+    for (int t = 0; t < HD / 8; ++t) {
+        const int d = t * 8 + 2 * tq;
+        so[(warp * 16 + g) * HD + d] = o[t][0];
+        so[(warp * 16 + g) * HD + d + 1] = o[t][1];
+        so[(warp * 16 + g + 8) * HD + d] = o[t][2];
+        so[(warp * 16 + g + 8) * HD + d + 1] = o[t][3];
+    }
+    if (tq == 0) {
+        sml[((warp * 16 + g) << 1)] = m[0];
+        sml[((warp * 16 + g) << 1) + 1] = l[0];
+        sml[((warp * 16 + g + 8) << 1)] = m[1];
+        sml[((warp * 16 + g + 8) << 1) + 1] = l[1];
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < n_rep * HD; idx += THREADS) {
+        const int r = idx / HD, d = idx % HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, sml[(w * 16 + r) << 1]);
+        float L = 0.f, acc = 0.f;
+        if (M != -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float f = expf(sml[(w * 16 + r) << 1] - M);
+                L += f * sml[((w * 16 + r) << 1) + 1];
+                acc += f * so[(w * 16 + r) * HD + d];
+            }
+        }
+        const int h = kvh * n_rep + r;
+        if (n_splits == 1) {
+            out[(size_t)token * out_ld + (size_t)h * HD + d] = __float2bfloat16_rn(acc / L);
+        } else {
+            const size_t row = ((size_t)b * n_heads + h) * n_splits + split;
+            part_o[row * HD + d] = acc;
+            if (d == 0) {
+                part_ml[row * 2] = M;
+                part_ml[row * 2 + 1] = L;
+            }
+        }
+    }
+}
+
+// out[b, h, :] = sum_s exp(M_s - M) O_s / sum_s exp(M_s - M) L_s over the splits
+__global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                    const int* __restrict__ cu_seqlens, int n_heads, int hd, int n_splits,
+                                    __nv_bfloat16* __restrict__ out, int out_ld) {
+    const int b = blockIdx.x, h = blockIdx.y;
+    const size_t row0 = ((size_t)b * n_heads + h) * n_splits;
+    float M = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[(row0 + s) * 2]);
+    float L = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+        const float ms = part_ml[(row0 + s) * 2];
+        if (ms != -INFINITY) L += expf(ms - M) * part_ml[(row0 + s) * 2 + 1];
+    }
+    const float inv = 1.0f / L;
+    const int token = cu_seqlens[b];
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+        float acc = 0.f;
+        for (int s = 0; s < n_splits; ++s) {
+            const float ms = part_ml[(row0 + s) * 2];
+            if (ms != -INFINITY) acc += expf(ms - M) * part_o[(row0 + s) * hd + d];
+        }
+        out[(size_t)token * out_ld + (size_t)h * hd + d] = __float2bfloat16_rn(acc * inv);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// prefill / continuation: 64 query tokens of one head per CTA
+// ---------------------------------------------------------------------------------------------
+template <int HD>
+__global__ void __launch_bounds__(THREADS)
+attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_ld, const __nv_bfloat16* __restrict__ kcache,
+                    const __nv_bfloat16* __restrict__ vcache, const int* __restrict__ page_table, int max_pages,
+                    const int* __restrict__ seq_slot, const int* __restrict__ seq_start,
+                    const int* __restrict__ cu_seqlens, int n_heads, int n_kv_heads, float scale, int window,
+                    __nv_bfloat16* __restrict__ out, int out_ld) {
+    constexpr int TILE = PAGE * HD * 2;
+    extern __shared__ __align__(128) uint8_t smem[];
+    const uint32_t kv_base = smem_u32(smem);
+    const uint32_t q_tile = kv_base + 4 * TILE;           // [64][HD]
+
+    const int b = blockIdx.z, h = blockIdx.y;
+    const int tok0 = cu_seqlens[b], n_new = cu_seqlens[b + 1] - tok0;
+    const int q0 = blockIdx.x * 64;                       // first query (among the new tokens) of this CTA
+    if (q0 >= n_new) return;
+    const int kvh = h / (n_heads / n_kv_heads);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
+    const int start = seq_start[b];                       // positions cached before this step
+    const int* pages = page_table + (size_t)seq_slot[b] * max_pages;
+    const int rows = min(64, n_new - q0);
+
+    // positions of the CTA's first and last query
+    const int pos_lo = start + q0, pos_hi = start + q0 + rows - 1;
+    const int first_key = (window > 0 && pos_lo - window + 1 > 0) ? pos_lo - window + 1 : 0;
+    const int pg_begin = first_key / PAGE, pg_end = pos_hi / PAGE + 1;
+
+    for (int idx = threadIdx.x; idx < 64 * (HD / 8); idx += THREADS) {
+        const int r = idx / (HD / 8), c = idx % (HD / 8);
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < rows) v = *reinterpret_cast<const uint4*>(q + (size_t)(tok0 + q0 + r) * q_ld + (size_t)h * HD + c * 8);
+        *reinterpret_cast<uint4*>(smem + 4 * TILE + tile_off<HD>(r, c)) = v;
+    }
+    auto issue = [&](int pg, int buf) {
+        const size_t base = ((size_t)pages[pg] * n_kv_heads + kvh) * PAGE * HD;
+        load_tile_async<HD>(kv_base + (2 * buf) * TILE, kcache + base, PAGE);
+        load_tile_async<HD>(kv_base + (2 * buf + 1) * TILE, vcache + base, PAGE);
+        cp_async_commit();
+    };
+    issue(pg_begin, 0);
+    __syncthreads();
+
+    uint32_t qf[HD / 16][4];
+    {
+        const int row = warp * 16 + (lane & 15), half = lane >> 4;
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks)
+            ldmatrix_x4(q_tile + tile_off<HD>(row, ks * 2 + half), qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
+    }
+    // this thread's two query rows and their positions
+    const int r0 = warp * 16 + g, r1 = r0 + 8;
+    const int p0 = start + q0 + r0, p1 = start + q0 + r1;
+    const int warp_pos_lo = start + q0 + warp * 16, warp_pos_hi = warp_pos_lo + 15;
+
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float o[HD / 8][4];
+#pragma unroll
+    for (int t = 0; t < HD / 8; ++t) o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.f;
+
+    for (int pg = pg_begin; pg < pg_end; ++pg) {
+        const int buf = (pg - pg_begin) & 1;
+        if (pg + 1 < pg_end) {
+            issue(pg + 1, buf ^ 1);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const uint32_t ktile = kv_base + (2 * buf) * TILE, vtile = ktile + TILE;
+        const int key_lo = pg * PAGE;
+        // the warp skips pages none of its rows can see
+        const bool any = key_lo <= warp_pos_hi && (window <= 0 || key_lo + PAGE - 1 > warp_pos_lo - window);
+        if (any) {
+            const bool full = key_lo + PAGE - 1 <= warp_pos_lo && (window <= 0 || key_lo > warp_pos_hi - window);
+#pragma unroll
+            for (int kb = 0; kb < PAGE / 16; ++kb) {
+                float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+                qk_16keys<HD>(qf, ktile, kb * 16, s);
+#pragma unroll
+                for (int t = 0; t < 2; ++t)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int key = key_lo + kb * 16 + t * 8 + 2 * tq + (e & 1);
+                        const int pos = (e & 2) ? p1 : p0;
+                        const bool vis = full || (key <= pos && (window <= 0 || key > pos - window));
+                        s[t][e] = vis ? s[t][e] * scale : -INFINITY;
+                    }
+                softmax_update<2, HD / 8>(s, m, l, o);
+                uint32_t pf[4] = {pack_bf16(s[0][0], s[0][1]), pack_bf16(s[0][2], s[0][3]),
+                                  pack_bf16(s[1][0], s[1][1]), pack_bf16(s[1][2], s[1][3])};
+                pv_16keys<HD>(pf, vtile, kb * 16, o);
+            }
+        }
+        __syncthreads();
+    }
+
+    const float inv0 = 1.0f / l[0], inv1 = 1.0f / l[1];
+#pragma unroll
+    for (int t = 0; t < HD / 8; ++t) {
+        const int d = t * 8 + 2 * tq;
+        if (r0 < rows)
+            *reinterpret_cast<uint32_t*>(out + (size_t)(tok0 + q0 + r0) * out_ld + (size_t)h * HD + d) =
+                pack_bf16(o[t][0] * inv0, o[t][1] * inv0);
+        if (r1 < rows)
+            *reinterpret_cast<uint32_t*>(out + (size_t)(tok0 + q0 + r1) * out_ld + (size_t)h * HD + d) =
+                pack_bf16(o[t][2] * inv1, o[t][3] * inv1);
+    }
+}
+
+template <int HD>
+int launch_decode(const void* q, int q_ld, const void* kc, const void* vc, const int* page_table, int max_pages,
+                  const int* seq_slot, const int* seq_len, const int* cu_seqlens, int n_seqs, int n_heads,
+                  int n_kv_heads, float scale, int window, int n_splits, float* part_o, float* part_ml, void* out,
+                  int out_ld, cudaStream_t stream) {
+    constexpr int SMEM = 4 * PAGE * HD * 2 + 16 * HD * 2;      // also covers the merge area 4*16*HD*4 + 512
+    static_assert(4 * 16 * HD * 4 + 4 * 16 * 2 * 4 <= SMEM, "merge area must fit");
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e != cudaSuccess) return fail("attention: cannot raise dynamic shared memory: %s", cudaGetErrorString(e));
+        configured = true;
+    }
+    dim3 grid(n_seqs, n_kv_heads, n_splits);
+    attn_decode_kernel<HD><<<grid, THREADS, SMEM, stream>>>(
+        (const __nv_bfloat16*)q, q_ld, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, page_table, max_pages,
+        seq_slot, seq_len, cu_seqlens, n_heads, n_kv_heads, scale, window, n_splits, part_o, part_ml,
+        (__nv_bfloat16*)out, out_ld);
+    if (int rc = check_launch("attn_decode")) return rc;
+    if (n_splits > 1) {
+        attn_combine_kernel<<<dim3(n_seqs, n_heads), HD >= 128 ? 128 : 64, 0, stream>>>(
+            part_o, part_ml, cu_seqlens, n_heads, HD, n_splits, (__nv_bfloat16*)out, out_ld);
+        return check_launch("attn_combine");
+    }
+    return 0;
+}
+
+template <int HD>
+int launch_prefill(const void* q, int q_ld, const void* kc, const void* vc, const int* page_table, int max_pages,
+                   const int* seq_slot, const int* seq_start, const int* cu_seqlens, int n_seqs, int max_new,
+                   int n_heads, int n_kv_heads, float scale, int window, void* out, int out_ld, cudaStream_t stream) {
+    constexpr int SMEM = 4 * PAGE * HD * 2 + 64 * HD * 2;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e != cudaSuccess) return fail("attention: cannot raise dynamic shared memory: %s", cudaGetErrorString(e));
+        configured = true;
+    }
+    dim3 grid((max_new + 63) / 64, n_heads, n_seqs);
+    attn_prefill_kernel<HD><<<grid, THREADS, SMEM, stream>>>(
+        (const __nv_bfloat16*)q, q_ld, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, page_table, max_pages,
+        seq_slot, seq_start, cu_seqlens, n_heads, n_kv_heads, scale, window, (__nv_bfloat16*)out, out_ld);
+    return check_launch("attn_prefill");
+}
+
+int check_common(int hd, int page_size, int n_heads, int n_kv_heads, int q_ld, int out_ld, const void* q,
+                 const void* out) {
+    if (hd != 64 && hd != 128) return fail("attention_mma: head_dim %d is not 64 or 128", hd);
+    if (page_size != PAGE) return fail("attention_mma: cache pages of %d positions, the kernel is built for %d", page_size, PAGE);
+    if (n_kv_heads <= 0 || n_heads % n_kv_heads) return fail("attention_mma: %d heads, %d kv heads", n_heads, n_kv_heads);
+    if (q_ld % 8 || out_ld % 2 || (uintptr_t)q % 16 || (uintptr_t)out % 4)
+        return fail("attention_mma: q rows must be 16-byte aligned (ld %d), out rows 4-byte aligned (ld %d)", q_ld, out_ld);
+    return 0;
+}
+
+}  // namespace
+
+// 1 if the tensor-core kernels take this shape (the caller falls back to the generic kernel otherwise)
+RI_API int ri_attention_mma_supports(int hd, int page_size, int n_heads, int n_kv_heads, int decode) {
+    if (hd != 64 && hd != 128) return 0;
+    if (page_size != PAGE) return 0;
+    if (n_kv_heads <= 0 || n_heads % n_kv_heads) return 0;
+    if (decode && n_heads / n_kv_heads > 16) return 0;
+    return 1;
+}
+
+// Scratch for the split partial results, in floats: part_o needs n_seqs*n_heads*n_splits*hd,
+// part_ml n_seqs*n_heads*n_splits*2.  They may be null when n_splits == 1.
+RI_API int ri_attention_decode(const void* q, int q_ld, const void* kcache, const void* vcache, const int* page_table,
+                               int max_pages, const int* seq_slot, const int* seq_len, const int* cu_seqlens,
+                               void* out, int out_ld, int n_seqs, int n_heads, int n_kv_heads, int hd, int page_size,
+                               float scale, int window, int n_splits, float* part_o, float* part_ml,
+                               cudaStream_t stream) {
+    if (n_seqs <= 0) return 0;
+    if (int rc = check_common(hd, page_size, n_heads, n_kv_heads, q_ld, out_ld, q, out)) return rc;
+    if (n_heads / n_kv_heads > 16) return fail("attention_decode: %d query heads per kv head exceed 16", n_heads / n_kv_heads);
+    if (n_splits < 1 || n_splits > 65535) return fail("attention_decode: %d splits", n_splits);
+    if (n_splits > 1 && (part_o == nullptr || part_ml == nullptr)) return fail("attention_decode: splits need scratch");
+    if (n_kv_heads > 65535) return fail("attention_decode: %d kv heads exceed the grid limit", n_kv_heads);
+    if (hd == 64)
+        return launch_decode<64>(q, q_ld, kcache, vcache, page_table, max_pages, seq_slot, seq_len, cu_seqlens, n_seqs,
+                                 n_heads, n_kv_heads, scale, window, n_splits, part_o, part_ml, out, out_ld, stream);
+    return launch_decode<128>(q, q_ld, kcache, vcache, page_table, max_pages, seq_slot, seq_len, cu_seqlens, n_seqs,
+                              n_heads, n_kv_heads, scale, window, n_splits, part_o, part_ml, out, out_ld, stream);
+}
+
+RI_API int ri_attention_prefill(const void* q, int q_ld, const void* kcache, const void* vcache, const int* page_table,
+                                int max_pages, const int* seq_slot, const int* seq_start, const int* cu_seqlens,
+                                void* out, int out_ld, int n_seqs, int max_new, int n_heads, int n_kv_heads, int hd,
+                                int page_size, float scale, int window, cudaStream_t stream) {
+    if (n_seqs <= 0 || max_new <= 0) return 0;
+    if (int rc = check_common(hd, page_size, n_heads, n_kv_heads, q_ld, out_ld, q, out)) return rc;
+    if (n_heads > 65535 || n_seqs > 65535) return fail("attention_prefill: %d heads / %d sequences exceed the grid limit", n_heads, n_seqs);
+    if (hd == 64)
+        return launch_prefill<64>(q, q_ld, kcache, vcache, page_table, max_pages, seq_slot, seq_start, cu_seqlens, n_seqs,
+                                  max_new, n_heads, n_kv_heads, scale, window, out, out_ld, stream);
+    return launch_prefill<128>(q, q_ld, kcache, vcache, page_table, max_pages, seq_slot, seq_start, cu_seqlens, n_seqs,
+                               max_new, n_heads, n_kv_heads, scale, window, out, out_ld, stream);
+}
+
+RI_DEFINE_LAST_ERROR()

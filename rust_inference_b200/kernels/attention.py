@@ -1,13 +1,53 @@
-"""Attention over the paged cache: which kernel runs, by dtype, head size and step shape."""
+"""Attention over the paged cache: which kernel runs, by dtype, head size and step shape.
+
+  bfloat16, head_dim 64 or 128   tensor-core kernels (`attention_mma`): split-K over runs of
+                                 pages when every sequence brings one token, a flash-style
+                                 causal kernel otherwise
+  anything else                  the generic kernel (`attention_generic`): any head size, any
+                                 dtype, float32 arithmetic
+"""
 from __future__ import annotations
 
+import torch
+
 from . import ops
+
+N_SMS = 148
+
+
+def decode_splits(n_seqs: int, n_kv_heads: int, max_seq_len: int, page_size: int) -> int:
+    """Runs of pages per (sequence, kv head): enough CTAs for about two per SM, never more
+    runs than the longest sequence has pages.  Depends on the batch size and the cache
+    geometry only, so a captured step keeps its grid."""
+    pairs = max(1, n_seqs * n_kv_heads)
+    want = -(-2 * N_SMS // pairs)
+    return max(1, min(want, 32, -(-max_seq_len // page_size)))
 
 
 def attention(qkv, cache_layer, out, ctx, *, n_heads, n_kv_heads, head_dim, scale, window=0):
     """out[t] = softmax(q_t K^T * scale) V over the keys 0..pos(t) of t's slot.  q is the
     leading n_heads*head_dim columns of `qkv`, already rotated."""
+    q_ld = qkv.shape[1]
+    if qkv.dtype == torch.bfloat16:
+        decode = ctx.all_single
+        if ops.attention_mma_supports(head_dim, ctx.page_size, n_heads, n_kv_heads, decode):
+            if decode:
+                max_len = ctx.page_table.shape[1] * ctx.page_size
+                splits = decode_splits(ctx.n_seqs, n_kv_heads, max_len, ctx.page_size)
+                part_o = part_ml = None
+                if splits > 1:
+                    part_o = ctx.buffer("attn_part_o", (ctx.n_seqs * n_heads * splits * head_dim,), torch.float32)
+                    part_ml = ctx.buffer("attn_part_ml", (ctx.n_seqs * n_heads * splits * 2,), torch.float32)
+                return ops.attention_decode(
+                    qkv, q_ld, cache_layer.k, cache_layer.v, ctx.page_table, ctx.seq_slot, ctx.seq_len,
+                    ctx.cu_seqlens, out, n_seqs=ctx.n_seqs, n_heads=n_heads, n_kv_heads=n_kv_heads,
+                    head_dim=head_dim, page_size=ctx.page_size, scale=scale, window=window, n_splits=splits,
+                    part_o=part_o, part_ml=part_ml)
+            return ops.attention_prefill(
+                qkv, q_ld, cache_layer.k, cache_layer.v, ctx.page_table, ctx.seq_slot, ctx.seq_start,
+                ctx.cu_seqlens, out, n_seqs=ctx.n_seqs, max_new=ctx.max_new, n_heads=n_heads,
+                n_kv_heads=n_kv_heads, head_dim=head_dim, page_size=ctx.page_size, scale=scale, window=window)
     return ops.attention_generic(
-        qkv, qkv.shape[1], cache_layer.k, cache_layer.v, ctx.page_table, ctx.token_pos, ctx.token_seq,
+        qkv, q_ld, cache_layer.k, cache_layer.v, ctx.page_table, ctx.token_pos, ctx.token_seq,
         ctx.seq_slot, out, n_tokens=qkv.shape[0], n_heads=n_heads, n_kv_heads=n_kv_heads,
         head_dim=head_dim, page_size=ctx.page_size, scale=scale, window=window)

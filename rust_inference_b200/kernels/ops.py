@@ -183,3 +183,43 @@ def sample(logits: torch.Tensor, out: torch.Tensor, *, temperature: float, top_k
           c_int(recent.shape[1] if recent is not None else 0), _p(recent_count),
           c_ulonglong(seed & 0xFFFFFFFFFFFFFFFF), _p(row_stream), _p(row_counter), _stream())
     return out
+
+
+def attention_mma_supports(head_dim: int, page_size: int, n_heads: int, n_kv_heads: int, decode: bool) -> bool:
+    lib = load("attention_mma")
+    return bool(lib.ri_attention_mma_supports(c_int(head_dim), c_int(page_size), c_int(n_heads),
+                                              c_int(n_kv_heads), c_int(1 if decode else 0)))
+
+
+def attention_decode(q: torch.Tensor, q_ld: int, kcache, vcache, page_table, seq_slot, seq_len, cu_seqlens,
+                     out: torch.Tensor, *, n_seqs: int, n_heads: int, n_kv_heads: int, head_dim: int,
+                     page_size: int, scale: float, window: int, n_splits: int, part_o=None, part_ml=None):
+    """bf16 attention of one new token per sequence over its slot's keys, split into runs of
+    pages; partial results go through the float32 scratch part_o / part_ml when n_splits > 1."""
+    _need_cuda(q, kcache, vcache, page_table, seq_slot, seq_len, cu_seqlens, out, part_o, part_ml)
+    _need(q.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16,
+          "attention_decode: bf16 only")
+    if n_splits > 1:
+        _need(part_o is not None and part_o.dtype == torch.float32
+              and part_o.numel() >= n_seqs * n_heads * n_splits * head_dim
+              and part_ml is not None and part_ml.numel() >= n_seqs * n_heads * n_splits * 2,
+              "attention_decode: scratch too small")
+    _call("attention_mma", "ri_attention_decode", _p(q), c_int(q_ld), _p(kcache), _p(vcache), _p(page_table),
+          c_int(page_table.shape[1]), _p(seq_slot), _p(seq_len), _p(cu_seqlens), _p(out), c_int(out.shape[1]),
+          c_int(n_seqs), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_int(page_size), c_float(scale),
+          c_int(window), c_int(n_splits), _p(part_o), _p(part_ml), _stream())
+    return out
+
+
+def attention_prefill(q: torch.Tensor, q_ld: int, kcache, vcache, page_table, seq_slot, seq_start, cu_seqlens,
+                      out: torch.Tensor, *, n_seqs: int, max_new: int, n_heads: int, n_kv_heads: int,
+                      head_dim: int, page_size: int, scale: float, window: int):
+    """bf16 causal attention of every new token of every sequence over its slot's keys."""
+    _need_cuda(q, kcache, vcache, page_table, seq_slot, seq_start, cu_seqlens, out)
+    _need(q.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16,
+          "attention_prefill: bf16 only")
+    _call("attention_mma", "ri_attention_prefill", _p(q), c_int(q_ld), _p(kcache), _p(vcache), _p(page_table),
+          c_int(page_table.shape[1]), _p(seq_slot), _p(seq_start), _p(cu_seqlens), _p(out), c_int(out.shape[1]),
+          c_int(n_seqs), c_int(max_new), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_int(page_size),
+          c_float(scale), c_int(window), _stream())
+    return out
