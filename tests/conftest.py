@@ -1,0 +1,116 @@
+import json
+import os
+import sys
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+for p in (ROOT, os.path.dirname(os.path.abspath(__file__))):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run on a B200)")
+
+
+def pytest_collection_modifyitems(config, items):
+    if torch.cuda.is_available():
+        return
+    skip = pytest.mark.skip(reason="no CUDA device")
+    for item in items:
+        if "gpu" in item.keywords:
+            item.add_marker(skip)
+
+
+# ----------------------------------------------------------------------------------------
+# Tiny configurations.  A and B differ in every size and option; C and D are head sizes the
+# tensor-core kernels refuse (8 and 24), so they run on the generic kernels in both dtypes.
+# ----------------------------------------------------------------------------------------
+TINY = {
+    "A": {   # Llama style: tied, no bias, explicit head_dim != hidden/heads, half pairing
+        "architectures": ["LlamaForCausalLM"], "hidden_size": 128, "num_hidden_layers": 2,
+        "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64, "intermediate_size": 176,
+        "vocab_size": 264, "rope_theta": 10000.0, "rms_norm_eps": 1e-5, "attention_bias": False,
+        "tie_word_embeddings": True, "max_position_embeddings": 1024, "rope_style": "half",
+    },
+    "B": {   # Qwen2 style: untied, biases, odd vocabulary, interleaved pairing, 3 query heads per kv head
+        "architectures": ["Qwen2ForCausalLM"], "hidden_size": 192, "num_hidden_layers": 3,
+        "num_attention_heads": 6, "num_key_value_heads": 2, "head_dim": 128, "intermediate_size": 328,
+        "vocab_size": 391, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "attention_bias": True,
+        "tie_word_embeddings": False, "max_position_embeddings": 2048, "rope_style": "interleaved",
+    },
+    "C": {   # the 2-layer Llama-style config with head_dim 8
+        "architectures": ["LlamaForCausalLM"], "hidden_size": 64, "num_hidden_layers": 2,
+        "num_attention_heads": 8, "num_key_value_heads": 2, "intermediate_size": 176, "vocab_size": 256,
+        "rope_theta": 10000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": True,
+        "max_position_embeddings": 128,
+    },
+    "D": {   # the 3-layer Qwen2-style config with head_dim 24
+        "architectures": ["Qwen2ForCausalLM"], "hidden_size": 144, "num_hidden_layers": 3,
+        "num_attention_heads": 6, "num_key_value_heads": 3, "intermediate_size": 352, "vocab_size": 384,
+        "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": False,
+        "max_position_embeddings": 256,
+    },
+}
+
+# bf16 runs are compared with the plain float32 implementation holding the same bf16 weights:
+# what differs is the rounding of activations, the cache and the outputs.
+TOL = {"float32": 1e-4, "bfloat16": 4e-2}
+
+
+def rel_err(got: torch.Tensor, want: torch.Tensor) -> float:
+    """Per row max|a - b| / max|b|, the worst row."""
+    got, want = got.float().cpu(), want.float().cpu()
+    if got.ndim == 1:
+        got, want = got[None], want[None]
+    return float(((got - want).abs().amax(dim=1) / want.abs().amax(dim=1).clamp_min(1e-30)).max())
+
+
+class TinyModel:
+    """A model folder made in a temporary place, with its weights for the plain implementation."""
+
+    def __init__(self, folder, cfg_dict, weights):
+        self.folder = folder
+        self.cfg = cfg_dict            # as written to config.json
+        self.weights = weights         # name -> float32 tensor (the stored values, widened)
+
+    def plain_logits(self, tokens, **kw):
+        import plain_impl
+        return plain_impl.forward(self.weights, self.cfg, tokens, **kw)
+
+
+def make_model(tmp_path, name, *, seed=0, std=0.05, matrix_dtype=torch.bfloat16, overrides=None):
+    from rust_inference_b200 import config_from_dict, write_random_model
+    from rust_inference_b200.weights.safetensors_io import ModelFiles
+    d = dict(TINY[name])
+    if overrides:
+        d.update(overrides)
+    cfg = config_from_dict(d)
+    folder = str(tmp_path / f"model_{name}_{seed}")
+    write_random_model(folder, cfg, seed=seed, std=std, matrix_dtype=matrix_dtype)
+    files = ModelFiles(folder)
+    weights = {n: files.tensor(n).float() for n in files.names()}
+    files.close()
+    with open(os.path.join(folder, "config.json")) as f:
+        cfg_dict = json.load(f)
+    return TinyModel(folder, cfg_dict, weights)
+
+
+@pytest.fixture(scope="session")
+def model_factory(tmp_path_factory):
+    cache = {}
+
+    def get(name, seed=0, std=0.05, matrix_dtype=torch.bfloat16):
+        key = (name, seed, std, matrix_dtype)
+        if key not in cache:
+            cache[key] = make_model(tmp_path_factory.mktemp("models"), name, seed=seed, std=std,
+                                    matrix_dtype=matrix_dtype)
+        return cache[key]
+    return get
+
+
+def random_tokens(n, vocab, seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, vocab, (n,), generator=g).tolist()

@@ -1,0 +1,402 @@
+"""Each kernel alone against a plain float32 reference of the same operation, at sizes other
+than the engine tests use (odd widths, head sizes in steps of 16, many heads and groups)."""
+import math
+
+import pytest
+import torch
+
+import plain_impl
+from rust_inference_b200.sampling import rng
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _ops():
+    from rust_inference_b200.kernels import ops
+    return ops
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("hidden", [7, 64, 1000, 3584])
+def test_embed_gather(dtype, hidden):
+    ops = _ops()
+    table = torch.randn(50, hidden, device=DEV).to(dtype)
+    ids = torch.tensor([0, 49, 7, 7, 13], dtype=torch.int32, device=DEV)
+    out = torch.empty(5, hidden, device=DEV)
+    ops.embed_gather(table, ids, out)
+    assert torch.equal(out, plain_impl.embedding(table.float(), ids.tolist()))
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n, eps", [(5, 1e-5), (144, 1e-6), (1000, 1e-3), (3584, 1e-6), (5120, 1e-5)])
+def test_rmsnorm(out_dtype, n, eps):
+    ops = _ops()
+    x = torch.randn(9, n, device=DEV) * 3
+    x[3] *= 1e-3                                     # a row where eps matters
+    w = torch.randn(n, device=DEV)
+    out = torch.empty(9, n, device=DEV, dtype=out_dtype)
+    ops.rmsnorm(x, w, eps, out)
+    want = plain_impl.rmsnorm(x.double().cpu(), w.double().cpu(), eps)
+    tol = 2e-6 if out_dtype == torch.float32 else 5e-3
+    assert ((out.double().cpu() - want).abs() <= tol * want.abs().clamp_min(1e-3)).all()
+    rows = torch.tensor([8, 0, 3], dtype=torch.int32, device=DEV)
+    picked = torch.empty(3, n, device=DEV, dtype=out_dtype)
+    ops.rmsnorm(x, w, eps, picked, rows)
+    assert torch.equal(picked, out[[8, 0, 3]])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("inter", [11, 176, 18944])
+def test_silu_mul(dtype, inter):
+    ops = _ops()
+    gu = (torch.randn(5, 2 * inter, device=DEV) * 4).to(dtype)
+    out = torch.empty(5, inter, device=DEV, dtype=dtype)
+    ops.silu_mul(gu, out)
+    g = gu.float().cpu()
+    want = plain_impl.silu(g[:, :inter]) * g[:, inter:]
+    tol = 1e-6 if dtype == torch.float32 else 1e-2
+    assert torch.allclose(out.float().cpu(), want, rtol=tol, atol=tol)
+
+
+@pytest.mark.parametrize("style", ["half", "interleaved"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh, nkv, hd", [(3, 1, 6), (8, 2, 16), (5, 5, 48), (28, 4, 128)])
+def test_rope_and_cache_write(style, dtype, nh, nkv, hd):
+    """Rotation against the plain table and rotation; keys and values must land at the page and
+    offset of their position, with pages handed out in a scrambled order."""
+    ops = _ops()
+    from rust_inference_b200.parts.rope import rope_tables
+    page, n_pages, base = 64, 9, 500000.0
+    starts, news = [0, 100, 63], [70, 1, 2]
+    cos, sin = rope_tables(hd, base, 256)
+    pcos, psin = plain_impl.rope_table(hd, base, 256)
+    assert torch.equal(torch.from_numpy(cos), pcos) and torch.equal(torch.from_numpy(sin), psin)
+    table = torch.tensor([[5, 2, 0], [7, 1, 0], [3, 8, 0]], dtype=torch.int32)       # [slot][logical page]
+    slots = [2, 0, 1]
+    T = sum(news)
+    qkv = torch.randn(T, (nh + 2 * nkv) * hd).to(dtype)
+    token_pos = torch.tensor([s + i for s, n in zip(starts, news) for i in range(n)], dtype=torch.int32)
+    token_seq = torch.tensor([b for b, n in enumerate(news) for _ in range(n)], dtype=torch.int32)
+    kc = torch.full((n_pages, nkv, page, hd), 77.0).to(dtype)
+    vc = torch.full((n_pages, nkv, page, hd), 77.0).to(dtype)
+    d = lambda t: t.to(DEV)
+    q_dev, kc_dev, vc_dev = d(qkv.clone()), d(kc), d(vc)
+    ops.rope_cache_write(q_dev, d(torch.from_numpy(cos)), d(torch.from_numpy(sin)), d(token_pos), d(token_seq),
+                         d(torch.tensor(slots, dtype=torch.int32)), d(table), kc_dev, vc_dev, n_heads=nh,
+                         n_kv_heads=nkv, head_dim=hd, page_size=page, style={"half": 0, "interleaved": 1}[style],
+                         write_kv=True)
+    tol = 1e-6 if dtype == torch.float32 else 1e-2
+    x = qkv.float()
+    written = torch.zeros(n_pages, page, dtype=torch.bool)
+    for t in range(T):
+        pos, b = int(token_pos[t]), int(token_seq[t])
+        c, s_ = pcos[pos:pos + 1], psin[pos:pos + 1]
+        for h in range(nh):
+            want = plain_impl.rope_apply(x[t, h * hd:(h + 1) * hd][None], c, s_, style)[0]
+            assert torch.allclose(q_dev[t, h * hd:(h + 1) * hd].float().cpu(), want, atol=tol * 4)
+        pg, off = int(table[slots[b], pos // page]), pos % page
+        written[pg, off] = True
+        for h in range(nkv):
+            k = x[t, (nh + h) * hd:(nh + h + 1) * hd]
+            want = plain_impl.rope_apply(k[None], c, s_, style)[0]
+            assert torch.allclose(kc_dev[pg, h, off].float().cpu(), want, atol=tol * 4)
+            v = qkv[t, (nh + nkv + h) * hd:(nh + nkv + h + 1) * hd]
+            assert torch.equal(vc_dev[pg, h, off].cpu(), v)
+    # nothing else was touched
+    untouched = ~written                                                    # [page, offset]
+    assert (kc_dev.float().cpu().permute(0, 2, 1, 3)[untouched] == 77.0).all()
+    assert (vc_dev.float().cpu().permute(0, 2, 1, 3)[untouched] == 77.0).all()
+    # a layer that only reads another layer's cache rotates q and writes nothing
+    q2, k2 = d(qkv.clone()), d(kc)
+    ops.rope_cache_write(q2, d(torch.from_numpy(cos)), d(torch.from_numpy(sin)), d(token_pos), d(token_seq),
+                         d(torch.tensor(slots, dtype=torch.int32)), d(table), k2, k2, n_heads=nh, n_kv_heads=nkv,
+                         head_dim=hd, page_size=page, style={"half": 0, "interleaved": 1}[style], write_kv=False)
+    assert torch.equal(q2[:, :nh * hd], q_dev[:, :nh * hd]) and (k2.float() == 77.0).all()
+
+
+GEMM_SHAPES = [(1, 7, 5), (3, 100, 33), (17, 264, 128), (64, 391, 192), (130, 77, 1000), (5, 3584, 64), (300, 130, 520)]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("m, n, k", GEMM_SHAPES)
+def test_gemm_simt_all_epilogues(dtype, m, n, k):
+    ops = _ops()
+    x = (torch.randn(m, k, device=DEV) * 0.5).to(dtype)
+    w = (torch.randn(n, k, device=DEV) * 0.1).to(dtype)
+    w2 = (torch.randn(n, k, device=DEV) * 0.1).to(dtype)
+    bias = torch.randn(n, device=DEV)
+    ref = x.double() @ w.double().t()
+    ref2 = x.double() @ w2.double().t()
+    tol = 2e-6 if dtype == torch.float32 else 8e-3
+    scale = ref.abs().max().item()
+
+    out = torch.empty(m, n, device=DEV, dtype=dtype)
+    ops.gemm_simt(x, w, out, ops.EPI_STORE, bias=bias)
+    assert (out.double() - (ref + bias)).abs().max().item() <= tol * (scale + bias.abs().max().item())
+    out32 = torch.empty(m, n, device=DEV)
+    ops.gemm_simt(x, w, out32, ops.EPI_STORE_F32)
+    assert (out32.double() - ref).abs().max().item() <= 2e-6 * scale + 1e-30
+    res = torch.randn(m, n, device=DEV)
+    before = res.clone()
+    ops.gemm_simt(x, w, res, ops.EPI_RESIDUAL)
+    assert (res.double() - (before + ref)).abs().max().item() <= 2e-6 * (scale + 4)
+    act = torch.empty(m, n, device=DEV, dtype=dtype)
+    ops.gemm_simt(x, w, act, ops.EPI_SILU_MUL, w2=w2)
+    want = plain_impl.silu(ref.float()).double() * ref2
+    assert (act.double() - want).abs().max().item() <= tol * (want.abs().max().item() + 1e-3) * 2
+
+
+@pytest.mark.parametrize("m", [1, 8, 33, 64, 100, 130, 300, 700])
+@pytest.mark.parametrize("n, k", [(128, 64), (391, 192), (200, 136), (640, 1032), (3584, 3584)])
+def test_gemm_tcgen05_all_epilogues(m, n, k):
+    """bf16 operands on the tensor cores: every token tile (16..256), ragged features and K."""
+    ops = _ops()
+    from rust_inference_b200.kernels import linear, tcgen05
+    x = (torch.randn(m, k, device=DEV) * 0.5).bfloat16()
+    w = linear.Weight((torch.randn(n, k, device=DEV) * 0.1).bfloat16())
+    w2 = linear.Weight((torch.randn(n, k, device=DEV) * 0.1).bfloat16())
+    bias = torch.randn(n, device=DEV)
+    assert tcgen05.supports(x, w)
+    ref = x.double() @ w.t.double().t()
+    ref2 = x.double() @ w2.t.double().t()
+    scale = ref.abs().max().item()
+    out32 = torch.full((m, n), 9.0, device=DEV)
+    tcgen05.gemm(x, w, out32, ops.EPI_STORE_F32)
+    assert (out32.double() - ref).abs().max().item() <= 1e-5 * scale           # float32 accumulation
+    out = torch.empty(m, n, device=DEV, dtype=torch.bfloat16)
+    tcgen05.gemm(x, w, out, ops.EPI_STORE, bias=bias)
+    assert (out.double() - (ref + bias)).abs().max().item() <= 8e-3 * (scale + bias.abs().max().item())
+    for split in (1, 3):
+        res = torch.randn(m, n, device=DEV)
+        before = res.clone()
+        tcgen05.gemm(x, w, res, ops.EPI_RESIDUAL, split_k=split)
+        assert (res.double() - (before + ref)).abs().max().item() <= 1e-5 * (scale + 4)
+    act = torch.empty(m, n, device=DEV, dtype=torch.bfloat16)
+    tcgen05.gemm(x, w, act, ops.EPI_SILU_MUL, w2=w2)
+    want = plain_impl.silu(ref.float()).double() * ref2
+    assert (act.double() - want).abs().max().item() <= 8e-3 * (want.abs().max().item() + 1e-3)
+    torch.cuda.synchronize()
+    tcgen05.check_status()
+
+
+def test_gemm_tcgen05_refuses_what_it_cannot_do():
+    from rust_inference_b200.kernels import linear, ops, tcgen05
+    x = torch.zeros(4, 100, device=DEV, dtype=torch.bfloat16)
+    w = linear.Weight(torch.zeros(8, 100, device=DEV, dtype=torch.bfloat16))
+    assert not tcgen05.supports(x, w)                     # rows of 200 bytes: not a multiple of 16
+    with pytest.raises(ops.KernelError, match="multiple of 8"):
+        tcgen05.gemm(x, w, torch.zeros(4, 8, device=DEV), ops.EPI_STORE_F32)
+    # the dispatcher takes the FFMA kernel for such a shape instead
+    out = torch.empty(4, 8, device=DEV)
+    linear.logits(x, w, out, None)
+    assert (out == 0).all()
+    with pytest.raises(ops.KernelError, match="CUDA"):
+        ops.rmsnorm(torch.zeros(2, 4), torch.ones(4), 1e-5, torch.zeros(2, 4))
+
+
+def _attention_case(nh, nkv, hd, news, starts, dtype, window=0, sharp=None, seed=0):
+    """Random q, K, V in a scrambled paged cache; returns the kernel inputs and the plain result."""
+    g = torch.Generator().manual_seed(seed)
+    page = 64
+    B = len(news)
+    total = [s + n for s, n in zip(starts, news)]
+    max_pages = max(-(-t // page) for t in total) + 1
+    n_pages = sum(-(-t // page) for t in total) + 2
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    slots = list(range(B - 1, -1, -1))
+    table = torch.zeros(B, max_pages, dtype=torch.int32)
+    kc = torch.randn(n_pages, nkv, page, hd, generator=g).to(dtype)         # unused places hold noise
+    vc = torch.randn(n_pages, nkv, page, hd, generator=g).to(dtype)
+    Ks, Vs, pi = [], [], 0
+    for b in range(B):
+        K = torch.randn(total[b], nkv, hd, generator=g).to(dtype)
+        V = torch.randn(total[b], nkv, hd, generator=g).to(dtype)
+        if sharp is not None:
+            K[sharp % total[b]] *= 6.0                                       # one key stands out
+        Ks.append(K)
+        Vs.append(V)
+        for pg in range(-(-total[b] // page)):
+            p = perm[pi]
+            pi += 1
+            table[slots[b], pg] = p
+            n = min(page, total[b] - pg * page)
+            kc[p, :, :n] = K[pg * page:pg * page + n].transpose(0, 1)
+            vc[p, :, :n] = V[pg * page:pg * page + n].transpose(0, 1)
+    T = sum(news)
+    q = torch.randn(T, (nh + 2 * nkv) * hd, generator=g).to(dtype)
+    cu = [0]
+    for n in news:
+        cu.append(cu[-1] + n)
+    scale = 1.0 / math.sqrt(hd)
+    ref = torch.zeros(T, nh * hd)
+    rep = nh // nkv
+    for b in range(B):
+        for i in range(news[b]):
+            t, pos = cu[b] + i, starts[b] + i
+            lo = max(0, pos - window + 1) if window > 0 else 0
+            for h in range(nh):
+                k = Ks[b][lo:pos + 1, h // rep].float()
+                v = Vs[b][lo:pos + 1, h // rep].float()
+                s = (k @ q[t, h * hd:(h + 1) * hd].float()) * scale
+                ref[t, h * hd:(h + 1) * hd] = plain_impl.softmax_rows(s[None])[0] @ v
+    d = lambda t: t.to(DEV)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    pos = [starts[b] + i for b in range(B) for i in range(news[b])]
+    seq = [b for b in range(B) for _ in range(news[b])]
+    return dict(q=d(q), kc=d(kc), vc=d(vc), table=d(table), slot=i32(slots), start=i32(starts), length=i32(total),
+                cu=i32(cu), pos=i32(pos), seq=i32(seq), ref=ref, scale=scale, T=T, B=B)
+
+
+ATTN_CASES = [
+    # heads, kv heads, head_dim, new tokens per sequence, cached before, window
+    (4, 2, 64, [5], [0], 0),
+    (28, 4, 128, [130, 1, 77], [0, 0, 0], 0),
+    (14, 2, 128, [1, 1, 1, 1], [1000, 64, 127, 128], 0),
+    (8, 8, 64, [1, 1, 1], [0, 63, 200], 0),
+    (6, 3, 64, [33, 2], [100, 700], 0),
+    (16, 1, 64, [1], [999], 0),
+    (4, 2, 128, [70, 200], [30, 0], 50),
+    (4, 1, 64, [1, 1], [300, 5], 100),
+    (5, 5, 16, [40, 1], [0, 90], 0),          # head sizes the tensor-core kernels refuse
+    (6, 2, 48, [1, 1], [10, 300], 0),
+    (3, 1, 80, [20], [50], 30),
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh, nkv, hd, news, starts, window", ATTN_CASES)
+def test_attention_kernels(dtype, nh, nkv, hd, news, starts, window):
+    ops = _ops()
+    c = _attention_case(nh, nkv, hd, news, starts, dtype, window=window)
+    tol = 2e-5 if dtype == torch.float32 else 2e-2
+    out = torch.zeros(c["T"], nh * hd, device=DEV, dtype=dtype)
+    ops.attention_generic(c["q"], c["q"].shape[1], c["kc"], c["vc"], c["table"], c["pos"], c["seq"], c["slot"], out,
+                          n_tokens=c["T"], n_heads=nh, n_kv_heads=nkv, head_dim=hd, page_size=64,
+                          scale=c["scale"], window=window)
+    assert (out.float().cpu() - c["ref"]).abs().max().item() <= tol * c["ref"].abs().max().item()
+    if dtype != torch.bfloat16:
+        return
+    decode = all(n == 1 for n in news)
+    if ops.attention_mma_supports(hd, 64, nh, nkv, False):
+        out = torch.zeros_like(out)
+        ops.attention_prefill(c["q"], c["q"].shape[1], c["kc"], c["vc"], c["table"], c["slot"], c["start"], c["cu"],
+                              out, n_seqs=c["B"], max_new=max(news), n_heads=nh, n_kv_heads=nkv, head_dim=hd,
+                              page_size=64, scale=c["scale"], window=window)
+        assert (out.float().cpu() - c["ref"]).abs().max().item() <= tol * c["ref"].abs().max().item()
+    else:
+        assert hd not in (64, 128)
+    if decode and ops.attention_mma_supports(hd, 64, nh, nkv, True):
+        for splits in (1, 2, 7, 32):
+            out = torch.zeros_like(out)
+            po = torch.full((c["B"] * nh * splits * hd,), float("nan"), device=DEV)
+            pml = torch.full((c["B"] * nh * splits * 2,), float("nan"), device=DEV)
+            ops.attention_decode(c["q"], c["q"].shape[1], c["kc"], c["vc"], c["table"], c["slot"], c["length"],
+                                 c["cu"], out, n_seqs=c["B"], n_heads=nh, n_kv_heads=nkv, head_dim=hd, page_size=64,
+                                 scale=c["scale"], window=window, n_splits=splits, part_o=po, part_ml=pml)
+            assert (out.float().cpu() - c["ref"]).abs().max().item() <= tol * c["ref"].abs().max().item(), splits
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_finds_a_far_key(dtype):
+    """One key among hundreds is scaled up so that its score stands out: the result must be
+    (nearly) that key's value, wherever the key lies (first page, a page boundary, the last key)."""
+    ops = _ops()
+    nh, nkv, hd = 4, 2, 64
+    for far in (0, 63, 64, 500, 898):
+        c = _attention_case(nh, nkv, hd, [1, 3], [898, 897], dtype, sharp=far, seed=far)
+        out = torch.zeros(c["T"], nh * hd, device=DEV, dtype=dtype)
+        ops.attention_generic(c["q"], c["q"].shape[1], c["kc"], c["vc"], c["table"], c["pos"], c["seq"], c["slot"],
+                              out, n_tokens=c["T"], n_heads=nh, n_kv_heads=nkv, head_dim=hd, page_size=64,
+                              scale=c["scale"])
+        tol = 2e-5 if dtype == torch.float32 else 2e-2
+        assert (out.float().cpu() - c["ref"]).abs().max().item() <= tol * c["ref"].abs().max().item()
+        if dtype == torch.bfloat16:
+            out2 = torch.zeros_like(out)
+            ops.attention_prefill(c["q"], c["q"].shape[1], c["kc"], c["vc"], c["table"], c["slot"], c["start"],
+                                  c["cu"], out2, n_seqs=2, max_new=3, n_heads=nh, n_kv_heads=nkv, head_dim=hd,
+                                  page_size=64, scale=c["scale"], window=0)
+            assert (out2.float().cpu() - c["ref"]).abs().max().item() <= tol * c["ref"].abs().max().item()
+
+
+def _sample(logits, **kw):
+    ops = _ops()
+    rows = logits.shape[0]
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    kw.setdefault("row_stream", i32(list(range(rows))))
+    kw.setdefault("row_counter", i32([0] * rows))
+    ops.sample(logits.clone().to(DEV), out, **kw)
+    return out.cpu().tolist()
+
+
+def test_sampling_greedy_first_maximum():
+    g = torch.Generator().manual_seed(0)
+    logits = torch.randn(6, 152064, generator=g)
+    logits[1, 777] = logits[1, 151000] = 50.0                 # a tie: the first wins (math.rs:328-339)
+    logits[2, 0] = 60.0
+    logits[3, 152063] = 60.0
+    logits[4] = 1.0                                            # all equal
+    got = _sample(logits, temperature=0.0)
+    assert got == [plain_impl.argmax_first(logits[i]) for i in range(6)]
+    assert got[1] == 777 and got[2] == 0 and got[3] == 152063 and got[4] == 0
+    small = torch.tensor([[0.1, 0.7, 0.7], [-1.0, -3.0, -0.5]])
+    assert _sample(small, temperature=0.0) == [1, 2]
+
+
+@pytest.mark.parametrize("vocab", [5, 384, 1000, 152064])
+def test_sampling_temperature_matches_the_cdf(vocab):
+    """The drawn token must be the one whose CDF interval holds u, up to rounding at the edges."""
+    g = torch.Generator().manual_seed(vocab)
+    rows, T, seed = 64, 0.7, 4
+    logits = torch.randn(rows, vocab, generator=g) * 3
+    counters = [(3 * r) % 11 for r in range(rows)]
+    got = _sample(logits, temperature=T, seed=seed,
+                  row_counter=torch.tensor(counters, dtype=torch.int32, device=DEV))
+    for r in range(rows):
+        u = rng.uniform(seed, r, counters[r])
+        cdf = torch.cumsum(torch.softmax(logits[r].double() / T, dim=0), dim=0)
+        lo = cdf[got[r] - 1].item() if got[r] > 0 else 0.0
+        assert lo - 1e-5 <= u <= cdf[got[r]].item() + 1e-5, (r, got[r], u)
+        if vocab <= 1000:
+            probs = plain_impl.softmax_rows((logits[r] / T)[None])[0]
+            assert got[r] == plain_impl.draw(probs, u) or abs(cdf[got[r]].item() - u) < 1e-5 or abs(lo - u) < 1e-5
+
+
+def test_sampling_frequencies_follow_the_distribution():
+    probs = torch.tensor([0.5, 0.25, 0.125, 0.0625, 0.0625])
+    n = 4000
+    logits = probs.log()[None].repeat(n, 1)
+    got = _sample(logits, temperature=1.0, seed=99)
+    freq = torch.bincount(torch.tensor(got), minlength=5).float() / n
+    assert (freq - probs).abs().max().item() < 0.03
+
+
+def test_sampling_top_k_top_p_and_penalty_follow_the_reference():
+    g = torch.Generator().manual_seed(1)
+    vocab, rows, seed = 500, 48, 7
+    logits = torch.randn(rows, vocab, generator=g) * 2
+    logits[:, 10] = logits[:, 20]                               # ties inside the distribution
+    recent = torch.randint(0, vocab, (rows, 8), generator=g).int()
+    counts = torch.tensor([r % 9 for r in range(rows)], dtype=torch.int32)
+    for kw in (dict(top_k=5), dict(top_p=0.6), dict(top_k=40, top_p=0.95), dict(top_k=1),
+               dict(top_k=40, top_p=0.95, penalty=1.1), dict(penalty=1.5), dict(top_p=0.999)):
+        use_recent = "penalty" in kw
+        got = _sample(logits, temperature=0.8, seed=seed, **kw,
+                      **({"recent": recent.to(DEV), "recent_count": counts.to(DEV)} if use_recent else {}))
+        for r in range(rows):
+            u = rng.uniform(seed, r, 0)
+            hist = recent[r, :counts[r]].tolist() if use_recent else []
+            l = plain_impl.repetition_penalty(logits[r], hist, kw.get("penalty", 1.0), 64) if hist else logits[r]
+            p = plain_impl.softmax_rows((l.double() / 0.8)[None])[0]
+            p = plain_impl.top_k_filter(p, kw.get("top_k", 0))
+            p = plain_impl.top_p_filter(p, kw.get("top_p", 1.0))
+            assert p[got[r]] > 0, (kw, r, "a filtered token was drawn")
+            cdf = torch.cumsum(p, dim=0)
+            lo = cdf[got[r] - 1].item() if got[r] > 0 else 0.0
+            assert lo - 2e-5 <= u <= cdf[got[r]].item() + 2e-5, (kw, r, got[r], u)
+    # greedy after a penalty (sampler.rs:76-83): the penalised maximum loses
+    l = torch.tensor([[1.0, 5.0, 4.9, -2.0]])
+    assert _sample(l, temperature=0.0) == [1]
+    assert _sample(l, temperature=0.0, penalty=1.1, recent=torch.tensor([[1]], dtype=torch.int32, device=DEV),
+                   recent_count=torch.tensor([1], dtype=torch.int32, device=DEV)) == [2]

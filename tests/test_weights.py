@@ -1,0 +1,187 @@
+"""safetensors reading and writing, the loader's single error, the random-weights mode (no GPU)."""
+import json
+import os
+import struct
+
+import pytest
+import torch
+
+from conftest import TINY
+from rust_inference_b200 import config_from_dict, write_random_model
+from rust_inference_b200.config.registry import get_architecture
+from rust_inference_b200.engine.model import declared_tensors
+from rust_inference_b200.weights.loader import WeightError, random_tensors, read_model_tensors
+from rust_inference_b200.weights.safetensors_io import (ModelFiles, SafetensorsFile, WeightFileError,
+                                                        write_safetensors)
+
+
+def _spec(name):
+    cfg = config_from_dict(TINY[name])
+    return cfg, get_architecture(cfg.architecture).build_spec(cfg)
+
+
+def test_round_trip_keeps_stored_precision(tmp_path):
+    t = {
+        "a": torch.randn(3, 5),
+        "b": torch.randn(7, 2).bfloat16(),
+        "c": torch.randn(4).half(),
+        "d": torch.arange(6, dtype=torch.int64).view(2, 3),
+        "e": torch.arange(4, dtype=torch.int32),
+    }
+    path = str(tmp_path / "x.safetensors")
+    write_safetensors(path, t, metadata={"k": "v"})
+    f = SafetensorsFile(path)
+    assert set(f.names()) == set(t) and f.metadata == {"k": "v"}
+    assert f.tensor("a").dtype == torch.float32 and torch.equal(f.tensor("a"), t["a"])
+    assert f.tensor("b").dtype == torch.bfloat16 and torch.equal(f.tensor("b"), t["b"])       # stays bf16
+    assert f.tensor("c").dtype == torch.float32 and torch.equal(f.tensor("c"), t["c"].float())  # exact widening
+    assert f.tensor("d").dtype == torch.int32 and torch.equal(f.tensor("d"), t["d"].int())      # tables are int32
+    assert f.tensor("e").dtype == torch.int32
+    f.close()
+    # the file is readable by the reference reader of the format too
+    from safetensors.torch import load_file
+    other = load_file(path)
+    assert torch.equal(other["b"], t["b"]) and torch.equal(other["a"], t["a"])
+
+
+def test_bad_files(tmp_path):
+    p = tmp_path / "bad.safetensors"
+    p.write_bytes(b"\x01\x02")
+    with pytest.raises(WeightFileError, match="too short"):
+        SafetensorsFile(str(p))
+    p.write_bytes(struct.pack("<Q", 10_000) + b"{}")
+    with pytest.raises(WeightFileError, match="header length"):
+        SafetensorsFile(str(p))
+    p.write_bytes(struct.pack("<Q", 5) + b"{oops")
+    with pytest.raises(WeightFileError, match="JSON"):
+        SafetensorsFile(str(p))
+    hdr = json.dumps({"w": {"dtype": "F32", "shape": [4], "data_offsets": [0, 16]}}).encode()
+    p.write_bytes(struct.pack("<Q", len(hdr)) + hdr + b"\0" * 8)             # truncated data
+    with pytest.raises(WeightFileError, match="outside"):
+        SafetensorsFile(str(p))
+    hdr = json.dumps({"w": {"dtype": "F32", "shape": [4], "data_offsets": [0, 12]}}).encode()
+    p.write_bytes(struct.pack("<Q", len(hdr)) + hdr + b"\0" * 16)            # size does not match shape
+    with pytest.raises(WeightFileError, match="needs"):
+        SafetensorsFile(str(p))
+    with pytest.raises(WeightFileError, match="no model.safetensors"):
+        ModelFiles(str(tmp_path / "nowhere"))
+
+
+def test_declared_tensors_follow_the_config():
+    cfg, spec = _spec("B")
+    d = declared_tensors(spec)
+    assert d["model.embed_tokens.weight"].shape == (391, 192)
+    assert d["model.layers.2.self_attn.q_proj.weight"].shape == (768, 192)
+    assert d["model.layers.2.self_attn.k_proj.weight"].shape == (256, 192)
+    assert d["model.layers.0.self_attn.o_proj.weight"].shape == (192, 768)
+    assert d["model.layers.0.self_attn.v_proj.bias"].shape == (256,)
+    assert d["model.layers.1.mlp.gate_proj.weight"].shape == (328, 192)
+    assert d["model.layers.1.mlp.down_proj.weight"].shape == (192, 328)
+    assert d["model.layers.1.input_layernorm.weight"].role == "vector"
+    assert d["lm_head.weight"].shape == (391, 192) and d["model.norm.weight"].shape == (192,)
+    cfg_a, spec_a = _spec("A")
+    da = declared_tensors(spec_a)
+    assert "lm_head.weight" not in da and "model.layers.0.self_attn.q_proj.bias" not in da
+
+
+def test_random_mode_writes_a_folder_and_is_deterministic(tmp_path):
+    cfg, spec = _spec("A")
+    d1 = write_random_model(str(tmp_path / "m1"), cfg, seed=3)
+    d2 = write_random_model(str(tmp_path / "m2"), cfg, seed=3)
+    d3 = write_random_model(str(tmp_path / "m3"), cfg, seed=4)
+    assert sorted(os.listdir(d1)) == ["config.json", "model.safetensors"]
+    assert config_from_dict(json.load(open(os.path.join(d1, "config.json")))) == cfg
+    t1 = dict(read_model_tensors(d1, declared_tensors(spec)))
+    t2 = dict(read_model_tensors(d2, declared_tensors(spec)))
+    t3 = dict(read_model_tensors(d3, declared_tensors(spec)))
+    assert all(torch.equal(t1[k], t2[k]) for k in t1)
+    assert not torch.equal(t1["model.embed_tokens.weight"], t3["model.embed_tokens.weight"])
+    assert t1["model.embed_tokens.weight"].dtype == torch.bfloat16            # matrices in bf16
+    assert t1["model.norm.weight"].dtype == torch.float32                     # stored in 32-bit, stays so
+    assert torch.all(t1["model.norm.weight"] == 1.0)
+    w = t1["model.layers.0.mlp.up_proj.weight"].float()
+    assert abs(w.std().item() - 0.02) < 0.003 and abs(w.mean().item()) < 0.002
+    # tensors are keyed by name, not by creation order
+    sub = {k: v for k, v in declared_tensors(spec).items() if "layers.1" in k}
+    again = dict(random_tensors(sub, 3))
+    assert all(torch.equal(again[k], t1[k]) for k in sub)
+
+
+def _rewrite(folder, change):
+    files = ModelFiles(folder)
+    tensors = {n: files.tensor(n) for n in files.names()}
+    files.close()
+    change(tensors)
+    write_safetensors(os.path.join(folder, "model.safetensors"), tensors)
+
+
+def test_one_error_lists_everything(tmp_path):
+    cfg, spec = _spec("B")
+    folder = write_random_model(str(tmp_path / "m"), cfg, seed=0)
+
+    def change(t):
+        del t["model.layers.1.mlp.up_proj.weight"]                    # missing
+        del t["model.layers.0.self_attn.k_proj.bias"]                 # missing
+        t["model.layers.0.rotary.inv_freq"] = torch.zeros(4)          # unexpected
+        t["model.layers.2.self_attn.o_proj.weight"] = torch.zeros(5, 5).bfloat16()   # wrong shape
+        t["model.norm.weight"] = torch.zeros(192, dtype=torch.int32)  # integer where floats belong
+    _rewrite(folder, change)
+    with pytest.raises(WeightError) as e:
+        list(read_model_tensors(folder, declared_tensors(spec)))
+    err = e.value
+    assert err.missing == ["model.layers.0.self_attn.k_proj.bias", "model.layers.1.mlp.up_proj.weight"]
+    assert err.unexpected == ["model.layers.0.rotary.inv_freq"]
+    assert err.wrong_shape == [("model.layers.2.self_attn.o_proj.weight", (192, 768), (5, 5))]
+    assert err.bad_dtype == [("model.norm.weight", "I32")]
+    msg = str(err)
+    for word in ("missing (2)", "unexpected (1)", "wrong shape", "expected [192, 768], found [5, 5]", "unsupported dtype"):
+        assert word in msg
+
+
+def test_bias_and_tied_head_must_match_the_config(tmp_path):
+    cfg, spec = _spec("A")                                   # no biases, tied head
+    folder = write_random_model(str(tmp_path / "m"), cfg, seed=0)
+
+    def change(t):
+        t["lm_head.weight"] = torch.zeros(264, 128).bfloat16()
+        t["model.layers.0.self_attn.q_proj.bias"] = torch.zeros(256)
+    _rewrite(folder, change)
+    with pytest.raises(WeightError) as e:
+        list(read_model_tensors(folder, declared_tensors(spec)))
+    assert e.value.unexpected == ["lm_head.weight", "model.layers.0.self_attn.q_proj.bias"]
+
+
+def test_unsupported_dtype_is_reported(tmp_path):
+    cfg, spec = _spec("A")
+    folder = write_random_model(str(tmp_path / "m"), cfg, seed=0)
+    path = os.path.join(folder, "model.safetensors")
+    raw = open(path, "rb").read()
+    (hlen,) = struct.unpack("<Q", raw[:8])
+    header = json.loads(raw[8:8 + hlen])
+    e = header["model.norm.weight"]
+    e["dtype"] = "F8_E4M3"
+    e["shape"] = [128 * 4]
+    blob = json.dumps(header, separators=(",", ":")).encode()
+    open(path, "wb").write(struct.pack("<Q", len(blob)) + blob + raw[8 + hlen:])
+    with pytest.raises(WeightError) as ex:
+        list(read_model_tensors(folder, declared_tensors(spec)))
+    assert ("model.norm.weight", "F8_E4M3") in ex.value.bad_dtype
+
+
+def test_sharded_folder(tmp_path):
+    cfg, spec = _spec("A")
+    folder = write_random_model(str(tmp_path / "m"), cfg, seed=1)
+    files = ModelFiles(folder)
+    tensors = {n: files.tensor(n) for n in files.names()}
+    files.close()
+    os.remove(os.path.join(folder, "model.safetensors"))
+    names = sorted(tensors)
+    half = len(names) // 2
+    parts = {"model-00001-of-00002.safetensors": names[:half], "model-00002-of-00002.safetensors": names[half:]}
+    weight_map = {}
+    for fname, ns in parts.items():
+        write_safetensors(os.path.join(folder, fname), {n: tensors[n] for n in ns})
+        weight_map.update({n: fname for n in ns})
+    json.dump({"weight_map": weight_map}, open(os.path.join(folder, "model.safetensors.index.json"), "w"))
+    got = dict(read_model_tensors(folder, declared_tensors(spec)))
+    assert all(torch.equal(got[n], tensors[n]) for n in names)
