@@ -23,9 +23,8 @@ class Model:
         reference (model.rs:142-144): it caps the cache and the rotary table.
         max_tokens_in_cache: positions all live sequences may hold together (default: 8 sequences
         of max_seq_len, at most 65,536 positions)."""
-        from .config.registry import load_config
-        cfg = load_config(path)
-        limit = getattr(cfg, "max_position_embeddings", None) or 32768
+        from .config.registry import load_spec
+        limit = load_spec(path)[1].max_positions
         seq = min(max_seq_len or limit, limit)
         if max_tokens_in_cache is None:
             max_tokens_in_cache = min(8 * seq, max(seq, 65536))

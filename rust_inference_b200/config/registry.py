@@ -62,6 +62,18 @@ def load_config(model_dir: str):
     return config_from_dict(read_config_json(model_dir))
 
 
+def load_spec(model_dir: str):
+    """(config, ModelSpec) of a model folder: config.json's architecture name picks the
+    architecture, which parses the config and builds the spec."""
+    d = read_config_json(model_dir)
+    archs = d.get("architectures")
+    if not archs or not isinstance(archs, (list, tuple)):
+        raise ConfigError("config.json: 'architectures' must be a non-empty list")
+    arch = get_architecture(str(archs[0]))
+    config = arch.parse_config(d)
+    return config, arch.build_spec(config)
+
+
 def _ensure_builtin() -> None:
     # The dense decoder registers itself on import.
     from ..models import dense_decoder  # noqa: F401

@@ -59,6 +59,11 @@ class StepContext:
     device: torch.device
     workspace: Workspace
     extras: dict = field(default_factory=dict)
+    # host copies of the per-sequence arrays (None inside a captured graph, whose arrays change
+    # between replays): for parts that are not graph_safe
+    host_slots: list | None = None
+    host_starts: list | None = None
+    host_counts: list | None = None
 
     def buffer(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
         return self.workspace.get(name, shape, dtype)

@@ -13,7 +13,7 @@ import numpy as np
 import torch
 
 from ..cache.sequence_cache import SequenceCache
-from ..config.registry import get_architecture, load_config
+from ..config.registry import get_architecture, load_spec
 from ..weights.loader import random_tensors, read_model_tensors
 from .context import StepContext, Workspace, pack_step
 from .model import DecoderModel
@@ -69,7 +69,7 @@ class Engine:
     def __init__(self, model: DecoderModel, *, max_tokens: int, max_seq_len: int | None = None,
                  n_slots: int | None = None, use_graphs: bool = True):
         self.model = model
-        self.use_graphs = use_graphs
+        self.use_graphs = use_graphs and model.graph_safe()
         self._graphs: dict = {}
         self.device = require_cuda(model.device)
         self.dtype = model.dtype
@@ -91,8 +91,7 @@ class Engine:
         """Load a model folder (config.json + safetensors); the model class comes from
         config.json's architecture name."""
         device = require_cuda(device)
-        config = load_config(model_dir)
-        spec = get_architecture(config.architecture).build_spec(config)
+        config, spec = load_spec(model_dir)
         model = DecoderModel(spec, dtype=resolve_dtype(dtype), device=device)
         model.load(read_model_tensors(model_dir, model.declared_tensors()))
         eng = cls(model, max_tokens=max_tokens, max_seq_len=max_seq_len, n_slots=n_slots, use_graphs=use_graphs)
@@ -153,6 +152,7 @@ class Engine:
         meta[o:o + c] = slots
         dev = self._ring.stage(meta, self.device)
         self.h2d_bytes += meta.nbytes
+        sc["host"] = (list(slots), starts, [len(t) for t in tokens])
         return dev, layout, sc
 
     def make_context(self, slots, tokens, wants) -> StepContext:
@@ -168,7 +168,8 @@ class Engine:
             seq_start=view("seq_start"), seq_len=view("seq_len"), cu_seqlens=view("cu_seqlens"),
             logit_rows=view("logit_rows"), n_logit_rows=sc["n_logit_rows"], max_new=sc["max_new"],
             max_len=sc["max_len"], all_single=sc["all_single"], page_table=self.cache.page_table,
-            page_size=self.cache.page_size, dtype=self.dtype, device=self.device, workspace=self.workspace)
+            page_size=self.cache.page_size, dtype=self.dtype, device=self.device, workspace=self.workspace,
+            host_slots=sc["host"][0], host_starts=sc["host"][1], host_counts=sc["host"][2])
 
     def step(self, slots: list, tokens: list, wants="last", borrow: bool = False):
         """Run one step.
@@ -215,6 +216,8 @@ class Engine:
         cfg = sampler_config or SamplerConfig.plain(temperature=0.0)
         if cfg.uses_history:
             raise ValueError("decode_steps keeps no token history: use it without a repetition penalty")
+        if not self.model.graph_safe():
+            raise RuntimeError("decode_steps replays a captured step; this model has a part that is not graph_safe")
         n = len(slots)
         self._check_batch(slots, [[t] for t in first_tokens], [[0]] * n)
         starts = [self.cache.length(s) for s in slots]

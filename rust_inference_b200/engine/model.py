@@ -127,6 +127,10 @@ class DecoderModel:
         if self.spec.head_name is None:
             self.head = linear.Weight(self.embedding)      # tied: the same storage, no copy
 
+    def graph_safe(self) -> bool:
+        """True if every part can run inside a captured CUDA graph."""
+        return all(getattr(part, "graph_safe", True) for _, part in self._named_parts())
+
     # ---- cache and tables ----------------------------------------------------
     def cache_requests(self) -> list:
         return list(self._cache_requests)

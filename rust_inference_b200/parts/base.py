@@ -18,6 +18,10 @@ from .spec import TensorSpec
 
 
 class Part:
+    # False if `forward` needs the host between kernels (reads a tensor back, loops in Python
+    # over device data): the engine then runs decode steps eagerly instead of replaying a graph.
+    graph_safe = True
+
     def __init__(self, *, hidden_size: int, dtype: torch.dtype, device):
         self.hidden_size = hidden_size
         self.dtype = dtype
