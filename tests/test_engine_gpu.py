@@ -136,13 +136,16 @@ def test_greedy_generation_through_the_entry_point(model_factory):
     m2.engine.cache.pager.audit()
     # one prompt given as a plain list
     assert m.generate(prompts[0], 8, SamplerConfig.plain(0.0), stop_ids=()).tokens == want[0]
-    # bf16: every generated token must be (nearly) the plain maximum at its place
+    # bf16: rows within TOL of the plain logits (relative to the row maximum) put the engine's
+    # maximum within 2 TOL of the plain maximum, so that is the bound for every generated token
     mb = Model.load(model.folder, dtype="bfloat16", max_tokens_in_cache=1024)
     for p, g in zip(prompts, mb.generate(prompts, 8, SamplerConfig.plain(0.0), stop_ids=())):
         seq = list(p)
+        assert len(g.tokens) == 8
         for tok in g.tokens:
             ref = model.plain_logits(seq)[-1]
-            assert (ref.max() - ref[tok]) / ref.abs().max() < 0.05
+            gap = float((ref.max() - ref[tok]) / ref.abs().max())
+            assert gap <= 2 * TOL["bfloat16"], (tok, gap)
             seq.append(tok)
 
 
