@@ -24,6 +24,7 @@
 // there (after rotation) before attention runs, so prefill, continuation and decode use
 // one convention.
 #include "common.cuh"
+#include "attention_decode_static.h"
 
 using namespace ri;
 
@@ -515,6 +516,59 @@ RI_API int ri_attention_prefill(const void* q, int q_ld, const void* kcache, con
                                   max_new, n_heads, n_kv_heads, scale, window, out, out_ld, stream);
     return launch_prefill<128>(q, q_ld, kcache, vcache, page_table, max_pages, seq_slot, seq_start, cu_seqlens, n_seqs,
                                max_new, n_heads, n_kv_heads, scale, window, out, out_ld, stream);
+}
+
+// ---------------------------------------------------------------------------------------------
+// The allocation-free variant (see attention_decode_static.h).  The scratch for the split
+// partial results is this file-scope device array.  In host code its name is only a stand-in
+// for the symbol, not a device address, so the address is looked up once per device with
+// cudaGetSymbolAddress and that pointer is what the kernel receives.
+// ---------------------------------------------------------------------------------------------
+static __device__ __align__(256) float g_decode_static_scratch[RI_DECODE_STATIC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int MAX_DEVICES = 64;
+float* g_decode_static_ptr[MAX_DEVICES] = {nullptr};
+
+// The device address of the scratch array on the current device; looked up on the first call.
+int decode_static_scratch(float** ptr) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail("attention_decode_static: cudaGetDevice failed: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= MAX_DEVICES) return fail("attention_decode_static: device %d is out of range", dev);
+    if (g_decode_static_ptr[dev] == nullptr) {
+        float* p = nullptr;
+        e = cudaGetSymbolAddress((void**)&p, g_decode_static_scratch);
+        if (e != cudaSuccess || p == nullptr)
+            return fail("attention_decode_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+        g_decode_static_ptr[dev] = p;
+    }
+    *ptr = g_decode_static_ptr[dev];
+    return 0;
+}
+}  // namespace
+
+RI_API int ri_attention_decode_static(const void* q, int q_ld, const void* kcache, const void* vcache,
+                                      const int* page_table, int max_pages, const int* seq_slot, const int* seq_len,
+                                      const int* cu_seqlens, void* out, int out_ld, int n_seqs, int n_heads,
+                                      int n_kv_heads, int hd, int page_size, float scale, int window, int n_splits,
+                                      cudaStream_t stream) {
+    if (n_seqs <= 0) return 0;
+    if (n_heads <= 0 || hd <= 0 || n_splits < 1)
+        return fail("attention_decode_static: %d heads, head_dim %d, %d splits", n_heads, hd, n_splits);
+    const long long rows = (long long)n_seqs * n_heads * n_splits;
+    const long long need = rows * (hd + 2);
+    if (need > RI_DECODE_STATIC_SCRATCH_FLOATS)
+        return fail("attention_decode_static: %d sequences x %d heads x %d splits x (head_dim %d + 2) = %lld floats "
+                    "exceed the built-in scratch of %d floats; use fewer splits or ri_attention_decode with your own scratch",
+                    n_seqs, n_heads, n_splits, hd, need, RI_DECODE_STATIC_SCRATCH_FLOATS);
+    float* scratch = nullptr;
+    if (int rc = decode_static_scratch(&scratch)) return rc;
+    float* part_o = scratch;                    // rows * hd floats
+    float* part_ml = scratch + rows * hd;       // rows * 2 floats
+    return ri_attention_decode(q, q_ld, kcache, vcache, page_table, max_pages, seq_slot, seq_len, cu_seqlens, out,
+                               out_ld, n_seqs, n_heads, n_kv_heads, hd, page_size, scale, window, n_splits, part_o,
+                               part_ml, stream);
 }
 
 RI_DEFINE_LAST_ERROR()
