@@ -165,6 +165,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_ld, const __nv_bfl
     const uint32_t q_tile = kv_base + 4 * TILE;
 
     const int b = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    let_next_kernel_start();
+    wait_for_previous_kernels();          // q and the newest key and value come from the kernel before
     const int n_rep = n_heads / n_kv_heads;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
     const int n_keys = seq_len[b];                       // the new token's key is in the cache already
@@ -286,6 +288,8 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o, const floa
                                     const int* __restrict__ cu_seqlens, int n_heads, int hd, int n_splits,
                                     __nv_bfloat16* __restrict__ out, int out_ld) {
     const int b = blockIdx.x, h = blockIdx.y;
+    let_next_kernel_start();
+    wait_for_previous_kernels();
     const size_t row0 = ((size_t)b * n_heads + h) * n_splits;
     float M = -INFINITY;
     for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[(row0 + s) * 2]);
@@ -322,6 +326,8 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_ld, const __nv_bf
     const uint32_t q_tile = kv_base + 4 * TILE;           // [64][HD]
 
     const int b = blockIdx.z, h = blockIdx.y;
+    let_next_kernel_start();
+    wait_for_previous_kernels();
     const int tok0 = cu_seqlens[b], n_new = cu_seqlens[b + 1] - tok0;
     const int q0 = blockIdx.x * 64;                       // first query (among the new tokens) of this CTA
     if (q0 >= n_new) return;
@@ -432,15 +438,16 @@ int launch_decode(const void* q, int q_ld, const void* kc, const void* vc, const
         configured = true;
     }
     dim3 grid(n_seqs, n_kv_heads, n_splits);
-    attn_decode_kernel<HD><<<grid, THREADS, SMEM, stream>>>(
-        (const __nv_bfloat16*)q, q_ld, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, page_table, max_pages,
-        seq_slot, seq_len, cu_seqlens, n_heads, n_kv_heads, scale, window, n_splits, part_o, part_ml,
-        (__nv_bfloat16*)out, out_ld);
-    if (int rc = check_launch("attn_decode")) return rc;
+    cudaError_t e = launch_dependent(
+        attn_decode_kernel<HD>, grid, dim3(THREADS), (size_t)SMEM, stream, (const __nv_bfloat16*)q, q_ld,
+        (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, page_table, max_pages, seq_slot, seq_len, cu_seqlens,
+        n_heads, n_kv_heads, scale, window, n_splits, part_o, part_ml, (__nv_bfloat16*)out, out_ld);
+    if (int rc = check_launch(e, "attn_decode")) return rc;
     if (n_splits > 1) {
-        attn_combine_kernel<<<dim3(n_seqs, n_heads), HD >= 128 ? 128 : 64, 0, stream>>>(
-            part_o, part_ml, cu_seqlens, n_heads, HD, n_splits, (__nv_bfloat16*)out, out_ld);
-        return check_launch("attn_combine");
+        e = launch_dependent(attn_combine_kernel, dim3(n_seqs, n_heads), dim3(HD >= 128 ? 128 : 64), (size_t)0, stream,
+                             (const float*)part_o, (const float*)part_ml, cu_seqlens, n_heads, (int)HD, n_splits,
+                             (__nv_bfloat16*)out, out_ld);
+        return check_launch(e, "attn_combine");
     }
     return 0;
 }
@@ -457,10 +464,11 @@ int launch_prefill(const void* q, int q_ld, const void* kc, const void* vc, cons
         configured = true;
     }
     dim3 grid((max_new + 63) / 64, n_heads, n_seqs);
-    attn_prefill_kernel<HD><<<grid, THREADS, SMEM, stream>>>(
-        (const __nv_bfloat16*)q, q_ld, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, page_table, max_pages,
-        seq_slot, seq_start, cu_seqlens, n_heads, n_kv_heads, scale, window, (__nv_bfloat16*)out, out_ld);
-    return check_launch("attn_prefill");
+    cudaError_t e = launch_dependent(
+        attn_prefill_kernel<HD>, grid, dim3(THREADS), (size_t)SMEM, stream, (const __nv_bfloat16*)q, q_ld,
+        (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, page_table, max_pages, seq_slot, seq_start, cu_seqlens,
+        n_heads, n_kv_heads, scale, window, (__nv_bfloat16*)out, out_ld);
+    return check_launch(e, "attn_prefill");
 }
 
 int check_common(int hd, int page_size, int n_heads, int n_kv_heads, int q_ld, int out_ld, const void* q,

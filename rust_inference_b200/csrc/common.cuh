@@ -11,6 +11,7 @@
 #include <stdint.h>
 #include <stdio.h>
 #include <stdarg.h>
+#include <stdlib.h>
 
 #define RI_API extern "C" __attribute__((visibility("default")))
 
@@ -97,6 +98,48 @@ __device__ __forceinline__ float silu_f32(float x) {
         float e = expf(x);
         return x * e / (1.f + e);
     }
+}
+
+// ---------------------------------------------------------------------------------------
+// Programmatic dependent launch.  A kernel launched with `launch_dependent` may start while
+// the kernel before it in the stream is still running: it runs its prologue (index math,
+// barrier set-up, loads of data no earlier kernel writes, such as weights) and must call
+// `wait_for_previous_kernels()` before it touches anything an earlier kernel reads or writes.
+// `let_next_kernel_start()` tells the scheduler that the next kernel may be brought onto the
+// SMs; its own wait still holds it until this kernel has finished and its writes are visible.
+// Setting RI_B200_NO_PDL=1 launches everything strictly one after another.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void wait_for_previous_kernels() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void let_next_kernel_start() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+inline bool pdl_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* e = getenv("RI_B200_NO_PDL");
+        on = (e != nullptr && e[0] == '1') ? 0 : 1;
+    }
+    return on == 1;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                    cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+inline int check_launch(cudaError_t e, const char* what) {
+    if (e != cudaSuccess) return fail("%s: launch failed: %s", what, cudaGetErrorString(e));
+    return check_launch(what);
 }
 
 }  // namespace ri

@@ -14,6 +14,8 @@ template <typename T>
 __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                                     float* __restrict__ out, int hidden) {
     const int t = blockIdx.x;
+    let_next_kernel_start();
+    wait_for_previous_kernels();          // the ids may come from the previous step's sampler
     const T* row = table + (size_t)ids[t] * hidden;
     float* o = out + (size_t)t * hidden;
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_f32<T>(row[i]);
@@ -22,13 +24,14 @@ __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __re
 RI_API int ri_embed_gather(const void* table, int dtype, const int* ids, float* out, int n_tokens,
                            int hidden, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
+    cudaError_t e = cudaSuccess;
     if (dtype == RI_F32)
-        embed_gather_kernel<float><<<n_tokens, 256, 0, stream>>>((const float*)table, ids, out, hidden);
+        e = launch_dependent(embed_gather_kernel<float>, n_tokens, 256, 0, stream, (const float*)table, ids, out, hidden);
     else if (dtype == RI_BF16)
-        embed_gather_kernel<__nv_bfloat16><<<n_tokens, 256, 0, stream>>>((const __nv_bfloat16*)table, ids, out, hidden);
+        e = launch_dependent(embed_gather_kernel<__nv_bfloat16>, n_tokens, 256, 0, stream, (const __nv_bfloat16*)table, ids, out, hidden);
     else
         return fail("embed_gather: unknown dtype %d", dtype);
-    return check_launch("embed_gather");
+    return check_launch(e, "embed_gather");
 }
 
 // ----------------------------------------------------------------------------
@@ -41,6 +44,8 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
                                const int* __restrict__ rows, T* __restrict__ out, int n, float eps) {
     __shared__ float scratch[33];
     const int r = blockIdx.x;
+    let_next_kernel_start();
+    wait_for_previous_kernels();          // x is the residual stream the previous kernel wrote
     const float* xr = x + (size_t)(rows ? rows[r] : r) * n;
     float ss = 0.f;
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
@@ -54,17 +59,85 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
     for (int i = threadIdx.x; i < n; i += blockDim.x) o[i] = from_f32<T>(xr[i] * scale * w[i]);
 }
 
+template <typename T> __device__ __forceinline__ void store4(T* p, float a, float b, float c, float d);
+template <> __device__ __forceinline__ void store4<float>(float* p, float a, float b, float c, float d) {
+    *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+}
+template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, float a, float b, float c, float d) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    uint2 v;
+    v.x = *reinterpret_cast<uint32_t*>(&lo);
+    v.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p) = v;
+}
+
+// The same in one pass for rows that are a multiple of 4 wide and at most 4 * PER * blockDim long:
+// every thread keeps its float4s of the row in registers, so the row is read once, and the weights
+// (which no kernel writes) are fetched before the wait for the previous kernel.
+template <typename T, int PER>
+__global__ void __launch_bounds__(1024)
+rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ w, const int* __restrict__ rows,
+                   T* __restrict__ out, int n, float eps) {
+    __shared__ float scratch[33];
+    const int r = blockIdx.x, n4 = n >> 2;
+    float4 wv[PER], xv[PER];
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        wv[j] = i < n4 ? reinterpret_cast<const float4*>(w)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    let_next_kernel_start();
+    wait_for_previous_kernels();
+    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * n);
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        xv[j] = i < n4 ? xr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        ss += xv[j].x * xv[j].x + xv[j].y * xv[j].y + xv[j].z * xv[j].z + xv[j].w * xv[j].w;
+    }
+    ss = block_sum(ss, scratch);
+    const float rms = sqrtf(ss / (float)n + eps);
+    const float scale = 1.0f / rms;
+    T* o = out + (size_t)r * n;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < n4)
+            store4<T>(o + 4 * i, xv[j].x * scale * wv[j].x, xv[j].y * scale * wv[j].y, xv[j].z * scale * wv[j].z,
+                      xv[j].w * scale * wv[j].w);
+    }
+}
+
+template <typename T>
+cudaError_t launch_rmsnorm(const float* x, const float* w, const int* rows, T* out, int n_rows, int n, float eps,
+                           cudaStream_t stream) {
+    const bool vec = n % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)out % 16 == 0;
+    const int n4 = n / 4;
+    if (vec && n4 <= 4 * 1024) {
+        // as many threads as float4s, rounded up to whole warps, at most 1024
+        int threads = ((n4 + 31) / 32) * 32;
+        if (threads > 1024) threads = 1024;
+        const int per = (n4 + threads - 1) / threads;
+        if (per <= 1) return launch_dependent(rmsnorm_vec_kernel<T, 1>, n_rows, threads, 0, stream, x, w, rows, out, n, eps);
+        if (per <= 2) return launch_dependent(rmsnorm_vec_kernel<T, 2>, n_rows, threads, 0, stream, x, w, rows, out, n, eps);
+        return launch_dependent(rmsnorm_vec_kernel<T, 4>, n_rows, threads, 0, stream, x, w, rows, out, n, eps);
+    }
+    const int threads = n >= 1024 ? 256 : 128;
+    return launch_dependent(rmsnorm_kernel<T>, n_rows, threads, 0, stream, x, w, rows, out, n, eps);
+}
+
 RI_API int ri_rmsnorm(const float* x, const float* w, const int* rows, void* out, int out_dtype,
                       int n_rows, int n, float eps, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
-    const int threads = n >= 1024 ? 256 : 128;
+    cudaError_t e = cudaSuccess;
     if (out_dtype == RI_F32)
-        rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(x, w, rows, (float*)out, n, eps);
+        e = launch_rmsnorm<float>(x, w, rows, (float*)out, n_rows, n, eps, stream);
     else if (out_dtype == RI_BF16)
-        rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(x, w, rows, (__nv_bfloat16*)out, n, eps);
+        e = launch_rmsnorm<__nv_bfloat16>(x, w, rows, (__nv_bfloat16*)out, n_rows, n, eps, stream);
     else
         return fail("rmsnorm: unknown dtype %d", out_dtype);
-    return check_launch("rmsnorm");
+    return check_launch(e, "rmsnorm");
 }
 
 // ----------------------------------------------------------------------------
@@ -88,6 +161,8 @@ __global__ void rope_cache_write_kernel(T* __restrict__ qkv, int ld, const float
                                         int n_heads, int n_kv_heads, int hd, int page_size, int style,
                                         int write_kv) {
     const int t = blockIdx.x;
+    let_next_kernel_start();
+    wait_for_previous_kernels();          // the projections come from the previous kernel
     const int pos = token_pos[t];
     const int half = hd >> 1;
     T* row = qkv + (size_t)t * ld;
@@ -142,17 +217,105 @@ RI_API int ri_rope_cache_write(void* qkv, int dtype, int ld, const float* cos_t,
     if (style != 0 && style != 1) return fail("rope_cache_write: unknown style %d", style);
     const int work = n_heads * hd / 2;
     const int threads = work >= 256 ? 256 : (work >= 128 ? 128 : 64);
+    cudaError_t e = cudaSuccess;
     if (dtype == RI_F32)
-        rope_cache_write_kernel<float><<<n_tokens, threads, 0, stream>>>(
+        e = launch_dependent(rope_cache_write_kernel<float>, n_tokens, threads, 0, stream,
             (float*)qkv, ld, cos_t, sin_t, token_pos, token_seq, seq_slot, page_table, max_pages,
             (float*)kcache, (float*)vcache, n_heads, n_kv_heads, hd, page_size, style, write_kv);
     else if (dtype == RI_BF16)
-        rope_cache_write_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(
+        e = launch_dependent(rope_cache_write_kernel<__nv_bfloat16>, n_tokens, threads, 0, stream,
             (__nv_bfloat16*)qkv, ld, cos_t, sin_t, token_pos, token_seq, seq_slot, page_table, max_pages,
             (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, n_heads, n_kv_heads, hd, page_size, style, write_kv);
     else
         return fail("rope_cache_write: unknown dtype %d", dtype);
-    return check_launch("rope_cache_write");
+    return check_launch(e, "rope_cache_write");
+}
+
+// ----------------------------------------------------------------------------
+// The same, fed from float32 accumulators.  When the q/k/v projection of a small step is split
+// over K, its pieces are summed into a zeroed float32 buffer acc[n_tokens, ld]; this kernel adds
+// the bias, rotates in float32 (q and k never pass through the storage type before rotation),
+// writes q to q_out[n_tokens, q_dim] and k, v to the cache, and puts zeros back into `acc`, so
+// that the buffer is clean for the next projection.
+// ----------------------------------------------------------------------------
+template <typename T>
+__global__ void rope_cache_write_acc_kernel(float* __restrict__ acc, int ld, const float* __restrict__ bias,
+                                            T* __restrict__ q_out, const float* __restrict__ cos_t,
+                                            const float* __restrict__ sin_t, const int* __restrict__ token_pos,
+                                            const int* __restrict__ token_seq, const int* __restrict__ seq_slot,
+                                            const int* __restrict__ page_table, int max_pages,
+                                            T* __restrict__ kcache, T* __restrict__ vcache, int n_heads,
+                                            int n_kv_heads, int hd, int page_size, int style, int write_kv) {
+    const int t = blockIdx.x;
+    let_next_kernel_start();
+    wait_for_previous_kernels();          // the projections come from the previous kernel
+    const int pos = token_pos[t];
+    const int half = hd >> 1;
+    float* row = acc + (size_t)t * ld;
+    const float* c = cos_t + (size_t)pos * half;
+    const float* s = sin_t + (size_t)pos * half;
+    const int q_dim = n_heads * hd, kv_dim = n_kv_heads * hd;
+
+    size_t cache_base = 0;
+    if (write_kv) {
+        const int slot = seq_slot[token_seq[t]];
+        const int page = page_table[(size_t)slot * max_pages + pos / page_size];
+        cache_base = ((size_t)page * n_kv_heads * page_size + (pos % page_size)) * hd;
+    }
+    const size_t head_stride = (size_t)page_size * hd;
+
+    for (int idx = threadIdx.x; idx < (n_heads + n_kv_heads) * half; idx += blockDim.x) {
+        const int h = idx / half, i = idx % half;
+        const int i0 = style == 0 ? i : 2 * i;
+        const int i1 = style == 0 ? i + half : 2 * i + 1;
+        const int col = h * hd;                       // q heads first, then the k heads: same column order
+        float x0 = row[col + i0], x1 = row[col + i1];
+        if (bias) { x0 += bias[col + i0]; x1 += bias[col + i1]; }
+        row[col + i0] = 0.f;
+        row[col + i1] = 0.f;
+        const float y0 = x0 * c[i] - x1 * s[i], y1 = x0 * s[i] + x1 * c[i];
+        if (h < n_heads) {
+            T* dst = q_out + (size_t)t * q_dim + col;
+            dst[i0] = from_f32<T>(y0);
+            dst[i1] = from_f32<T>(y1);
+        } else if (write_kv) {
+            T* dst = kcache + cache_base + (h - n_heads) * head_stride;
+            dst[i0] = from_f32<T>(y0);
+            dst[i1] = from_f32<T>(y1);
+        }
+    }
+    for (int idx = threadIdx.x; idx < kv_dim; idx += blockDim.x) {
+        const int col = q_dim + kv_dim + idx;
+        float v = row[col];
+        if (bias) v += bias[col];
+        row[col] = 0.f;
+        if (write_kv) vcache[cache_base + (idx / hd) * head_stride + (idx % hd)] = from_f32<T>(v);
+    }
+}
+
+RI_API int ri_rope_cache_write_acc(float* acc, int ld, const float* bias, void* q_out, int dtype, const float* cos_t,
+                                   const float* sin_t, const int* token_pos, const int* token_seq,
+                                   const int* seq_slot, const int* page_table, int max_pages, void* kcache,
+                                   void* vcache, int n_tokens, int n_heads, int n_kv_heads, int hd, int page_size,
+                                   int style, int write_kv, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (hd % 2) return fail("rope_cache_write: head_dim %d is odd", hd);
+    if (style != 0 && style != 1) return fail("rope_cache_write: unknown style %d", style);
+    if (ld != (n_heads + 2 * n_kv_heads) * hd) return fail("rope_cache_write: accumulator rows of %d, expected %d", ld, (n_heads + 2 * n_kv_heads) * hd);
+    const int work = (n_heads + n_kv_heads) * hd / 2;
+    const int threads = work >= 512 ? 512 : (work >= 256 ? 256 : 128);
+    cudaError_t e = cudaSuccess;
+    if (dtype == RI_F32)
+        e = launch_dependent(rope_cache_write_acc_kernel<float>, n_tokens, threads, 0, stream,
+            acc, ld, bias, (float*)q_out, cos_t, sin_t, token_pos, token_seq, seq_slot, page_table, max_pages,
+            (float*)kcache, (float*)vcache, n_heads, n_kv_heads, hd, page_size, style, write_kv);
+    else if (dtype == RI_BF16)
+        e = launch_dependent(rope_cache_write_acc_kernel<__nv_bfloat16>, n_tokens, threads, 0, stream,
+            acc, ld, bias, (__nv_bfloat16*)q_out, cos_t, sin_t, token_pos, token_seq, seq_slot, page_table, max_pages,
+            (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, n_heads, n_kv_heads, hd, page_size, style, write_kv);
+    else
+        return fail("rope_cache_write: unknown dtype %d", dtype);
+    return check_launch(e, "rope_cache_write_acc");
 }
 
 // ----------------------------------------------------------------------------

@@ -178,12 +178,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
+    let_next_kernel_start();
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
             int issued = 0;
-            for (int i = 0; i < n_kb; ++i) {
+            // The weights are written by no kernel, so their tiles for the first round of stages go
+            // out at once; the activations come from the kernel before this one and wait for it.
+            const int ahead = min(stages, n_kb);
+            for (int i = 0; i < ahead; ++i) {
+                const uint32_t bar = smem_u32(&full_bar[i]);
+                const uint32_t stage = smem_base + (uint32_t)i * STAGE_BYTES;
+                const int kx = (kb_begin + i) * BLOCK_K;
+                mbar_expect_tx(bar, STAGE_BYTES);
+                tma_load_2d(stage, &map_w, bar, kx, f0);
+                if (DUAL) tma_load_2d(stage + A_BYTES, &map_w2, bar, kx, f0);
+            }
+            wait_for_previous_kernels();
+            for (int i = 0; i < ahead; ++i) {
+                const uint32_t stage = smem_base + (uint32_t)i * STAGE_BYTES;
+                tma_load_2d(stage + (DUAL ? 2 : 1) * A_BYTES, &map_x, smem_u32(&full_bar[i]),
+                            (kb_begin + i) * BLOCK_K, t0);
+                issued = i + 1;
+            }
+            for (int i = ahead; i < n_kb; ++i) {
                 const int s = i % stages;
                 const uint32_t ph = (uint32_t)(i / stages) & 1u;
                 if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1u)) {
@@ -244,6 +263,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         }
     } else {
         // ---------------- epilogue: warps 2..5 ----------------
+        wait_for_previous_kernels();          // `out` may still be read or written by the kernel before
         const bool landed = mbar_wait(smem_u32(&accum_bar), 0);
         if (!landed && lane == 0) {
             report(status, ST_EPILOGUE_TIMEOUT);
@@ -334,12 +354,18 @@ int make_map(CUtensorMap* map, const void* ptr, long long rows, long long K, int
     return 0;
 }
 
+int g_smem_budget = 0;       // 0: the default for the tile; set through ri_gemm_tcgen05_set_smem_budget
+
 template <int TN, bool DUAL, int MODE>
 int launch(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx, const float* bias, void* out,
            int n_tok, int n_feat, int K, int split_k, int* status, cudaStream_t stream) {
     constexpr int STAGE_BYTES = (DUAL ? 2 : 1) * A_BYTES + TN * BLOCK_K * 2;
     const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
-    int stages = SMEM_BUDGET / STAGE_BYTES;
+    // Small token tiles (decode) leave room for a second CTA on the SM, so that the next kernel's
+    // CTAs can settle in and prefetch their weights while this one drains.
+    int budget = g_smem_budget > 0 ? g_smem_budget : (TN <= 32 ? 108 * 1024 : SMEM_BUDGET);
+    if (budget > SMEM_BUDGET) budget = SMEM_BUDGET;
+    int stages = budget / STAGE_BYTES;
     if (stages > MAX_STAGES) stages = MAX_STAGES;
     if (stages > total_kb) stages = total_kb;
     if (stages < 1) stages = 1;
@@ -356,8 +382,9 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx,
         configured = true;
     }
     dim3 grid((n_feat + BLOCK_F - 1) / BLOCK_F, (n_tok + TN - 1) / TN, split_k);
-    kernel<<<grid, THREADS, smem, stream>>>(mw, mw2, mx, bias, out, n_tok, n_feat, K, kb_per_split, stages, status);
-    return check_launch("gemm_tcgen05");
+    cudaError_t e = launch_dependent(kernel, grid, dim3(THREADS), smem, stream, mw, mw2, mx, bias, out, n_tok, n_feat, K,
+                                     kb_per_split, stages, status);
+    return check_launch(e, "gemm_tcgen05");
 }
 
 template <bool DUAL, int MODE>
@@ -376,6 +403,12 @@ int pick_tile(int tn, const CUtensorMap& mw, const CUtensorMap& mw2, const CUten
 }
 
 }  // namespace
+
+// Shared memory a CTA may use for its stage ring, in bytes (0 restores the defaults).  For tuning.
+RI_API int ri_gemm_tcgen05_set_smem_budget(int bytes) {
+    g_smem_budget = bytes;
+    return 0;
+}
 
 // The token tile a call with n_tok tokens uses.
 RI_API int ri_gemm_tcgen05_tile(int n_tok, int dual) {

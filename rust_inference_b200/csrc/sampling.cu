@@ -73,6 +73,8 @@ sample_kernel(float* __restrict__ logits, int vocab, int* __restrict__ out, floa
     __shared__ int s_token;
 
     const int r = blockIdx.x, tid = threadIdx.x;
+    let_next_kernel_start();
+    wait_for_previous_kernels();          // the logits come from the kernel before
     float* p = logits + (size_t)r * vocab;
 
     // ---- repetition penalty (sampler.rs:109-127) ----
@@ -277,9 +279,10 @@ RI_API int ri_sample(float* logits, int rows, int vocab, int* out, float tempera
     if (penalty <= 0.f) return fail("sample: repetition penalty %f must be positive", penalty);
     if (temperature > 0.f && (row_stream == nullptr || row_counter == nullptr))
         return fail("sample: temperature sampling needs row streams and counters");
-    sample_kernel<<<rows, THREADS, 0, stream>>>(logits, vocab, out, temperature, top_k, top_p, penalty, recent,
-                                                recent_ld, recent_count, seed, row_stream, row_counter);
-    return check_launch("sample");
+    cudaError_t e = launch_dependent(sample_kernel, dim3(rows), dim3(THREADS), (size_t)0, stream, logits, vocab, out,
+                                     temperature, top_k, top_p, penalty, recent, recent_ld, recent_count, seed,
+                                     row_stream, row_counter);
+    return check_launch(e, "sample");
 }
 
 RI_DEFINE_LAST_ERROR()

@@ -27,6 +27,25 @@ class Workspace:
             self._flat[key] = flat
         return flat[:n].view(*shape)
 
+    def get_zeroed(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
+        """A buffer that holds zeros whenever it is handed out: it is zero-filled when made, and
+        whoever uses it must leave it zeroed again (the kernel that consumes an accumulator puts
+        the zeros back).  `rezero` restores that after a step that did not finish."""
+        n = 1
+        for s in shape:
+            n *= int(s)
+        key = ("zeroed:" + name, dtype)
+        flat = self._flat.get(key)
+        if flat is None or flat.numel() < n:
+            flat = torch.zeros(max(n, 1), dtype=dtype, device=self.device)
+            self._flat[key] = flat
+        return flat[:n].view(*shape)
+
+    def rezero(self) -> None:
+        for (name, _), flat in self._flat.items():
+            if isinstance(name, str) and name.startswith("zeroed:"):
+                flat.zero_()
+
     def bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self._flat.values())
 
@@ -67,6 +86,9 @@ class StepContext:
 
     def buffer(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
         return self.workspace.get(name, shape, dtype)
+
+    def zeroed_buffer(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
+        return self.workspace.get_zeroed(name, shape, dtype)
 
 
 def pack_step(starts: list, tokens: list, wants: list) -> tuple:

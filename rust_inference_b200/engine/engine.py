@@ -200,7 +200,11 @@ class Engine:
                     logits = logits.clone()
             else:
                 ctx = self.make_context(slots, tokens, wants)
-                logits = self.model.forward(ctx, self.cache)
+                try:
+                    logits = self.model.forward(ctx, self.cache)
+                except Exception:
+                    self.workspace.rezero()          # accumulators a failed step may have left dirty
+                    raise
         for s, t in zip(slots, tokens):
             self.cache.commit(s, self.cache.length(s) + len(t))
         return logits

@@ -61,3 +61,22 @@ def gated(x, w_gate: Weight, w_up: Weight, out, ctx):
         from . import tcgen05
         return tcgen05.gemm(x, w_gate, out, ops.EPI_SILU_MUL, ctx, w2=w_up)
     return ops.gemm_simt(x, w_gate.t, out, ops.EPI_SILU_MUL, w2=w_up.t)
+
+
+def accumulate_split(x, w: Weight, acc, ctx) -> bool:
+    """acc<float32> += x W^T with K split over enough CTAs to fill the GPU, if the tensor-core
+    kernel takes the shape (returns False otherwise and does nothing).  For small steps whose
+    output has too few tiles to keep every SM streaming weights."""
+    if not _use_tensor_cores(x, w):
+        return False
+    from . import tcgen05
+    tcgen05.gemm(x, w, acc, ops.EPI_RESIDUAL, ctx)
+    return True
+
+
+def wants_split(x, w: Weight) -> bool:
+    """True for a small step (at most 64 tokens) whose projection would leave most SMs idle."""
+    if not _use_tensor_cores(x, w) or x.shape[0] > 64:
+        return False
+    from . import tcgen05
+    return tcgen05.pick_split(x.shape[0], w.n, w.k, False) > 1

@@ -116,6 +116,26 @@ def rope_cache_write(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, to
           c_int(head_dim), c_int(page_size), c_int(style), c_int(1 if write_kv else 0), _stream())
 
 
+def rope_cache_write_acc(acc: torch.Tensor, bias, q_out: torch.Tensor, cos, sin, token_pos, token_seq, seq_slot,
+                         page_table, kcache, vcache, *, n_heads: int, n_kv_heads: int, head_dim: int,
+                         page_size: int, style: int, write_kv: bool) -> None:
+    """The rotary + cache-write kernel fed from float32 accumulators acc[T, (heads + 2 kv heads) * head_dim]
+    (+ bias): q goes to q_out[T, heads * head_dim], k and v to the cache, and `acc` is zeroed again."""
+    _need_cuda(acc, bias, q_out, cos, sin, token_pos, token_seq, seq_slot, page_table, kcache, vcache)
+    n = acc.shape[0]
+    _need(acc.dtype == torch.float32 and acc.is_contiguous()
+          and acc.shape[1] == (n_heads + 2 * n_kv_heads) * head_dim, "rope_cache_write_acc: accumulator shape")
+    _need(q_out.is_contiguous() and q_out.shape == (n, n_heads * head_dim), "rope_cache_write_acc: q_out shape")
+    _need(bias is None or (bias.dtype == torch.float32 and bias.numel() == acc.shape[1]), "rope_cache_write_acc: bias")
+    if write_kv:
+        _need(kcache.dtype == q_out.dtype and vcache.dtype == q_out.dtype
+              and tuple(kcache.shape[1:]) == (n_kv_heads, page_size, head_dim), "rope_cache_write_acc: cache")
+    _call("elementwise", "ri_rope_cache_write_acc", _p(acc), c_int(acc.shape[1]), _p(bias), _p(q_out),
+          c_int(dtype_code(q_out.dtype)), _p(cos), _p(sin), _p(token_pos), _p(token_seq), _p(seq_slot),
+          _p(page_table), c_int(page_table.shape[1]), _p(kcache), _p(vcache), c_int(n), c_int(n_heads),
+          c_int(n_kv_heads), c_int(head_dim), c_int(page_size), c_int(style), c_int(1 if write_kv else 0), _stream())
+
+
 def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
     _need_cuda(gate_up, out)

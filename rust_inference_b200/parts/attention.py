@@ -65,11 +65,22 @@ class GQAttention(Mixer):
 
     def forward(self, x, residual, ctx, cache_layer, writes_cache):
         n = x.shape[0]
-        qkv = ctx.buffer("qkv", (n, self.q_dim + 2 * self.kv_dim), self.dtype)
-        linear.project(x, self.w_qkv, qkv, ctx, bias=self.b_qkv)
-        self.position.apply_and_store(qkv, ctx, cache_layer, n_heads=self.n_heads,
-                                      n_kv_heads=self.n_kv_heads, head_dim=self.head_dim,
-                                      write_kv=writes_cache)
+        width = self.q_dim + 2 * self.kv_dim
+        from_acc = getattr(self.position, "apply_and_store_from_accumulators", None)
+        if from_acc is not None and linear.wants_split(x, self.w_qkv):
+            # a small step: the projection is split over K into float32 accumulators, and the
+            # position encoding adds the bias, rotates and stores from there
+            acc = ctx.zeroed_buffer("qkv_acc", (n, width), torch.float32)
+            linear.accumulate_split(x, self.w_qkv, acc, ctx)
+            qkv = ctx.buffer("q_rot", (n, self.q_dim), self.dtype)
+            from_acc(acc, self.b_qkv, qkv, ctx, cache_layer, n_heads=self.n_heads, n_kv_heads=self.n_kv_heads,
+                     head_dim=self.head_dim, write_kv=writes_cache)
+        else:
+            qkv = ctx.buffer("qkv", (n, width), self.dtype)
+            linear.project(x, self.w_qkv, qkv, ctx, bias=self.b_qkv)
+            self.position.apply_and_store(qkv, ctx, cache_layer, n_heads=self.n_heads,
+                                          n_kv_heads=self.n_kv_heads, head_dim=self.head_dim,
+                                          write_kv=writes_cache)
         mixed = ctx.buffer("attn_out", (n, self.q_dim), self.dtype)
         attn_kernels.attention(qkv, cache_layer, mixed, ctx, n_heads=self.n_heads,
                                n_kv_heads=self.n_kv_heads, head_dim=self.head_dim, scale=self.scale,

@@ -56,3 +56,14 @@ class RotaryEncoding(PositionEncoding):
                              ctx.page_table, cache_layer.k, cache_layer.v, n_heads=n_heads,
                              n_kv_heads=n_kv_heads, head_dim=head_dim, page_size=ctx.page_size,
                              style=self.style, write_kv=write_kv)
+
+    def apply_and_store_from_accumulators(self, acc, bias, q_out, ctx, cache_layer, *, n_heads, n_kv_heads,
+                                          head_dim, write_kv):
+        """The same from float32 accumulators of a K-split projection (bias not yet added): q goes
+        to q_out, and `acc` is left zeroed."""
+        if self.cos is None or self.cos.shape[0] < ctx.max_len:
+            raise RuntimeError("rope tables do not cover the step's positions; call prepare() first")
+        ops.rope_cache_write_acc(acc, bias, q_out, self.cos, self.sin, ctx.token_pos, ctx.token_seq, ctx.seq_slot,
+                                 ctx.page_table, cache_layer.k, cache_layer.v, n_heads=n_heads,
+                                 n_kv_heads=n_kv_heads, head_dim=head_dim, page_size=ctx.page_size,
+                                 style=self.style, write_kv=write_kv)

@@ -115,6 +115,49 @@ def test_rope_and_cache_write(style, dtype, nh, nkv, hd):
     assert torch.equal(q2[:, :nh * hd], q_dev[:, :nh * hd]) and (k2.float() == 77.0).all()
 
 
+@pytest.mark.parametrize("style", ["half", "interleaved"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh, nkv, hd, bias", [(3, 1, 6, True), (8, 2, 16, False), (28, 4, 128, True)])
+def test_rope_and_cache_write_from_accumulators(style, dtype, nh, nkv, hd, bias):
+    """The variant fed from float32 accumulators must give what the plain path gives on
+    (accumulator + bias), write q to its own buffer and leave the accumulator zeroed."""
+    ops = _ops()
+    from rust_inference_b200.parts.rope import rope_tables
+    page, n_pages = 64, 5
+    cos, sin = rope_tables(hd, 10000.0, 200)
+    pcos, psin = plain_impl.rope_table(hd, 10000.0, 200)
+    table = torch.tensor([[4, 1, 0], [2, 3, 0]], dtype=torch.int32)
+    positions, seqs, slots = [0, 70, 127], [0, 1, 1], [1, 0]
+    T, width = 3, (nh + 2 * nkv) * hd
+    acc = torch.randn(T, width)
+    b = torch.randn(width) if bias else None
+    d = lambda t: t.to(DEV)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    acc_dev = d(acc.clone())
+    q_out = torch.full((T, nh * hd), 5.0, device=DEV, dtype=dtype)
+    kc = torch.zeros(n_pages, nkv, page, hd, device=DEV, dtype=dtype)
+    vc = torch.zeros_like(kc)
+    ops.rope_cache_write_acc(acc_dev, d(b) if bias else None, q_out, d(torch.from_numpy(cos)),
+                             d(torch.from_numpy(sin)), i32(positions), i32(seqs), i32(slots), d(table), kc, vc,
+                             n_heads=nh, n_kv_heads=nkv, head_dim=hd, page_size=page,
+                             style={"half": 0, "interleaved": 1}[style], write_kv=True)
+    assert (acc_dev == 0).all()                                   # clean for the next projection
+    x = acc + (b if bias else 0)
+    tol = 2e-6 if dtype == torch.float32 else 1e-2
+    for t in range(T):
+        pos, slot = positions[t], slots[seqs[t]]
+        c, s_ = pcos[pos:pos + 1], psin[pos:pos + 1]
+        pg, off = int(table[slot, pos // page]), pos % page
+        for h in range(nh):
+            want = plain_impl.rope_apply(x[t, h * hd:(h + 1) * hd][None], c, s_, style)[0]
+            assert torch.allclose(q_out[t, h * hd:(h + 1) * hd].float().cpu(), want, atol=tol * 4, rtol=tol)
+        for h in range(nkv):
+            want = plain_impl.rope_apply(x[t, (nh + h) * hd:(nh + h + 1) * hd][None], c, s_, style)[0]
+            assert torch.allclose(kc[pg, h, off].float().cpu(), want, atol=tol * 4, rtol=tol)
+            v = x[t, (nh + nkv + h) * hd:(nh + nkv + h + 1) * hd]
+            assert torch.allclose(vc[pg, h, off].float().cpu(), v, atol=tol * 4, rtol=tol)
+
+
 GEMM_SHAPES = [(1, 7, 5), (3, 100, 33), (17, 264, 128), (64, 391, 192), (130, 77, 1000), (5, 3584, 64), (300, 130, 520)]
 
 

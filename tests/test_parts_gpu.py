@@ -74,25 +74,30 @@ def test_swiglu_part(dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("style, bias, nh, nkv, hd", [("half", False, 4, 2, 64), ("interleaved", True, 6, 1, 32),
-                                                      ("half", True, 3, 3, 128)])
-def test_attention_part_with_cache(dtype, style, bias, nh, nkv, hd):
+@pytest.mark.parametrize("style, bias, nh, nkv, hd, h", [
+    ("half", False, 4, 2, 64, 80), ("interleaved", True, 6, 1, 32, 80), ("half", True, 3, 3, 128, 80),
+    # a width at which the single-token projections are split over K into float32 accumulators
+    ("half", True, 4, 2, 64, 1536), ("interleaved", False, 2, 1, 128, 1024)])
+def test_attention_part_with_cache(dtype, style, bias, nh, nkv, hd, h):
     """The mixer alone: a prompt in one step and then token by token must equal the plain
     attention over the whole sequence."""
     from rust_inference_b200.cache.sequence_cache import SequenceCache
+    from rust_inference_b200.kernels import linear
     from rust_inference_b200.parts.registry import lookup
     from rust_inference_b200.parts.spec import PartSpec
-    h, n, cut = 80, 150, 100
+    n, cut = 150, 100
     part = lookup("mixer", "gqa_attention")(
         n_heads=nh, n_kv_heads=nkv, head_dim=hd, qkv_bias=bias,
         position=PartSpec("rope", {"head_dim": hd, "base": 50000.0, "style": style}),
         hidden_size=h, dtype=dtype, device=DEV)
     specs = part.tensor_specs()
     assert ("q_proj.bias" in specs) == bias and specs["k_proj.weight"].shape == (nkv * hd, h)
-    p = {name: (torch.randn(ts.shape) * (0.25 if ts.role == "matrix" else 0.1)).to(dtype).float()
+    p = {name: (torch.randn(ts.shape) * ((2.0 / h ** 0.5) if ts.role == "matrix" else 0.1)).to(dtype).float()
          for name, ts in specs.items()}
     _place(part, p, dtype)
     part.prepare(256)
+    one = torch.zeros(1, h, device=DEV, dtype=dtype)
+    assert linear.wants_split(one, part.w_qkv) == (dtype == torch.bfloat16 and h >= 1024)
     cache = SequenceCache([part.cache_request()], max_tokens=512, max_seq_len=256, dtype=dtype, device=DEV)
     x = (torch.randn(n, h) * 0.5).to(dtype)
     cos, sin = plain_impl.rope_table(hd, 50000.0, n)
