@@ -133,6 +133,27 @@ __device__ __forceinline__ void report(int* status, int code) {
     }
 }
 
+// SiLU without a branch, for results that are rounded to bf16 right away: x / (1 + e^-x).  For very
+// negative x the exponential overflows to +inf and the quotient is -0, the limit of the reference's
+// x e^x / (1 + e^x) (math.rs:137-146); the fast exponential and division are exact to a few ulp of
+// float32, far below bf16's 8 bits.
+__device__ __forceinline__ float silu_to_bf16(float x) { return __fdividef(x, 1.f + __expf(-x)); }
+
+template <int MODE>
+__device__ __forceinline__ void store_result(void* out_, size_t o, float acc, float bias, float acc2) {
+    if (MODE == 0) {
+        reinterpret_cast<__nv_bfloat16*>(out_)[o] = __float2bfloat16_rn(acc + bias);
+    } else if (MODE == 1) {
+        reinterpret_cast<float*>(out_)[o] = acc + bias;
+    } else if (MODE == 2) {
+        // one add per element and split: a reduction without a return value, so the epilogue never
+        // waits on a load
+        atomicAdd(reinterpret_cast<float*>(out_) + o, acc);
+    } else {
+        reinterpret_cast<__nv_bfloat16*>(out_)[o] = __float2bfloat16_rn(silu_to_bf16(acc) * acc2);
+    }
+}
+
 __host__ __device__ constexpr int tmem_cols(int need) { return need <= 32 ? 32 : need <= 64 ? 64 : need <= 128 ? 128 : need <= 256 ? 256 : 512; }
 
 template <int TN, bool DUAL, int MODE>
@@ -154,7 +175,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;     // swizzled tiles want 1024-byte alignment
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int f0 = blockIdx.x * BLOCK_F, t0 = blockIdx.y * TN;
+    // token tiles vary fastest over the grid: CTAs that run together share a weight tile in L2
+    const int f0 = blockIdx.y * BLOCK_F, t0 = blockIdx.x * TN;
     const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
     const int kb_begin = blockIdx.z * kb_per_split;
     const int n_kb = min(total_kb, kb_begin + kb_per_split) - kb_begin;    // >= 1 by construction of the grid
@@ -284,25 +306,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 if (DUAL) tmem_ld16(trow + TN + c0, u);
                 tmem_wait_ld();
                 if (f_ok) {
+                    // a group of 16 tokens that lies inside the matrix runs without per-token branches,
+                    // so the 16 independent chains interleave; the ragged last group takes the checked path
+                    const bool whole = t0 + c0 + 16 <= n_tok;
+                    const size_t o0 = (size_t)(t0 + c0) * n_feat + f;
+                    if (whole) {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const int t = t0 + c0 + j;
-                        if (t < n_tok) {
-                            const size_t o = (size_t)t * n_feat + f;
-                            const float acc = __uint_as_float(v[j]);
-                            if (MODE == 0) {
-                                reinterpret_cast<__nv_bfloat16*>(out_)[o] = __float2bfloat16_rn(acc + b);
-                            } else if (MODE == 1) {
-                                reinterpret_cast<float*>(out_)[o] = acc + b;
-                            } else if (MODE == 2) {
-                                // one add per element and split: a reduction without a return value,
-                                // so the epilogue never waits on a load
-                                atomicAdd(reinterpret_cast<float*>(out_) + o, acc);
-                            } else {
-                                reinterpret_cast<__nv_bfloat16*>(out_)[o] =
-                                    __float2bfloat16_rn(silu_f32(acc) * __uint_as_float(u[j]));
-                            }
-                        }
+                        for (int j = 0; j < 16; ++j)
+                            store_result<MODE>(out_, o0 + (size_t)j * n_feat, __uint_as_float(v[j]), b,
+                                               DUAL ? __uint_as_float(u[j]) : 0.f);
+                    } else {
+                        for (int j = 0; j < 16; ++j)
+                            if (t0 + c0 + j < n_tok)
+                                store_result<MODE>(out_, o0 + (size_t)j * n_feat, __uint_as_float(v[j]), b,
+                                                   DUAL ? __uint_as_float(u[j]) : 0.f);
                     }
                 }
             }
@@ -363,7 +380,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx,
     const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
     // Small token tiles (decode) leave room for a second CTA on the SM, so that the next kernel's
     // CTAs can settle in and prefetch their weights while this one drains.
-    int budget = g_smem_budget > 0 ? g_smem_budget : (TN <= 32 ? 108 * 1024 : SMEM_BUDGET);
+    int budget = g_smem_budget > 0 ? g_smem_budget : (3 * STAGE_BYTES <= 108 * 1024 && TN <= 64 ? 108 * 1024 : SMEM_BUDGET);
     if (budget > SMEM_BUDGET) budget = SMEM_BUDGET;
     int stages = budget / STAGE_BYTES;
     if (stages > MAX_STAGES) stages = MAX_STAGES;
@@ -381,7 +398,8 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx,
         if (e != cudaSuccess) return fail("gemm_tcgen05: cannot raise dynamic shared memory: %s", cudaGetErrorString(e));
         configured = true;
     }
-    dim3 grid((n_feat + BLOCK_F - 1) / BLOCK_F, (n_tok + TN - 1) / TN, split_k);
+    dim3 grid((n_tok + TN - 1) / TN, (n_feat + BLOCK_F - 1) / BLOCK_F, split_k);
+    if (grid.y > 65535) return fail("gemm_tcgen05: %d features exceed the grid limit", n_feat);
     cudaError_t e = launch_dependent(kernel, grid, dim3(THREADS), smem, stream, mw, mw2, mx, bias, out, n_tok, n_feat, K,
                                      kb_per_split, stages, status);
     return check_launch(e, "gemm_tcgen05");
