@@ -117,6 +117,11 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the model has (recorded)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--skip-points", action="store_true", help="skip the batch-1 and batch-64 points")
+    ap.add_argument("--kernel", default=None, help="time ONE kernel at the benchmark model's sizes instead "
+                    "(qkv, qkv_split, o_proj, gate_up, down, lm_head, attn_decode, attn_prefill, attn_prefill_mma, rmsnorm, rope)")
+    ap.add_argument("--tokens", type=int, default=8, help="with --kernel: tokens in the step")
+    ap.add_argument("--context", type=int, default=1024, help="with --kernel: cached positions per sequence")
+    ap.add_argument("--once", action="store_true", help="with --kernel: launch the workload once, untimed (for ncu)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -128,6 +133,9 @@ def main() -> int:
     if args.gpus != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    if args.kernel:
+        from rust_inference_b200.kernels import microbench
+        return microbench.main(args.kernel, MODEL, args.tokens, args.context, args.once)
     warmup = max(3, args.warmup)
     steps = max(1, args.steps)
 

@@ -30,11 +30,10 @@
 // TMA needs 16-byte row strides: K must be a multiple of 8.  Everything else (tokens,
 // features, K not a multiple of the tile) is handled by TMA's zero fill and by bounds
 // checks in the epilogue.
-#include "common.cuh"
-
-#include <cuda.h>
+#include "tcgen05_common.cuh"
 
 using namespace ri;
+using namespace ri::tc;
 
 namespace {
 
@@ -43,94 +42,14 @@ constexpr int BLOCK_K = 64;                        // bf16 per k-block: one 128-
 constexpr int A_BYTES = BLOCK_F * BLOCK_K * 2;     // 16 KiB
 constexpr int MAX_STAGES = 8;
 constexpr int THREADS = 192;
-constexpr uint32_t WAIT_LIMIT = 4u << 20;
 constexpr int SMEM_BUDGET = 200 * 1024;
 
 enum Status { ST_OK = 0, ST_PRODUCER_TIMEOUT = 1, ST_MMA_TIMEOUT = 2, ST_EPILOGUE_TIMEOUT = 3, ST_DRAIN_TIMEOUT = 4 };
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Bounded wait: false when the limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if (i > 128) __nanosleep(64);
-    }
-    return false;
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
-        : "memory");
-}
-
-// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bf16),
-// written by TMA with 128-byte swizzle: 8-row groups are 1024 bytes apart (stride byte
-// offset), the leading byte offset is unused for swizzled K-major tiles, version 1
-// (Blackwell), layout type 2 (128-byte swizzle).
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((addr & 0x3FFFF) >> 4);          // start address, bits [0, 14)
-    d |= (uint64_t)1 << 16;                          // leading byte offset (ignored), bits [16, 30)
-    d |= (uint64_t)(1024 >> 4) << 32;                // stride byte offset, bits [32, 46)
-    d |= (uint64_t)1 << 46;                          // descriptor version, bits [46, 48)
-    d |= (uint64_t)2 << 61;                          // SWIZZLE_128B, bits [61, 64)
-    return d;
-}
 
 // Instruction descriptor of kind::f16: D float32, A and B bf16, both K-major, M = 128, N = TN.
 template <int TN>
 __host__ __device__ constexpr uint32_t make_idesc() {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(BLOCK_F >> 4) << 24);
-}
-
-__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, bool accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"((uint32_t)accumulate)
-        : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void report(int* status, int code) {
-    if (status) {
-        *reinterpret_cast<volatile int*>(status) = code;
-        __threadfence_system();
-    }
 }
 
 // SiLU without a branch, for results that are rounded to bf16 right away: x / (1 + e^-x).  For very
@@ -338,22 +257,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 // ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(p);
-    }
-    return fn;
-}
-
 // A bf16 matrix [rows, K] row-major as a 2-D tensor map with a {64, box_rows} box, 128-byte swizzle,
 // zero fill outside the tensor.
 int make_map(CUtensorMap* map, const void* ptr, long long rows, long long K, int box_rows, const char* what) {

@@ -1,18 +1,22 @@
 """Attention over the paged cache: which kernel runs, by dtype, head size and step shape.
 
-  bfloat16, head_dim 64 or 128   tensor-core kernels (`attention_mma`): split-K over runs of
-                                 pages when every sequence brings one token, a flash-style
-                                 causal kernel otherwise
+  bfloat16, head_dim 64 or 128   one token per sequence: split-K over runs of pages
+                                 (`attention_mma`); otherwise the tcgen05 flash-style causal
+                                 kernel (`attention_tcgen05`), with the mma.sync one behind it
   anything else                  the generic kernel (`attention_generic`): any head size, any
                                  dtype, float32 arithmetic
 """
 from __future__ import annotations
+
+import os
 
 import torch
 
 from . import ops
 
 N_SMS = 148
+# RI_B200_PREFILL_ATTENTION=mma keeps the mma.sync prefill kernel (for comparisons)
+_PREFILL = os.environ.get("RI_B200_PREFILL_ATTENTION", "tcgen05")
 
 
 def decode_splits(n_seqs: int, n_kv_heads: int, max_seq_len: int, page_size: int) -> int:
@@ -43,6 +47,13 @@ def attention(qkv, cache_layer, out, ctx, *, n_heads, n_kv_heads, head_dim, scal
                     ctx.cu_seqlens, out, n_seqs=ctx.n_seqs, n_heads=n_heads, n_kv_heads=n_kv_heads,
                     head_dim=head_dim, page_size=ctx.page_size, scale=scale, window=window, n_splits=splits,
                     part_o=part_o, part_ml=part_ml)
+            from . import attention_tc
+            if _PREFILL != "mma" and attention_tc.supports(head_dim, ctx.page_size, n_heads, n_kv_heads, q_ld,
+                                                           out.shape[1]):
+                return attention_tc.prefill(
+                    qkv, cache_layer.k, cache_layer.v, ctx.page_table, ctx.seq_slot, ctx.seq_start, ctx.cu_seqlens,
+                    out, n_seqs=ctx.n_seqs, max_new=ctx.max_new, n_heads=n_heads, n_kv_heads=n_kv_heads,
+                    head_dim=head_dim, page_size=ctx.page_size, scale=scale, window=window)
             return ops.attention_prefill(
                 qkv, q_ld, cache_layer.k, cache_layer.v, ctx.page_table, ctx.seq_slot, ctx.seq_start,
                 ctx.cu_seqlens, out, n_seqs=ctx.n_seqs, max_new=ctx.max_new, n_heads=n_heads,

@@ -1,0 +1,55 @@
+"""Python face of the tcgen05 prefill attention: tensor maps (kept per buffer) and the call."""
+from __future__ import annotations
+
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from . import ops
+from .build import load
+from .ops import _call, _need, _need_cuda, _p, _stream
+from .tcgen05 import status_word
+
+_maps: dict = {}
+
+
+def supports(head_dim: int, page_size: int, n_heads: int, n_kv_heads: int, q_ld: int, out_ld: int) -> bool:
+    lib = load("attention_tcgen05")
+    return bool(lib.ri_attention_tcgen05_supports(c_int(head_dim), c_int(page_size), c_int(n_heads),
+                                                  c_int(n_kv_heads), c_int(q_ld), c_int(out_ld)))
+
+
+def _map(which: int, t: torch.Tensor, rows: int, cols: int, ld: int) -> torch.Tensor:
+    key = (which, t.data_ptr(), rows, cols, ld)
+    m = _maps.get(key)
+    if m is None:
+        if len(_maps) > 8192:
+            _maps.clear()
+        m = torch.empty(128, dtype=torch.uint8)
+        _call("attention_tcgen05", "ri_attention_tcgen05_encode", c_void_p(m.data_ptr()), c_int(which), _p(t),
+              c_longlong(rows), c_longlong(cols), c_longlong(ld))
+        ops._launches -= 1
+        _maps[key] = m
+    return m
+
+
+def prefill(qkv: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, page_table, seq_slot, seq_start,
+            cu_seqlens, out: torch.Tensor, *, n_seqs: int, max_new: int, n_heads: int, n_kv_heads: int,
+            head_dim: int, page_size: int, scale: float, window: int = 0) -> torch.Tensor:
+    """bf16 causal attention of every new token over its slot's keys, on tcgen05.  q is the leading
+    n_heads * head_dim columns of `qkv`; kcache / vcache are one layer, [pages, kv heads, 64, head_dim]."""
+    _need_cuda(qkv, kcache, vcache, page_table, seq_slot, seq_start, cu_seqlens, out)
+    _need(qkv.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+          and qkv.is_contiguous() and kcache.is_contiguous() and vcache.is_contiguous() and out.is_contiguous(),
+          "attention_tcgen05: bf16 contiguous tensors only")
+    rows = kcache.shape[0] * kcache.shape[1] * kcache.shape[2]
+    mq = _map(0, qkv, qkv.shape[0], qkv.shape[1], qkv.shape[1])
+    mk = _map(1, kcache, rows, head_dim, head_dim)
+    mv = _map(1, vcache, rows, head_dim, head_dim)
+    st = status_word()
+    _call("attention_tcgen05", "ri_attention_tcgen05_prefill", c_void_p(mq.data_ptr()), c_void_p(mk.data_ptr()),
+          c_void_p(mv.data_ptr()), _p(page_table), c_int(page_table.shape[1]), _p(seq_slot), _p(seq_start),
+          _p(cu_seqlens), _p(out), c_int(out.shape[1]), c_int(n_seqs), c_int(max_new), c_int(n_heads),
+          c_int(n_kv_heads), c_int(head_dim), c_int(page_size), c_float(scale), c_int(window),
+          c_void_p(st.data_ptr()), _stream())
+    return out

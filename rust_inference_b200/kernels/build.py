@@ -27,6 +27,7 @@ MODULES = {
     "sampling": "sampling.cu",
     "gemm_tcgen05": "gemm_tcgen05.cu",
     "attention_mma": "attention_mma.cu",
+    "attention_tcgen05": "attention_tcgen05.cu",
 }
 
 NVCC_FLAGS = [

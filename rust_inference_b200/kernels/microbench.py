@@ -1,0 +1,167 @@
+"""One kernel of the decoder at given sizes, timed on the device.
+
+    python bench.py --kernel gate_up --tokens 8
+    python bench.py --kernel attn_decode --tokens 64 --context 1024
+
+The operand that a step streams (weights, or the cache) is rotated over enough copies to
+exceed L2, and the launches are replayed from a CUDA graph so that host launch cost is
+not in the number.  Sizes default to the benchmark model of bench.py.  Used for the
+profiles under profiles/ and for tuning.
+"""
+from __future__ import annotations
+
+import json
+import math
+
+import torch
+
+KERNELS = ("qkv", "qkv_split", "o_proj", "gate_up", "down", "lm_head", "attn_decode", "attn_prefill",
+           "attn_prefill_mma", "rmsnorm", "rope")
+
+
+def _graph_time(fn, launches_per_replay: int, reps: int = 10) -> float:
+    """Microseconds per launch: fn() enqueues `launches_per_replay` launches; replayed `reps` times."""
+    fn()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        fn()
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / (reps * launches_per_replay)
+
+
+def run(kernel: str, model: dict, tokens: int, context: int = 1024, eager_only: bool = False) -> dict:
+    from . import linear, ops, tcgen05
+    from . import attention as attn
+    dev = "cuda"
+    h, inter, vocab = model["hidden_size"], model["intermediate_size"], model["vocab_size"]
+    nh, nkv, hd = model["num_attention_heads"], model["num_key_value_heads"], model["head_dim"]
+    qd, kvd = nh * hd, nkv * hd
+    bf = torch.bfloat16
+
+    def weights(n, k, copies):
+        return [linear.Weight((torch.randn(n, k, device=dev) * 0.02).to(bf)) for _ in range(copies)]
+
+    def copies_for(nbytes):
+        return max(2, int(400e6 // nbytes) + 1)
+
+    out = {"kernel": kernel, "tokens": tokens}
+    if kernel in ("qkv", "qkv_split", "o_proj", "gate_up", "down", "lm_head"):
+        n, k, mode = {"qkv": (qd + 2 * kvd, h, ops.EPI_STORE), "qkv_split": (qd + 2 * kvd, h, ops.EPI_RESIDUAL),
+                      "o_proj": (h, qd, ops.EPI_RESIDUAL), "gate_up": (inter, h, ops.EPI_SILU_MUL),
+                      "down": (h, inter, ops.EPI_RESIDUAL), "lm_head": (vocab, h, ops.EPI_STORE_F32)}[kernel]
+        dual = mode == ops.EPI_SILU_MUL
+        nbytes = n * k * 2 * (2 if dual else 1)
+        c = copies_for(nbytes)
+        ws = weights(n, k, c)
+        w2s = weights(n, k, c) if dual else [None] * c
+        x = (torch.randn(tokens, k, device=dev) * 0.5).to(bf)
+        bias = torch.randn(n, device=dev) if kernel == "qkv" else None
+        res = torch.zeros(tokens, n, device=dev, dtype=torch.float32 if mode in (ops.EPI_STORE_F32, ops.EPI_RESIDUAL) else bf)
+
+        def fn():
+            for i in range(c):
+                tcgen05.gemm(x, ws[i], res, mode, bias=bias, w2=w2s[i])
+        launches = c
+        flops = 2.0 * tokens * n * k * (2 if dual else 1)
+        out.update(n=n, k=k, bytes=nbytes + tokens * k * 2, flops=flops)
+    elif kernel == "rmsnorm":
+        x = torch.randn(tokens, h, device=dev)
+        w = torch.ones(h, device=dev)
+        y = torch.empty(tokens, h, device=dev, dtype=bf)
+
+        def fn():
+            for _ in range(20):
+                ops.rmsnorm(x, w, 1e-6, y)
+        launches = 20
+        out.update(bytes=tokens * h * 6, flops=0.0)
+    else:
+        # a paged cache holding `context` positions per sequence (attn_decode: one new token per
+        # sequence; attn_prefill: `tokens` new tokens of one sequence after `context - tokens` cached)
+        page = 64
+        n_seqs = tokens if kernel in ("attn_decode", "rope") else 1
+        context = max(context, 1 if n_seqs > 1 else tokens)
+        total = context
+        pages_per = -(-total // page)
+        layer_bytes = n_seqs * pages_per * nkv * page * hd * 2 * 2
+        c = copies_for(layer_bytes) if kernel == "attn_decode" else 1
+        kc = [torch.randn(n_seqs * pages_per, nkv, page, hd, device=dev).to(bf) for _ in range(c)]
+        vc = [torch.randn(n_seqs * pages_per, nkv, page, hd, device=dev).to(bf) for _ in range(c)]
+        table = torch.arange(n_seqs * pages_per, dtype=torch.int32, device=dev).view(n_seqs, pages_per)
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+        n_new = 1 if kernel in ("attn_decode", "rope") else tokens
+        t_total = n_seqs * n_new
+        slot, start = i32(list(range(n_seqs))), i32([total - n_new] * n_seqs)
+        length, cu = i32([total] * n_seqs), i32([b * n_new for b in range(n_seqs + 1)])
+        q = torch.randn(t_total, qd + 2 * kvd, device=dev).to(bf)
+        o = torch.empty(t_total, qd, device=dev, dtype=bf)
+        scale = 1.0 / math.sqrt(hd)
+        if kernel == "attn_decode":
+            splits = attn.decode_splits(n_seqs, nkv, pages_per * page, page)
+            po = torch.empty(n_seqs * nh * splits * hd, device=dev)
+            pml = torch.empty(n_seqs * nh * splits * 2, device=dev)
+
+            def fn():
+                for i in range(c):
+                    ops.attention_decode(q, q.shape[1], kc[i], vc[i], table, slot, length, cu, o, n_seqs=n_seqs,
+                                         n_heads=nh, n_kv_heads=nkv, head_dim=hd, page_size=page, scale=scale,
+                                         window=0, n_splits=splits, part_o=po, part_ml=pml)
+            launches = c
+            out.update(bytes=layer_bytes, flops=4.0 * n_seqs * total * qd, splits=splits)
+        elif kernel in ("attn_prefill", "attn_prefill_mma"):
+            from . import attention_tc
+
+            def fn():
+                for _ in range(4):
+                    if kernel == "attn_prefill":
+                        attention_tc.prefill(q, kc[0], vc[0], table, slot, start, cu, o, n_seqs=1, max_new=n_new,
+                                             n_heads=nh, n_kv_heads=nkv, head_dim=hd, page_size=page, scale=scale)
+                    else:
+                        ops.attention_prefill(q, q.shape[1], kc[0], vc[0], table, slot, start, cu, o, n_seqs=1,
+                                              max_new=n_new, n_heads=nh, n_kv_heads=nkv, head_dim=hd,
+                                              page_size=page, scale=scale, window=0)
+            launches = 4
+            first = total - n_new
+            keys = sum(first + i + 1 for i in range(n_new))
+            out.update(bytes=layer_bytes, flops=4.0 * keys * qd)
+        else:   # rope + cache write from float32 accumulators
+            from ..parts.rope import rope_tables
+            cos, sin = rope_tables(hd, 1e6, total)
+            cos, sin = torch.from_numpy(cos).to(dev), torch.from_numpy(sin).to(dev)
+            acc = torch.zeros(t_total, qd + 2 * kvd, device=dev)
+            bias = torch.randn(qd + 2 * kvd, device=dev)
+            pos, seq = i32([total - 1] * n_seqs), i32(list(range(n_seqs)))
+
+            def fn():
+                for _ in range(20):
+                    ops.rope_cache_write_acc(acc, bias, o, cos, sin, pos, seq, slot, table, kc[0], vc[0], n_heads=nh,
+                                             n_kv_heads=nkv, head_dim=hd, page_size=page, style=0, write_kv=True)
+            launches = 20
+            out.update(bytes=t_total * (qd + 2 * kvd) * 6, flops=0.0)
+    if eager_only:
+        fn()
+        torch.cuda.synchronize()
+        out["us"] = None
+    else:
+        us = _graph_time(fn, launches)
+        out["us"] = us
+        out["gb_per_s"] = out["bytes"] / us / 1e3
+        out["tflop_per_s"] = out["flops"] / us / 1e6
+    tcgen05.check_status()
+    return out
+
+
+def main(kernel: str, model: dict, tokens: int, context: int, eager_only: bool = False) -> int:
+    if kernel not in KERNELS:
+        print(f"unknown kernel {kernel!r}; choose from {', '.join(KERNELS)}")
+        return 2
+    print(json.dumps(run(kernel, model, tokens, context, eager_only)))
+    return 0

@@ -292,6 +292,8 @@ def _attention_case(nh, nkv, hd, news, starts, dtype, window=0, sharp=None, seed
 
 
 ATTN_CASES = [
+    (2, 1, 128, [300], [0], 0),
+    (4, 2, 64, [129, 128, 1], [0, 70, 5], 0),
     # heads, kv heads, head_dim, new tokens per sequence, cached before, window
     (4, 2, 64, [5], [0], 0),
     (28, 4, 128, [130, 1, 77], [0, 0, 0], 0),
@@ -327,6 +329,15 @@ def test_attention_kernels(dtype, nh, nkv, hd, news, starts, window):
                               out, n_seqs=c["B"], max_new=max(news), n_heads=nh, n_kv_heads=nkv, head_dim=hd,
                               page_size=64, scale=c["scale"], window=window)
         assert (out.float().cpu() - c["ref"]).abs().max().item() <= tol * c["ref"].abs().max().item()
+        from rust_inference_b200.kernels import attention_tc, tcgen05
+        assert attention_tc.supports(hd, 64, nh, nkv, c["q"].shape[1], nh * hd)
+        out = torch.zeros_like(out)
+        attention_tc.prefill(c["q"], c["kc"], c["vc"], c["table"], c["slot"], c["start"], c["cu"], out,
+                             n_seqs=c["B"], max_new=max(news), n_heads=nh, n_kv_heads=nkv, head_dim=hd,
+                             page_size=64, scale=c["scale"], window=window)
+        torch.cuda.synchronize()
+        tcgen05.check_status()
+        assert (out.float().cpu() - c["ref"]).abs().max().item() <= tol * c["ref"].abs().max().item()
     else:
         assert hd not in (64, 128)
     if decode and ops.attention_mma_supports(hd, 64, nh, nkv, True):
@@ -360,6 +371,11 @@ def test_attention_finds_a_far_key(dtype):
                                   c["cu"], out2, n_seqs=2, max_new=3, n_heads=nh, n_kv_heads=nkv, head_dim=hd,
                                   page_size=64, scale=c["scale"], window=0)
             assert (out2.float().cpu() - c["ref"]).abs().max().item() <= tol * c["ref"].abs().max().item()
+            from rust_inference_b200.kernels import attention_tc
+            out3 = torch.zeros_like(out)
+            attention_tc.prefill(c["q"], c["kc"], c["vc"], c["table"], c["slot"], c["start"], c["cu"], out3, n_seqs=2,
+                                 max_new=3, n_heads=nh, n_kv_heads=nkv, head_dim=hd, page_size=64, scale=c["scale"])
+            assert (out3.float().cpu() - c["ref"]).abs().max().item() <= tol * c["ref"].abs().max().item()
 
 
 def _sample(logits, **kw):
