@@ -9,11 +9,14 @@
 // Both operands are K-major, which is how the reference lays its matrices out
 // ([out, in] row-major, quant.rs:45-50) and how activations are packed.
 //
-// One output tile per CTA.  Warp 0 issues the TMA loads, warp 1 allocates tensor
-// memory and issues the MMAs (one elected thread), warps 2-5 run the epilogue: each
-// reads its 32 lanes of the accumulator with tcgen05.ld and writes the result.
-// blockIdx.z splits K; the split pieces are combined with float32 atomic adds, which
-// only the residual epilogue allows.
+// The grid is persistent: as many CTAs as fit the GPU at once, each walking its share of
+// the output tiles (token tile fastest, so CTAs that run together share a weight tile in
+// L2).  Warp 0 issues the TMA loads, warp 1 allocates tensor memory and issues the MMAs
+// (one elected thread), warps 2-5 run the epilogue: each reads its 32 lanes of the
+// accumulator with tcgen05.ld and writes the result.  There are two accumulator buffers
+// in tensor memory, so the epilogue of one tile runs while the MMAs of the next fill the
+// other.  K can be split over tiles; the split pieces are combined with float32 atomic
+// adds, which only the residual epilogue allows.
 //
 // Epilogues (float32 arithmetic):
 //   0  out<bf16> = acc + bias                         (q/k/v projection, attention.rs:66-76)
@@ -79,33 +82,39 @@ template <int TN, bool DUAL, int MODE>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_w2,
                const __grid_constant__ CUtensorMap map_x, const float* __restrict__ bias, void* __restrict__ out_,
-               int n_tok, int n_feat, int K, int kb_per_split, int stages, int* status) {
+               int n_tok, int n_feat, int K, int kb_per_split, int split_k, int stages, int* status) {
     constexpr int B_BYTES = TN * BLOCK_K * 2;
     constexpr int STAGE_BYTES = (DUAL ? 2 : 1) * A_BYTES + B_BYTES;
-    constexpr int TMEM_COLS = tmem_cols(DUAL ? 2 * TN : TN);
+    constexpr int ACC_COLS = DUAL ? 2 * TN : TN;               // columns of one accumulator buffer
+    constexpr int TMEM_COLS = tmem_cols(2 * ACC_COLS);         // two buffers: epilogue of a tile overlaps the next main loop
     constexpr uint32_t IDESC = make_idesc<TN>();
 
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[MAX_STAGES];
     __shared__ __align__(8) uint64_t empty_bar[MAX_STAGES];
-    __shared__ __align__(8) uint64_t accum_bar;
+    __shared__ __align__(8) uint64_t acc_full[2];
+    __shared__ __align__(8) uint64_t acc_empty[2];
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile int abort_flag;
 
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;     // swizzled tiles want 1024-byte alignment
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // token tiles vary fastest over the grid: CTAs that run together share a weight tile in L2
-    const int f0 = blockIdx.y * BLOCK_F, t0 = blockIdx.x * TN;
     const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
-    const int kb_begin = blockIdx.z * kb_per_split;
-    const int n_kb = min(total_kb, kb_begin + kb_per_split) - kb_begin;    // >= 1 by construction of the grid
+    // Tiles are numbered with the token tile fastest, so that CTAs running together share a weight
+    // tile in L2; a CTA takes tiles blockIdx.x, blockIdx.x + gridDim.x, ...
+    const int n_tok_tiles = (n_tok + TN - 1) / TN, n_feat_tiles = (n_feat + BLOCK_F - 1) / BLOCK_F;
+    const int total_tiles = n_tok_tiles * n_feat_tiles * split_k;
+    const int my_tiles = ((int)blockIdx.x < total_tiles) ? (total_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < stages; ++s) {
             mbar_init(smem_u32(&full_bar[s]), 1);
             mbar_init(smem_u32(&empty_bar[s]), 1);
         }
-        mbar_init(smem_u32(&accum_bar), 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(smem_u32(&acc_full[i]), 1);
+            mbar_init(smem_u32(&acc_empty[i]), 4);             // one arrival per epilogue warp
+        }
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -121,51 +130,70 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const uint32_t tmem_base = tmem_base_slot;
     let_next_kernel_start();
 
+    // coordinates of the CTA's i-th tile
+    auto tile_coords = [&](int i, int& f0, int& t0, int& kb_begin, int& n_kb) {
+        const int tile = (int)blockIdx.x + i * (int)gridDim.x;
+        const int tt = tile % n_tok_tiles, rest = tile / n_tok_tiles;
+        const int ft = rest % n_feat_tiles, sp = rest / n_feat_tiles;
+        f0 = ft * BLOCK_F;
+        t0 = tt * TN;
+        kb_begin = sp * kb_per_split;
+        n_kb = min(total_kb, kb_begin + kb_per_split) - kb_begin;          // >= 1 by construction of the split
+    };
+
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
-            int issued = 0;
-            // The weights are written by no kernel, so their tiles for the first round of stages go
-            // out at once; the activations come from the kernel before this one and wait for it.
-            const int ahead = min(stages, n_kb);
-            for (int i = 0; i < ahead; ++i) {
-                const uint32_t bar = smem_u32(&full_bar[i]);
-                const uint32_t stage = smem_base + (uint32_t)i * STAGE_BYTES;
-                const int kx = (kb_begin + i) * BLOCK_K;
-                mbar_expect_tx(bar, STAGE_BYTES);
-                tma_load_2d(stage, &map_w, bar, kx, f0);
-                if (DUAL) tma_load_2d(stage + A_BYTES, &map_w2, bar, kx, f0);
-            }
-            wait_for_previous_kernels();
-            for (int i = 0; i < ahead; ++i) {
-                const uint32_t stage = smem_base + (uint32_t)i * STAGE_BYTES;
-                tma_load_2d(stage + (DUAL ? 2 : 1) * A_BYTES, &map_x, smem_u32(&full_bar[i]),
-                            (kb_begin + i) * BLOCK_K, t0);
-                issued = i + 1;
-            }
-            for (int i = ahead; i < n_kb; ++i) {
-                const int s = i % stages;
-                const uint32_t ph = (uint32_t)(i / stages) & 1u;
-                if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1u)) {
-                    report(status, ST_PRODUCER_TIMEOUT);
-                    abort_flag = 1;
-                    break;
+            int it = 0;                      // k-blocks issued so far, over all of this CTA's tiles
+            bool waited = false;             // the activations come from the kernel before: wait once
+            bool alive = true;
+            for (int i = 0; i < my_tiles && alive; ++i) {
+                int f0, t0, kb_begin, n_kb;
+                tile_coords(i, f0, t0, kb_begin, n_kb);
+                int kb = 0;
+                if (!waited) {
+                    // The weights are written by no kernel, so their tiles for the first round of stages
+                    // go out at once; the activations wait for the previous kernel.
+                    const int ahead = min(stages, n_kb);
+                    for (int j = 0; j < ahead; ++j) {
+                        const uint32_t bar = smem_u32(&full_bar[j]);
+                        const uint32_t stage = smem_base + (uint32_t)j * STAGE_BYTES;
+                        const int kx = (kb_begin + j) * BLOCK_K;
+                        mbar_expect_tx(bar, STAGE_BYTES);
+                        tma_load_2d(stage, &map_w, bar, kx, f0);
+                        if (DUAL) tma_load_2d(stage + A_BYTES, &map_w2, bar, kx, f0);
+                    }
+                    wait_for_previous_kernels();
+                    waited = true;
+                    for (int j = 0; j < ahead; ++j)
+                        tma_load_2d(smem_base + (uint32_t)j * STAGE_BYTES + (DUAL ? 2 : 1) * A_BYTES, &map_x,
+                                    smem_u32(&full_bar[j]), (kb_begin + j) * BLOCK_K, t0);
+                    kb = ahead;
+                    it = ahead;
                 }
-                if (abort_flag) break;
-                const uint32_t bar = smem_u32(&full_bar[s]);
-                const uint32_t stage = smem_base + (uint32_t)s * STAGE_BYTES;
-                const int kx = (kb_begin + i) * BLOCK_K;
-                mbar_expect_tx(bar, STAGE_BYTES);
-                tma_load_2d(stage, &map_w, bar, kx, f0);
-                if (DUAL) tma_load_2d(stage + A_BYTES, &map_w2, bar, kx, f0);
-                tma_load_2d(stage + (DUAL ? 2 : 1) * A_BYTES, &map_x, bar, kx, t0);
-                issued = i + 1;
+                for (; kb < n_kb; ++kb, ++it) {
+                    const int s = it % stages;
+                    const uint32_t ph = (uint32_t)(it / stages) & 1u;
+                    if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1u) || abort_flag) {
+                        if (!abort_flag) report(status, ST_PRODUCER_TIMEOUT);
+                        abort_flag = 1;
+                        alive = false;
+                        break;
+                    }
+                    const uint32_t bar = smem_u32(&full_bar[s]);
+                    const uint32_t stage = smem_base + (uint32_t)s * STAGE_BYTES;
+                    const int kx = (kb_begin + kb) * BLOCK_K;
+                    mbar_expect_tx(bar, STAGE_BYTES);
+                    tma_load_2d(stage, &map_w, bar, kx, f0);
+                    if (DUAL) tma_load_2d(stage + A_BYTES, &map_w2, bar, kx, f0);
+                    tma_load_2d(stage + (DUAL ? 2 : 1) * A_BYTES, &map_x, bar, kx, t0);
+                }
             }
             // Do not leave while a copy into this CTA's shared memory may still be in flight:
             // the last `stages` loads issued must have landed (immediate on the normal path).
-            for (int i = max(0, issued - stages); i < issued; ++i) {
-                const int s = i % stages;
-                const uint32_t ph = (uint32_t)(i / stages) & 1u;
+            for (int j = max(0, it - stages); j < it; ++j) {
+                const int s = j % stages;
+                const uint32_t ph = (uint32_t)(j / stages) & 1u;
                 if (!mbar_wait(smem_u32(&full_bar[s]), ph)) {
                     report(status, ST_DRAIN_TIMEOUT);
                     break;
@@ -175,48 +203,66 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
-            bool ok = true;
-            for (int i = 0; i < n_kb && ok; ++i) {
-                const int s = i % stages;
-                const uint32_t ph = (uint32_t)(i / stages) & 1u;
-                if (!mbar_wait(smem_u32(&full_bar[s]), ph)) {
+            int it = 0;
+            bool alive = true;
+            for (int i = 0; i < my_tiles && alive; ++i) {
+                int f0, t0, kb_begin, n_kb;
+                tile_coords(i, f0, t0, kb_begin, n_kb);
+                const int buf = i & 1;
+                // the epilogue must have emptied this accumulator buffer (two tiles ago)
+                if (!mbar_wait(smem_u32(&acc_empty[buf]), (uint32_t)((i >> 1) & 1) ^ 1u)) {
                     report(status, ST_MMA_TIMEOUT);
                     abort_flag = 1;
-                    ok = false;
                     break;
                 }
                 tc_fence_after();
-                const uint32_t stage = smem_base + (uint32_t)s * STAGE_BYTES;
-#pragma unroll
-                for (int k = 0; k < BLOCK_K / 16; ++k) {
-                    // 16 bf16 = 32 bytes further along K inside the swizzled row
-                    const uint64_t a = make_smem_desc(stage + k * 32);
-                    const uint64_t b = make_smem_desc(stage + (DUAL ? 2 : 1) * A_BYTES + k * 32);
-                    umma(tmem_base, a, b, IDESC, i > 0 || k > 0);
-                    if (DUAL) {
-                        const uint64_t a2 = make_smem_desc(stage + A_BYTES + k * 32);
-                        umma(tmem_base + TN, a2, b, IDESC, i > 0 || k > 0);
+                const uint32_t acc = tmem_base + (uint32_t)(buf * ACC_COLS);
+                for (int kb = 0; kb < n_kb; ++kb, ++it) {
+                    const int s = it % stages;
+                    const uint32_t ph = (uint32_t)(it / stages) & 1u;
+                    if (!mbar_wait(smem_u32(&full_bar[s]), ph)) {
+                        report(status, ST_MMA_TIMEOUT);
+                        abort_flag = 1;
+                        alive = false;
+                        break;
                     }
+                    tc_fence_after();
+                    const uint32_t stage = smem_base + (uint32_t)s * STAGE_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BLOCK_K / 16; ++k) {
+                        // 16 bf16 = 32 bytes further along K inside the swizzled row
+                        const uint64_t a = make_smem_desc(stage + k * 32);
+                        const uint64_t b = make_smem_desc(stage + (DUAL ? 2 : 1) * A_BYTES + k * 32);
+                        umma(acc, a, b, IDESC, kb > 0 || k > 0);
+                        if (DUAL) {
+                            const uint64_t a2 = make_smem_desc(stage + A_BYTES + k * 32);
+                            umma(acc + TN, a2, b, IDESC, kb > 0 || k > 0);
+                        }
+                    }
+                    umma_commit(smem_u32(&empty_bar[s]));      // frees the stage once these MMAs have read it
                 }
-                umma_commit(smem_u32(&empty_bar[s]));      // frees the stage once these MMAs have read it
+                umma_commit(smem_u32(&acc_full[buf]));         // accumulator complete (or aborted: flag says which)
             }
-            umma_commit(smem_u32(&accum_bar));            // accumulator complete (or aborted: flag says which)
         }
     } else {
         // ---------------- epilogue: warps 2..5 ----------------
         wait_for_previous_kernels();          // `out` may still be read or written by the kernel before
-        const bool landed = mbar_wait(smem_u32(&accum_bar), 0);
-        if (!landed && lane == 0) {
-            report(status, ST_EPILOGUE_TIMEOUT);
-            abort_flag = 1;
-        }
-        tc_fence_after();
-        if (landed && !abort_flag) {
-            const int lane_base = (warp & 3) * 32;             // the TMEM lanes this warp may read
+        const int lane_base = (warp & 3) * 32;                 // the TMEM lanes this warp may read
+        for (int i = 0; i < my_tiles; ++i) {
+            int f0, t0, kb_begin, n_kb;
+            tile_coords(i, f0, t0, kb_begin, n_kb);
+            const int buf = i & 1;
+            const bool landed = mbar_wait(smem_u32(&acc_full[buf]), (uint32_t)((i >> 1) & 1));
+            if (!landed && lane == 0) {
+                report(status, ST_EPILOGUE_TIMEOUT);
+                abort_flag = 1;
+            }
+            tc_fence_after();
+            if (!landed || abort_flag) break;
             const int f = f0 + lane_base + lane;
             const bool f_ok = f < n_feat;
             const float b = (bias != nullptr && f_ok) ? bias[f] : 0.f;
-            const uint32_t trow = tmem_base + ((uint32_t)lane_base << 16);
+            const uint32_t trow = tmem_base + ((uint32_t)lane_base << 16) + (uint32_t)(buf * ACC_COLS);
 #pragma unroll 1
             for (int c0 = 0; c0 < TN; c0 += 16) {
                 if (t0 + c0 >= n_tok) break;                   // uniform over the warp
@@ -242,6 +288,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     }
                 }
             }
+            // this warp has read its part of the buffer: hand it back to the MMA issuer
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&acc_empty[buf]));
         }
     }
 
@@ -274,6 +324,16 @@ int make_map(CUtensorMap* map, const void* ptr, long long rows, long long K, int
     return 0;
 }
 
+int sm_count() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    }
+    return n;
+}
+
 int g_smem_budget = 0;       // 0: the default for the tile; set through ri_gemm_tcgen05_set_smem_budget
 
 template <int TN, bool DUAL, int MODE>
@@ -301,10 +361,17 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx,
         if (e != cudaSuccess) return fail("gemm_tcgen05: cannot raise dynamic shared memory: %s", cudaGetErrorString(e));
         configured = true;
     }
-    dim3 grid((n_tok + TN - 1) / TN, (n_feat + BLOCK_F - 1) / BLOCK_F, split_k);
-    if (grid.y > 65535) return fail("gemm_tcgen05: %d features exceed the grid limit", n_feat);
+    const long long total_tiles = (long long)((n_tok + TN - 1) / TN) * ((n_feat + BLOCK_F - 1) / BLOCK_F) * split_k;
+    if (total_tiles > 0x7fffffffLL) return fail("gemm_tcgen05: %lld tiles exceed the index range", total_tiles);
+    // a persistent grid: as many CTAs as fit the GPU at once (two per SM when the ring is small and
+    // two accumulator buffers of each fit tensor memory), each walking its share of the tiles
+    constexpr int ACC_COLS = DUAL ? 2 * TN : TN;
+    const int per_sm = (smem <= 110 * 1024 && 4 * ACC_COLS <= 512) ? 2 : 1;
+    long long ctas = (long long)sm_count() * per_sm;
+    if (ctas > total_tiles) ctas = total_tiles;
+    dim3 grid((unsigned)ctas);
     cudaError_t e = launch_dependent(kernel, grid, dim3(THREADS), smem, stream, mw, mw2, mx, bias, out, n_tok, n_feat, K,
-                                     kb_per_split, stages, status);
+                                     kb_per_split, split_k, stages, status);
     return check_launch(e, "gemm_tcgen05");
 }
 
