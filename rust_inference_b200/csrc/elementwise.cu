@@ -246,16 +246,17 @@ __global__ void rope_cache_write_acc_kernel(float* __restrict__ acc, int ld, con
                                             const int* __restrict__ page_table, int max_pages,
                                             T* __restrict__ kcache, T* __restrict__ vcache, int n_heads,
                                             int n_kv_heads, int hd, int page_size, int style, int write_kv) {
+    constexpr int PER = 4;                 // items a thread handles at once: their loads go out together
     const int t = blockIdx.x;
+    const int half = hd >> 1;
+    const int q_dim = n_heads * hd, kv_dim = n_kv_heads * hd;
+    const int n_pairs = (n_heads + n_kv_heads) * half;
+    float* row = acc + (size_t)t * ld;
     let_next_kernel_start();
     wait_for_previous_kernels();          // the projections come from the previous kernel
     const int pos = token_pos[t];
-    const int half = hd >> 1;
-    float* row = acc + (size_t)t * ld;
     const float* c = cos_t + (size_t)pos * half;
     const float* s = sin_t + (size_t)pos * half;
-    const int q_dim = n_heads * hd, kv_dim = n_kv_heads * hd;
-
     size_t cache_base = 0;
     if (write_kv) {
         const int slot = seq_slot[token_seq[t]];
@@ -264,32 +265,62 @@ __global__ void rope_cache_write_acc_kernel(float* __restrict__ acc, int ld, con
     }
     const size_t head_stride = (size_t)page_size * hd;
 
-    for (int idx = threadIdx.x; idx < (n_heads + n_kv_heads) * half; idx += blockDim.x) {
-        const int h = idx / half, i = idx % half;
-        const int i0 = style == 0 ? i : 2 * i;
-        const int i1 = style == 0 ? i + half : 2 * i + 1;
-        const int col = h * hd;                       // q heads first, then the k heads: same column order
-        float x0 = row[col + i0], x1 = row[col + i1];
-        if (bias) { x0 += bias[col + i0]; x1 += bias[col + i1]; }
-        row[col + i0] = 0.f;
-        row[col + i1] = 0.f;
-        const float y0 = x0 * c[i] - x1 * s[i], y1 = x0 * s[i] + x1 * c[i];
-        if (h < n_heads) {
-            T* dst = q_out + (size_t)t * q_dim + col;
-            dst[i0] = from_f32<T>(y0);
-            dst[i1] = from_f32<T>(y1);
-        } else if (write_kv) {
-            T* dst = kcache + cache_base + (h - n_heads) * head_stride;
-            dst[i0] = from_f32<T>(y0);
-            dst[i1] = from_f32<T>(y1);
+    // rotary pairs of the q heads and then the k heads (same column order in the accumulator)
+    for (int base = threadIdx.x; base < n_pairs; base += PER * blockDim.x) {
+        float x0[PER], x1[PER], cs[PER], sn[PER];
+        int c0[PER], c1[PER];
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+            const int idx = base + j * blockDim.x;
+            if (idx < n_pairs) {
+                const int h = idx / half, i = idx % half;
+                c0[j] = h * hd + (style == 0 ? i : 2 * i);
+                c1[j] = h * hd + (style == 0 ? i + half : 2 * i + 1);
+                x0[j] = row[c0[j]];
+                x1[j] = row[c1[j]];
+                if (bias) { x0[j] += bias[c0[j]]; x1[j] += bias[c1[j]]; }
+                cs[j] = c[i];
+                sn[j] = s[i];
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+            const int idx = base + j * blockDim.x;
+            if (idx < n_pairs) {
+                row[c0[j]] = 0.f;
+                row[c1[j]] = 0.f;
+                const float y0 = x0[j] * cs[j] - x1[j] * sn[j], y1 = x0[j] * sn[j] + x1[j] * cs[j];
+                if (c0[j] < q_dim) {
+                    q_out[(size_t)t * q_dim + c0[j]] = from_f32<T>(y0);
+                    q_out[(size_t)t * q_dim + c1[j]] = from_f32<T>(y1);
+                } else if (write_kv) {
+                    const int h = (c0[j] - q_dim) / hd;
+                    T* dst = kcache + cache_base + h * head_stride;
+                    dst[c0[j] - q_dim - h * hd] = from_f32<T>(y0);
+                    dst[c1[j] - q_dim - h * hd] = from_f32<T>(y1);
+                }
+            }
         }
     }
-    for (int idx = threadIdx.x; idx < kv_dim; idx += blockDim.x) {
-        const int col = q_dim + kv_dim + idx;
-        float v = row[col];
-        if (bias) v += bias[col];
-        row[col] = 0.f;
-        if (write_kv) vcache[cache_base + (idx / hd) * head_stride + (idx % hd)] = from_f32<T>(v);
+    // values: bias added, stored as they are
+    for (int base = threadIdx.x; base < kv_dim; base += PER * blockDim.x) {
+        float v[PER];
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+            const int idx = base + j * blockDim.x;
+            if (idx < kv_dim) {
+                v[j] = row[q_dim + kv_dim + idx];
+                if (bias) v[j] += bias[q_dim + kv_dim + idx];
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+            const int idx = base + j * blockDim.x;
+            if (idx < kv_dim) {
+                row[q_dim + kv_dim + idx] = 0.f;
+                if (write_kv) vcache[cache_base + (idx / hd) * head_stride + (idx % hd)] = from_f32<T>(v[j]);
+            }
+        }
     }
 }
 
