@@ -23,7 +23,7 @@
 // Keys and values are only ever read from the cache: the step's new tokens were written
 // there (after rotation) before attention runs, so prefill, continuation and decode use
 // one convention.
-#include "common.cuh"
+#include "tcgen05_common.cuh"
 #include "attention_decode_static.h"
 
 using namespace ri;
@@ -283,6 +283,215 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_ld, const __nv_bfl
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// decode, fed by TMA: the same computation, with the K and V pages brought in by tensor-map copies
+// (128-byte swizzle, one elected thread) through a ring of RING stages guarded by mbarriers, so
+// that several pages are in flight per CTA and the compute warps never meet at a block-wide
+// barrier.  A page tile is [head_dim / 64][64 keys][128 bytes]; inside a 128-byte row the 16-byte
+// chunk c sits at c ^ (row & 7), which is what the TMA swizzle writes and what ldmatrix wants.
+// ---------------------------------------------------------------------------------------------
+constexpr int RING = 3;
+constexpr int DECODE_TMA_THREADS = 160;              // 4 compute warps + 1 producer warp
+
+template <int HD>
+__device__ __forceinline__ uint32_t atom_off(int r, int c) {      // c: 16-byte chunk index along head_dim
+    return (uint32_t)((c >> 3) * (PAGE * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4));
+}
+
+template <int HD>
+__device__ __forceinline__ void qk_16keys_atoms(const uint32_t (*q)[4], uint32_t ktile, int kbase, float (*s)[4]) {
+    const int lane = threadIdx.x & 31;
+    const int mi = lane >> 3, rr = lane & 7;
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks) {
+        const int row = kbase + (mi >> 1) * 8 + rr;
+        const int chunk = ks * 2 + (mi & 1);
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4(ktile + atom_off<HD>(row, chunk), b0, b1, b2, b3);
+        mma_bf16(s[0], q[ks], b0, b1);
+        mma_bf16(s[1], q[ks], b2, b3);
+    }
+}
+
+template <int HD>
+__device__ __forceinline__ void pv_16keys_atoms(const uint32_t* p, uint32_t vtile, int kbase, float (*o)[4]) {
+    const int lane = threadIdx.x & 31;
+    const int mi = lane >> 3, rr = lane & 7;
+#pragma unroll
+    for (int dp = 0; dp < HD / 16; ++dp) {
+        const int row = kbase + (mi & 1) * 8 + rr;
+        const int chunk = dp * 2 + (mi >> 1);
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4_trans(vtile + atom_off<HD>(row, chunk), b0, b1, b2, b3);
+        mma_bf16(o[2 * dp], p, b0, b1);
+        mma_bf16(o[2 * dp + 1], p, b2, b3);
+    }
+}
+
+template <int HD>
+__global__ void __launch_bounds__(DECODE_TMA_THREADS)
+attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                       const __nv_bfloat16* __restrict__ q, int q_ld, const int* __restrict__ page_table,
+                       int max_pages, const int* __restrict__ seq_slot, const int* __restrict__ seq_len,
+                       const int* __restrict__ cu_seqlens, int n_heads, int n_kv_heads, float scale, int window,
+                       int n_splits, float* __restrict__ part_o, float* __restrict__ part_ml,
+                       __nv_bfloat16* __restrict__ out, int out_ld, int* status) {
+    constexpr int TILE = PAGE * HD * 2;                 // bytes of one K or V page tile
+    constexpr int ATOMS = HD / 64;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[RING], empty_bar[RING];
+    __shared__ volatile int abort_flag;
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);      // swizzled tiles: 1024-byte aligned
+    const uint32_t kv_base = smem_u32(smem);            // [RING][K tile, V tile], then the Q tile [16][HD]
+    const uint32_t q_tile = kv_base + 2 * RING * TILE;
+
+    const int b = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    const int n_rep = n_heads / n_kv_heads;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < RING; ++i) {
+            tc::mbar_init(smem_u32(&full_bar[i]), 1);
+            tc::mbar_init(smem_u32(&empty_bar[i]), 4);          // one arrival per compute warp
+        }
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    let_next_kernel_start();
+    wait_for_previous_kernels();          // q and the newest key and value come from the kernel before
+    const int n_keys = seq_len[b];
+    const int token = cu_seqlens[b];
+    const int first_key = (window > 0 && n_keys - window > 0) ? n_keys - window : 0;
+    const int pg_lo = first_key / PAGE, pg_hi = (n_keys + PAGE - 1) / PAGE;
+    const int per = (pg_hi - pg_lo + n_splits - 1) / n_splits;
+    const int pg_begin = pg_lo + split * per, pg_end = min(pg_hi, pg_begin + per);
+
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float o[HD / 8][4];
+#pragma unroll
+    for (int t = 0; t < HD / 8; ++t) o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.f;
+
+    if (warp == 4) {
+        // ---------------- producer ----------------
+        if (lane == 0) {
+            const int* pages = page_table + (size_t)seq_slot[b] * max_pages;
+            int issued = 0;
+            for (int pg = pg_begin; pg < pg_end; ++pg) {
+                const int j = pg - pg_begin, s = j % RING;
+                if (!tc::mbar_wait(smem_u32(&empty_bar[s]), (uint32_t)((j / RING) & 1) ^ 1u) || abort_flag) {
+                    tc::report(status, 21);
+                    abort_flag = 1;
+                    break;
+                }
+                const int row = (pages[pg] * n_kv_heads + kvh) * PAGE;
+                const uint32_t bar = smem_u32(&full_bar[s]);
+                tc::mbar_expect_tx(bar, 2 * TILE);
+#pragma unroll
+                for (int a = 0; a < ATOMS; ++a) {
+                    tc::tma_load_2d(kv_base + (2 * s) * TILE + a * PAGE * 128, &map_k, bar, a * 64, row);
+                    tc::tma_load_2d(kv_base + (2 * s + 1) * TILE + a * PAGE * 128, &map_v, bar, a * 64, row);
+                }
+                issued = j + 1;
+            }
+            // do not leave while a copy into this CTA's shared memory may be in flight
+            for (int j = max(0, issued - RING); j < issued; ++j)
+                if (!tc::mbar_wait(smem_u32(&full_bar[j % RING]), (uint32_t)((j / RING) & 1))) { tc::report(status, 24); break; }
+        }
+    } else {
+        // ---------------- compute: warp w takes keys 16w .. 16w+15 of every page ----------------
+        for (int idx = threadIdx.x; idx < 16 * (HD / 8); idx += 128) {
+            const int r = idx / (HD / 8), c = idx % (HD / 8);
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (r < n_rep) v = *reinterpret_cast<const uint4*>(q + (size_t)token * q_ld + (size_t)(kvh * n_rep + r) * HD + c * 8);
+            *reinterpret_cast<uint4*>(smem + 2 * RING * TILE + tile_off<HD>(r, c)) = v;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");          // the four compute warps: Q tile written
+        uint32_t qf[HD / 16][4];
+        {
+            const int row = lane & 15, half = lane >> 4;
+#pragma unroll
+            for (int ks = 0; ks < HD / 16; ++ks)
+                ldmatrix_x4(q_tile + tile_off<HD>(row, ks * 2 + half), qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
+        }
+        for (int pg = pg_begin; pg < pg_end; ++pg) {
+            const int j = pg - pg_begin, s = j % RING;
+            if (!tc::mbar_wait(smem_u32(&full_bar[s]), (uint32_t)((j / RING) & 1)) || abort_flag) {
+                if (lane == 0) { tc::report(status, 22); abort_flag = 1; }
+                break;
+            }
+            const uint32_t ktile = kv_base + (2 * s) * TILE, vtile = ktile + TILE;
+            const int kbase = warp * 16;
+            const int key0 = pg * PAGE + kbase;
+            if (key0 < n_keys && key0 + 16 > first_key) {
+                float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+                qk_16keys_atoms<HD>(qf, ktile, kbase, sc);
+#pragma unroll
+                for (int t = 0; t < 2; ++t)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int key = key0 + t * 8 + 2 * tq + (e & 1);
+                        sc[t][e] = (key < n_keys && key >= first_key) ? sc[t][e] * scale : -INFINITY;
+                    }
+                softmax_update<2, HD / 8>(sc, m, l, o);
+                uint32_t pf[4] = {pack_bf16(sc[0][0], sc[0][1]), pack_bf16(sc[0][2], sc[0][3]),
+                                  pack_bf16(sc[1][0], sc[1][1]), pack_bf16(sc[1][2], sc[1][3])};
+                pv_16keys_atoms<HD>(pf, vtile, kbase, o);
+            }
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(smem_u32(&empty_bar[s]));       // this warp is done with the stage
+        }
+    }
+    __syncthreads();                      // every page consumed, every copy landed: the ring is free
+
+    // ---- merge the 4 compute warps (each saw a quarter of the keys) through shared memory ----
+    float* so = reinterpret_cast<float*>(smem);           // [4][16][HD]
+    float* sml = so + 4 * 16 * HD;                        // [4][16][2]
+    if (warp < 4) {
+#pragma unroll
+        for (int t = 0; t < HD / 8; ++t) {
+            const int d = t * 8 + 2 * tq;
+            so[(warp * 16 + g) * HD + d] = o[t][0];
+            so[(warp * 16 + g) * HD + d + 1] = o[t][1];
+            so[(warp * 16 + g + 8) * HD + d] = o[t][2];
+            so[(warp * 16 + g + 8) * HD + d + 1] = o[t][3];
+        }
+        if (tq == 0) {
+            sml[((warp * 16 + g) << 1)] = m[0];
+            sml[((warp * 16 + g) << 1) + 1] = l[0];
+            sml[((warp * 16 + g + 8) << 1)] = m[1];
+            sml[((warp * 16 + g + 8) << 1) + 1] = l[1];
+        }
+    }
+    __syncthreads();
+    if (abort_flag) return;
+    for (int idx = threadIdx.x; idx < n_rep * HD; idx += DECODE_TMA_THREADS) {
+        const int r = idx / HD, d = idx % HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, sml[(w * 16 + r) << 1]);
+        float L = 0.f, acc = 0.f;
+        if (M != -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float f = expf(sml[(w * 16 + r) << 1] - M);
+                L += f * sml[((w * 16 + r) << 1) + 1];
+                acc += f * so[(w * 16 + r) * HD + d];
+            }
+        }
+        const int h = kvh * n_rep + r;
+        if (n_splits == 1) {
+            out[(size_t)token * out_ld + (size_t)h * HD + d] = __float2bfloat16_rn(acc / L);
+        } else {
+            const size_t row = ((size_t)b * n_heads + h) * n_splits + split;
+            part_o[row * HD + d] = acc;
+            if (d == 0) {
+                part_ml[row * 2] = M;
+                part_ml[row * 2 + 1] = L;
+            }
+        }
+    }
+}
+
 // out[b, h, :] = sum_s exp(M_s - M) O_s / sum_s exp(M_s - M) L_s over the splits
 __global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     const int* __restrict__ cu_seqlens, int n_heads, int hd, int n_splits,
@@ -453,6 +662,34 @@ int launch_decode(const void* q, int q_ld, const void* kc, const void* vc, const
 }
 
 template <int HD>
+int launch_decode_tma(const CUtensorMap& mk, const CUtensorMap& mv, const void* q, int q_ld, const int* page_table,
+                      int max_pages, const int* seq_slot, const int* seq_len, const int* cu_seqlens, int n_seqs,
+                      int n_heads, int n_kv_heads, float scale, int window, int n_splits, float* part_o,
+                      float* part_ml, void* out, int out_ld, int* status, cudaStream_t stream) {
+    constexpr int SMEM = 2 * RING * PAGE * HD * 2 + 16 * HD * 2 + 1024;
+    static_assert(4 * 16 * HD * 4 + 4 * 16 * 2 * 4 <= 2 * RING * PAGE * HD * 2, "merge area must fit the ring");
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_tma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e != cudaSuccess) return fail("attention: cannot raise dynamic shared memory: %s", cudaGetErrorString(e));
+        configured = true;
+    }
+    dim3 grid(n_seqs, n_kv_heads, n_splits);
+    cudaError_t e = launch_dependent(
+        attn_decode_tma_kernel<HD>, grid, dim3(DECODE_TMA_THREADS), (size_t)SMEM, stream, mk, mv, (const __nv_bfloat16*)q,
+        q_ld, page_table, max_pages, seq_slot, seq_len, cu_seqlens, n_heads, n_kv_heads, scale, window, n_splits, part_o,
+        part_ml, (__nv_bfloat16*)out, out_ld, status);
+    if (int rc = check_launch(e, "attn_decode_tma")) return rc;
+    if (n_splits > 1) {
+        e = launch_dependent(attn_combine_kernel, dim3(n_seqs, n_heads), dim3(HD >= 128 ? 128 : 64), (size_t)0, stream,
+                             (const float*)part_o, (const float*)part_ml, cu_seqlens, n_heads, (int)HD, n_splits,
+                             (__nv_bfloat16*)out, out_ld);
+        return check_launch(e, "attn_combine");
+    }
+    return 0;
+}
+
+template <int HD>
 int launch_prefill(const void* q, int q_ld, const void* kc, const void* vc, const int* page_table, int max_pages,
                    const int* seq_slot, const int* seq_start, const int* cu_seqlens, int n_seqs, int max_new,
                    int n_heads, int n_kv_heads, float scale, int window, void* out, int out_ld, cudaStream_t stream) {
@@ -510,6 +747,29 @@ RI_API int ri_attention_decode(const void* q, int q_ld, const void* kcache, cons
                                  n_heads, n_kv_heads, scale, window, n_splits, part_o, part_ml, out, out_ld, stream);
     return launch_decode<128>(q, q_ld, kcache, vcache, page_table, max_pages, seq_slot, seq_len, cu_seqlens, n_seqs,
                               n_heads, n_kv_heads, scale, window, n_splits, part_o, part_ml, out, out_ld, stream);
+}
+
+// The same with the cache pages brought in by TMA.  map_k / map_v: tensor maps (128 bytes each) of the
+// layer's K and V viewed as [pages * kv heads * 64, head_dim] with a {64, 64} box and 128-byte swizzle.
+// `status` (may be null) is a host-visible int that receives a code if a bounded wait ran out.
+RI_API int ri_attention_decode_tma(const void* map_k, const void* map_v, const void* q, int q_ld,
+                                   const int* page_table, int max_pages, const int* seq_slot, const int* seq_len,
+                                   const int* cu_seqlens, void* out, int out_ld, int n_seqs, int n_heads,
+                                   int n_kv_heads, int hd, int page_size, float scale, int window, int n_splits,
+                                   float* part_o, float* part_ml, int* status, cudaStream_t stream) {
+    if (n_seqs <= 0) return 0;
+    if (int rc = check_common(hd, page_size, n_heads, n_kv_heads, q_ld, out_ld, q, out)) return rc;
+    if (n_heads / n_kv_heads > 16) return fail("attention_decode: %d query heads per kv head exceed 16", n_heads / n_kv_heads);
+    if (n_splits < 1 || n_splits > 65535) return fail("attention_decode: %d splits", n_splits);
+    if (n_splits > 1 && (part_o == nullptr || part_ml == nullptr)) return fail("attention_decode: splits need scratch");
+    if (n_kv_heads > 65535) return fail("attention_decode: %d kv heads exceed the grid limit", n_kv_heads);
+    const CUtensorMap& mk = *reinterpret_cast<const CUtensorMap*>(map_k);
+    const CUtensorMap& mv = *reinterpret_cast<const CUtensorMap*>(map_v);
+    if (hd == 64)
+        return launch_decode_tma<64>(mk, mv, q, q_ld, page_table, max_pages, seq_slot, seq_len, cu_seqlens, n_seqs, n_heads,
+                                     n_kv_heads, scale, window, n_splits, part_o, part_ml, out, out_ld, status, stream);
+    return launch_decode_tma<128>(mk, mv, q, q_ld, page_table, max_pages, seq_slot, seq_len, cu_seqlens, n_seqs, n_heads,
+                                  n_kv_heads, scale, window, n_splits, part_o, part_ml, out, out_ld, status, stream);
 }
 
 RI_API int ri_attention_prefill(const void* q, int q_ld, const void* kcache, const void* vcache, const int* page_table,

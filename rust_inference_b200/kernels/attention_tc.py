@@ -53,3 +53,26 @@ def prefill(qkv: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, page_
           c_int(n_kv_heads), c_int(head_dim), c_int(page_size), c_float(scale), c_int(window),
           c_void_p(st.data_ptr()), _stream())
     return out
+
+
+def decode(q: torch.Tensor, q_ld: int, kcache: torch.Tensor, vcache: torch.Tensor, page_table, seq_slot, seq_len,
+           cu_seqlens, out: torch.Tensor, *, n_seqs: int, n_heads: int, n_kv_heads: int, head_dim: int,
+           page_size: int, scale: float, window: int, n_splits: int, part_o=None, part_ml=None) -> torch.Tensor:
+    """Split-K decode attention (one new token per sequence) with the cache pages brought in by TMA
+    through a three-stage ring; same arguments and scratch as `ops.attention_decode`."""
+    _need_cuda(q, kcache, vcache, page_table, seq_slot, seq_len, cu_seqlens, out, part_o, part_ml)
+    _need(q.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+          and kcache.is_contiguous() and vcache.is_contiguous(), "attention_decode: bf16 contiguous tensors only")
+    if n_splits > 1:
+        _need(part_o is not None and part_o.numel() >= n_seqs * n_heads * n_splits * head_dim
+              and part_ml is not None and part_ml.numel() >= n_seqs * n_heads * n_splits * 2,
+              "attention_decode: scratch too small")
+    rows = kcache.shape[0] * kcache.shape[1] * kcache.shape[2]
+    mk = _map(1, kcache, rows, head_dim, head_dim)
+    mv = _map(1, vcache, rows, head_dim, head_dim)
+    st = status_word()
+    _call("attention_mma", "ri_attention_decode_tma", c_void_p(mk.data_ptr()), c_void_p(mv.data_ptr()), _p(q),
+          c_int(q_ld), _p(page_table), c_int(page_table.shape[1]), _p(seq_slot), _p(seq_len), _p(cu_seqlens), _p(out),
+          c_int(out.shape[1]), c_int(n_seqs), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_int(page_size),
+          c_float(scale), c_int(window), c_int(n_splits), _p(part_o), _p(part_ml), c_void_p(st.data_ptr()), _stream())
+    return out

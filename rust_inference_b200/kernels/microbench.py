@@ -109,9 +109,13 @@ def run(kernel: str, model: dict, tokens: int, context: int = 1024, eager_only: 
             po = torch.empty(n_seqs * nh * splits * hd, device=dev)
             pml = torch.empty(n_seqs * nh * splits * 2, device=dev)
 
+            from . import attention_tc
+            use_tma = attn._DECODE == "tma" or (attn._DECODE == "auto" and splits == 1)
+            decode_fn = attention_tc.decode if use_tma else ops.attention_decode
+
             def fn():
                 for i in range(c):
-                    ops.attention_decode(q, q.shape[1], kc[i], vc[i], table, slot, length, cu, o, n_seqs=n_seqs,
+                    decode_fn(q, q.shape[1], kc[i], vc[i], table, slot, length, cu, o, n_seqs=n_seqs,
                                          n_heads=nh, n_kv_heads=nkv, head_dim=hd, page_size=page, scale=scale,
                                          window=0, n_splits=splits, part_o=po, part_ml=pml)
             launches = c

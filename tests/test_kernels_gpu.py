@@ -349,6 +349,14 @@ def test_attention_kernels(dtype, nh, nkv, hd, news, starts, window):
                                  c["cu"], out, n_seqs=c["B"], n_heads=nh, n_kv_heads=nkv, head_dim=hd, page_size=64,
                                  scale=c["scale"], window=window, n_splits=splits, part_o=po, part_ml=pml)
             assert (out.float().cpu() - c["ref"]).abs().max().item() <= tol * c["ref"].abs().max().item(), splits
+            from rust_inference_b200.kernels import attention_tc, tcgen05
+            out2 = torch.zeros_like(out)
+            attention_tc.decode(c["q"], c["q"].shape[1], c["kc"], c["vc"], c["table"], c["slot"], c["length"], c["cu"],
+                                out2, n_seqs=c["B"], n_heads=nh, n_kv_heads=nkv, head_dim=hd, page_size=64,
+                                scale=c["scale"], window=window, n_splits=splits, part_o=po, part_ml=pml)
+            torch.cuda.synchronize()
+            tcgen05.check_status()
+            assert (out2.float().cpu() - c["ref"]).abs().max().item() <= tol * c["ref"].abs().max().item(), splits
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
