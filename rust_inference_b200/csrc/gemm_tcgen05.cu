@@ -4,8 +4,9 @@
 //
 // The product is computed transposed: the MMA's M dimension runs over 128 *features*
 // (rows of W, the A operand), its N dimension over TN *tokens* (rows of X, the B
-// operand), TN in {16, 32, 64, 128, 256}.  So a decode step with a handful of tokens
-// still fills the 128-row MMA with weights, and a prefill step uses 128 x 256 tiles.
+// operand), TN in {16, 32, 64, 128, 256}.  So a decode step with a handful of tokens still
+// fills the 128-row MMA with weights.  The SiLU-gate projection of steps of more than 128
+// tokens takes the token-major kernel further down (128 tokens x 256 weight rows per tile).
 // Both operands are K-major, which is how the reference lays its matrices out
 // ([out, in] row-major, quant.rs:45-50) and how activations are packed.
 //
@@ -74,6 +75,11 @@ __device__ __forceinline__ void store_result(void* out_, size_t o, float acc, fl
     } else {
         reinterpret_cast<__nv_bfloat16*>(out_)[o] = __float2bfloat16_rn(silu_to_bf16(acc) * acc2);
     }
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
 }
 
 __host__ __device__ constexpr int tmem_cols(int need) { return need <= 32 ? 32 : need <= 64 ? 64 : need <= 128 ? 128 : need <= 256 ? 256 : 512; }
@@ -305,6 +311,243 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 }
 
 // ---------------------------------------------------------------------------------------------
+// The token-major orientation, for steps of more than 128 tokens (prompts).
+//
+// Here the MMA's M dimension runs over 128 tokens (rows of X, the A operand) and its N dimension
+// over 256 rows of W (the B operand): 256 features, or, for the SiLU-gate epilogue, 128 gate rows
+// stacked on the 128 up rows of the same features, so that one MMA per K-slice feeds both and a
+// token's gate and up values sit in the same TMEM lane.  Against the feature-major kernel with two
+// N = 128 MMAs per K-slice this reads 25% fewer operand bytes from shared memory per MAC (the main
+// loop of that shape sat at the 128 B/clk shared-memory limit), and every epilogue thread owns a
+// token and writes runs of 16 consecutive features with 16-byte stores.
+// Same ring, same persistent grid, same two accumulator buffers.
+// ---------------------------------------------------------------------------------------------
+constexpr int TM_TOK = 128;                         // tokens per tile (MMA M)
+constexpr int TM_ROWS = 256;                        // rows of W per tile (MMA N)
+constexpr int TM_STAGE_BYTES = (TM_TOK + TM_ROWS) * BLOCK_K * 2;     // 48 KiB
+
+template <bool DUAL, int MODE>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_w2,
+               const __grid_constant__ CUtensorMap map_x, const float* __restrict__ bias, void* __restrict__ out_,
+               int n_tok, int n_feat, int K, int stages, int* status) {
+    constexpr int FEATS = DUAL ? TM_ROWS / 2 : TM_ROWS;        // output features per tile
+    constexpr int X_BYTES = TM_TOK * BLOCK_K * 2;
+    constexpr int TMEM_COLS = 2 * TM_ROWS;                     // two accumulator buffers
+    constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TM_ROWS >> 3) << 17) |
+                               ((uint32_t)(TM_TOK >> 4) << 24);
+
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[MAX_STAGES];
+    __shared__ __align__(8) uint64_t empty_bar[MAX_STAGES];
+    __shared__ __align__(8) uint64_t acc_full[2];
+    __shared__ __align__(8) uint64_t acc_empty[2];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ volatile int abort_flag;
+
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_kb = (K + BLOCK_K - 1) / BLOCK_K;
+    const int n_tok_tiles = (n_tok + TM_TOK - 1) / TM_TOK, n_feat_tiles = (n_feat + FEATS - 1) / FEATS;
+    const int total_tiles = n_tok_tiles * n_feat_tiles;
+    const int my_tiles = ((int)blockIdx.x < total_tiles) ? (total_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; ++s) {
+            mbar_init(smem_u32(&full_bar[s]), 1);
+            mbar_init(smem_u32(&empty_bar[s]), 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(smem_u32(&acc_full[i]), 1);
+            mbar_init(smem_u32(&acc_empty[i]), 4);
+        }
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
+                     "r"((uint32_t)TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+    let_next_kernel_start();
+
+    // token tiles vary fastest, so CTAs that run together share the weight rows in L2
+    auto tile_coords = [&](int i, int& f0, int& t0) {
+        const int tile = (int)blockIdx.x + i * (int)gridDim.x;
+        t0 = (tile % n_tok_tiles) * TM_TOK;
+        f0 = (tile / n_tok_tiles) * FEATS;
+    };
+    // the W rows of one stage: 256 features, or 128 gate rows then the 128 up rows of the same features
+    auto load_w = [&](uint32_t stage, uint32_t bar, int kx, int f0) {
+        tma_load_2d(stage + X_BYTES, &map_w, bar, kx, f0);
+        if (DUAL) tma_load_2d(stage + X_BYTES + A_BYTES, &map_w2, bar, kx, f0);
+        else tma_load_2d(stage + X_BYTES + A_BYTES, &map_w, bar, kx, f0 + BLOCK_F);
+    };
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int it = 0;
+            bool waited = false, alive = true;
+            for (int i = 0; i < my_tiles && alive; ++i) {
+                int f0, t0;
+                tile_coords(i, f0, t0);
+                int kb = 0;
+                if (!waited) {
+                    const int ahead = min(stages, n_kb);
+                    for (int j = 0; j < ahead; ++j) {            // weights first: no kernel writes them
+                        const uint32_t bar = smem_u32(&full_bar[j]);
+                        mbar_expect_tx(bar, TM_STAGE_BYTES);
+                        load_w(smem_base + (uint32_t)j * TM_STAGE_BYTES, bar, j * BLOCK_K, f0);
+                    }
+                    wait_for_previous_kernels();                 // the activations come from the kernel before
+                    waited = true;
+                    for (int j = 0; j < ahead; ++j)
+                        tma_load_2d(smem_base + (uint32_t)j * TM_STAGE_BYTES, &map_x, smem_u32(&full_bar[j]), j * BLOCK_K, t0);
+                    kb = ahead;
+                    it = ahead;
+                }
+                for (; kb < n_kb; ++kb, ++it) {
+                    const int s = it % stages;
+                    if (!mbar_wait(smem_u32(&empty_bar[s]), ((uint32_t)(it / stages) & 1u) ^ 1u) || abort_flag) {
+                        if (!abort_flag) report(status, ST_PRODUCER_TIMEOUT);
+                        abort_flag = 1;
+                        alive = false;
+                        break;
+                    }
+                    const uint32_t bar = smem_u32(&full_bar[s]);
+                    const uint32_t stage = smem_base + (uint32_t)s * TM_STAGE_BYTES;
+                    mbar_expect_tx(bar, TM_STAGE_BYTES);
+                    load_w(stage, bar, kb * BLOCK_K, f0);
+                    tma_load_2d(stage, &map_x, bar, kb * BLOCK_K, t0);
+                }
+            }
+            for (int j = max(0, it - stages); j < it; ++j)
+                if (!mbar_wait(smem_u32(&full_bar[j % stages]), (uint32_t)(j / stages) & 1u)) {
+                    report(status, ST_DRAIN_TIMEOUT);
+                    break;
+                }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            int it = 0;
+            bool alive = true;
+            for (int i = 0; i < my_tiles && alive; ++i) {
+                const int buf = i & 1;
+                if (!mbar_wait(smem_u32(&acc_empty[buf]), ((uint32_t)(i >> 1) & 1u) ^ 1u)) {
+                    report(status, ST_MMA_TIMEOUT);
+                    abort_flag = 1;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t acc = tmem_base + (uint32_t)(buf * TM_ROWS);
+                for (int kb = 0; kb < n_kb; ++kb, ++it) {
+                    const int s = it % stages;
+                    if (!mbar_wait(smem_u32(&full_bar[s]), (uint32_t)(it / stages) & 1u)) {
+                        report(status, ST_MMA_TIMEOUT);
+                        abort_flag = 1;
+                        alive = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t stage = smem_base + (uint32_t)s * TM_STAGE_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BLOCK_K / 16; ++k)
+                        umma(acc, make_smem_desc(stage + k * 32), make_smem_desc(stage + X_BYTES + k * 32), IDESC,
+                             kb > 0 || k > 0);
+                    umma_commit(smem_u32(&empty_bar[s]));
+                }
+                umma_commit(smem_u32(&acc_full[buf]));
+            }
+        }
+    } else {
+        // ---------------- epilogue: a thread owns a token, writes runs of 16 features ----------------
+        wait_for_previous_kernels();
+        const int lane_base = (warp & 3) * 32;
+        const bool aligned = n_feat % 8 == 0;                      // rows of `out` keep 16-byte alignment
+        for (int i = 0; i < my_tiles; ++i) {
+            int f0, t0;
+            tile_coords(i, f0, t0);
+            const int buf = i & 1;
+            const bool landed = mbar_wait(smem_u32(&acc_full[buf]), (uint32_t)(i >> 1) & 1u);
+            if (!landed && lane == 0) {
+                report(status, ST_EPILOGUE_TIMEOUT);
+                abort_flag = 1;
+            }
+            tc_fence_after();
+            if (!landed || abort_flag) break;
+            const int t = t0 + lane_base + lane;
+            const bool t_ok = t < n_tok;
+            const uint32_t trow = tmem_base + ((uint32_t)lane_base << 16) + (uint32_t)(buf * TM_ROWS);
+#pragma unroll 1
+            for (int c0 = 0; c0 < FEATS; c0 += 16) {
+                if (f0 + c0 >= n_feat) break;                       // uniform over the warp
+                uint32_t v[16], u[16];
+                tmem_ld16(trow + c0, v);
+                if (DUAL) tmem_ld16(trow + TM_ROWS / 2 + c0, u);
+                tmem_wait_ld();
+                if (!t_ok) continue;
+                const size_t o0 = (size_t)t * n_feat + f0 + c0;
+                const bool whole = aligned && f0 + c0 + 16 <= n_feat;
+                float r[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const float a = __uint_as_float(v[j]);
+                    if (MODE == 3) r[j] = silu_to_bf16(a) * __uint_as_float(u[j]);
+                    else if (MODE == 2) r[j] = a;
+                    else r[j] = a + ((bias != nullptr && f0 + c0 + j < n_feat) ? bias[f0 + c0 + j] : 0.f);
+                }
+                if (whole) {
+                    if (MODE == 0 || MODE == 3) {
+                        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(out_) + o0;
+                        uint4 lo, hi;
+                        lo.x = pack_bf16x2(r[0], r[1]);  lo.y = pack_bf16x2(r[2], r[3]);
+                        lo.z = pack_bf16x2(r[4], r[5]);  lo.w = pack_bf16x2(r[6], r[7]);
+                        hi.x = pack_bf16x2(r[8], r[9]);  hi.y = pack_bf16x2(r[10], r[11]);
+                        hi.z = pack_bf16x2(r[12], r[13]); hi.w = pack_bf16x2(r[14], r[15]);
+                        *reinterpret_cast<uint4*>(dst) = lo;
+                        *reinterpret_cast<uint4*>(dst + 8) = hi;
+                    } else {
+                        float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(out_) + o0);
+#pragma unroll
+                        for (int q4 = 0; q4 < 4; ++q4) {
+                            float4 x = make_float4(r[4 * q4], r[4 * q4 + 1], r[4 * q4 + 2], r[4 * q4 + 3]);
+                            if (MODE == 2) {                     // K is not split here: a plain read-add-write
+                                const float4 old = dst[q4];
+                                x.x += old.x; x.y += old.y; x.z += old.z; x.w += old.w;
+                            }
+                            dst[q4] = x;
+                        }
+                    }
+                } else {
+                    for (int j = 0; j < 16; ++j)
+                        if (f0 + c0 + j < n_feat) {
+                            if (MODE == 0 || MODE == 3) reinterpret_cast<__nv_bfloat16*>(out_)[o0 + j] = __float2bfloat16_rn(r[j]);
+                            else if (MODE == 1) reinterpret_cast<float*>(out_)[o0 + j] = r[j];
+                            else reinterpret_cast<float*>(out_)[o0 + j] += r[j];
+                        }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&acc_empty[buf]));
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS)
+                     : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
 // A bf16 matrix [rows, K] row-major as a 2-D tensor map with a {64, box_rows} box, 128-byte swizzle,
@@ -376,6 +619,30 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx,
 }
 
 template <bool DUAL, int MODE>
+int launch_tm(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx, const float* bias, void* out,
+              int n_tok, int n_feat, int K, int* status, cudaStream_t stream) {
+    const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
+    int stages = SMEM_BUDGET / TM_STAGE_BYTES;
+    if (stages > total_kb) stages = total_kb;
+    const size_t smem = (size_t)stages * TM_STAGE_BYTES + 1024;
+    auto kernel = gemm_tm_kernel<DUAL, MODE>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BUDGET + 1024);
+        if (e != cudaSuccess) return fail("gemm_tcgen05: cannot raise dynamic shared memory: %s", cudaGetErrorString(e));
+        configured = true;
+    }
+    constexpr int FEATS = DUAL ? TM_ROWS / 2 : TM_ROWS;
+    const long long total_tiles = (long long)((n_tok + TM_TOK - 1) / TM_TOK) * ((n_feat + FEATS - 1) / FEATS);
+    if (total_tiles > 0x7fffffffLL) return fail("gemm_tcgen05: %lld tiles exceed the index range", total_tiles);
+    long long ctas = sm_count();
+    if (ctas > total_tiles) ctas = total_tiles;
+    cudaError_t e = launch_dependent(kernel, dim3((unsigned)ctas), dim3(THREADS), smem, stream, mw, mw2, mx, bias, out,
+                                     n_tok, n_feat, K, stages, status);
+    return check_launch(e, "gemm_tcgen05 (token-major)");
+}
+
+template <bool DUAL, int MODE>
 int pick_tile(int tn, const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx, const float* bias,
               void* out, int n_tok, int n_feat, int K, int split_k, int* status, cudaStream_t stream) {
     switch (tn) {
@@ -403,6 +670,8 @@ RI_API int ri_gemm_tcgen05_tile(int n_tok, int dual) {
     if (n_tok <= 16) return 16;
     if (n_tok <= 32) return 32;
     if (n_tok <= 64) return 64;
+    // beyond 128 tokens: the SiLU-gate projection takes the token-major kernel (128 tokens per tile),
+    // the others the feature-major kernel with 256 tokens per tile
     if (n_tok <= 128 || dual) return 128;
     return 256;
 }
@@ -433,6 +702,9 @@ RI_API int ri_gemm_tcgen05(const void* map_x, const void* map_w, const void* map
     const CUtensorMap& mw = *reinterpret_cast<const CUtensorMap*>(map_w);
     const CUtensorMap& mw2 = dual ? *reinterpret_cast<const CUtensorMap*>(map_w2) : mw;
     const CUtensorMap& mx = *reinterpret_cast<const CUtensorMap*>(map_x);
+    // Measured at 2,048 tokens of a 3584-wide model: the SiLU-gate projection runs at 1,334 TFLOP/s
+    // token-major against 1,145 feature-major; q/k/v, o and down are 3-12% faster feature-major.
+    if (dual && n_tok > TM_TOK) return launch_tm<true, 3>(mw, mw2, mx, bias, out, n_tok, n_feat, K, status, stream);
     switch (mode) {
         case 0: return pick_tile<false, 0>(tn, mw, mw2, mx, bias, out, n_tok, n_feat, K, split_k, status, stream);
         case 1: return pick_tile<false, 1>(tn, mw, mw2, mx, bias, out, n_tok, n_feat, K, split_k, status, stream);

@@ -42,6 +42,8 @@ def supports(x: torch.Tensor, w) -> bool:
 
 
 def token_tile(n_tok: int, dual: bool) -> int:
+    """Rows of the activation tile: 16..256 tokens in the feature-major kernel; the SiLU-gate
+    projection of more than 128 tokens takes the token-major kernel, 128 tokens per tile."""
     return 16 if n_tok <= 16 else 32 if n_tok <= 32 else 64 if n_tok <= 64 else 128 if (n_tok <= 128 or dual) else 256
 
 
