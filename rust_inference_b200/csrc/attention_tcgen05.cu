@@ -18,9 +18,10 @@
 //   O += P V      P is written to shared memory as bf16 in the swizzled K-major layout and is the
 //                 A operand; the V page, [keys][head_dim] as the cache holds it, is the B operand
 //                 in MN-major form; O accumulates in tensor memory in float32.
-// Warp 0 issues the TMA loads, warp 1 the MMAs, warps 2-5 are the softmax rows.  Two CTAs fit on an
-// SM (96 KiB of shared memory, 256 TMEM columns at head_dim 128), so one CTA's softmax overlaps
-// the other's MMAs.
+// Warp 0 issues the TMA loads, warp 1 the MMAs, warps 2-5 are the softmax rows.  There are two score
+// buffers in tensor memory: S of page j+1 is computed while the softmax of page j runs, and the
+// softmax computes its exponentials before it waits for P V of the page before (it needs that only
+// to overwrite P and to rescale O).  Two CTAs fit on an SM (96 KiB of shared memory, 256 TMEM columns).
 //
 // All mbarrier waits are bounded; on a timeout the kernel records a code in the host-visible
 // status word and winds down.
@@ -59,6 +60,13 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
         : "memory");
 }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// 2^x on the special-function unit.  Its relative error (about 2^-22) is far below the bf16 rounding
+// of P that follows; -inf gives 0.
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -75,14 +83,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     constexpr int Q_BYTES = ATOMS * BM * 128;            // [atom][128 queries][64]
     constexpr int K_BYTES = ATOMS * BN * 128;            // one buffer: [atom][64 keys][64]
     constexpr int V_BYTES = ATOMS * BN * 128;
-    constexpr int S_COL = 0, O_COL = BN;
-    constexpr int TMEM_COLS = (BN + HD) <= 128 ? 128 : 256;
+    constexpr int S_COL = 0, O_COL = 2 * BN;             // two score buffers, then the output accumulator
+    constexpr int TMEM_COLS = 256;
     constexpr uint32_t IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
     constexpr uint32_t IDESC_PV = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) |
                                   ((uint32_t)(BM >> 4) << 24);
 
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t q_full, k_full[2], k_empty[2], v_full, v_empty, s_full, p_full, pv_done;
+    __shared__ __align__(8) uint64_t q_full, k_full[2], k_empty[2], v_full, v_empty, s_full[2], p_full, pv_done;
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile int abort_flag;
 
@@ -107,7 +115,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         for (int i = 0; i < 2; ++i) { mbar_init(smem_u32(&k_full[i]), 1); mbar_init(smem_u32(&k_empty[i]), 1); }
         mbar_init(smem_u32(&v_full), 1);
         mbar_init(smem_u32(&v_empty), 1);
-        mbar_init(smem_u32(&s_full), 1);
+        mbar_init(smem_u32(&s_full[0]), 1);
+        mbar_init(smem_u32(&s_full[1]), 1);
         mbar_init(smem_u32(&p_full), 4);          // one arrival per softmax warp
         mbar_init(smem_u32(&pv_done), 1);
         abort_flag = 0;
@@ -162,18 +171,25 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         if (lane == 0) {
             bool ok = mbar_wait(smem_u32(&q_full), 0);
             if (!ok) { report(status, ST_ATTN_MMA); abort_flag = 1; }
-            for (int j = 0; j < n_pages && ok; ++j) {
+            // scores of page j go to buffer j & 1, so S(j+1) is computed while the softmax of page j runs
+            auto issue_s = [&](int j) -> bool {
                 const int kb = j & 1;
-                if (!mbar_wait(smem_u32(&k_full[kb]), (uint32_t)((j >> 1) & 1))) { report(status, ST_ATTN_MMA); abort_flag = 1; break; }
+                if (!mbar_wait(smem_u32(&k_full[kb]), (uint32_t)((j >> 1) & 1))) return false;
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ++ks) {
                     const uint64_t a = make_smem_desc(q_smem + (ks / 4) * BM * 128 + (ks % 4) * 32);
                     const uint64_t bd = make_smem_desc(k_smem + kb * K_BYTES + (ks / 4) * BN * 128 + (ks % 4) * 32);
-                    umma(tmem_base + S_COL, a, bd, IDESC_S, ks > 0);
+                    umma(tmem_base + S_COL + kb * BN, a, bd, IDESC_S, ks > 0);
                 }
                 umma_commit(smem_u32(&k_empty[kb]));
-                umma_commit(smem_u32(&s_full));
+                umma_commit(smem_u32(&s_full[kb]));
+                return true;
+            };
+            if (ok && !issue_s(0)) { report(status, ST_ATTN_MMA); abort_flag = 1; ok = false; }
+            for (int j = 0; j < n_pages && ok; ++j) {
+                // the buffer S(j+1) goes to was read by the softmax of page j-1, which arrived on p_full before PV(j-1)
+                if (j + 1 < n_pages && !issue_s(j + 1)) { report(status, ST_ATTN_MMA); abort_flag = 1; break; }
                 if (!mbar_wait(smem_u32(&p_full), (uint32_t)(j & 1)) || !mbar_wait(smem_u32(&v_full), (uint32_t)(j & 1))) {
                     report(status, ST_ATTN_MMA); abort_flag = 1; break;
                 }
@@ -197,7 +213,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         float m_used = -INFINITY, l = 0.f;
         bool ok = true;
         for (int j = 0; j < n_pages; ++j) {
-            if (!mbar_wait(smem_u32(&s_full), (uint32_t)(j & 1)) || abort_flag) {
+            if (!mbar_wait(smem_u32(&s_full[j & 1]), (uint32_t)((j >> 1) & 1)) || abort_flag) {
                 if (lane == 0) { report(status, ST_ATTN_SOFTMAX); abort_flag = 1; }
                 ok = false;
                 break;
@@ -205,53 +221,72 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             tc_fence_after();
             uint32_t sv[BN];
 #pragma unroll
-            for (int c = 0; c < BN; c += 16) tmem_ld16(trow + S_COL + c, sv + c);
+            for (int c = 0; c < BN; c += 16) tmem_ld16(trow + S_COL + (j & 1) * BN + c, sv + c);
             tmem_wait_ld();
             const int key0 = (pg_begin + j) * BN;
-            float mx = -INFINITY;
+            // The maximum is taken over the raw scores (the scale is positive), and scale and maximum
+            // are folded into one multiply-add per score: p = 2^(s * scale_log2 - m).
+            float mx_raw = -INFINITY;
+            // pages that every row of the warp sees whole need no mask
+            const bool whole = key0 + BN - 1 <= pos_lo + lane_base && (window <= 0 || key0 > pos_lo + lane_base + 31 - window);
+            if (whole) {
 #pragma unroll
-            for (int c = 0; c < BN; ++c) {
-                const int key = key0 + c;
-                const bool vis = key <= pos && (window <= 0 || key > pos - window);
-                const float s2 = vis ? __uint_as_float(sv[c]) * scale_log2 : -INFINITY;
-                sv[c] = __float_as_uint(s2);
-                mx = fmaxf(mx, s2);
+                for (int c = 0; c < BN; ++c) mx_raw = fmaxf(mx_raw, __uint_as_float(sv[c]));
+            } else {
+#pragma unroll
+                for (int c = 0; c < BN; ++c) {
+                    const int key = key0 + c;
+                    const bool vis = key <= pos && (window <= 0 || key > pos - window);
+                    if (!vis) sv[c] = 0xff800000u;              // -inf
+                    mx_raw = fmaxf(mx_raw, __uint_as_float(sv[c]));
+                }
             }
+            const float mx = mx_raw * scale_log2;                // -inf stays -inf
             // move the scaling maximum only when the true one ran ahead of it by more than 2^8
             const bool move = mx > m_used + (float)RESCALE_LOG2;
-            if (__any_sync(0xffffffffu, move)) {
-                const float m_new = move ? mx : m_used;
-                const float alpha = (m_used == -INFINITY) ? 0.f : exp2f(m_used - m_new);
-                if (j > 0) {                                   // rescale the accumulator (uniform over the warp)
+            const float m_new = move ? mx : m_used;
+            const float alpha = (!move) ? 1.f : ((m_used == -INFINITY) ? 0.f : fast_exp2(m_used - m_new));
+            const float neg_mref = (m_new == -INFINITY) ? 0.f : -m_new;   // nothing visible yet: every p is 0
+            // the exponentials do not need the previous P V product; everything after this does
+            float sum = 0.f;
+            uint32_t pk[BN / 2];
+#pragma unroll
+            for (int c = 0; c < BN; c += 2) {
+                const float p0 = fast_exp2(fmaf(__uint_as_float(sv[c]), scale_log2, neg_mref));
+                const float p1 = fast_exp2(fmaf(__uint_as_float(sv[c + 1]), scale_log2, neg_mref));
+                sum += p0 + p1;
+                pk[c >> 1] = pack2(p0, p1);
+            }
+            if (j > 0) {
+                // P's buffer and the accumulator are free once PV of the page before has finished
+                if (!mbar_wait(smem_u32(&pv_done), (uint32_t)((j - 1) & 1)) || abort_flag) {
+                    if (lane == 0) { report(status, ST_ATTN_SOFTMAX); abort_flag = 1; }
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                if (__any_sync(0xffffffffu, move)) {            // rescale the accumulator (uniform over the warp)
 #pragma unroll 1
                     for (int c = 0; c < HD; c += 16) {
                         uint32_t o[16];
                         tmem_ld16(trow + O_COL + c, o);
                         tmem_wait_ld();
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * (move ? alpha : 1.f));
+                        for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
                         tmem_st16(trow + O_COL + c, o);
                     }
                     tmem_wait_st();
                 }
-                if (move) { l *= alpha; m_used = m_new; }
             }
-            const float mref = (m_used == -INFINITY) ? 0.f : m_used;     // nothing visible yet: every p is 0
-            float sum = 0.f;
+            l = l * alpha + sum;
+            m_used = m_new;
             const uint32_t prow = p_smem + (uint32_t)r * 128;
 #pragma unroll
             for (int c8 = 0; c8 < BN / 8; ++c8) {
-                float p[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    p[i] = exp2f(__uint_as_float(sv[c8 * 8 + i]) - mref);
-                    sum += p[i];
-                }
                 const uint32_t dst = prow + (uint32_t)((c8 ^ (r & 7)) << 4);
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pack2(p[0], p[1])),
-                             "r"(pack2(p[2], p[3])), "r"(pack2(p[4], p[5])), "r"(pack2(p[6], p[7])) : "memory");
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pk[4 * c8]), "r"(pk[4 * c8 + 1]),
+                             "r"(pk[4 * c8 + 2]), "r"(pk[4 * c8 + 3]) : "memory");
             }
-            l += sum;
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is read by the tensor core's proxy
             tc_fence_before();
             __syncwarp();
