@@ -9,6 +9,9 @@ lengths, so one capture serves every step of that batch size.
 """
 from __future__ import annotations
 
+import gc
+import weakref
+
 import numpy as np
 import torch
 
@@ -18,7 +21,10 @@ from .context import StepContext, Workspace, pack_step
 
 class DecodeGraph:
     def __init__(self, engine, n_seqs: int):
-        self.engine = engine
+        # a weak reference: the engine owns its graphs, and a cycle would leave both to the cyclic
+        # collector, which may run in the middle of some later capture and destroy a CUDA graph there
+        # (not permitted while a stream is capturing)
+        self.engine = weakref.proxy(engine)
         self.n_seqs = n_seqs
         dev = engine.device
         # the layout of a step with one token per sequence depends on B only
@@ -60,8 +66,14 @@ class DecodeGraph:
             self.launches = ops.launch_count() - before
             torch.cuda.synchronize(self.engine.device)
             g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
-                self.engine.model.forward(self.ctx, self.engine.cache, self.logits)
+            collecting = gc.isenabled()
+            gc.disable()                  # no finalizer may touch CUDA while the stream is capturing
+            try:
+                with torch.cuda.graph(g):
+                    self.engine.model.forward(self.ctx, self.engine.cache, self.logits)
+            finally:
+                if collecting:
+                    gc.enable()
             self.graph = g
             # the eager run already produced this step's logits
             return self.logits
