@@ -77,6 +77,10 @@ class SequenceCache:
         self.page_table = torch.zeros((n_slots, self.pager.max_pages_per_slot), dtype=torch.int32,
                                       device=self.device)
 
+        self._stage_bufs = [None] * 4
+        self._stage_events = [None] * 4
+        self._stage_turn = 0
+
         # group layers by their needs
         self.groups: dict = {}
         self._layers: list = [None] * len(requests)
@@ -122,16 +126,43 @@ class SequenceCache:
     def length(self, slot: int) -> int:
         return self.pager.length(slot)
 
+    def _staging(self, n: int) -> torch.Tensor:
+        """A pinned int32 buffer of n entries whose earlier use has been copied out: page-table
+        updates go through these, so that publishing them never blocks the host on the stream."""
+        i = self._stage_turn
+        self._stage_turn = (i + 1) % len(self._stage_bufs)
+        if self._stage_events[i] is not None:
+            self._stage_events[i].synchronize()
+        buf = self._stage_bufs[i]
+        if buf is None or buf.numel() < n:
+            buf = torch.empty(max(256, 2 * n), dtype=torch.int32).pin_memory()
+            self._stage_bufs[i] = buf
+        return buf
+
     def reserve(self, wants: list[tuple]) -> None:
-        """Make room for (slot, new_length) pairs, all or nothing, and publish the page
-        table rows that changed to the device."""
-        added = self.pager.reserve_many(wants)
-        for slot, pages in added.items():
-            if pages:
+        """Make room for (slot, new_length) pairs, all or nothing, and publish the page table
+        entries that were added to the device (asynchronously, in stream order)."""
+        added = {slot: pages for slot, pages in self.pager.reserve_many(wants).items() if pages}
+        if not added:
+            return
+        total = sum(len(p) for p in added.values())
+        if self.device.type != "cuda":
+            for slot, pages in added.items():
                 have = len(self.pager._pages[slot])
                 self.page_table_host[slot, have - len(pages):have] = pages
-                row = torch.from_numpy(self.page_table_host[slot, :have].copy())
-                self.page_table[slot, :have].copy_(row, non_blocking=False)
+                self.page_table[slot, have - len(pages):have] = torch.tensor(pages, dtype=torch.int32)
+            return
+        buf = self._staging(total)
+        off = 0
+        for slot, pages in added.items():
+            have = len(self.pager._pages[slot])
+            self.page_table_host[slot, have - len(pages):have] = pages
+            buf[off:off + len(pages)] = torch.tensor(pages, dtype=torch.int32)
+            self.page_table[slot, have - len(pages):have].copy_(buf[off:off + len(pages)], non_blocking=True)
+            off += len(pages)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._stage_events[(self._stage_turn - 1) % len(self._stage_bufs)] = ev
 
     def commit(self, slot: int, new_length: int) -> None:
         self.pager.set_length(slot, new_length)

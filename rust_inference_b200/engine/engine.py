@@ -209,6 +209,31 @@ class Engine:
             self.cache.commit(s, self.cache.length(s) + len(t))
         return logits
 
+    def can_feed_from_device(self) -> bool:
+        """True if decode steps replay a captured graph, so a step can take its tokens from a
+        device tensor (`step_from_device`)."""
+        return self.use_graphs
+
+    def step_from_device(self, slots: list, tokens_dev: torch.Tensor):
+        """One decode step whose tokens (one per sequence, int32 [B]) are already on the device,
+        for instance straight from the sampler: no host round trip between sampling and the next
+        step.  Returns the step's logits [B, vocab] in a buffer the next step overwrites."""
+        from .graphs import DecodeGraph
+        n = len(slots)
+        if tokens_dev.numel() != n or tokens_dev.dtype != torch.int32:
+            raise ValueError("step_from_device: one int32 token per sequence")
+        with torch.cuda.device(self.device):
+            dev, _, _ = self._stage(slots, [[0]] * n, [[0]] * n)
+            graph = self._graphs.get(n)
+            if graph is None:
+                graph = self._graphs[n] = DecodeGraph(self, n)
+            graph.load_meta(dev, keep_tokens=True)
+            graph.ctx.token_ids.copy_(tokens_dev, non_blocking=True)
+            logits = graph.launch()
+        for s in slots:
+            self.cache.commit(s, self.cache.length(s) + 1)
+        return logits
+
     def decode_steps(self, slots: list, first_tokens: list, n_steps: int, sampler_config=None) -> torch.Tensor:
         """Device-resident decoding: n_steps steps of one token per sequence in which each
         sampled token is fed to the next step on the device, with no host round trip and no

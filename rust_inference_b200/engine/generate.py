@@ -7,6 +7,11 @@ prompts in one step), then each live sequence gets one token per step; a sequenc
 ends gives its slot back at once and the batch shrinks; when a batch is done the next
 requests start, until all are served.
 
+When the engine can take a step's tokens from the device, the loop looks one step ahead: the
+next step is launched with the sampled tokens fed on the device, and the host reads the
+tokens of the step before while it runs.  Which sequences end by length is known in advance;
+a sequence that turns out to have sampled a stop token has simply run one step for nothing.
+
 Kept from the reference: a sampled stop token ends the sequence and is not emitted
 (model.rs:383-387); at most max_tokens tokens are generated (model.rs:373).  Changed: a
 sequence that reaches the cache's max_seq_len ends with reason "length" instead of the
@@ -80,6 +85,108 @@ class Generator:
             self.d2h_bytes += tokens.numel() * tokens.element_size()
         return [int(t) for t in (tokens.tolist() if hasattr(tokens, "tolist") else tokens)]
 
+    def _finish_or_keep(self, s, tok, max_tokens, results) -> bool:
+        """Book one sampled token of sequence s; returns True if s goes on."""
+        reason = None
+        if tok in self.stop_ids:
+            reason = "stop"                                          # not emitted, not fed back
+        else:
+            s.tokens.append(tok)
+            if len(s.tokens) >= max_tokens:
+                reason = "length"
+            elif s.prompt_length + len(s.tokens) > self.engine.max_seq_len:
+                reason = "length"                                    # no position left to feed it at
+        if reason is None:
+            return True
+        results[s.index] = GenerationResult(s.tokens, reason, s.prompt_length)
+        self.engine.free_slot(s.slot)                                # the slot is free for the next batch
+        s.slot = -1
+        return False
+
+    def _run_batch(self, live, prompts, max_tokens, results, uses_history) -> None:
+        """Step, sample, read the tokens, decide, step again."""
+        feed = [list(prompts[s.index]) for s in live]                # first step: whole prompts
+        while True:
+            logits = self.engine.step([s.slot for s in live], feed, "last", borrow=True)
+            self.steps += 1
+            sampled = self._to_host(self.sampler.sample(
+                logits, [s.index for s in live], [len(s.tokens) for s in live],
+                [s.history for s in live] if uses_history else None))
+            if hasattr(self.engine, "check_device_status"):
+                self.engine.check_device_status()
+            if self.step_times is not None:
+                self.step_times.append(time.perf_counter())
+            still, feed = [], []
+            for s, tok in zip(list(live), sampled):
+                if self._finish_or_keep(s, tok, max_tokens, results):
+                    if uses_history:
+                        s.history.append(tok)
+                    still.append(s)
+                    feed.append([tok])
+            live[:] = still
+            if not live:
+                return
+
+    def _run_batch_ahead(self, live, prompts, max_tokens, results) -> None:
+        """The same with one step of lookahead: while the host reads the tokens sampled by step i,
+        step i+1 already runs on them."""
+        import torch
+        eng = self.engine
+
+        # a few pinned buffers, taken in turn: at most two copies are outstanding at any time
+        ring = [torch.empty(len(live), dtype=torch.int32).pin_memory() for _ in range(4)]
+        turn = [0]
+
+        def read_later(tokens_dev):
+            host = ring[turn[0] % len(ring)][:tokens_dev.numel()]
+            turn[0] += 1
+            host.copy_(tokens_dev, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+            self.d2h_bytes += host.numel() * 4
+            return host, ev
+
+        logits = eng.step([s.slot for s in live], [list(prompts[s.index]) for s in live], "last", borrow=True)
+        self.steps += 1
+        sampled = self.sampler.sample(logits, [s.index for s in live], [len(s.tokens) for s in live], None)
+        pending = (list(live), sampled, read_later(sampled))         # sequences, their tokens on the device, the copy
+        while pending is not None:
+            seqs, tokens_dev, (host, ev) = pending
+            # Who certainly goes on after the token just sampled (length limits are known; stop tokens are not)?
+            rows = [i for i, s in enumerate(seqs)
+                    if len(s.tokens) + 1 < max_tokens and s.prompt_length + len(s.tokens) + 1 <= eng.max_seq_len]
+            nxt = None
+            if rows:
+                ahead = [seqs[i] for i in rows]
+                feed_dev = tokens_dev if len(rows) == len(seqs) else tokens_dev[
+                    torch.tensor(rows, dtype=torch.long, device=tokens_dev.device)]
+                logits = eng.step_from_device([s.slot for s in ahead], feed_dev)
+                self.steps += 1
+                sampled = self.sampler.sample(logits, [s.index for s in ahead], [len(s.tokens) + 1 for s in ahead], None)
+                nxt = (ahead, sampled, read_later(sampled))
+            ev.synchronize()                                         # the earlier tokens; the step just launched keeps running
+            if hasattr(eng, "check_device_status"):
+                eng.check_device_status()
+            if self.step_times is not None:
+                self.step_times.append(time.perf_counter())
+            stopped = set()
+            for s, tok in zip(seqs, host.tolist()):
+                if not self._finish_or_keep(s, int(tok), max_tokens, results):
+                    stopped.add(id(s))
+            if nxt is not None and stopped:
+                # a sequence that sampled a stop token ran the step ahead for nothing: drop its row
+                ahead, sampled, (host2, ev2) = nxt
+                keep = [i for i, s in enumerate(ahead) if id(s) not in stopped]
+                if not keep:
+                    nxt = None
+                elif len(keep) < len(ahead):
+                    ev2.synchronize()
+                    idx = torch.tensor(keep, dtype=torch.long, device=sampled.device)
+                    nxt = ([ahead[i] for i in keep], sampled[idx].contiguous(),
+                           (host2[torch.tensor(keep, dtype=torch.long)].clone(), ev2))
+            pending = nxt
+        live[:] = [s for s in live if s.slot >= 0]
+
     # ---- the loop ---------------------------------------------------------------------
     def generate(self, prompts: list, max_tokens: int) -> list:
         for i, p in enumerate(prompts):
@@ -100,39 +207,13 @@ class Generator:
                 live.append(_Live(index=i, slot=self.engine.alloc_slot(), prompt_length=len(prompts[i]),
                                   history=list(prompts[i]) if uses_history else []))
             nxt += count
-            feed = [list(prompts[s.index]) for s in live]          # first step: whole prompts
+            lookahead = (not uses_history and hasattr(self.sampler, "sample")
+                         and getattr(self.engine, "can_feed_from_device", lambda: False)())
             try:
-                while live:
-                    logits = self.engine.step([s.slot for s in live], feed, "last", borrow=True)
-                    self.steps += 1
-                    sampled = self._to_host(self.sampler.sample(
-                        logits, [s.index for s in live], [len(s.tokens) for s in live],
-                        [s.history for s in live] if uses_history else None))
-                    if hasattr(self.engine, "check_device_status"):
-                        self.engine.check_device_status()
-                    if self.step_times is not None:
-                        self.step_times.append(time.perf_counter())
-                    still, feed = [], []
-                    for s, tok in zip(live, sampled):
-                        reason = None
-                        if tok in self.stop_ids:
-                            reason = "stop"                         # not emitted, not fed back
-                        else:
-                            s.tokens.append(tok)
-                            if uses_history:
-                                s.history.append(tok)
-                            if len(s.tokens) >= max_tokens:
-                                reason = "length"
-                            elif s.prompt_length + len(s.tokens) > self.engine.max_seq_len:
-                                reason = "length"                   # no position left to feed it at
-                        if reason is None:
-                            still.append(s)
-                            feed.append([tok])
-                        else:
-                            results[s.index] = GenerationResult(s.tokens, reason, s.prompt_length)
-                            self.engine.free_slot(s.slot)           # the slot is free for the next batch
-                            s.slot = -1
-                    live = still
+                if lookahead:
+                    self._run_batch_ahead(live, prompts, max_tokens, results)
+                else:
+                    self._run_batch(live, prompts, max_tokens, results, uses_history)
             finally:
                 for s in live:                                       # only on an exception
                     if s.slot >= 0:

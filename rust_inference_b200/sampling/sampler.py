@@ -16,6 +16,26 @@ class Sampler:
     def __init__(self, params: SamplerConfig, device):
         self.params = params
         self.device = torch.device(device)
+        self._pinned = [None] * 4         # staging buffers for the per-row arrays, taken in turn
+        self._events = [None] * 4
+        self._turn = 0
+
+    def _stage(self, meta: np.ndarray) -> torch.Tensor:
+        """The per-row int32 arrays to the device, through pinned memory (no blocking copy)."""
+        i = self._turn
+        self._turn = (i + 1) % len(self._pinned)
+        if self._events[i] is not None:
+            self._events[i].synchronize()
+        buf = self._pinned[i]
+        if buf is None or buf.numel() < meta.size:
+            buf = torch.empty(max(256, 2 * meta.size), dtype=torch.int32).pin_memory()
+            self._pinned[i] = buf
+        buf[:meta.size].copy_(torch.from_numpy(meta.reshape(-1)))
+        dev = buf[:meta.size].to(self.device, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._events[i] = ev
+        return dev
 
     def sample(self, logits: torch.Tensor, streams: list, counters: list, histories: list | None = None) -> torch.Tensor:
         """logits: float32 [R, V] on the device (overwritten).  Returns int32 [R] on the device."""
@@ -24,20 +44,21 @@ class Sampler:
         out = torch.empty(rows, dtype=torch.int32, device=self.device)
         recent = recent_count = None
         width = p.repetition_window if p.uses_history else 0
-        meta = np.zeros((rows, 2 + 1 + width), dtype=np.int32)
-        meta[:, 0] = streams
-        meta[:, 1] = counters
+        # layout: streams [R], counters [R], history lengths [R], histories [R, width]: each contiguous
+        meta = np.zeros(3 * rows + rows * width, dtype=np.int32)
+        meta[:rows] = streams
+        meta[rows:2 * rows] = counters
         if width:
+            hist = meta[3 * rows:].reshape(rows, width)
             for r, h in enumerate(histories):
                 tail = h[-width:]
-                meta[r, 2] = len(tail)
-                meta[r, 3:3 + len(tail)] = tail
-        dev = torch.from_numpy(meta).to(self.device, non_blocking=True)
-        row_stream = dev[:, 0].contiguous()
-        row_counter = dev[:, 1].contiguous()
+                meta[2 * rows + r] = len(tail)
+                hist[r, :len(tail)] = tail
+        dev = self._stage(meta)
+        row_stream, row_counter = dev[:rows], dev[rows:2 * rows]
         if width:
-            recent_count = dev[:, 2].contiguous()
-            recent = dev[:, 3:].contiguous()
+            recent_count = dev[2 * rows:3 * rows]
+            recent = dev[3 * rows:].view(rows, width)
         ops.sample(logits, out, temperature=p.temperature, top_k=p.top_k, top_p=p.top_p,
                    penalty=p.repetition_penalty, recent=recent, recent_count=recent_count, seed=p.seed,
                    row_stream=row_stream, row_counter=row_counter)
