@@ -4,8 +4,10 @@
 //
 // The product is computed transposed: the MMA's M dimension runs over 128 *features*
 // (rows of W, the A operand), its N dimension over TN *tokens* (rows of X, the B
-// operand), TN in {16, 32, 64, 128, 256}.  So a decode step with a handful of tokens still
-// fills the 128-row MMA with weights.  The SiLU-gate projection of steps of more than 128
+// operand), TN any multiple of 16 up to 256 (the kernel is compiled for 16, 32, 64, 128 and 256
+// and runs a narrower tile inside the next larger one).  So a decode step with a handful of tokens
+// still fills the 128-row MMA with weights, and a long step can take the tile width that leaves the
+// least idle tail in the last wave of its persistent grid.  The SiLU-gate projection of steps of more than 128
 // tokens takes the token-major kernel further down (128 tokens x 256 weight rows per tile).
 // Both operands are K-major, which is how the reference lays its matrices out
 // ([out, in] row-major, quant.rs:45-50) and how activations are packed.
@@ -51,9 +53,8 @@ constexpr int SMEM_BUDGET = 200 * 1024;
 enum Status { ST_OK = 0, ST_PRODUCER_TIMEOUT = 1, ST_MMA_TIMEOUT = 2, ST_EPILOGUE_TIMEOUT = 3, ST_DRAIN_TIMEOUT = 4 };
 
 // Instruction descriptor of kind::f16: D float32, A and B bf16, both K-major, M = 128, N = TN.
-template <int TN>
-__host__ __device__ constexpr uint32_t make_idesc() {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(BLOCK_F >> 4) << 24);
+__host__ __device__ constexpr uint32_t make_idesc(int tn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(tn >> 3) << 17) | ((uint32_t)(BLOCK_F >> 4) << 24);
 }
 
 // SiLU without a branch, for results that are rounded to bf16 right away: x / (1 + e^-x).  For very
@@ -88,12 +89,15 @@ template <int TN, bool DUAL, int MODE>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_w2,
                const __grid_constant__ CUtensorMap map_x, const float* __restrict__ bias, void* __restrict__ out_,
-               int n_tok, int n_feat, int K, int kb_per_split, int split_k, int stages, int* status) {
+               int n_tok, int n_feat, int K, int kb_per_split, int split_k, int stages, int tn, int* status) {
+    // TN is the widest token tile this instance holds (shared memory and tensor memory are laid out
+    // for it); tn <= TN, a multiple of 16, is the width it runs: the box of map_x has tn rows.
     constexpr int B_BYTES = TN * BLOCK_K * 2;
     constexpr int STAGE_BYTES = (DUAL ? 2 : 1) * A_BYTES + B_BYTES;
+    const uint32_t stage_tx = (uint32_t)((DUAL ? 2 : 1) * A_BYTES + tn * BLOCK_K * 2);   // bytes TMA brings per stage
     constexpr int ACC_COLS = DUAL ? 2 * TN : TN;               // columns of one accumulator buffer
     constexpr int TMEM_COLS = tmem_cols(2 * ACC_COLS);         // two buffers: epilogue of a tile overlaps the next main loop
-    constexpr uint32_t IDESC = make_idesc<TN>();
+    const uint32_t IDESC = make_idesc(tn);
 
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[MAX_STAGES];
@@ -108,7 +112,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
     // Tiles are numbered with the token tile fastest, so that CTAs running together share a weight
     // tile in L2; a CTA takes tiles blockIdx.x, blockIdx.x + gridDim.x, ...
-    const int n_tok_tiles = (n_tok + TN - 1) / TN, n_feat_tiles = (n_feat + BLOCK_F - 1) / BLOCK_F;
+    const int n_tok_tiles = (n_tok + tn - 1) / tn, n_feat_tiles = (n_feat + BLOCK_F - 1) / BLOCK_F;
     const int total_tiles = n_tok_tiles * n_feat_tiles * split_k;
     const int my_tiles = ((int)blockIdx.x < total_tiles) ? (total_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
 
@@ -134,6 +138,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
+    const uint32_t full0 = smem_u32(&full_bar[0]), empty0 = smem_u32(&empty_bar[0]);
     let_next_kernel_start();
 
     // coordinates of the CTA's i-th tile
@@ -142,7 +147,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const int tt = tile % n_tok_tiles, rest = tile / n_tok_tiles;
         const int ft = rest % n_feat_tiles, sp = rest / n_feat_tiles;
         f0 = ft * BLOCK_F;
-        t0 = tt * TN;
+        t0 = tt * tn;
         kb_begin = sp * kb_per_split;
         n_kb = min(total_kb, kb_begin + kb_per_split) - kb_begin;          // >= 1 by construction of the split
     };
@@ -150,12 +155,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
+            // One thread runs this loop once per k-block, and a lone thread issues a dependent
+            // instruction only every few cycles: the ring position and its parity are carried along
+            // instead of being divided out of a counter, so that an iteration stays well below the
+            // time the tensor core needs for a k-block.
             int it = 0;                      // k-blocks issued so far, over all of this CTA's tiles
+            int s = 0;                       // ring position of the next k-block
+            uint32_t ph = 0;                 // its pass through the ring, modulo 2
             bool waited = false;             // the activations come from the kernel before: wait once
             bool alive = true;
             for (int i = 0; i < my_tiles && alive; ++i) {
                 int f0, t0, kb_begin, n_kb;
                 tile_coords(i, f0, t0, kb_begin, n_kb);
+                if (abort_flag) break;
                 int kb = 0;
                 if (!waited) {
                     // The weights are written by no kernel, so their tiles for the first round of stages
@@ -165,7 +177,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         const uint32_t bar = smem_u32(&full_bar[j]);
                         const uint32_t stage = smem_base + (uint32_t)j * STAGE_BYTES;
                         const int kx = (kb_begin + j) * BLOCK_K;
-                        mbar_expect_tx(bar, STAGE_BYTES);
+                        mbar_expect_tx(bar, stage_tx);
                         tma_load_2d(stage, &map_w, bar, kx, f0);
                         if (DUAL) tma_load_2d(stage + A_BYTES, &map_w2, bar, kx, f0);
                     }
@@ -176,31 +188,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                                     smem_u32(&full_bar[j]), (kb_begin + j) * BLOCK_K, t0);
                     kb = ahead;
                     it = ahead;
+                    if (ahead == stages) ph = 1; else s = ahead;
                 }
-                for (; kb < n_kb; ++kb, ++it) {
-                    const int s = it % stages;
-                    const uint32_t ph = (uint32_t)(it / stages) & 1u;
-                    if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1u) || abort_flag) {
+                int kx = (kb_begin + kb) * BLOCK_K;
+                for (; kb < n_kb; ++kb, ++it, kx += BLOCK_K) {
+                    if (!mbar_wait(empty0 + 8u * s, ph ^ 1u)) {
                         if (!abort_flag) report(status, ST_PRODUCER_TIMEOUT);
                         abort_flag = 1;
                         alive = false;
                         break;
                     }
-                    const uint32_t bar = smem_u32(&full_bar[s]);
+                    const uint32_t bar = full0 + 8u * s;
                     const uint32_t stage = smem_base + (uint32_t)s * STAGE_BYTES;
-                    const int kx = (kb_begin + kb) * BLOCK_K;
-                    mbar_expect_tx(bar, STAGE_BYTES);
+                    mbar_expect_tx(bar, stage_tx);
                     tma_load_2d(stage, &map_w, bar, kx, f0);
                     if (DUAL) tma_load_2d(stage + A_BYTES, &map_w2, bar, kx, f0);
                     tma_load_2d(stage + (DUAL ? 2 : 1) * A_BYTES, &map_x, bar, kx, t0);
+                    if (++s == stages) { s = 0; ph ^= 1u; }
                 }
             }
             // Do not leave while a copy into this CTA's shared memory may still be in flight:
             // the last `stages` loads issued must have landed (immediate on the normal path).
             for (int j = max(0, it - stages); j < it; ++j) {
-                const int s = j % stages;
-                const uint32_t ph = (uint32_t)(j / stages) & 1u;
-                if (!mbar_wait(smem_u32(&full_bar[s]), ph)) {
+                if (!mbar_wait(full0 + 8u * (uint32_t)(j % stages), (uint32_t)(j / stages) & 1u)) {
                     report(status, ST_DRAIN_TIMEOUT);
                     break;
                 }
@@ -209,8 +219,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
-            int it = 0;
+            int s = 0;
+            uint32_t ph = 0;
             bool alive = true;
+            // descriptors of stage 0; a stage further on adds its byte offset / 16 to the address field
+            // (shared memory ends below 256 KiB, so the 14-bit field never carries)
+            const uint64_t desc_a0 = make_smem_desc(smem_base);
+            const uint64_t desc_b0 = make_smem_desc(smem_base + (DUAL ? 2 : 1) * A_BYTES);
             for (int i = 0; i < my_tiles && alive; ++i) {
                 int f0, t0, kb_begin, n_kb;
                 tile_coords(i, f0, t0, kb_begin, n_kb);
@@ -223,29 +238,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 }
                 tc_fence_after();
                 const uint32_t acc = tmem_base + (uint32_t)(buf * ACC_COLS);
-                for (int kb = 0; kb < n_kb; ++kb, ++it) {
-                    const int s = it % stages;
-                    const uint32_t ph = (uint32_t)(it / stages) & 1u;
-                    if (!mbar_wait(smem_u32(&full_bar[s]), ph)) {
+                for (int kb = 0; kb < n_kb; ++kb) {
+                    if (!mbar_wait(full0 + 8u * s, ph)) {
                         report(status, ST_MMA_TIMEOUT);
                         abort_flag = 1;
                         alive = false;
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t stage = smem_base + (uint32_t)s * STAGE_BYTES;
+                    const uint64_t off = (uint64_t)((uint32_t)s * (uint32_t)(STAGE_BYTES >> 4));
+                    const uint64_t a0 = desc_a0 + off, b0 = desc_b0 + off;
 #pragma unroll
                     for (int k = 0; k < BLOCK_K / 16; ++k) {
-                        // 16 bf16 = 32 bytes further along K inside the swizzled row
-                        const uint64_t a = make_smem_desc(stage + k * 32);
-                        const uint64_t b = make_smem_desc(stage + (DUAL ? 2 : 1) * A_BYTES + k * 32);
-                        umma(acc, a, b, IDESC, kb > 0 || k > 0);
-                        if (DUAL) {
-                            const uint64_t a2 = make_smem_desc(stage + A_BYTES + k * 32);
-                            umma(acc + TN, a2, b, IDESC, kb > 0 || k > 0);
-                        }
+                        // 16 bf16 = 32 bytes further along K inside the swizzled row: 2 in the address field
+                        umma(acc, a0 + 2 * k, b0 + 2 * k, IDESC, kb > 0 || k > 0);
+                        if (DUAL) umma(acc + TN, a0 + (A_BYTES >> 4) + 2 * k, b0 + 2 * k, IDESC, kb > 0 || k > 0);
                     }
-                    umma_commit(smem_u32(&empty_bar[s]));      // frees the stage once these MMAs have read it
+                    umma_commit(empty0 + 8u * s);              // frees the stage once these MMAs have read it
+                    if (++s == stages) { s = 0; ph ^= 1u; }
                 }
                 umma_commit(smem_u32(&acc_full[buf]));         // accumulator complete (or aborted: flag says which)
             }
@@ -270,7 +280,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             const float b = (bias != nullptr && f_ok) ? bias[f] : 0.f;
             const uint32_t trow = tmem_base + ((uint32_t)lane_base << 16) + (uint32_t)(buf * ACC_COLS);
 #pragma unroll 1
-            for (int c0 = 0; c0 < TN; c0 += 16) {
+            for (int c0 = 0; c0 < tn; c0 += 16) {
                 if (t0 + c0 >= n_tok) break;                   // uniform over the warp
                 uint32_t v[16], u[16];
                 tmem_ld16(trow + c0, v);
@@ -374,6 +384,7 @@ gemm_tm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
+    const uint32_t full0 = smem_u32(&full_bar[0]), empty0 = smem_u32(&empty_bar[0]);
     let_next_kernel_start();
 
     // token tiles vary fastest, so CTAs that run together share the weight rows in L2
@@ -389,13 +400,16 @@ gemm_tm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         else tma_load_2d(stage + X_BYTES + A_BYTES, &map_w, bar, kx, f0 + BLOCK_F);
     };
 
+
     if (warp == 0) {
         if (lane == 0) {
-            int it = 0;
+            int it = 0, s = 0;               // k-blocks issued; ring position and pass parity, carried along
+            uint32_t ph = 0;
             bool waited = false, alive = true;
             for (int i = 0; i < my_tiles && alive; ++i) {
                 int f0, t0;
                 tile_coords(i, f0, t0);
+                if (abort_flag) break;
                 int kb = 0;
                 if (!waited) {
                     const int ahead = min(stages, n_kb);
@@ -410,20 +424,21 @@ gemm_tm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         tma_load_2d(smem_base + (uint32_t)j * TM_STAGE_BYTES, &map_x, smem_u32(&full_bar[j]), j * BLOCK_K, t0);
                     kb = ahead;
                     it = ahead;
+                    if (ahead == stages) ph = 1; else s = ahead;
                 }
                 for (; kb < n_kb; ++kb, ++it) {
-                    const int s = it % stages;
-                    if (!mbar_wait(smem_u32(&empty_bar[s]), ((uint32_t)(it / stages) & 1u) ^ 1u) || abort_flag) {
+                    if (!mbar_wait(empty0 + 8u * s, ph ^ 1u)) {
                         if (!abort_flag) report(status, ST_PRODUCER_TIMEOUT);
                         abort_flag = 1;
                         alive = false;
                         break;
                     }
-                    const uint32_t bar = smem_u32(&full_bar[s]);
+                    const uint32_t bar = full0 + 8u * s;
                     const uint32_t stage = smem_base + (uint32_t)s * TM_STAGE_BYTES;
                     mbar_expect_tx(bar, TM_STAGE_BYTES);
                     load_w(stage, bar, kb * BLOCK_K, f0);
                     tma_load_2d(stage, &map_x, bar, kb * BLOCK_K, t0);
+                    if (++s == stages) { s = 0; ph ^= 1u; }
                 }
             }
             for (int j = max(0, it - stages); j < it; ++j)
@@ -434,8 +449,10 @@ gemm_tm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            int it = 0;
+            int s = 0;
+            uint32_t ph = 0;
             bool alive = true;
+            const uint64_t desc_x0 = make_smem_desc(smem_base), desc_w0 = make_smem_desc(smem_base + X_BYTES);
             for (int i = 0; i < my_tiles && alive; ++i) {
                 const int buf = i & 1;
                 if (!mbar_wait(smem_u32(&acc_empty[buf]), ((uint32_t)(i >> 1) & 1u) ^ 1u)) {
@@ -445,21 +462,20 @@ gemm_tm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 }
                 tc_fence_after();
                 const uint32_t acc = tmem_base + (uint32_t)(buf * TM_ROWS);
-                for (int kb = 0; kb < n_kb; ++kb, ++it) {
-                    const int s = it % stages;
-                    if (!mbar_wait(smem_u32(&full_bar[s]), (uint32_t)(it / stages) & 1u)) {
+                for (int kb = 0; kb < n_kb; ++kb) {
+                    if (!mbar_wait(full0 + 8u * s, ph)) {
                         report(status, ST_MMA_TIMEOUT);
                         abort_flag = 1;
                         alive = false;
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t stage = smem_base + (uint32_t)s * TM_STAGE_BYTES;
+                    const uint64_t off = (uint64_t)((uint32_t)s * (uint32_t)(TM_STAGE_BYTES >> 4));
 #pragma unroll
                     for (int k = 0; k < BLOCK_K / 16; ++k)
-                        umma(acc, make_smem_desc(stage + k * 32), make_smem_desc(stage + X_BYTES + k * 32), IDESC,
-                             kb > 0 || k > 0);
-                    umma_commit(smem_u32(&empty_bar[s]));
+                        umma(acc, desc_x0 + off + 2 * k, desc_w0 + off + 2 * k, IDESC, kb > 0 || k > 0);
+                    umma_commit(empty0 + 8u * s);
+                    if (++s == stages) { s = 0; ph ^= 1u; }
                 }
                 umma_commit(smem_u32(&acc_full[buf]));
             }
@@ -580,7 +596,7 @@ int sm_count() {
 int g_smem_budget = 0;       // 0: the default for the tile; set through ri_gemm_tcgen05_set_smem_budget
 
 template <int TN, bool DUAL, int MODE>
-int launch(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx, const float* bias, void* out,
+int launch(int tn, const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx, const float* bias, void* out,
            int n_tok, int n_feat, int K, int split_k, int* status, cudaStream_t stream) {
     constexpr int STAGE_BYTES = (DUAL ? 2 : 1) * A_BYTES + TN * BLOCK_K * 2;
     const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
@@ -604,7 +620,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx,
         if (e != cudaSuccess) return fail("gemm_tcgen05: cannot raise dynamic shared memory: %s", cudaGetErrorString(e));
         configured = true;
     }
-    const long long total_tiles = (long long)((n_tok + TN - 1) / TN) * ((n_feat + BLOCK_F - 1) / BLOCK_F) * split_k;
+    const long long total_tiles = (long long)((n_tok + tn - 1) / tn) * ((n_feat + BLOCK_F - 1) / BLOCK_F) * split_k;
     if (total_tiles > 0x7fffffffLL) return fail("gemm_tcgen05: %lld tiles exceed the index range", total_tiles);
     // a persistent grid: as many CTAs as fit the GPU at once (two per SM when the ring is small and
     // two accumulator buffers of each fit tensor memory), each walking its share of the tiles
@@ -614,7 +630,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx,
     if (ctas > total_tiles) ctas = total_tiles;
     dim3 grid((unsigned)ctas);
     cudaError_t e = launch_dependent(kernel, grid, dim3(THREADS), smem, stream, mw, mw2, mx, bias, out, n_tok, n_feat, K,
-                                     kb_per_split, split_k, stages, status);
+                                     kb_per_split, split_k, stages, tn, status);
     return check_launch(e, "gemm_tcgen05");
 }
 
@@ -645,16 +661,15 @@ int launch_tm(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& 
 template <bool DUAL, int MODE>
 int pick_tile(int tn, const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx, const float* bias,
               void* out, int n_tok, int n_feat, int K, int split_k, int* status, cudaStream_t stream) {
-    switch (tn) {
-        case 16: return launch<16, DUAL, MODE>(mw, mw2, mx, bias, out, n_tok, n_feat, K, split_k, status, stream);
-        case 32: return launch<32, DUAL, MODE>(mw, mw2, mx, bias, out, n_tok, n_feat, K, split_k, status, stream);
-        case 64: return launch<64, DUAL, MODE>(mw, mw2, mx, bias, out, n_tok, n_feat, K, split_k, status, stream);
-        case 128: return launch<128, DUAL, MODE>(mw, mw2, mx, bias, out, n_tok, n_feat, K, split_k, status, stream);
-        case 256:
-            if constexpr (!DUAL)
-                return launch<256, DUAL, MODE>(mw, mw2, mx, bias, out, n_tok, n_feat, K, split_k, status, stream);
-    }
-    return fail("gemm_tcgen05: no tile of %d tokens", tn);
+    // the narrowest compiled instance that holds a tile of tn tokens
+    if (tn < 16 || tn > 256 || tn % 16) return fail("gemm_tcgen05: no tile of %d tokens", tn);
+    if (tn <= 16) return launch<16, DUAL, MODE>(tn, mw, mw2, mx, bias, out, n_tok, n_feat, K, split_k, status, stream);
+    if (tn <= 32) return launch<32, DUAL, MODE>(tn, mw, mw2, mx, bias, out, n_tok, n_feat, K, split_k, status, stream);
+    if (tn <= 64) return launch<64, DUAL, MODE>(tn, mw, mw2, mx, bias, out, n_tok, n_feat, K, split_k, status, stream);
+    if (tn <= 128) return launch<128, DUAL, MODE>(tn, mw, mw2, mx, bias, out, n_tok, n_feat, K, split_k, status, stream);
+    if constexpr (!DUAL)
+        return launch<256, DUAL, MODE>(tn, mw, mw2, mx, bias, out, n_tok, n_feat, K, split_k, status, stream);
+    return fail("gemm_tcgen05: the SiLU-gate epilogue has no tile of %d tokens", tn);
 }
 
 }  // namespace
@@ -665,20 +680,45 @@ RI_API int ri_gemm_tcgen05_set_smem_budget(int bytes) {
     return 0;
 }
 
-// The token tile a call with n_tok tokens uses.
-RI_API int ri_gemm_tcgen05_tile(int n_tok, int dual) {
-    if (n_tok <= 16) return 16;
-    if (n_tok <= 32) return 32;
-    if (n_tok <= 64) return 64;
-    // beyond 128 tokens: the SiLU-gate projection takes the token-major kernel (128 tokens per tile),
-    // the others the feature-major kernel with 256 tokens per tile
-    if (n_tok <= 128 || dual) return 128;
-    return 256;
+int g_long_tile = 0;         // 0: pick by the grid; set through ri_gemm_tcgen05_set_long_tile
+
+// Token tile of steps of more than 128 tokens in the feature-major kernel: a multiple of 16 in
+// 128..256, or 0 to let the grid decide.  For tuning.
+RI_API int ri_gemm_tcgen05_set_long_tile(int tn) {
+    if (tn != 0 && (tn < 128 || tn > 256 || tn % 16)) return fail("gemm_tcgen05: no long tile of %d tokens", tn);
+    g_long_tile = tn;
+    return 0;
+}
+
+// The token tile (rows of the activation box) a call with n_tok tokens and n_feat features uses.
+RI_API int ri_gemm_tcgen05_tile(int n_tok, int n_feat, int dual) {
+    // up to 128 tokens: one token tile, as narrow as the step allows
+    if (n_tok <= 128) return n_tok <= 16 ? 16 : (n_tok + 15) / 16 * 16;
+    // beyond: the SiLU-gate projection takes the token-major kernel (128 tokens per tile) ...
+    if (dual) return 128;
+    if (g_long_tile) return g_long_tile;
+    // ... the others the feature-major kernel.  A tile costs time in proportion to its width, and
+    // the persistent grid runs ceil(tiles / CTAs) tiles deep: take the width of 128..256 tokens for
+    // which depth x width is least (3584 features at 2,048 tokens: 208, 1.9 waves of 208 instead of
+    // 1.5 -> 2 waves of 256).  Ties go to the wider tile.
+    const long long feat_tiles = (n_feat + BLOCK_F - 1) / BLOCK_F;
+    const long long ctas = sm_count();
+    int best = 256;
+    long long best_cost = -1;
+    for (int tn = 256; tn >= 128; tn -= 16) {
+        const long long tiles = (long long)((n_tok + tn - 1) / tn) * feat_tiles;
+        const long long cost = ((tiles + ctas - 1) / ctas) * tn;
+        if (best_cost < 0 || cost < best_cost) {
+            best_cost = cost;
+            best = tn;
+        }
+    }
+    return best;
 }
 
 // Encode the tensor map of a bf16 matrix [rows, K] (row-major, 16-byte aligned, K a multiple of 8)
 // into the 128 bytes at `map_out` (64-byte aligned).  box_rows is 128 for a weight matrix and the
-// token tile (ri_gemm_tcgen05_tile) for activations.  Maps only depend on pointer and shape, so the
+// token tile (ri_gemm_tcgen05_tile, for the same n_tok and n_feat as the product) for activations.  Maps only depend on pointer and shape, so the
 // caller keeps them: weights encode once, activation buffers once per shape.
 RI_API int ri_gemm_tcgen05_encode(void* map_out, const void* ptr, long long rows, long long K, int box_rows) {
     if ((uintptr_t)map_out % 64) return fail("gemm_tcgen05: tensor map storage must be 64-byte aligned");
@@ -698,7 +738,7 @@ RI_API int ri_gemm_tcgen05(const void* map_x, const void* map_w, const void* map
     if (mode == 2 && bias != nullptr) return fail("gemm_tcgen05: the residual epilogue takes no bias");
     if (mode != 2 && split_k > 1) return fail("gemm_tcgen05: only the residual epilogue can split K");
     const bool dual = mode == 3;
-    const int tn = ri_gemm_tcgen05_tile(n_tok, dual);
+    const int tn = ri_gemm_tcgen05_tile(n_tok, n_feat, dual);
     const CUtensorMap& mw = *reinterpret_cast<const CUtensorMap*>(map_w);
     const CUtensorMap& mw2 = dual ? *reinterpret_cast<const CUtensorMap*>(map_w2) : mw;
     const CUtensorMap& mx = *reinterpret_cast<const CUtensorMap*>(map_x);

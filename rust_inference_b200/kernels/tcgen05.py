@@ -1,11 +1,12 @@
 """Python face of the tcgen05 + TMA contraction kernel (bf16 operands, float32 accumulate)."""
 from __future__ import annotations
 
+import functools
 from ctypes import c_int, c_longlong, c_void_p
 
 import torch
 
-from . import ops
+from . import build, ops
 from .ops import KernelError, _call, _need, _need_cuda, _p, _stream
 
 N_SMS = 148
@@ -41,17 +42,20 @@ def supports(x: torch.Tensor, w) -> bool:
     return x.dtype == torch.bfloat16 and w.t.dtype == torch.bfloat16 and w.k % 8 == 0 and w.k >= 8
 
 
-def token_tile(n_tok: int, dual: bool) -> int:
-    """Rows of the activation tile: 16..256 tokens in the feature-major kernel; the SiLU-gate
-    projection of more than 128 tokens takes the token-major kernel, 128 tokens per tile."""
-    return 16 if n_tok <= 16 else 32 if n_tok <= 32 else 64 if n_tok <= 64 else 128 if (n_tok <= 128 or dual) else 256
+@functools.lru_cache(maxsize=4096)
+def token_tile(n_tok: int, n_feat: int, dual: bool) -> int:
+    """Rows of the activation tile, as the kernel library picks them: the step rounded up to 16
+    up to 128 tokens; beyond, 128 for the SiLU-gate projection (token-major kernel) and for the
+    others the width of 128..256 that leaves the least idle tail in the persistent grid."""
+    lib = build.load("gemm_tcgen05")
+    return int(lib.ri_gemm_tcgen05_tile(c_int(n_tok), c_int(n_feat), c_int(1 if dual else 0)))
 
 
 def pick_split(n_tok: int, n_feat: int, k: int, dual: bool) -> int:
     """K splits for the residual epilogue.  Small steps stream weights: measured in a replayed
     graph at 8 tokens, the o, q/k/v and down projections of a 3584-wide model are fastest with
     about two CTAs per SM (7-10 splits) and at least 4 k-blocks per split."""
-    tiles = -(-n_feat // 128) * -(-n_tok // token_tile(n_tok, dual))
+    tiles = -(-n_feat // 128) * -(-n_tok // token_tile(n_tok, n_feat, dual))
     kb = -(-k // 64)
     if tiles >= N_SMS:
         return 1
@@ -100,7 +104,7 @@ def gemm(x: torch.Tensor, w, out: torch.Tensor, mode: int, ctx=None, bias=None, 
         split_k = pick_split(m, n, k, w2 is not None) if mode == ops.EPI_RESIDUAL else 1
     if m == 0:
         return out
-    map_x = _x_map(x, token_tile(m, w2 is not None))
+    map_x = _x_map(x, token_tile(m, n, w2 is not None))
     st = status_word()
     _call("gemm_tcgen05", "ri_gemm_tcgen05", c_void_p(map_x.data_ptr()), c_void_p(weight_map(w).data_ptr()),
           c_void_p(map_w2.data_ptr() if map_w2 is not None else 0), _p(bias), _p(out), c_int(mode), c_int(m),

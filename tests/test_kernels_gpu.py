@@ -223,6 +223,33 @@ def test_gemm_tcgen05_all_epilogues(m, n, k):
     tcgen05.check_status()
 
 
+@pytest.mark.parametrize("m, n, k", [(2048, 3584, 256), (1111, 1000, 72), (257, 19 * 128, 64)])
+def test_gemm_tcgen05_token_tile_follows_the_grid(m, n, k):
+    """Long steps run the token tile of 128..256 rows that leaves the shortest tail in the persistent
+    grid (208 for 3584 features at 2,048 tokens); whatever width is picked, the product is the same."""
+    ops = _ops()
+    from rust_inference_b200.kernels import linear, tcgen05
+    tn = tcgen05.token_tile(m, n, False)
+    assert 128 <= tn <= 256 and tn % 16 == 0
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    cost = lambda t: -(-(-(-m // t) * -(-n // 128)) // sms) * t
+    assert cost(tn) == min(cost(t) for t in range(128, 257, 16))
+    if (m, n) == (2048, 3584) and sms == 148:
+        assert tn == 208
+    x = (torch.randn(m, k, device=DEV) * 0.5).bfloat16()
+    w = linear.Weight((torch.randn(n, k, device=DEV) * 0.1).bfloat16())
+    ref = x.double() @ w.t.double().t()
+    out32 = torch.full((m, n), 9.0, device=DEV)
+    tcgen05.gemm(x, w, out32, ops.EPI_STORE_F32)
+    assert (out32.double() - ref).abs().max().item() <= 1e-5 * ref.abs().max().item()
+    res = torch.randn(m, n, device=DEV)
+    before = res.clone()
+    tcgen05.gemm(x, w, res, ops.EPI_RESIDUAL)
+    assert (res.double() - (before + ref)).abs().max().item() <= 1e-5 * (ref.abs().max().item() + 4)
+    torch.cuda.synchronize()
+    tcgen05.check_status()
+
+
 def test_gemm_tcgen05_refuses_what_it_cannot_do():
     from rust_inference_b200.kernels import linear, ops, tcgen05
     x = torch.zeros(4, 100, device=DEV, dtype=torch.bfloat16)
