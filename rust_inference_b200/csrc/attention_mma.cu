@@ -14,7 +14,11 @@
 //                sequence are cut into `n_splits` runs of pages so that a small batch still
 //                fills the GPU; inside a CTA the 4 warps take 16 keys of each page each.
 //                Every split writes an un-normalised partial result and its (max, sum) to
-//                scratch memory; attn_combine merges them by log-sum-exp.
+//                scratch memory; attn_combine merges them by log-sum-exp.  With up to 8
+//                splits the CTAs of one (sequence, kv head) can instead form a thread-block
+//                cluster: each keeps its partial result in shared memory, and after a
+//                cluster barrier every CTA merges a slice of the outputs from its peers'
+//                shared memory and writes the final rows: no scratch, no second kernel.
 //  attn_prefill  any number of new tokens per sequence (whole prompts, or a continuation).
 //                A CTA serves 64 consecutive query tokens of one head; the warps take 16
 //                query rows each and walk the key pages up to the causal limit: the token
@@ -25,6 +29,8 @@
 // one convention.
 #include "tcgen05_common.cuh"
 #include "attention_decode_static.h"
+
+#include <cooperative_groups.h>
 
 using namespace ri;
 
@@ -150,7 +156,7 @@ __device__ __forceinline__ void softmax_update(float (*s)[4], float* m, float* l
 // ---------------------------------------------------------------------------------------------
 // decode: one token per sequence, split over runs of pages
 // ---------------------------------------------------------------------------------------------
-template <int HD>
+template <int HD, bool CLUSTER>
 __global__ void __launch_bounds__(THREADS)
 attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_ld, const __nv_bfloat16* __restrict__ kcache,
                    const __nv_bfloat16* __restrict__ vcache, const int* __restrict__ page_table, int max_pages,
@@ -166,10 +172,12 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_ld, const __nv_bfl
 
     const int b = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
     let_next_kernel_start();
-    wait_for_previous_kernels();          // q and the newest key and value come from the kernel before
+    // What the step fixed before its first kernel (lengths, slots, the page table) and the pages that
+    // hold only older positions are written by no kernel of this step: they are read, and the first
+    // page's copy is started, while the kernel before this one still runs.
     const int n_rep = n_heads / n_kv_heads;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
-    const int n_keys = seq_len[b];                       // the new token's key is in the cache already
+    const int n_keys = seq_len[b];                       // counts the new token, whose key is in the cache by then
     const int token = cu_seqlens[b];
     const int first_key = (window > 0 && n_keys - window > 0) ? n_keys - window : 0;
     const int* pages = page_table + (size_t)seq_slot[b] * max_pages;
@@ -178,6 +186,16 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_ld, const __nv_bfl
     const int per = (pg_hi - pg_lo + n_splits - 1) / n_splits;
     const int pg_begin = pg_lo + split * per, pg_end = min(pg_hi, pg_begin + per);
 
+    auto issue = [&](int pg, int buf) {
+        const size_t base = ((size_t)pages[pg] * n_kv_heads + kvh) * PAGE * HD;
+        load_tile_async<HD>(kv_base + (2 * buf) * TILE, kcache + base, PAGE);
+        load_tile_async<HD>(kv_base + (2 * buf + 1) * TILE, vcache + base, PAGE);
+        cp_async_commit();
+    };
+    // the page of the new token (the sequence's last) is still being written by the kernel before
+    const bool early = pg_begin < pg_end && pg_begin != pg_hi - 1;
+    if (early) issue(pg_begin, 0);
+    wait_for_previous_kernels();          // q and the newest key and value come from the kernel before
     // Q rows: head kvh*n_rep + r for r < n_rep, zero above
     for (int idx = threadIdx.x; idx < 16 * (HD / 8); idx += THREADS) {
         const int r = idx / (HD / 8), c = idx % (HD / 8);
@@ -185,13 +203,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_ld, const __nv_bfl
         if (r < n_rep) v = *reinterpret_cast<const uint4*>(q + (size_t)token * q_ld + (size_t)(kvh * n_rep + r) * HD + c * 8);
         *reinterpret_cast<uint4*>(smem + 4 * TILE + tile_off<HD>(r, c)) = v;
     }
-    auto issue = [&](int pg, int buf) {
-        const size_t base = ((size_t)pages[pg] * n_kv_heads + kvh) * PAGE * HD;
-        load_tile_async<HD>(kv_base + (2 * buf) * TILE, kcache + base, PAGE);
-        load_tile_async<HD>(kv_base + (2 * buf + 1) * TILE, vcache + base, PAGE);
-        cp_async_commit();
-    };
-    if (pg_begin < pg_end) issue(pg_begin, 0);
+    if (pg_begin < pg_end && !early) issue(pg_begin, 0);
     __syncthreads();                                      // Q tile written
 
     uint32_t qf[HD / 16][4];
@@ -255,6 +267,9 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_ld, const __nv_bfl
         sml[((warp * 16 + g + 8) << 1) + 1] = l[1];
     }
     __syncthreads();
+    // the CTA's merged partial result for the cluster: [n_rep][HD] and [n_rep][2], behind the warps' areas
+    float* fo = sml + 4 * 16 * 2;
+    float* fml = fo + 16 * HD;
     for (int idx = threadIdx.x; idx < n_rep * HD; idx += THREADS) {
         const int r = idx / HD, d = idx % HD;
         float M = -INFINITY;
@@ -270,7 +285,13 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_ld, const __nv_bfl
             }
         }
         const int h = kvh * n_rep + r;
-        if (n_splits == 1) {
+        if (CLUSTER) {
+            fo[idx] = acc;
+            if (d == 0) {
+                fml[2 * r] = M;
+                fml[2 * r + 1] = L;
+            }
+        } else if (n_splits == 1) {
             out[(size_t)token * out_ld + (size_t)h * HD + d] = __float2bfloat16_rn(acc / L);
         } else {
             const size_t row = ((size_t)b * n_heads + h) * n_splits + split;
@@ -280,6 +301,34 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_ld, const __nv_bfl
                 part_ml[row * 2 + 1] = L;
             }
         }
+    }
+    if (CLUSTER) {
+        // The splits of this (sequence, kv head) are the CTAs of one cluster (its z extent).  After the
+        // barrier each merges its slice of the n_rep * HD outputs over all peers by log-sum-exp, reading
+        // their partial results through distributed shared memory, and writes the final rows.
+        namespace cg = cooperative_groups;
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync();
+        const int total = n_rep * HD;
+        const int chunk = (total + n_splits - 1) / n_splits;
+        const int lo = split * chunk, hi = min(total, lo + chunk);
+        for (int idx = lo + (int)threadIdx.x; idx < hi; idx += THREADS) {
+            const int r = idx / HD, d = idx % HD;
+            float M = -INFINITY;
+            for (int sp = 0; sp < n_splits; ++sp) M = fmaxf(M, cluster.map_shared_rank(fml, sp)[2 * r]);
+            float L = 0.f, acc = 0.f;
+            for (int sp = 0; sp < n_splits; ++sp) {
+                const float* pml = cluster.map_shared_rank(fml, sp);
+                const float ms = pml[2 * r];
+                if (ms != -INFINITY) {
+                    const float f = expf(ms - M);
+                    L += f * pml[2 * r + 1];
+                    acc += f * cluster.map_shared_rank(fo, sp)[idx];
+                }
+            }
+            out[(size_t)token * out_ld + (size_t)(kvh * n_rep + r) * HD + d] = __float2bfloat16_rn(acc / L);
+        }
+        cluster.sync();                                   // nobody leaves while a peer may still read its shared memory
     }
 }
 
@@ -642,13 +691,13 @@ int launch_decode(const void* q, int q_ld, const void* kc, const void* vc, const
     static_assert(4 * 16 * HD * 4 + 4 * 16 * 2 * 4 <= SMEM, "merge area must fit");
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) return fail("attention: cannot raise dynamic shared memory: %s", cudaGetErrorString(e));
         configured = true;
     }
     dim3 grid(n_seqs, n_kv_heads, n_splits);
     cudaError_t e = launch_dependent(
-        attn_decode_kernel<HD>, grid, dim3(THREADS), (size_t)SMEM, stream, (const __nv_bfloat16*)q, q_ld,
+        attn_decode_kernel<HD, false>, grid, dim3(THREADS), (size_t)SMEM, stream, (const __nv_bfloat16*)q, q_ld,
         (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, page_table, max_pages, seq_slot, seq_len, cu_seqlens,
         n_heads, n_kv_heads, scale, window, n_splits, part_o, part_ml, (__nv_bfloat16*)out, out_ld);
     if (int rc = check_launch(e, "attn_decode")) return rc;
@@ -659,6 +708,44 @@ int launch_decode(const void* q, int q_ld, const void* kc, const void* vc, const
         return check_launch(e, "attn_combine");
     }
     return 0;
+}
+
+// The splits of a (sequence, kv head) as one thread-block cluster that merges its own partial results.
+constexpr int MAX_CLUSTER_SPLITS = 8;                          // the portable cluster size
+
+template <int HD>
+int launch_decode_cluster(const void* q, int q_ld, const void* kc, const void* vc, const int* page_table, int max_pages,
+                          const int* seq_slot, const int* seq_len, const int* cu_seqlens, int n_seqs, int n_heads,
+                          int n_kv_heads, float scale, int window, int n_splits, void* out, int out_ld,
+                          cudaStream_t stream) {
+    constexpr int SMEM = 4 * PAGE * HD * 2 + 16 * HD * 2;
+    static_assert((4 * 16 * HD + 4 * 16 * 2 + 16 * HD + 16 * 2) * 4 <= SMEM, "merge areas must fit");
+    auto kernel = attn_decode_kernel<HD, true>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e != cudaSuccess) return fail("attention: cannot raise dynamic shared memory: %s", cudaGetErrorString(e));
+        configured = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(n_seqs, n_kv_heads, n_splits);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = SMEM;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = (unsigned)n_splits;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, (const __nv_bfloat16*)q, q_ld, (const __nv_bfloat16*)kc,
+                                       (const __nv_bfloat16*)vc, page_table, max_pages, seq_slot, seq_len, cu_seqlens,
+                                       n_heads, n_kv_heads, scale, window, n_splits, (float*)nullptr, (float*)nullptr,
+                                       (__nv_bfloat16*)out, out_ld);
+    return check_launch(e, "attn_decode (cluster)");
 }
 
 template <int HD>
@@ -747,6 +834,27 @@ RI_API int ri_attention_decode(const void* q, int q_ld, const void* kcache, cons
                                  n_heads, n_kv_heads, scale, window, n_splits, part_o, part_ml, out, out_ld, stream);
     return launch_decode<128>(q, q_ld, kcache, vcache, page_table, max_pages, seq_slot, seq_len, cu_seqlens, n_seqs,
                               n_heads, n_kv_heads, scale, window, n_splits, part_o, part_ml, out, out_ld, stream);
+}
+
+// The same with the splits of a (sequence, kv head) as one thread-block cluster, 2 <= n_splits <= 8: the
+// partial results are merged through distributed shared memory inside the kernel, so there is no
+// scratch and no second kernel.
+RI_API int ri_attention_decode_cluster(const void* q, int q_ld, const void* kcache, const void* vcache,
+                                       const int* page_table, int max_pages, const int* seq_slot, const int* seq_len,
+                                       const int* cu_seqlens, void* out, int out_ld, int n_seqs, int n_heads,
+                                       int n_kv_heads, int hd, int page_size, float scale, int window, int n_splits,
+                                       cudaStream_t stream) {
+    if (n_seqs <= 0) return 0;
+    if (int rc = check_common(hd, page_size, n_heads, n_kv_heads, q_ld, out_ld, q, out)) return rc;
+    if (n_heads / n_kv_heads > 16) return fail("attention_decode: %d query heads per kv head exceed 16", n_heads / n_kv_heads);
+    if (n_splits < 2 || n_splits > MAX_CLUSTER_SPLITS)
+        return fail("attention_decode: a cluster takes 2 to %d splits, not %d", MAX_CLUSTER_SPLITS, n_splits);
+    if (n_kv_heads > 65535) return fail("attention_decode: %d kv heads exceed the grid limit", n_kv_heads);
+    if (hd == 64)
+        return launch_decode_cluster<64>(q, q_ld, kcache, vcache, page_table, max_pages, seq_slot, seq_len, cu_seqlens,
+                                         n_seqs, n_heads, n_kv_heads, scale, window, n_splits, out, out_ld, stream);
+    return launch_decode_cluster<128>(q, q_ld, kcache, vcache, page_table, max_pages, seq_slot, seq_len, cu_seqlens,
+                                      n_seqs, n_heads, n_kv_heads, scale, window, n_splits, out, out_ld, stream);
 }
 
 // The same with the cache pages brought in by TMA.  map_k / map_v: tensor maps (128 bytes each) of the

@@ -253,7 +253,8 @@ __global__ void rope_cache_write_acc_kernel(float* __restrict__ acc, int ld, con
     const int n_pairs = (n_heads + n_kv_heads) * half;
     float* row = acc + (size_t)t * ld;
     let_next_kernel_start();
-    wait_for_previous_kernels();          // the projections come from the previous kernel
+    // Positions, slots, the page table, the angle tables and the bias are written by no kernel of the
+    // step: they are read (for the first round of items) while the projection before this still runs.
     const int pos = token_pos[t];
     const float* c = cos_t + (size_t)pos * half;
     const float* s = sin_t + (size_t)pos * half;
@@ -265,10 +266,9 @@ __global__ void rope_cache_write_acc_kernel(float* __restrict__ acc, int ld, con
     }
     const size_t head_stride = (size_t)page_size * hd;
 
-    // rotary pairs of the q heads and then the k heads (same column order in the accumulator)
-    for (int base = threadIdx.x; base < n_pairs; base += PER * blockDim.x) {
-        float x0[PER], x1[PER], cs[PER], sn[PER];
-        int c0[PER], c1[PER];
+    float cs[PER], sn[PER], b0[PER], b1[PER];
+    int c0[PER], c1[PER];
+    auto constants = [&](int base) {
 #pragma unroll
         for (int j = 0; j < PER; ++j) {
             const int idx = base + j * blockDim.x;
@@ -276,11 +276,26 @@ __global__ void rope_cache_write_acc_kernel(float* __restrict__ acc, int ld, con
                 const int h = idx / half, i = idx % half;
                 c0[j] = h * hd + (style == 0 ? i : 2 * i);
                 c1[j] = h * hd + (style == 0 ? i + half : 2 * i + 1);
-                x0[j] = row[c0[j]];
-                x1[j] = row[c1[j]];
-                if (bias) { x0[j] += bias[c0[j]]; x1[j] += bias[c1[j]]; }
+                b0[j] = bias ? bias[c0[j]] : 0.f;
+                b1[j] = bias ? bias[c1[j]] : 0.f;
                 cs[j] = c[i];
                 sn[j] = s[i];
+            }
+        }
+    };
+    constants(threadIdx.x);
+    wait_for_previous_kernels();          // the projections come from the previous kernel
+
+    // rotary pairs of the q heads and then the k heads (same column order in the accumulator)
+    for (int base = threadIdx.x; base < n_pairs; base += PER * blockDim.x) {
+        if (base != (int)threadIdx.x) constants(base);
+        float x0[PER], x1[PER];
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+            const int idx = base + j * blockDim.x;
+            if (idx < n_pairs) {
+                x0[j] = row[c0[j]] + b0[j];
+                x1[j] = row[c1[j]] + b1[j];
             }
         }
 #pragma unroll

@@ -17,17 +17,49 @@ from . import ops
 N_SMS = 148
 # RI_B200_PREFILL_ATTENTION=mma keeps the mma.sync prefill kernel (for comparisons)
 _PREFILL = os.environ.get("RI_B200_PREFILL_ATTENTION", "tcgen05")
-# RI_B200_DECODE_ATTENTION=cp_async / tma forces one of the two decode kernels (default: by batch size)
+# RI_B200_DECODE_ATTENTION=cluster / cp_async / tma forces one of the decode kernels (default: by batch size)
 _DECODE = os.environ.get("RI_B200_DECODE_ATTENTION", "auto")
+CLUSTER_SPLITS = 8     # a thread-block cluster holds at most 8 CTAs portably
 
 
-def decode_splits(n_seqs: int, n_kv_heads: int, max_seq_len: int, page_size: int) -> int:
+def decode_splits(n_seqs: int, n_kv_heads: int, max_seq_len: int, page_size: int, limit: int = 32) -> int:
     """Runs of pages per (sequence, kv head): as many CTAs as are resident at once (two per SM),
     never more, so the grid is one wave; never more runs than the longest sequence has pages.
     Depends on the batch size and the cache geometry only, so a captured step keeps its grid."""
     pairs = max(1, n_seqs * n_kv_heads)
     want = (2 * N_SMS) // pairs
-    return max(1, min(want, 32, -(-max_seq_len // page_size)))
+    if os.environ.get("RI_B200_DECODE_SPLITS"):
+        want = int(os.environ["RI_B200_DECODE_SPLITS"])
+    return max(1, min(want, limit, -(-max_seq_len // page_size)))
+
+
+def decode_plan(n_seqs: int, n_kv_heads: int, max_seq_len: int, page_size: int):
+    """Which decode kernel a step of n_seqs sequences takes, and into how many runs of pages it
+    cuts a sequence: ("cluster" | "tma" | "cp_async", splits).
+
+    Split runs are merged inside the kernel when the splits of a (sequence, kv head) fit a
+    thread-block cluster: no scratch round trip and no second kernel.  Large batches are not
+    split and stream many pages per CTA: there the TMA ring keeps more of them in flight (batch
+    64, 1,024 positions: 26.7 us against 40.9 us with cp.async)."""
+    if _DECODE in ("auto", "cluster"):
+        splits = decode_splits(n_seqs, n_kv_heads, max_seq_len, page_size, CLUSTER_SPLITS)
+        # measured at 1,024 positions: 8 sequences 10.4 us against 11.5 us with the merge kernel,
+        # 16 the same, 32 (two splits) 19.8 against 17.4
+        if splits >= (3 if _DECODE == "auto" else 2):
+            return "cluster", splits
+    splits = decode_splits(n_seqs, n_kv_heads, max_seq_len, page_size)
+    if _DECODE == "tma" or (_DECODE in ("auto", "cluster") and splits == 1):
+        return "tma", splits
+    return "cp_async", splits
+
+
+def decode_kernel(name: str):
+    if name == "cluster":
+        return ops.attention_decode_cluster
+    if name == "tma":
+        from . import attention_tc
+        return attention_tc.decode
+    return ops.attention_decode
 
 
 def attention(qkv, cache_layer, out, ctx, *, n_heads, n_kv_heads, head_dim, scale, window=0):
@@ -39,18 +71,12 @@ def attention(qkv, cache_layer, out, ctx, *, n_heads, n_kv_heads, head_dim, scal
         if ops.attention_mma_supports(head_dim, ctx.page_size, n_heads, n_kv_heads, decode):
             if decode:
                 max_len = ctx.page_table.shape[1] * ctx.page_size
-                splits = decode_splits(ctx.n_seqs, n_kv_heads, max_len, ctx.page_size)
+                name, splits = decode_plan(ctx.n_seqs, n_kv_heads, max_len, ctx.page_size)
                 part_o = part_ml = None
-                if splits > 1:
+                if splits > 1 and name != "cluster":
                     part_o = ctx.buffer("attn_part_o", (ctx.n_seqs * n_heads * splits * head_dim,), torch.float32)
                     part_ml = ctx.buffer("attn_part_ml", (ctx.n_seqs * n_heads * splits * 2,), torch.float32)
-                from . import attention_tc
-                # Large batches stream many pages per CTA: the TMA ring keeps more of them in flight
-                # (batch 64, 1,024 positions: 26.7 us against 40.9 us).  Small batches are cut into
-                # short runs that are latency bound, where the cp.async kernel is about 1 us quicker.
-                use_tma = _DECODE == "tma" or (_DECODE == "auto" and splits == 1)
-                decode_fn = attention_tc.decode if use_tma else ops.attention_decode
-                return decode_fn(
+                return decode_kernel(name)(
                     qkv, q_ld, cache_layer.k, cache_layer.v, ctx.page_table, ctx.seq_slot, ctx.seq_len,
                     ctx.cu_seqlens, out, n_seqs=ctx.n_seqs, n_heads=n_heads, n_kv_heads=n_kv_heads,
                     head_dim=head_dim, page_size=ctx.page_size, scale=scale, window=window, n_splits=splits,

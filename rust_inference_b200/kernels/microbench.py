@@ -105,13 +105,11 @@ def run(kernel: str, model: dict, tokens: int, context: int = 1024, eager_only: 
         o = torch.empty(t_total, qd, device=dev, dtype=bf)
         scale = 1.0 / math.sqrt(hd)
         if kernel == "attn_decode":
-            splits = attn.decode_splits(n_seqs, nkv, pages_per * page, page)
+            name, splits = attn.decode_plan(n_seqs, nkv, pages_per * page, page)
             po = torch.empty(n_seqs * nh * splits * hd, device=dev)
             pml = torch.empty(n_seqs * nh * splits * 2, device=dev)
-
-            from . import attention_tc
-            use_tma = attn._DECODE == "tma" or (attn._DECODE == "auto" and splits == 1)
-            decode_fn = attention_tc.decode if use_tma else ops.attention_decode
+            decode_fn = attn.decode_kernel(name)
+            out["decode_kernel"] = name
 
             def fn():
                 for i in range(c):
