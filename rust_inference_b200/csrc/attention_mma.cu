@@ -407,7 +407,9 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     }
     __syncthreads();
     let_next_kernel_start();
-    wait_for_previous_kernels();          // q and the newest key and value come from the kernel before
+    // Lengths, slots and the page table were fixed before the step's first kernel, and pages that hold
+    // only older positions are written by no kernel of this step: the producer starts on them while
+    // the kernel before this one still runs.  q and the sequence's last page wait for it.
     const int n_keys = seq_len[b];
     const int token = cu_seqlens[b];
     const int first_key = (window > 0 && n_keys - window > 0) ? n_keys - window : 0;
@@ -427,6 +429,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             int issued = 0;
             for (int pg = pg_begin; pg < pg_end; ++pg) {
                 const int j = pg - pg_begin, s = j % RING;
+                if (pg == pg_hi - 1) wait_for_previous_kernels();      // the page the new key and value went to
                 if (!tc::mbar_wait(smem_u32(&empty_bar[s]), (uint32_t)((j / RING) & 1) ^ 1u) || abort_flag) {
                     tc::report(status, 21);
                     abort_flag = 1;
@@ -448,6 +451,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         }
     } else {
         // ---------------- compute: warp w takes keys 16w .. 16w+15 of every page ----------------
+        wait_for_previous_kernels();          // q comes from the kernel before
         for (int idx = threadIdx.x; idx < 16 * (HD / 8); idx += 128) {
             const int r = idx / (HD / 8), c = idx % (HD / 8);
             uint4 v = make_uint4(0, 0, 0, 0);
