@@ -38,6 +38,17 @@ class Model:
         return cls(Engine.from_random(config, seed=seed, std=std, dtype=dtype, device=device,
                                       max_tokens=max_tokens_in_cache, max_seq_len=max_seq_len, n_slots=n_slots))
 
+    def logits(self, tokens, want="all"):
+        """float32 logits [wanted, vocab] of one list of token ids run whole, as one step of the
+        engine (the reference computes them for every position, transformer.rs:89-97).  `want`:
+        "all", "last", or a list of positions among the tokens.  The sequence's slot is given
+        back afterwards."""
+        slot = self.engine.alloc_slot()
+        try:
+            return self.engine.step([slot], [list(tokens)], want if isinstance(want, str) else [list(want)])
+        finally:
+            self.engine.free_slot(slot)
+
     def generate(self, prompts, max_tokens: int = 512, sampler_config: SamplerConfig | None = None,
                  stop_ids=None, max_batch: int | None = None, record_step_times: bool = False) -> list:
         """prompts: a list of token-id lists (or one list of ints).  Returns one
