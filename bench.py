@@ -215,8 +215,10 @@ def main() -> int:
     e2e_tok_s = args.batch * steps / e2e_s
     from rust_inference_b200.engine.context import pack_step
     step_arrays = pack_step([0] * args.batch, [[0]] * args.batch, [[0]] * args.batch)[0]
-    h2d_per_step = step_arrays.nbytes + args.batch * 3 * 4      # the step's arrays + the sampler's rows
-    d2h_per_step = args.batch * 4                               # the sampled tokens
+    # every decode step copies its arrays from pinned memory; the sampler's rows (stream, counter) go
+    # up once per batch and stay on the device while the same sequences advance together
+    h2d_per_step = step_arrays.nbytes
+    d2h_per_step = args.batch * 4                               # the sampled tokens, written to pinned host memory by the kernel
     assert all(len(r.tokens) == warmup + steps + 1 for r in results)
 
     # ---- prefill of 2,048 tokens ----

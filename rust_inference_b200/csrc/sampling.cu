@@ -61,11 +61,21 @@ __device__ __forceinline__ int block_sum_int(int v, int* scratch) {
     return scratch[32];
 }
 
+// The row's token, to the device array and, if given, to a second place as well: memory of the host
+// that the device can write, so that the host can read the token without a copy of its own.
+__device__ __forceinline__ void store_token(int* out, int* mirror, int r, int token) {
+    out[r] = token;
+    if (mirror != nullptr) {
+        *reinterpret_cast<volatile int*>(mirror + r) = token;
+        __threadfence_system();
+    }
+}
+
 __global__ void __launch_bounds__(THREADS)
 sample_kernel(float* __restrict__ logits, int vocab, int* __restrict__ out, float temperature, int top_k,
               float top_p, float penalty, const int* __restrict__ recent, int recent_ld,
               const int* __restrict__ recent_count, unsigned long long seed, const int* __restrict__ row_stream,
-              const int* __restrict__ row_counter) {
+              const int* __restrict__ row_counter, int counter_offset, int* __restrict__ mirror) {
     __shared__ float fscratch[33];
     __shared__ int iscratch[33];
     __shared__ float chunk_sum[THREADS];
@@ -111,7 +121,7 @@ sample_kernel(float* __restrict__ logits, int vocab, int* __restrict__ out, floa
             int t = iscratch[tid];
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) t = min(t, __shfl_xor_sync(0xffffffffu, t, o));
-            if (tid == 0) out[r] = (t == 0x7fffffff) ? 0 : t;
+            if (tid == 0) store_token(out, mirror, r, (t == 0x7fffffff) ? 0 : t);
         }
         return;
     }
@@ -222,7 +232,7 @@ sample_kernel(float* __restrict__ logits, int vocab, int* __restrict__ out, floa
     }
 
     // ---- draw (sampler.rs:199-210): first i whose running sum reaches u ----
-    const float u = uniform_open_closed(seed, (unsigned)row_stream[r], (unsigned)row_counter[r]);
+    const float u = uniform_open_closed(seed, (unsigned)row_stream[r], (unsigned)(row_counter[r] + counter_offset));
     float mine = 0.f;
     int last_pos = -1;
     for (int i = lo; i < hi; ++i) {
@@ -252,7 +262,7 @@ sample_kernel(float* __restrict__ logits, int vocab, int* __restrict__ out, floa
     if (owner < 0) {
         // rounding left the total just below u: the last id that has probability (the
         // reference falls back to the last id of the vocabulary, sampler.rs:208-209)
-        if (tid == 0) out[r] = iscratch[1] >= 0 ? iscratch[1] : vocab - 1;
+        if (tid == 0) store_token(out, mirror, r, iscratch[1] >= 0 ? iscratch[1] : vocab - 1);
         return;
     }
     if (tid == owner) {
@@ -262,7 +272,7 @@ sample_kernel(float* __restrict__ logits, int vocab, int* __restrict__ out, floa
             run += p[i];
             if (run >= u && p[i] > 0.f) { tok = i; break; }
         }
-        out[r] = tok;
+        store_token(out, mirror, r, tok);
     }
 }
 
@@ -270,18 +280,30 @@ sample_kernel(float* __restrict__ logits, int vocab, int* __restrict__ out, floa
 
 // logits: float32 [rows, vocab], overwritten.  out: int32 [rows].
 // recent (may be null): int32 [rows, recent_ld] with recent_count[r] valid ids per row, oldest first.
-// row_stream / row_counter: int32 [rows], which sequence a row is and how many tokens it has drawn.
+// row_stream / row_counter: int32 [rows], which sequence a row is and how many tokens it has drawn;
+// counter_offset is added to every row's counter (rows that advance together keep their array).
+// mirror (may be null): int32 [rows] in host memory the device can write; receives the tokens too.
 RI_API int ri_sample(float* logits, int rows, int vocab, int* out, float temperature, int top_k, float top_p,
                      float penalty, const int* recent, int recent_ld, const int* recent_count,
-                     unsigned long long seed, const int* row_stream, const int* row_counter, cudaStream_t stream) {
+                     unsigned long long seed, const int* row_stream, const int* row_counter, int counter_offset,
+                     int* mirror, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (vocab <= 0) return fail("sample: vocabulary of %d", vocab);
     if (penalty <= 0.f) return fail("sample: repetition penalty %f must be positive", penalty);
     if (temperature > 0.f && (row_stream == nullptr || row_counter == nullptr))
         return fail("sample: temperature sampling needs row streams and counters");
+    if (mirror != nullptr) {
+        // the kernel stores through this pointer: it must be host memory that the device reaches under the same address
+        cudaPointerAttributes attr;
+        if (cudaPointerGetAttributes(&attr, mirror) != cudaSuccess || attr.type != cudaMemoryTypeHost ||
+            attr.devicePointer != (void*)mirror) {
+            cudaGetLastError();
+            return fail("sample: the mirror is not pinned host memory that the device can write");
+        }
+    }
     cudaError_t e = launch_dependent(sample_kernel, dim3(rows), dim3(THREADS), (size_t)0, stream, logits, vocab, out,
                                      temperature, top_k, top_p, penalty, recent, recent_ld, recent_count, seed,
-                                     row_stream, row_counter);
+                                     row_stream, row_counter, counter_offset, mirror);
     return check_launch(e, "sample");
 }
 

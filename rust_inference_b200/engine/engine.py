@@ -214,6 +214,16 @@ class Engine:
         device tensor (`step_from_device`)."""
         return self.use_graphs
 
+    def decode_token_buffer(self, n: int) -> torch.Tensor:
+        """The int32 [n] device buffer from which the captured decode step of n sequences reads its
+        tokens: a sampler that writes there feeds `step_from_device` without a copy."""
+        from .graphs import DecodeGraph
+        with torch.cuda.device(self.device):
+            graph = self._graphs.get(n)
+            if graph is None:
+                graph = self._graphs[n] = DecodeGraph(self, n)
+        return graph.ctx.token_ids
+
     def step_from_device(self, slots: list, tokens_dev: torch.Tensor):
         """One decode step whose tokens (one per sequence, int32 [B]) are already on the device,
         for instance straight from the sampler: no host round trip between sampling and the next
@@ -228,7 +238,8 @@ class Engine:
             if graph is None:
                 graph = self._graphs[n] = DecodeGraph(self, n)
             graph.load_meta(dev, keep_tokens=True)
-            graph.ctx.token_ids.copy_(tokens_dev, non_blocking=True)
+            if tokens_dev.data_ptr() != graph.ctx.token_ids.data_ptr():       # else they are in place already
+                graph.ctx.token_ids.copy_(tokens_dev, non_blocking=True)
             logits = graph.launch()
         for s in slots:
             self.cache.commit(s, self.cache.length(s) + 1)

@@ -133,23 +133,26 @@ class Generator:
         import torch
         eng = self.engine
 
-        # a few pinned buffers, taken in turn: at most two copies are outstanding at any time
+        # A few pinned buffers, taken in turn (at most two are awaited at any time).  The sampling
+        # kernel writes its tokens there as well as to the device, so the host needs no copy: it waits
+        # for the event recorded behind the kernel.
         ring = [torch.empty(len(live), dtype=torch.int32).pin_memory() for _ in range(4)]
         turn = [0]
 
-        def read_later(tokens_dev):
-            host = ring[turn[0] % len(ring)][:tokens_dev.numel()]
+        def sample(logits, seqs, drawn):
+            host = ring[turn[0] % len(ring)][:len(seqs)]
             turn[0] += 1
-            host.copy_(tokens_dev, non_blocking=True)
+            # straight into the buffer the next step of this batch size reads its tokens from
+            out = eng.decode_token_buffer(len(seqs)) if hasattr(eng, "decode_token_buffer") else None
+            tokens_dev = self.sampler.sample(logits, [s.index for s in seqs], drawn, None, out=out, mirror=host)
             ev = torch.cuda.Event()
             ev.record()
             self.d2h_bytes += host.numel() * 4
-            return host, ev
+            return tokens_dev, (host, ev)
 
         logits = eng.step([s.slot for s in live], [list(prompts[s.index]) for s in live], "last", borrow=True)
         self.steps += 1
-        sampled = self.sampler.sample(logits, [s.index for s in live], [len(s.tokens) for s in live], None)
-        pending = (list(live), sampled, read_later(sampled))         # sequences, their tokens on the device, the copy
+        pending = (list(live),) + sample(logits, live, [len(s.tokens) for s in live])    # sequences, tokens on the device, (host copy, event)
         while pending is not None:
             seqs, tokens_dev, (host, ev) = pending
             # Who certainly goes on after the token just sampled (length limits are known; stop tokens are not)?
@@ -162,8 +165,7 @@ class Generator:
                     torch.tensor(rows, dtype=torch.long, device=tokens_dev.device)]
                 logits = eng.step_from_device([s.slot for s in ahead], feed_dev)
                 self.steps += 1
-                sampled = self.sampler.sample(logits, [s.index for s in ahead], [len(s.tokens) + 1 for s in ahead], None)
-                nxt = (ahead, sampled, read_later(sampled))
+                nxt = (ahead,) + sample(logits, ahead, [len(s.tokens) + 1 for s in ahead])
             ev.synchronize()                                         # the earlier tokens; the step just launched keeps running
             if hasattr(eng, "check_device_status"):
                 eng.check_device_status()

@@ -189,8 +189,10 @@ def attention_generic(q: torch.Tensor, q_ld: int, kcache, vcache, page_table, to
 def sample(logits: torch.Tensor, out: torch.Tensor, *, temperature: float, top_k: int = 0, top_p: float = 1.0,
            penalty: float = 1.0, recent: torch.Tensor | None = None, recent_count: torch.Tensor | None = None,
            seed: int = 0, row_stream: torch.Tensor | None = None,
-           row_counter: torch.Tensor | None = None) -> torch.Tensor:
-    """One token per row of float32 logits [R, V] (overwritten).  out: int32 [R]."""
+           row_counter: torch.Tensor | None = None, counter_offset: int = 0,
+           mirror: torch.Tensor | None = None) -> torch.Tensor:
+    """One token per row of float32 logits [R, V] (overwritten).  out: int32 [R].  `mirror`: a
+    pinned int32 host tensor [R] that receives the tokens as well (the kernel writes it directly)."""
     _need_cuda(logits, out, recent, recent_count, row_stream, row_counter)
     rows, vocab = logits.shape
     _need(logits.dtype == torch.float32 and logits.is_contiguous(), "sample: logits must be contiguous float32")
@@ -198,10 +200,14 @@ def sample(logits: torch.Tensor, out: torch.Tensor, *, temperature: float, top_k
     for t in (recent, recent_count, row_stream, row_counter):
         _need(t is None or (t.dtype == torch.int32 and t.is_contiguous()), "sample: index tensors must be int32")
     _need((recent is None) == (recent_count is None), "sample: recent and recent_count go together")
+    if mirror is not None:
+        _need(mirror.device.type == "cpu" and mirror.is_pinned() and mirror.dtype == torch.int32
+              and mirror.is_contiguous() and mirror.numel() >= rows, "sample: mirror must be pinned int32 [R]")
     _call("sampling", "ri_sample", _p(logits), c_int(rows), c_int(vocab), _p(out), c_float(temperature),
           c_int(top_k), c_float(top_p), c_float(penalty), _p(recent),
           c_int(recent.shape[1] if recent is not None else 0), _p(recent_count),
-          c_ulonglong(seed & 0xFFFFFFFFFFFFFFFF), _p(row_stream), _p(row_counter), _stream())
+          c_ulonglong(seed & 0xFFFFFFFFFFFFFFFF), _p(row_stream), _p(row_counter), c_int(counter_offset),
+          c_void_p(mirror.data_ptr() if mirror is not None else 0), _stream())
     return out
 
 

@@ -19,6 +19,10 @@ class Sampler:
         self._pinned = [None] * 4         # staging buffers for the per-row arrays, taken in turn
         self._events = [None] * 4
         self._turn = 0
+        # the rows' arrays as they were last sent: rows that only advance together need no new copy
+        self._rows_key = None
+        self._rows_dev = None
+        self._rows_counters = None
 
     def _stage(self, meta: np.ndarray) -> torch.Tensor:
         """The per-row int32 arrays to the device, through pinned memory (no blocking copy)."""
@@ -37,13 +41,33 @@ class Sampler:
         self._events[i] = ev
         return dev
 
-    def sample(self, logits: torch.Tensor, streams: list, counters: list, histories: list | None = None) -> torch.Tensor:
-        """logits: float32 [R, V] on the device (overwritten).  Returns int32 [R] on the device."""
+    def sample(self, logits: torch.Tensor, streams: list, counters: list, histories: list | None = None,
+               out: torch.Tensor | None = None, mirror: torch.Tensor | None = None) -> torch.Tensor:
+        """logits: float32 [R, V] on the device (overwritten).  Returns int32 [R] on the device
+        (`out` if given).  `mirror`: a pinned int32 host tensor that receives the tokens too,
+        written by the kernel itself."""
         p = self.params
         rows = logits.shape[0]
-        out = torch.empty(rows, dtype=torch.int32, device=self.device)
+        if out is None:
+            out = torch.empty(rows, dtype=torch.int32, device=self.device)
         recent = recent_count = None
         width = p.repetition_window if p.uses_history else 0
+        if not width:
+            # Without a history the rows' arrays are the streams and the counters.  The same rows one
+            # draw further on keep the arrays they have on the device; the kernel adds the difference.
+            key = tuple(streams)
+            counters = list(counters)
+            if key == self._rows_key and len(set(c - b for c, b in zip(counters, self._rows_counters))) <= 1:
+                offset = counters[0] - self._rows_counters[0] if counters else 0
+            else:
+                meta = np.zeros(2 * rows, dtype=np.int32)
+                meta[:rows] = streams
+                meta[rows:] = counters
+                self._rows_dev, self._rows_key, self._rows_counters, offset = self._stage(meta), key, counters, 0
+            dev = self._rows_dev
+            ops.sample(logits, out, temperature=p.temperature, top_k=p.top_k, top_p=p.top_p, penalty=1.0, seed=p.seed,
+                       row_stream=dev[:rows], row_counter=dev[rows:2 * rows], counter_offset=offset, mirror=mirror)
+            return out
         # layout: streams [R], counters [R], history lengths [R], histories [R, width]: each contiguous
         meta = np.zeros(3 * rows + rows * width, dtype=np.int32)
         meta[:rows] = streams
@@ -61,5 +85,5 @@ class Sampler:
             recent = dev[3 * rows:].view(rows, width)
         ops.sample(logits, out, temperature=p.temperature, top_k=p.top_k, top_p=p.top_p,
                    penalty=p.repetition_penalty, recent=recent, recent_count=recent_count, seed=p.seed,
-                   row_stream=row_stream, row_counter=row_counter)
+                   row_stream=row_stream, row_counter=row_counter, mirror=mirror)
         return out
