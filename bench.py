@@ -111,8 +111,11 @@ class ClockSampler:
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=64)
-    ap.add_argument("--warmup", type=int, default=3)
+    # The prompts' prefill just before the timed steps runs the GPU into its power cap, and for some
+    # tens of milliseconds afterwards decode steps take about a tenth longer: the default warm-up is
+    # long enough to leave that behind.
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=32)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the model has (recorded)")
     ap.add_argument("--batch", type=int, default=8)
