@@ -40,6 +40,23 @@ MODEL = {
     "vocab_size": 152064, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "attention_bias": True,
     "tie_word_embeddings": False, "max_position_embeddings": 32768,
 }
+# further sizes of the same architecture, for --sizes (the default stays the benchmark model)
+OTHER_SIZES = {
+    "qwen2.5-7b": MODEL,
+    "llama3-8b": {
+        "architectures": ["LlamaForCausalLM"], "hidden_size": 4096, "num_hidden_layers": 32,
+        "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 14336,
+        "vocab_size": 128256, "rope_theta": 500000.0, "rms_norm_eps": 1e-5, "attention_bias": False,
+        "tie_word_embeddings": False, "max_position_embeddings": 32768,
+    },
+    "qwen2.5-32b": {
+        "architectures": ["Qwen2ForCausalLM"], "hidden_size": 5120, "num_hidden_layers": 64,
+        "num_attention_heads": 40, "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 27648,
+        "vocab_size": 152064, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "attention_bias": True,
+        "tie_word_embeddings": False, "max_position_embeddings": 32768,
+    },
+}
+SIZE_NAMES = {"qwen2.5-7b": "Qwen2.5-7B-sized", "llama3-8b": "Llama-3-8B-sized", "qwen2.5-32b": "Qwen2.5-32B-sized"}
 CONTEXT = 8192
 PROMPT_MIN, PROMPT_MAX = 128, 2048
 PREFILL_TOKENS = 2048
@@ -119,6 +136,11 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the model has (recorded)")
     ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--sizes", default="qwen2.5-7b", choices=sorted(OTHER_SIZES),
+                    help="layer sizes of the model (default: the benchmark model)")
+    ap.add_argument("--prompt-min", type=int, default=PROMPT_MIN, help="shortest prompt of the decode runs")
+    ap.add_argument("--prompt-max", type=int, default=PROMPT_MAX, help="longest prompt of the decode runs")
+    ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS)
     ap.add_argument("--skip-points", action="store_true", help="skip the batch-1 and batch-64 points")
     ap.add_argument("--kernel", default=None, help="time ONE kernel at the benchmark model's sizes instead "
                     "(qkv, qkv_split, o_proj, gate_up, down, lm_head, attn_decode, attn_prefill, attn_prefill_mma, rmsnorm, rope)")
@@ -148,7 +170,9 @@ def main() -> int:
     from rust_inference_b200.kernels import ops
 
     peaks, peak_source = load_peaks()
-    model_cfg = dict(MODEL)
+    model_cfg = dict(OTHER_SIZES[args.sizes])
+    prompt_min, prompt_max = max(1, args.prompt_min), max(args.prompt_min, args.prompt_max)
+    prefill_tokens = max(1, args.prefill_tokens)
     layers_full = model_cfg["num_hidden_layers"]
     if args.layers:
         model_cfg["num_hidden_layers"] = args.layers
@@ -157,7 +181,7 @@ def main() -> int:
 
     total_steps = warmup + steps + 2
     biggest = 64 if not args.skip_points else args.batch
-    cache_tokens = biggest * (-(-(PROMPT_MAX + total_steps) // 64) * 64) + 4096
+    cache_tokens = max(biggest * (-(-(prompt_max + total_steps) // 64) * 64), prefill_tokens + 64) + 4096
     torch.cuda.set_device(0)
     t0 = time.time()
     model = Model.random(cfg, seed=0, dtype="bfloat16", device="cuda:0", max_seq_len=CONTEXT,
@@ -172,7 +196,7 @@ def main() -> int:
 
     def make_prompts(batch, seed):
         rng = random.Random(seed)
-        lens = [rng.randint(PROMPT_MIN, PROMPT_MAX) for _ in range(batch)]
+        lens = [rng.randint(prompt_min, prompt_max) for _ in range(batch)]
         return [[rng.randrange(cfg.vocab_size) for _ in range(n)] for n in lens]
 
     def device_decode(batch, seed):
@@ -226,7 +250,7 @@ def main() -> int:
 
     # ---- prefill of 2,048 tokens ----
     rng = random.Random(7)
-    prompt = [rng.randrange(cfg.vocab_size) for _ in range(PREFILL_TOKENS)]
+    prompt = [rng.randrange(cfg.vocab_size) for _ in range(prefill_tokens)]
     pre_ms = []
     for i in range(3 + 5):
         slot = engine.alloc_slot()
@@ -240,7 +264,7 @@ def main() -> int:
             pre_ms.append(e0.elapsed_time(e1))
     pre_ms.sort()
     pre = pre_ms[len(pre_ms) // 2]
-    t = PREFILL_TOKENS
+    t = prefill_tokens
     per_layer = (cfg.q_dim + 2 * cfg.kv_dim) * cfg.hidden_size + cfg.hidden_size * cfg.q_dim \
         + 3 * cfg.intermediate_size * cfg.hidden_size
     flops = 2.0 * t * per_layer * n_layers + n_layers * 4.0 * t * t * cfg.q_dim / 2.0 \
@@ -257,17 +281,18 @@ def main() -> int:
     clock_info = clocks.stop()
 
     line = {
-        "metric": "decode tok/s @ batch 8 (Qwen2.5-7B-sized dense decoder, random bf16 weights, 8,192-position cache)",
+        "metric": f"decode tok/s @ batch {args.batch} ({SIZE_NAMES[args.sizes]} dense decoder, random bf16 weights, "
+                  f"8,192-position cache)",
         "value": main_run["tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
         "ms_per_step": main_run["ms_per_step"], "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random weights N(0, 0.02), seeded random token ids)",
         "impl": "ours",
         "config": {
-            "model": "Qwen2.5-7B-sized dense decoder", "layers": n_layers, "layers_of_model": layers_full,
+            "model": f"{SIZE_NAMES[args.sizes]} dense decoder", "layers": n_layers, "layers_of_model": layers_full,
             "hidden_size": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
             "head_dim": cfg.head_dim, "intermediate_size": cfg.intermediate_size, "vocab_size": cfg.vocab_size,
             "qkv_bias": cfg.attention_bias, "tied_embeddings": cfg.tie_word_embeddings,
-            "global_batch": args.batch, "seq_len": CONTEXT, "prompt_lengths": f"uniform {PROMPT_MIN}-{PROMPT_MAX}",
+            "global_batch": args.batch, "seq_len": CONTEXT, "prompt_lengths": f"uniform {prompt_min}-{prompt_max}",
             "mean_context": round(main_run["mean_ctx_tokens"] / args.batch, 1), "parallelism": "single GPU",
             "l2": "inputs larger than L2 (weights read once per step)", "peaks": peak_source,
         },
