@@ -386,6 +386,33 @@ def test_attention_kernels(dtype, nh, nkv, hd, news, starts, window):
             assert (out2.float().cpu() - c["ref"]).abs().max().item() <= tol * c["ref"].abs().max().item(), splits
 
 
+DECODE_CASES = [
+    # heads, kv heads, head_dim, cached before the new token (one per sequence), window
+    (14, 2, 128, [1000, 64, 127, 128], 0),
+    (8, 8, 64, [0, 63, 200], 0),
+    (16, 1, 64, [999], 0),
+    (4, 1, 64, [300, 5], 100),
+    (28, 4, 128, [1, 0, 511, 700, 64, 65, 1300, 2047], 0),
+]
+
+
+@pytest.mark.parametrize("nh, nkv, hd, starts, window", DECODE_CASES)
+def test_decode_attention_as_a_cluster(nh, nkv, hd, starts, window):
+    """The runs of a (sequence, kv head) as one thread-block cluster that merges its own partial results."""
+    ops = _ops()
+    c = _attention_case(nh, nkv, hd, [1] * len(starts), starts, torch.bfloat16, window=window)
+    for splits in (2, 3, 5, 8):
+        out = torch.zeros(c["T"], nh * hd, device=DEV, dtype=torch.bfloat16)
+        ops.attention_decode_cluster(c["q"], c["q"].shape[1], c["kc"], c["vc"], c["table"], c["slot"], c["length"],
+                                     c["cu"], out, n_seqs=c["B"], n_heads=nh, n_kv_heads=nkv, head_dim=hd,
+                                     page_size=64, scale=c["scale"], window=window, n_splits=splits)
+        assert (out.float().cpu() - c["ref"]).abs().max().item() <= 2e-2 * c["ref"].abs().max().item(), splits
+    with pytest.raises(ops.KernelError, match="2 to 8 splits"):
+        ops.attention_decode_cluster(c["q"], c["q"].shape[1], c["kc"], c["vc"], c["table"], c["slot"], c["length"],
+                                     c["cu"], out, n_seqs=c["B"], n_heads=nh, n_kv_heads=nkv, head_dim=hd,
+                                     page_size=64, scale=c["scale"], window=window, n_splits=9)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_attention_finds_a_far_key(dtype):
     """One key among hundreds is scaled up so that its score stands out: the result must be
