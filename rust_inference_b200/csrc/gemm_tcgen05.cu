@@ -690,35 +690,62 @@ RI_API int ri_gemm_tcgen05_set_long_tile(int tn) {
     return 0;
 }
 
-// The token tile (rows of the activation box) a call with n_tok tokens and n_feat features uses.
-RI_API int ri_gemm_tcgen05_tile(int n_tok, int n_feat, int dual) {
-    // up to 128 tokens: one token tile, as narrow as the step allows
-    if (n_tok <= 128) return n_tok <= 16 ? 16 : (n_tok + 15) / 16 * 16;
-    // beyond: the SiLU-gate projection takes the token-major kernel (128 tokens per tile) ...
-    if (dual) return 128;
-    if (g_long_tile) return g_long_tile;
-    // ... the others the feature-major kernel.  A tile costs time in proportion to its width, and
-    // the persistent grid runs ceil(tiles / CTAs) tiles deep: take the width of 128..256 tokens for
-    // which depth x width is least (3584 features at 2,048 tokens: 208, 1.9 waves of 208 instead of
-    // 1.5 -> 2 waves of 256).  Ties go to the wider tile.
+// How a product of n_tok tokens, n_feat features and inner size K is cut: the token tile (rows of the
+// activation box, written to *tile) and, for the residual epilogue (mode 2, the only one that can
+// add partial sums), over how many pieces K is split (*split; 1 for the other modes).
+//
+//  up to 128 tokens   one token tile, as narrow as the step allows.  Such steps stream weights:
+//                     measured in a replayed graph at 8 tokens, the o, q/k/v and down projections of
+//                     a 3584-wide model are fastest with about two CTAs per SM (7-10 pieces) and at
+//                     least 4 k-blocks per piece.
+//  beyond, SiLU-gate  the token-major kernel, 128 tokens per tile.
+//  beyond, others     the feature-major kernel.  Measured at 192..4,096 tokens: a k-block takes about
+//                     as long whatever the tile's width (128..256), so what counts is how many rounds
+//                     the persistent grid makes and how long a work item's K run is.  Every width of
+//                     128..256 and every split is tried on depth x (k-blocks per item + a dozen for
+//                     the item's epilogue and ramp); ties go to the narrower tile.  (Down projection
+//                     of 512 tokens: 256 x 5 pieces, 63.5 us, against 128 x 2, 100 us.)
+RI_API int ri_gemm_tcgen05_plan(int n_tok, int n_feat, int K, int mode, int* tile, int* split) {
     const long long feat_tiles = (n_feat + BLOCK_F - 1) / BLOCK_F;
     const long long ctas = sm_count();
-    int best = 256;
-    long long best_cost = -1;
-    for (int tn = 256; tn >= 128; tn -= 16) {
-        const long long tiles = (long long)((n_tok + tn - 1) / tn) * feat_tiles;
-        const long long cost = ((tiles + ctas - 1) / ctas) * tn;
-        if (best_cost < 0 || cost < best_cost) {
-            best_cost = cost;
-            best = tn;
+    const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
+    const bool can_split = mode == 2;
+    int tn = 16, sp = 1;
+    if (n_tok <= 128) {
+        tn = n_tok <= 16 ? 16 : (n_tok + 15) / 16 * 16;
+        if (can_split && feat_tiles < ctas) {
+            long long want = (2 * ctas) / feat_tiles;
+            if (want > total_kb / 4) want = total_kb / 4;
+            sp = want < 1 ? 1 : (int)want;
+        }
+    } else if (mode == 3) {
+        tn = 128;
+    } else {
+        constexpr long long ITEM_OVERHEAD = 12;               // in k-blocks
+        long long best_cost = -1;
+        const int max_split = can_split ? (total_kb / 4 < 10 ? (total_kb / 4 < 1 ? 1 : total_kb / 4) : 10) : 1;
+        for (int t = 128; t <= 256; t += 16) {
+            if (g_long_tile && t != g_long_tile) continue;
+            const long long tiles = (long long)((n_tok + t - 1) / t) * feat_tiles;
+            for (int s = 1; s <= max_split; ++s) {
+                const long long items = tiles * s;
+                const long long cost = ((items + ctas - 1) / ctas) * ((total_kb + s - 1) / s + ITEM_OVERHEAD);
+                if (best_cost < 0 || cost < best_cost) {
+                    best_cost = cost;
+                    tn = t;
+                    sp = s;
+                }
+            }
         }
     }
-    return best;
+    if (tile) *tile = tn;
+    if (split) *split = sp;
+    return 0;
 }
 
 // Encode the tensor map of a bf16 matrix [rows, K] (row-major, 16-byte aligned, K a multiple of 8)
 // into the 128 bytes at `map_out` (64-byte aligned).  box_rows is 128 for a weight matrix and the
-// token tile (ri_gemm_tcgen05_tile, for the same n_tok and n_feat as the product) for activations.  Maps only depend on pointer and shape, so the
+// token tile (ri_gemm_tcgen05_plan, for the same sizes and mode as the product) for activations.  Maps only depend on pointer and shape, so the
 // caller keeps them: weights encode once, activation buffers once per shape.
 RI_API int ri_gemm_tcgen05_encode(void* map_out, const void* ptr, long long rows, long long K, int box_rows) {
     if ((uintptr_t)map_out % 64) return fail("gemm_tcgen05: tensor map storage must be 64-byte aligned");
@@ -727,8 +754,8 @@ RI_API int ri_gemm_tcgen05_encode(void* map_out, const void* ptr, long long rows
     return make_map(reinterpret_cast<CUtensorMap*>(map_out), ptr, rows, K, box_rows, "matrix");
 }
 
-// X [n_tok, K] with map_x (box rows = the token tile), W (and W2) [n_feat, K] with map_w / map_w2 (box
-// rows 128).  `status` (may be null) is a host-visible int that receives a non-zero code if a wait ran out.
+// X [n_tok, K] with map_x (box rows = the token tile of ri_gemm_tcgen05_plan), W (and W2) [n_feat, K] with
+// map_w / map_w2 (box rows 128).  split_k 0 takes the plan's split.  `status` (may be null) is a host-visible int that receives a non-zero code if a wait ran out.
 RI_API int ri_gemm_tcgen05(const void* map_x, const void* map_w, const void* map_w2, const float* bias, void* out,
                            int mode, int n_tok, int n_feat, int K, int split_k, int* status, cudaStream_t stream) {
     if (n_tok <= 0 || n_feat <= 0) return 0;
@@ -738,7 +765,9 @@ RI_API int ri_gemm_tcgen05(const void* map_x, const void* map_w, const void* map
     if (mode == 2 && bias != nullptr) return fail("gemm_tcgen05: the residual epilogue takes no bias");
     if (mode != 2 && split_k > 1) return fail("gemm_tcgen05: only the residual epilogue can split K");
     const bool dual = mode == 3;
-    const int tn = ri_gemm_tcgen05_tile(n_tok, n_feat, dual);
+    int tn = 0, planned_split = 1;
+    ri_gemm_tcgen05_plan(n_tok, n_feat, K, mode, &tn, &planned_split);
+    if (split_k <= 0) split_k = planned_split;
     const CUtensorMap& mw = *reinterpret_cast<const CUtensorMap*>(map_w);
     const CUtensorMap& mw2 = dual ? *reinterpret_cast<const CUtensorMap*>(map_w2) : mw;
     const CUtensorMap& mx = *reinterpret_cast<const CUtensorMap*>(map_x);

@@ -2,7 +2,7 @@
 from __future__ import annotations
 
 import functools
-from ctypes import c_int, c_longlong, c_void_p
+from ctypes import byref, c_int, c_longlong, c_void_p
 
 import torch
 
@@ -43,23 +43,24 @@ def supports(x: torch.Tensor, w) -> bool:
 
 
 @functools.lru_cache(maxsize=4096)
-def token_tile(n_tok: int, n_feat: int, dual: bool) -> int:
-    """Rows of the activation tile, as the kernel library picks them: the step rounded up to 16
-    up to 128 tokens; beyond, 128 for the SiLU-gate projection (token-major kernel) and for the
-    others the width of 128..256 that leaves the least idle tail in the persistent grid."""
+def plan(n_tok: int, n_feat: int, k: int, mode: int) -> tuple:
+    """(token tile, K split) of a product, as the kernel library cuts it: the step rounded up to 16
+    up to 128 tokens (with the residual epilogue split over about two CTAs per SM); beyond, 128
+    tokens for the SiLU-gate projection (token-major kernel) and for the others the width of
+    128..256 and the split that leave the shortest run in the persistent grid."""
     lib = build.load("gemm_tcgen05")
-    return int(lib.ri_gemm_tcgen05_tile(c_int(n_tok), c_int(n_feat), c_int(1 if dual else 0)))
+    tile, split = c_int(0), c_int(0)
+    lib.ri_gemm_tcgen05_plan(c_int(n_tok), c_int(n_feat), c_int(k), c_int(mode), byref(tile), byref(split))
+    return tile.value, split.value
 
 
-def pick_split(n_tok: int, n_feat: int, k: int, dual: bool) -> int:
-    """K splits for the residual epilogue.  Small steps stream weights: measured in a replayed
-    graph at 8 tokens, the o, q/k/v and down projections of a 3584-wide model are fastest with
-    about two CTAs per SM (7-10 splits) and at least 4 k-blocks per split."""
-    tiles = -(-n_feat // 128) * -(-n_tok // token_tile(n_tok, n_feat, dual))
-    kb = -(-k // 64)
-    if tiles >= N_SMS:
-        return 1
-    return max(1, min((2 * N_SMS) // tiles, kb // 4))
+def token_tile(n_tok: int, n_feat: int, k: int, mode: int) -> int:
+    return plan(n_tok, n_feat, k, mode)[0]
+
+
+def pick_split(n_tok: int, n_feat: int, k: int) -> int:
+    """K splits of the residual epilogue for a product of this size."""
+    return plan(n_tok, n_feat, k, ops.EPI_RESIDUAL)[1]
 
 
 def _encode(t: torch.Tensor, rows: int, k: int, box_rows: int) -> torch.Tensor:
@@ -100,11 +101,12 @@ def gemm(x: torch.Tensor, w, out: torch.Tensor, mode: int, ctx=None, bias=None, 
     if w2 is not None:
         _need((w2.n, w2.k) == (n, k) and w2.t.dtype == torch.bfloat16, "gemm_tcgen05: second matrix")
         map_w2 = weight_map(w2)
-    if split_k is None:
-        split_k = pick_split(m, n, k, w2 is not None) if mode == ops.EPI_RESIDUAL else 1
     if m == 0:
         return out
-    map_x = _x_map(x, token_tile(m, n, w2 is not None))
+    tile, planned = plan(m, n, k, mode)
+    if split_k is None:
+        split_k = planned
+    map_x = _x_map(x, tile)
     st = status_word()
     _call("gemm_tcgen05", "ri_gemm_tcgen05", c_void_p(map_x.data_ptr()), c_void_p(weight_map(w).data_ptr()),
           c_void_p(map_w2.data_ptr() if map_w2 is not None else 0), _p(bias), _p(out), c_int(mode), c_int(m),

@@ -225,17 +225,19 @@ def test_gemm_tcgen05_all_epilogues(m, n, k):
 
 @pytest.mark.parametrize("m, n, k", [(2048, 3584, 256), (1111, 1000, 72), (257, 19 * 128, 64)])
 def test_gemm_tcgen05_token_tile_follows_the_grid(m, n, k):
-    """Long steps run the token tile of 128..256 rows that leaves the shortest tail in the persistent
-    grid (208 for 3584 features at 2,048 tokens); whatever width is picked, the product is the same."""
+    """Long steps run the token tile of 128..256 rows, and the residual epilogue the K split, that
+    leave the shortest run in the persistent grid; however a product is cut, it is the same product."""
     ops = _ops()
     from rust_inference_b200.kernels import linear, tcgen05
-    tn = tcgen05.token_tile(m, n, False)
-    assert 128 <= tn <= 256 and tn % 16 == 0
     sms = torch.cuda.get_device_properties(0).multi_processor_count
-    cost = lambda t: -(-(-(-m // t) * -(-n // 128)) // sms) * t
-    assert cost(tn) == min(cost(t) for t in range(128, 257, 16))
-    if (m, n) == (2048, 3584) and sms == 148:
-        assert tn == 208
+    kb = -(-k // 64)
+    for mode in (ops.EPI_STORE_F32, ops.EPI_RESIDUAL):
+        tn, split = tcgen05.plan(m, n, k, mode)
+        assert 128 <= tn <= 256 and tn % 16 == 0 and 1 <= split <= max(1, kb // 4)
+        assert split == 1 or mode == ops.EPI_RESIDUAL
+        splits = range(1, max(1, min(10, kb // 4)) + 1) if mode == ops.EPI_RESIDUAL else (1,)
+        cost = lambda t, s: -(-(-(-m // t) * -(-n // 128) * s) // sms) * (-(-kb // s) + 12)
+        assert cost(tn, split) == min(cost(t, s) for t in range(128, 257, 16) for s in splits)
     x = (torch.randn(m, k, device=DEV) * 0.5).bfloat16()
     w = linear.Weight((torch.randn(n, k, device=DEV) * 0.1).bfloat16())
     ref = x.double() @ w.t.double().t()
