@@ -207,6 +207,101 @@ __global__ void rope_cache_write_kernel(T* __restrict__ qkv, int ld, const float
     }
 }
 
+// The same for bf16 rows whose head size is a multiple of 16, moved 16 bytes at a time: a thread takes
+// 8 consecutive elements of a head (and, for the half-split pairing, their 8 partners half a head on),
+// rotates them in float32 and writes them back the same way.
+__device__ __forceinline__ void unpack8(const uint4& v, float* f) {
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 x = __bfloat1622float2(p[i]);
+        f[2 * i] = x.x;
+        f[2 * i + 1] = x.y;
+    }
+}
+__device__ __forceinline__ uint4 pack8(const float* f) {
+    uint4 v;
+    __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) p[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    return v;
+}
+
+__global__ void rope_cache_write_vec_kernel(__nv_bfloat16* __restrict__ qkv, int ld, const float* __restrict__ cos_t,
+                                            const float* __restrict__ sin_t, const int* __restrict__ token_pos,
+                                            const int* __restrict__ token_seq, const int* __restrict__ seq_slot,
+                                            const int* __restrict__ page_table, int max_pages,
+                                            __nv_bfloat16* __restrict__ kcache, __nv_bfloat16* __restrict__ vcache,
+                                            int n_heads, int n_kv_heads, int hd, int page_size, int style,
+                                            int write_kv) {
+    const int t = blockIdx.x;
+    let_next_kernel_start();
+    const int pos = token_pos[t];                     // positions, slots, pages and angles: fixed before the step
+    const int half = hd >> 1;
+    const float* c = cos_t + (size_t)pos * half;
+    const float* s = sin_t + (size_t)pos * half;
+    const int q_dim = n_heads * hd, kv_dim = n_kv_heads * hd;
+    size_t cache_base = 0;
+    if (write_kv) {
+        const int slot = seq_slot[token_seq[t]];
+        const int page = page_table[(size_t)slot * max_pages + pos / page_size];
+        cache_base = ((size_t)page * n_kv_heads * page_size + (pos % page_size)) * hd;
+    }
+    const size_t head_stride = (size_t)page_size * hd;
+    wait_for_previous_kernels();          // the projections come from the previous kernel
+    __nv_bfloat16* row = qkv + (size_t)t * ld;
+
+    const int heads = n_heads + (write_kv ? n_kv_heads : 0);
+    if (style == 0) {
+        const int per_head = half / 8;                // chunk pairs of a head
+        for (int idx = threadIdx.x; idx < heads * per_head; idx += blockDim.x) {
+            const int h = idx / per_head, j = idx % per_head;
+            const __nv_bfloat16* src = row + (size_t)h * hd + 8 * j;      // q heads, then k heads: one run of columns
+            float lo[8], hi[8], cs[8], sn[8], ylo[8], yhi[8];
+            unpack8(*reinterpret_cast<const uint4*>(src), lo);
+            unpack8(*reinterpret_cast<const uint4*>(src + half), hi);
+            *reinterpret_cast<float4*>(cs) = *reinterpret_cast<const float4*>(c + 8 * j);
+            *reinterpret_cast<float4*>(cs + 4) = *reinterpret_cast<const float4*>(c + 8 * j + 4);
+            *reinterpret_cast<float4*>(sn) = *reinterpret_cast<const float4*>(s + 8 * j);
+            *reinterpret_cast<float4*>(sn + 4) = *reinterpret_cast<const float4*>(s + 8 * j + 4);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                ylo[i] = lo[i] * cs[i] - hi[i] * sn[i];
+                yhi[i] = lo[i] * sn[i] + hi[i] * cs[i];
+            }
+            __nv_bfloat16* dst = h < n_heads ? row + (size_t)h * hd + 8 * j
+                                             : kcache + cache_base + (size_t)(h - n_heads) * head_stride + 8 * j;
+            *reinterpret_cast<uint4*>(dst) = pack8(ylo);
+            *reinterpret_cast<uint4*>(dst + half) = pack8(yhi);
+        }
+    } else {
+        const int per_head = hd / 8;                  // chunks of a head, 4 adjacent pairs each
+        for (int idx = threadIdx.x; idx < heads * per_head; idx += blockDim.x) {
+            const int h = idx / per_head, j = idx % per_head;
+            const __nv_bfloat16* src = row + (size_t)h * hd + 8 * j;
+            float x[8], y[8], cs[4], sn[4];
+            unpack8(*reinterpret_cast<const uint4*>(src), x);
+            *reinterpret_cast<float4*>(cs) = *reinterpret_cast<const float4*>(c + 4 * j);
+            *reinterpret_cast<float4*>(sn) = *reinterpret_cast<const float4*>(s + 4 * j);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                y[2 * i] = x[2 * i] * cs[i] - x[2 * i + 1] * sn[i];
+                y[2 * i + 1] = x[2 * i] * sn[i] + x[2 * i + 1] * cs[i];
+            }
+            __nv_bfloat16* dst = h < n_heads ? row + (size_t)h * hd + 8 * j
+                                             : kcache + cache_base + (size_t)(h - n_heads) * head_stride + 8 * j;
+            *reinterpret_cast<uint4*>(dst) = pack8(y);
+        }
+    }
+    if (!write_kv) return;
+    const int v_chunks = hd / 8;
+    for (int idx = threadIdx.x; idx < n_kv_heads * v_chunks; idx += blockDim.x) {
+        const int h = idx / v_chunks, j = idx % v_chunks;
+        *reinterpret_cast<uint4*>(vcache + cache_base + (size_t)h * head_stride + 8 * j) =
+            *reinterpret_cast<const uint4*>(row + q_dim + kv_dim + (size_t)h * hd + 8 * j);
+    }
+}
+
 RI_API int ri_rope_cache_write(void* qkv, int dtype, int ld, const float* cos_t, const float* sin_t,
                                const int* token_pos, const int* token_seq, const int* seq_slot,
                                const int* page_table, int max_pages, void* kcache, void* vcache,
@@ -218,6 +313,16 @@ RI_API int ri_rope_cache_write(void* qkv, int dtype, int ld, const float* cos_t,
     const int work = n_heads * hd / 2;
     const int threads = work >= 256 ? 256 : (work >= 128 ? 128 : 64);
     cudaError_t e = cudaSuccess;
+    const bool aligned = hd % 16 == 0 && ld % 8 == 0 && (uintptr_t)qkv % 16 == 0 && (uintptr_t)kcache % 16 == 0 &&
+                         (uintptr_t)vcache % 16 == 0 && (uintptr_t)cos_t % 16 == 0 && (uintptr_t)sin_t % 16 == 0;
+    if (dtype == RI_BF16 && aligned) {
+        const int items = (n_heads + n_kv_heads) * hd / 16;
+        const int vthreads = items >= 256 ? 256 : (items >= 128 ? 128 : 64);
+        e = launch_dependent(rope_cache_write_vec_kernel, n_tokens, vthreads, 0, stream,
+            (__nv_bfloat16*)qkv, ld, cos_t, sin_t, token_pos, token_seq, seq_slot, page_table, max_pages,
+            (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, n_heads, n_kv_heads, hd, page_size, style, write_kv);
+        return check_launch(e, "rope_cache_write");
+    }
     if (dtype == RI_F32)
         e = launch_dependent(rope_cache_write_kernel<float>, n_tokens, threads, 0, stream,
             (float*)qkv, ld, cos_t, sin_t, token_pos, token_seq, seq_slot, page_table, max_pages,
