@@ -37,7 +37,7 @@ constexpr int BN = 64;             // keys per step = one cache page
 constexpr int THREADS = 192;
 constexpr int RESCALE_LOG2 = 8;    // the scaling maximum follows the true one in steps of at least 2^8
 
-enum AttnStatus { ST_ATTN_PRODUCER = 11, ST_ATTN_MMA = 12, ST_ATTN_SOFTMAX = 13, ST_ATTN_DRAIN = 14 };
+enum AttnStatus { ST_ATTN_PRODUCER = 11, ST_ATTN_MMA = 12, ST_ATTN_SOFTMAX = 13, ST_ATTN_DRAIN = 14, ST_ATTN_SMEM = 15 };
 
 // MN-major B operand (the V page: rows are keys, 128-byte rows of 64 head_dim values, written by TMA
 // with 128-byte swizzle): groups of 8 key rows are 1024 bytes apart (stride byte offset), the next 64
@@ -78,7 +78,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const __grid_constant__ CUtensorMap map_v, const int* __restrict__ page_table, int max_pages,
                        const int* __restrict__ seq_slot, const int* __restrict__ seq_start,
                        const int* __restrict__ cu_seqlens, int n_heads, int n_kv_heads, float scale_log2, int window,
-                       __nv_bfloat16* __restrict__ out, int out_ld, int* status) {
+                       __nv_bfloat16* __restrict__ out, int out_ld, uint32_t smem_bytes, int* status) {
     constexpr int ATOMS = HD / 64;                       // 64-wide (128-byte) column tiles per row of head_dim
     constexpr int Q_BYTES = ATOMS * BM * 128;            // [atom][128 queries][64]
     constexpr int K_BYTES = ATOMS * BN * 128;            // one buffer: [atom][64 keys][64]
@@ -89,15 +89,21 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     constexpr uint32_t IDESC_PV = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) |
                                   ((uint32_t)(BM >> 4) << 24);
 
+    // Everything lives in dynamic shared memory: the tiles (1024-byte aligned for the 128-byte swizzle) and,
+    // behind them, the barriers.  With head_dim 128 the tiles take 112 KiB and two CTAs share an SM only if
+    // nothing is spent on alignment: the kernel declares no static shared memory, so that the dynamic part
+    // starts at the CTA's window, and checks that it fits.
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t q_full, k_full[2], k_empty[2], v_full, v_empty, s_full[2], p_full, pv_done;
-    __shared__ uint32_t tmem_base_slot;
-    __shared__ volatile int abort_flag;
+    struct Sync {
+        uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full, pv_done;
+        uint32_t tmem_base_slot;
+        volatile int abort_flag;
+    };
 
-    const int b = blockIdx.z, h = blockIdx.y;
+    const int b = blockIdx.y, h = blockIdx.x;
     const int tok0 = cu_seqlens[b], n_new = cu_seqlens[b + 1] - tok0;
     // the last query tiles see the most keys: they go first, so the short ones fill the tail
-    const int q0 = (int)(gridDim.x - 1 - blockIdx.x) * BM;
+    const int q0 = (int)(gridDim.z - 1 - blockIdx.z) * BM;
     if (q0 >= n_new) return;                                                // uniform over the CTA
     const int kvh = h / (n_heads / n_kv_heads);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -107,14 +113,25 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int first_key = (window > 0 && pos_lo - window + 1 > 0) ? pos_lo - window + 1 : 0;
     const int pg_begin = first_key / BN, n_pages = pos_hi / BN + 1 - pg_begin;
 
-    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t q_smem = base, k_smem = q_smem + Q_BYTES, v_smem = k_smem + 2 * K_BYTES, p_smem = v_smem + V_BYTES;
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    const uint32_t q_smem = base, k_smem = q_smem + Q_BYTES, v_smem = k_smem + 2 * K_BYTES, p_smem = v_smem + 2 * V_BYTES;
+    constexpr uint32_t TILE_BYTES = Q_BYTES + 2 * K_BYTES + 2 * V_BYTES + BM * 128;
+    if (base - raw + TILE_BYTES + (uint32_t)sizeof(Sync) > smem_bytes) {          // uniform over the CTA
+        if (threadIdx.x == 0) report(status, ST_ATTN_SMEM);
+        return;
+    }
+    Sync& sy = *reinterpret_cast<Sync*>(smem_raw + (base - raw) + TILE_BYTES);
+    uint64_t &q_full = sy.q_full, &p_full = sy.p_full, &pv_done = sy.pv_done;
+    uint64_t (&k_full)[2] = sy.k_full, (&k_empty)[2] = sy.k_empty, (&v_full)[2] = sy.v_full, (&v_empty)[2] = sy.v_empty;
+    uint64_t (&s_full)[2] = sy.s_full;
+    uint32_t& tmem_base_slot = sy.tmem_base_slot;
+    volatile int& abort_flag = sy.abort_flag;
 
     if (threadIdx.x == 0) {
         mbar_init(smem_u32(&q_full), 1);
         for (int i = 0; i < 2; ++i) { mbar_init(smem_u32(&k_full[i]), 1); mbar_init(smem_u32(&k_empty[i]), 1); }
-        mbar_init(smem_u32(&v_full), 1);
-        mbar_init(smem_u32(&v_empty), 1);
+        for (int i = 0; i < 2; ++i) { mbar_init(smem_u32(&v_full[i]), 1); mbar_init(smem_u32(&v_empty[i]), 1); }
         mbar_init(smem_u32(&s_full[0]), 1);
         mbar_init(smem_u32(&s_full[1]), 1);
         mbar_init(smem_u32(&p_full), 4);          // one arrival per softmax warp
@@ -152,19 +169,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 for (int a = 0; a < ATOMS; ++a)
                     tma_load_2d(k_smem + kb * K_BYTES + a * BN * 128, &map_k, smem_u32(&k_full[kb]), a * 64, row);
                 k_issued = j + 1;
-                if (!mbar_wait(smem_u32(&v_empty), (uint32_t)(j & 1) ^ 1u) || abort_flag) {
+                if (!mbar_wait(smem_u32(&v_empty[kb]), (uint32_t)((j >> 1) & 1) ^ 1u) || abort_flag) {
                     report(status, ST_ATTN_PRODUCER); abort_flag = 1; break;
                 }
-                mbar_expect_tx(smem_u32(&v_full), V_BYTES);
+                mbar_expect_tx(smem_u32(&v_full[kb]), V_BYTES);
                 for (int a = 0; a < ATOMS; ++a)
-                    tma_load_2d(v_smem + a * BN * 128, &map_v, smem_u32(&v_full), a * 64, row);
+                    tma_load_2d(v_smem + kb * V_BYTES + a * BN * 128, &map_v, smem_u32(&v_full[kb]), a * 64, row);
                 v_issued = j + 1;
             }
             // do not leave while a copy into this CTA's shared memory may be in flight
             if (!mbar_wait(smem_u32(&q_full), 0)) report(status, ST_ATTN_DRAIN);
             for (int j = max(0, k_issued - 2); j < k_issued; ++j)
                 if (!mbar_wait(smem_u32(&k_full[j & 1]), (uint32_t)((j >> 1) & 1))) { report(status, ST_ATTN_DRAIN); break; }
-            if (v_issued > 0 && !mbar_wait(smem_u32(&v_full), (uint32_t)((v_issued - 1) & 1))) report(status, ST_ATTN_DRAIN);
+            for (int j = max(0, v_issued - 2); j < v_issued; ++j)
+                if (!mbar_wait(smem_u32(&v_full[j & 1]), (uint32_t)((j >> 1) & 1))) { report(status, ST_ATTN_DRAIN); break; }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
@@ -190,17 +208,18 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             for (int j = 0; j < n_pages && ok; ++j) {
                 // the buffer S(j+1) goes to was read by the softmax of page j-1, which arrived on p_full before PV(j-1)
                 if (j + 1 < n_pages && !issue_s(j + 1)) { report(status, ST_ATTN_MMA); abort_flag = 1; break; }
-                if (!mbar_wait(smem_u32(&p_full), (uint32_t)(j & 1)) || !mbar_wait(smem_u32(&v_full), (uint32_t)(j & 1))) {
+                if (!mbar_wait(smem_u32(&p_full), (uint32_t)(j & 1)) ||
+                    !mbar_wait(smem_u32(&v_full[j & 1]), (uint32_t)((j >> 1) & 1))) {
                     report(status, ST_ATTN_MMA); abort_flag = 1; break;
                 }
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < BN / 16; ++ks) {
                     const uint64_t a = make_smem_desc(p_smem + ks * 32);
-                    const uint64_t bd = make_smem_desc_mn(v_smem + ks * 16 * 128, BN * 128);
+                    const uint64_t bd = make_smem_desc_mn(v_smem + (j & 1) * V_BYTES + ks * 16 * 128, BN * 128);
                     umma(tmem_base + O_COL, a, bd, IDESC_PV, j > 0 || ks > 0);
                 }
-                umma_commit(smem_u32(&v_empty));
+                umma_commit(smem_u32(&v_empty[j & 1]));
                 umma_commit(smem_u32(&pv_done));
             }
         }
@@ -338,7 +357,10 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
            const int* seq_slot, const int* seq_start, const int* cu_seqlens, int n_seqs, int max_new, int n_heads,
            int n_kv_heads, float scale, int window, void* out, int out_ld, int* status, cudaStream_t stream) {
     constexpr int ATOMS = HD / 64;
-    constexpr int SMEM = ATOMS * BM * 128 + 3 * ATOMS * BN * 128 + BM * 128 + 1024;
+    // Q, two K and two V pages, P, the barriers; with head_dim 128 no room for alignment padding is left if
+    // two CTAs are to share an SM (the kernel refuses, with a status code, a shared window that needs any)
+    constexpr int TILES = ATOMS * BM * 128 + 4 * ATOMS * BN * 128 + BM * 128;
+    constexpr int SMEM = TILES + (HD >= 128 ? 256 : 1024 + 256);
     auto kernel = attn_prefill_tc_kernel<HD>;
     static bool configured = false;
     if (!configured) {
@@ -346,11 +368,13 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
         if (e != cudaSuccess) return fail("attention_tcgen05: cannot raise dynamic shared memory: %s", cudaGetErrorString(e));
         configured = true;
     }
-    dim3 grid((max_new + BM - 1) / BM, n_heads, n_seqs);
+    // blocks are handed out x fastest: every head and sequence of the longest query tiles first, the short
+    // tiles last, so the causal triangle's tail is filled with small pieces
+    dim3 grid(n_heads, n_seqs, (max_new + BM - 1) / BM);
     const float scale_log2 = scale * 1.4426950408889634f;
     cudaError_t e = launch_dependent(kernel, grid, dim3(THREADS), (size_t)SMEM, stream, mq, mk, mv, page_table, max_pages,
                                      seq_slot, seq_start, cu_seqlens, n_heads, n_kv_heads, scale_log2, window,
-                                     (__nv_bfloat16*)out, out_ld, status);
+                                     (__nv_bfloat16*)out, out_ld, (uint32_t)SMEM, status);
     return check_launch(e, "attention_tcgen05");
 }
 

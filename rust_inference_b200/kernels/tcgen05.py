@@ -18,6 +18,14 @@ STATUS_TEXT = {
     2: "the MMA issuer waited too long for a TMA load",
     3: "the epilogue waited too long for the accumulator",
     4: "a TMA load did not land before the CTA had to leave",
+    11: "attention: the TMA producer waited too long for a free page buffer",
+    12: "attention: the MMA issuer waited too long for a page or for the softmax",
+    13: "attention: the softmax waited too long for scores or for the previous product",
+    14: "attention: a TMA load did not land before the CTA had to leave",
+    15: "attention: the shared-memory window is not aligned as the tight layout needs",
+    21: "decode attention: the TMA producer waited too long for a free stage",
+    22: "decode attention: a compute warp waited too long for a page",
+    24: "decode attention: a TMA load did not land before the CTA had to leave",
 }
 
 
@@ -34,7 +42,7 @@ def check_status() -> None:
     if _status is not None and int(_status[0]) != 0:
         code = int(_status[0])
         _status[0] = 0
-        raise KernelError(f"gemm_tcgen05 gave up: {STATUS_TEXT.get(code, f'code {code}')}")
+        raise KernelError(f"a tensor-core kernel gave up: {STATUS_TEXT.get(code, f'code {code}')}")
 
 
 def supports(x: torch.Tensor, w) -> bool:
