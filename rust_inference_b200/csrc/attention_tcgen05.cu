@@ -52,6 +52,17 @@ __device__ __forceinline__ uint64_t make_smem_desc_mn(uint32_t addr, uint32_t at
     return d;
 }
 
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand (128 rows x 16 bf16, two to a 32-bit column, 8 columns) comes from
+// tensor memory, where the softmax threads put the probabilities.
+__device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t b_desc, uint32_t idesc, bool accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(b_desc), "r"(idesc), "r"((uint32_t)accumulate)
+        : "memory");
+}
+
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
@@ -115,8 +126,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
-    const uint32_t q_smem = base, k_smem = q_smem + Q_BYTES, v_smem = k_smem + 2 * K_BYTES, p_smem = v_smem + 2 * V_BYTES;
-    constexpr uint32_t TILE_BYTES = Q_BYTES + 2 * K_BYTES + 2 * V_BYTES + BM * 128;
+    const uint32_t q_smem = base, k_smem = q_smem + Q_BYTES, v_smem = k_smem + 2 * K_BYTES;
+    constexpr uint32_t TILE_BYTES = Q_BYTES + 2 * K_BYTES + 2 * V_BYTES;
     if (base - raw + TILE_BYTES + (uint32_t)sizeof(Sync) > smem_bytes) {          // uniform over the CTA
         if (threadIdx.x == 0) report(status, ST_ATTN_SMEM);
         return;
@@ -189,38 +200,46 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         if (lane == 0) {
             bool ok = mbar_wait(smem_u32(&q_full), 0);
             if (!ok) { report(status, ST_ATTN_MMA); abort_flag = 1; }
+            // One thread issues every MMA, and a lone thread gets a dependent instruction out only every few
+            // cycles: the descriptors are built once, and a page's MMAs add constants to their address field
+            // (shared memory ends below 256 KiB, so the 14-bit field never carries).
+            const uint64_t q_desc = make_smem_desc(q_smem), k_desc = make_smem_desc(k_smem);
+            const uint64_t v_desc = make_smem_desc_mn(v_smem, BN * 128);
+            const uint32_t k_full0 = smem_u32(&k_full[0]), k_empty0 = smem_u32(&k_empty[0]), s_full0 = smem_u32(&s_full[0]);
+            const uint32_t v_full0 = smem_u32(&v_full[0]), v_empty0 = smem_u32(&v_empty[0]);
+            const uint32_t p_full_a = smem_u32(&p_full), pv_done_a = smem_u32(&pv_done);
             // scores of page j go to buffer j & 1, so S(j+1) is computed while the softmax of page j runs
             auto issue_s = [&](int j) -> bool {
-                const int kb = j & 1;
-                if (!mbar_wait(smem_u32(&k_full[kb]), (uint32_t)((j >> 1) & 1))) return false;
+                const uint32_t kb = (uint32_t)j & 1u;
+                if (!mbar_wait(k_full0 + 8u * kb, (uint32_t)((j >> 1) & 1))) return false;
                 tc_fence_after();
+                const uint64_t kd = k_desc + (uint64_t)(kb * (uint32_t)(K_BYTES >> 4));
+                const uint32_t s_acc = tmem_base + S_COL + kb * BN;
 #pragma unroll
-                for (int ks = 0; ks < HD / 16; ++ks) {
-                    const uint64_t a = make_smem_desc(q_smem + (ks / 4) * BM * 128 + (ks % 4) * 32);
-                    const uint64_t bd = make_smem_desc(k_smem + kb * K_BYTES + (ks / 4) * BN * 128 + (ks % 4) * 32);
-                    umma(tmem_base + S_COL + kb * BN, a, bd, IDESC_S, ks > 0);
-                }
-                umma_commit(smem_u32(&k_empty[kb]));
-                umma_commit(smem_u32(&s_full[kb]));
+                for (int ks = 0; ks < HD / 16; ++ks)
+                    umma(s_acc, q_desc + (uint64_t)(((ks / 4) * BM * 128 + (ks % 4) * 32) >> 4),
+                         kd + (uint64_t)(((ks / 4) * BN * 128 + (ks % 4) * 32) >> 4), IDESC_S, ks > 0);
+                umma_commit(k_empty0 + 8u * kb);
+                umma_commit(s_full0 + 8u * kb);
                 return true;
             };
             if (ok && !issue_s(0)) { report(status, ST_ATTN_MMA); abort_flag = 1; ok = false; }
             for (int j = 0; j < n_pages && ok; ++j) {
                 // the buffer S(j+1) goes to was read by the softmax of page j-1, which arrived on p_full before PV(j-1)
                 if (j + 1 < n_pages && !issue_s(j + 1)) { report(status, ST_ATTN_MMA); abort_flag = 1; break; }
-                if (!mbar_wait(smem_u32(&p_full), (uint32_t)(j & 1)) ||
-                    !mbar_wait(smem_u32(&v_full[j & 1]), (uint32_t)((j >> 1) & 1))) {
+                const uint32_t vb = (uint32_t)j & 1u;
+                if (!mbar_wait(p_full_a, vb) || !mbar_wait(v_full0 + 8u * vb, (uint32_t)((j >> 1) & 1))) {
                     report(status, ST_ATTN_MMA); abort_flag = 1; break;
                 }
                 tc_fence_after();
+                const uint64_t vd = v_desc + (uint64_t)(vb * (uint32_t)(V_BYTES >> 4));
 #pragma unroll
-                for (int ks = 0; ks < BN / 16; ++ks) {
-                    const uint64_t a = make_smem_desc(p_smem + ks * 32);
-                    const uint64_t bd = make_smem_desc_mn(v_smem + (j & 1) * V_BYTES + ks * 16 * 128, BN * 128);
-                    umma(tmem_base + O_COL, a, bd, IDESC_PV, j > 0 || ks > 0);
-                }
-                umma_commit(smem_u32(&v_empty[j & 1]));
-                umma_commit(smem_u32(&pv_done));
+                for (int ks = 0; ks < BN / 16; ++ks)
+                    // P of page j lies, two bf16 to a column, over the first half of the score buffer it came from
+                    umma_ts(tmem_base + O_COL, tmem_base + S_COL + vb * BN + ks * 8, vd + (uint64_t)(ks * 16 * 128 >> 4),
+                            IDESC_PV, j > 0 || ks > 0);
+                umma_commit(v_empty0 + 8u * vb);
+                umma_commit(pv_done_a);
             }
         }
     } else {
@@ -250,7 +269,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             const bool whole = key0 + BN - 1 <= pos_lo + lane_base && (window <= 0 || key0 > pos_lo + lane_base + 31 - window);
             if (whole) {
 #pragma unroll
-                for (int c = 0; c < BN; ++c) mx_raw = fmaxf(mx_raw, __uint_as_float(sv[c]));
+                for (int c = 0; c < BN; c += 2)
+                    mx_raw = fmaxf(mx_raw, fmaxf(__uint_as_float(sv[c]), __uint_as_float(sv[c + 1])));
             } else {
 #pragma unroll
                 for (int c = 0; c < BN; ++c) {
@@ -267,15 +287,18 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             const float alpha = (!move) ? 1.f : ((m_used == -INFINITY) ? 0.f : fast_exp2(m_used - m_new));
             const float neg_mref = (m_new == -INFINITY) ? 0.f : -m_new;   // nothing visible yet: every p is 0
             // the exponentials do not need the previous P V product; everything after this does
-            float sum = 0.f;
+            // two scores at a time through the packed float32 pipe (one FMA and one ADD per pair)
+            const float2 scale2 = make_float2(scale_log2, scale_log2), shift2 = make_float2(neg_mref, neg_mref);
+            float2 sum2 = make_float2(0.f, 0.f);
             uint32_t pk[BN / 2];
 #pragma unroll
             for (int c = 0; c < BN; c += 2) {
-                const float p0 = fast_exp2(fmaf(__uint_as_float(sv[c]), scale_log2, neg_mref));
-                const float p1 = fast_exp2(fmaf(__uint_as_float(sv[c + 1]), scale_log2, neg_mref));
-                sum += p0 + p1;
-                pk[c >> 1] = pack2(p0, p1);
+                const float2 e = __ffma2_rn(make_float2(__uint_as_float(sv[c]), __uint_as_float(sv[c + 1])), scale2, shift2);
+                const float2 p = make_float2(fast_exp2(e.x), fast_exp2(e.y));
+                sum2 = __fadd2_rn(sum2, p);
+                pk[c >> 1] = pack2(p.x, p.y);
             }
+            const float sum = sum2.x + sum2.y;
             if (j > 0) {
                 // P's buffer and the accumulator are free once PV of the page before has finished
                 if (!mbar_wait(smem_u32(&pv_done), (uint32_t)((j - 1) & 1)) || abort_flag) {
@@ -299,14 +322,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             }
             l = l * alpha + sum;
             m_used = m_new;
-            const uint32_t prow = p_smem + (uint32_t)r * 128;
+            // P goes back to tensor memory, over the scores it was made from (this thread has read its row of
+            // them): the product P V takes its A operand from there, so P never passes through shared memory
 #pragma unroll
-            for (int c8 = 0; c8 < BN / 8; ++c8) {
-                const uint32_t dst = prow + (uint32_t)((c8 ^ (r & 7)) << 4);
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pk[4 * c8]), "r"(pk[4 * c8 + 1]),
-                             "r"(pk[4 * c8 + 2]), "r"(pk[4 * c8 + 3]) : "memory");
-            }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is read by the tensor core's proxy
+            for (int c = 0; c < BN / 2; c += 16) tmem_st16(trow + S_COL + (j & 1) * BN + c, pk + c);
+            tmem_wait_st();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&p_full));
@@ -359,7 +379,7 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
     constexpr int ATOMS = HD / 64;
     // Q, two K and two V pages, P, the barriers; with head_dim 128 no room for alignment padding is left if
     // two CTAs are to share an SM (the kernel refuses, with a status code, a shared window that needs any)
-    constexpr int TILES = ATOMS * BM * 128 + 4 * ATOMS * BN * 128 + BM * 128;
+    constexpr int TILES = ATOMS * BM * 128 + 4 * ATOMS * BN * 128;
     constexpr int SMEM = TILES + (HD >= 128 ? 256 : 1024 + 256);
     auto kernel = attn_prefill_tc_kernel<HD>;
     static bool configured = false;
