@@ -523,3 +523,44 @@ def test_sampling_top_k_top_p_and_penalty_follow_the_reference():
     assert _sample(l, temperature=0.0) == [1]
     assert _sample(l, temperature=0.0, penalty=1.1, recent=torch.tensor([[1]], dtype=torch.int32, device=DEV),
                    recent_count=torch.tensor([1], dtype=torch.int32, device=DEV)) == [2]
+
+
+@pytest.mark.parametrize("vocab, kw", [
+    (152064, dict(top_k=40, top_p=0.95)), (152064, dict(top_k=1000)), (152064, dict(top_k=1024, top_p=0.5)),
+    (4099, dict(top_k=7)), (5, dict(top_k=3, top_p=0.9)), (37, dict(top_k=36)),
+])
+def test_sampling_top_k_over_a_candidate_list(vocab, kw):
+    """With top-k the kernel keeps a short list of candidates instead of walking the vocabulary for every
+    threshold: the drawn token must lie where the plain filters put the uniform number."""
+    g = torch.Generator().manual_seed(vocab)
+    rows, seed = 6, 11
+    logits = torch.randn(rows, vocab, generator=g) * 3
+    logits[:, 1] = logits[:, 3]
+    got = _sample(logits, temperature=0.7, seed=seed, **kw)
+    for r in range(rows):
+        u = rng.uniform(seed, r, 0)
+        p = plain_impl.softmax_rows((logits[r].double() / 0.7)[None])[0]
+        p = plain_impl.top_k_filter(p, kw.get("top_k", 0))
+        p = plain_impl.top_p_filter(p, kw.get("top_p", 1.0))
+        assert p[got[r]] > 0, (kw, r, "a filtered token was drawn")
+        cdf = torch.cumsum(p, dim=0)
+        lo = cdf[got[r] - 1].item() if got[r] > 0 else 0.0
+        assert lo - 2e-5 <= u <= cdf[got[r]].item() + 2e-5, (kw, r, got[r], u)
+
+
+def test_sampling_top_k_with_more_ties_than_the_list_holds():
+    """Rows in which thousands of ids tie with the k-th largest: every one of them is kept (sampler.rs:130-160
+    keeps ties), the candidate list cannot hold them, and the kernel takes the long way."""
+    vocab, rows, seed = 20000, 4, 3
+    logits = torch.zeros(rows, vocab)
+    logits[:, ::2] = 1.0                                             # ten thousand ids share the maximum
+    logits[2, 77] = 3.0
+    got = _sample(logits, temperature=1.0, seed=seed, top_k=50)
+    for r in range(rows):
+        u = rng.uniform(seed, r, 0)
+        p = plain_impl.softmax_rows(logits[r].double()[None])[0]
+        p = plain_impl.top_k_filter(p, 50)
+        assert (p > 0).sum() >= 10000 and p[got[r]] > 0
+        cdf = torch.cumsum(p, dim=0)
+        lo = cdf[got[r] - 1].item() if got[r] > 0 else 0.0
+        assert lo - 2e-5 <= u <= cdf[got[r]].item() + 2e-5, (r, got[r], u)
