@@ -216,10 +216,11 @@ __device__ void finish_row(float* p, int n, const int* ids, int top_k, float top
 }
 
 __global__ void __launch_bounds__(THREADS)
-sample_kernel(float* __restrict__ logits, int vocab, int* __restrict__ out, float temperature, int top_k,
+sample_kernel(float* __restrict__ logits, int vocab, int* out, float temperature, int top_k,
               float top_p, float penalty, const int* __restrict__ recent, int recent_ld,
               const int* __restrict__ recent_count, unsigned long long seed, const int* __restrict__ row_stream,
-              const int* __restrict__ row_counter, int counter_offset, int* __restrict__ mirror) {
+              const int* __restrict__ row_counter, int counter_offset, int* __restrict__ mirror,
+              const int* newest) {      // `newest` and `out` may be the same buffer: a row reads before it writes
     __shared__ float fscratch[33];
     __shared__ int iscratch[33];
     __shared__ float chunk_sum[THREADS];
@@ -235,11 +236,13 @@ sample_kernel(float* __restrict__ logits, int vocab, int* __restrict__ out, floa
     float* p = logits + (size_t)r * vocab;
 
     // ---- repetition penalty (sampler.rs:109-127) ----
-    if (penalty != 1.0f && recent != nullptr) {
+    if (penalty != 1.0f && (recent != nullptr || newest != nullptr)) {
         if (tid == 0) {
-            const int n = recent_count[r];
-            for (int i = 0; i < n; ++i) {
-                const int id = recent[(size_t)r * recent_ld + i];
+            const int n = recent != nullptr ? recent_count[r] : 0;
+            for (int i = 0; i <= n; ++i) {
+                // the row's recent ids, then the newest one, which may still be on the device only
+                if (i == n && newest == nullptr) break;
+                const int id = i < n ? recent[(size_t)r * recent_ld + i] : newest[r];
                 if (id >= 0 && id < vocab) {
                     if (p[id] > 0.f) p[id] /= penalty; else p[id] *= penalty;
                 }
@@ -439,10 +442,12 @@ sample_kernel(float* __restrict__ logits, int vocab, int* __restrict__ out, floa
 // row_stream / row_counter: int32 [rows], which sequence a row is and how many tokens it has drawn;
 // counter_offset is added to every row's counter (rows that advance together keep their array).
 // mirror (may be null): int32 [rows] in host memory the device can write; receives the tokens too.
+// newest (may be null): int32 [rows] on the device, one more recent id per row (the token of the step
+// before, which the host may not have read yet); penalised after the ids of `recent`.
 RI_API int ri_sample(float* logits, int rows, int vocab, int* out, float temperature, int top_k, float top_p,
                      float penalty, const int* recent, int recent_ld, const int* recent_count,
                      unsigned long long seed, const int* row_stream, const int* row_counter, int counter_offset,
-                     int* mirror, cudaStream_t stream) {
+                     int* mirror, const int* newest, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (vocab <= 0) return fail("sample: vocabulary of %d", vocab);
     if (penalty <= 0.f) return fail("sample: repetition penalty %f must be positive", penalty);
@@ -459,7 +464,7 @@ RI_API int ri_sample(float* logits, int rows, int vocab, int* out, float tempera
     }
     cudaError_t e = launch_dependent(sample_kernel, dim3(rows), dim3(THREADS), (size_t)0, stream, logits, vocab, out,
                                      temperature, top_k, top_p, penalty, recent, recent_ld, recent_count, seed,
-                                     row_stream, row_counter, counter_offset, mirror);
+                                     row_stream, row_counter, counter_offset, mirror, newest);
     return check_launch(e, "sample");
 }
 

@@ -127,7 +127,7 @@ class Generator:
             if not live:
                 return
 
-    def _run_batch_ahead(self, live, prompts, max_tokens, results) -> None:
+    def _run_batch_ahead(self, live, prompts, max_tokens, results, uses_history=False) -> None:
         """The same with one step of lookahead: while the host reads the tokens sampled by step i,
         step i+1 already runs on them."""
         import torch
@@ -139,12 +139,17 @@ class Generator:
         ring = [torch.empty(len(live), dtype=torch.int32).pin_memory() for _ in range(4)]
         turn = [0]
 
-        def sample(logits, seqs, drawn):
+        def sample(logits, seqs, drawn, newest=None):
             host = ring[turn[0] % len(ring)][:len(seqs)]
             turn[0] += 1
             # straight into the buffer the next step of this batch size reads its tokens from
             out = eng.decode_token_buffer(len(seqs)) if hasattr(eng, "decode_token_buffer") else None
-            tokens_dev = self.sampler.sample(logits, [s.index for s in seqs], drawn, None, out=out, mirror=host)
+            # With a repetition penalty the host's histories lack the token that was just fed (it has not
+            # been read yet): the kernel takes that one from the device.  It reads `newest` before it writes
+            # `out`, so the two may be the same buffer.
+            tokens_dev = self.sampler.sample(logits, [s.index for s in seqs], drawn,
+                                             [s.history for s in seqs] if uses_history else None,
+                                             out=out, mirror=host, newest=newest if uses_history else None)
             ev = torch.cuda.Event()
             ev.record()
             self.d2h_bytes += host.numel() * 4
@@ -165,7 +170,7 @@ class Generator:
                     torch.tensor(rows, dtype=torch.long, device=tokens_dev.device)]
                 logits = eng.step_from_device([s.slot for s in ahead], feed_dev)
                 self.steps += 1
-                nxt = (ahead,) + sample(logits, ahead, [len(s.tokens) + 1 for s in ahead])
+                nxt = (ahead,) + sample(logits, ahead, [len(s.tokens) + 1 for s in ahead], newest=feed_dev)
             ev.synchronize()                                         # the earlier tokens; the step just launched keeps running
             if hasattr(eng, "check_device_status"):
                 eng.check_device_status()
@@ -175,6 +180,8 @@ class Generator:
             for s, tok in zip(seqs, host.tolist()):
                 if not self._finish_or_keep(s, int(tok), max_tokens, results):
                     stopped.add(id(s))
+                elif uses_history:
+                    s.history.append(int(tok))
             if nxt is not None and stopped:
                 # a sequence that sampled a stop token ran the step ahead for nothing: drop its row
                 ahead, sampled, (host2, ev2) = nxt
@@ -209,11 +216,11 @@ class Generator:
                 live.append(_Live(index=i, slot=self.engine.alloc_slot(), prompt_length=len(prompts[i]),
                                   history=list(prompts[i]) if uses_history else []))
             nxt += count
-            lookahead = (not uses_history and hasattr(self.sampler, "sample")
+            lookahead = (hasattr(self.sampler, "sample")
                          and getattr(self.engine, "can_feed_from_device", lambda: False)())
             try:
                 if lookahead:
-                    self._run_batch_ahead(live, prompts, max_tokens, results)
+                    self._run_batch_ahead(live, prompts, max_tokens, results, uses_history)
                 else:
                     self._run_batch(live, prompts, max_tokens, results, uses_history)
             finally:

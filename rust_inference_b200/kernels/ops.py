@@ -190,10 +190,13 @@ def sample(logits: torch.Tensor, out: torch.Tensor, *, temperature: float, top_k
            penalty: float = 1.0, recent: torch.Tensor | None = None, recent_count: torch.Tensor | None = None,
            seed: int = 0, row_stream: torch.Tensor | None = None,
            row_counter: torch.Tensor | None = None, counter_offset: int = 0,
-           mirror: torch.Tensor | None = None) -> torch.Tensor:
+           mirror: torch.Tensor | None = None, newest: torch.Tensor | None = None) -> torch.Tensor:
     """One token per row of float32 logits [R, V] (overwritten).  out: int32 [R].  `mirror`: a
-    pinned int32 host tensor [R] that receives the tokens as well (the kernel writes it directly)."""
-    _need_cuda(logits, out, recent, recent_count, row_stream, row_counter)
+    pinned int32 host tensor [R] that receives the tokens as well (the kernel writes it directly).
+    `newest`: int32 [R] on the device, one more recent id per row for the repetition penalty."""
+    _need_cuda(logits, out, recent, recent_count, row_stream, row_counter, newest)
+    _need(newest is None or (newest.dtype == torch.int32 and newest.is_contiguous() and newest.numel() >= logits.shape[0]),
+          "sample: newest must be int32 [R]")
     rows, vocab = logits.shape
     _need(logits.dtype == torch.float32 and logits.is_contiguous(), "sample: logits must be contiguous float32")
     _need(out.dtype == torch.int32 and out.numel() >= rows, "sample: out must be int32 [R]")
@@ -207,7 +210,7 @@ def sample(logits: torch.Tensor, out: torch.Tensor, *, temperature: float, top_k
           c_int(top_k), c_float(top_p), c_float(penalty), _p(recent),
           c_int(recent.shape[1] if recent is not None else 0), _p(recent_count),
           c_ulonglong(seed & 0xFFFFFFFFFFFFFFFF), _p(row_stream), _p(row_counter), c_int(counter_offset),
-          c_void_p(mirror.data_ptr() if mirror is not None else 0), _stream())
+          c_void_p(mirror.data_ptr() if mirror is not None else 0), _p(newest), _stream())
     return out
 
 

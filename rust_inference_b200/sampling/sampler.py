@@ -42,16 +42,20 @@ class Sampler:
         return dev
 
     def sample(self, logits: torch.Tensor, streams: list, counters: list, histories: list | None = None,
-               out: torch.Tensor | None = None, mirror: torch.Tensor | None = None) -> torch.Tensor:
+               out: torch.Tensor | None = None, mirror: torch.Tensor | None = None,
+               newest: torch.Tensor | None = None) -> torch.Tensor:
         """logits: float32 [R, V] on the device (overwritten).  Returns int32 [R] on the device
         (`out` if given).  `mirror`: a pinned int32 host tensor that receives the tokens too,
-        written by the kernel itself."""
+        written by the kernel itself.  `newest`: int32 [R] on the device, each row's latest token
+        when `histories` does not hold it yet (the host has not read it): it counts as the most
+        recent id of the repetition window."""
         p = self.params
         rows = logits.shape[0]
         if out is None:
             out = torch.empty(rows, dtype=torch.int32, device=self.device)
         recent = recent_count = None
         width = p.repetition_window if p.uses_history else 0
+        keep = width - 1 if (width and newest is not None) else width       # ids of the window the host supplies
         if not width:
             # Without a history the rows' arrays are the streams and the counters.  The same rows one
             # draw further on keep the arrays they have on the device; the kernel adds the difference.
@@ -75,7 +79,7 @@ class Sampler:
         if width:
             hist = meta[3 * rows:].reshape(rows, width)
             for r, h in enumerate(histories):
-                tail = h[-width:]
+                tail = h[-keep:] if keep > 0 else []
                 meta[2 * rows + r] = len(tail)
                 hist[r, :len(tail)] = tail
         dev = self._stage(meta)
@@ -85,5 +89,6 @@ class Sampler:
             recent = dev[3 * rows:].view(rows, width)
         ops.sample(logits, out, temperature=p.temperature, top_k=p.top_k, top_p=p.top_p,
                    penalty=p.repetition_penalty, recent=recent, recent_count=recent_count, seed=p.seed,
-                   row_stream=row_stream, row_counter=row_counter, mirror=mirror)
+                   row_stream=row_stream, row_counter=row_counter, mirror=mirror,
+                   newest=newest if width else None)
         return out

@@ -149,6 +149,35 @@ def test_greedy_generation_through_the_entry_point(model_factory):
             seq.append(tok)
 
 
+def test_greedy_generation_with_the_repetition_penalty(model_factory):
+    """Penalised greedy (the reference's command line always penalises, main.rs:187-188): every step the
+    logits of the last `window` ids of prompt + generated tokens are divided or multiplied by the penalty
+    (sampler.rs:76-78, :109-127), then the first maximum is taken.  The generation loop runs one step
+    ahead here, so the newest id of the window reaches the sampler on the device."""
+    from rust_inference_b200 import Model, SamplerConfig
+    model = model_factory("A", std=0.08)
+    prompts = [random_tokens(n, model.cfg["vocab_size"], seed=40 + n) for n in (3, 9, 70)]
+    cfg = SamplerConfig(temperature=0.0, top_k=0, top_p=1.0, repetition_penalty=1.6, repetition_window=5)
+    want = []
+    for p in prompts:
+        seq, out = list(p), []
+        for _ in range(12):
+            logits = plain_impl.repetition_penalty(model.plain_logits(seq)[-1], seq, 1.6, 5)
+            tok = plain_impl.argmax_first(logits)
+            out.append(tok)
+            seq.append(tok)
+        want.append(out)
+    plain_greedy = [plain_impl.greedy_generate(model.weights, model.cfg, p, 12) for p in prompts]
+    assert want != plain_greedy                                  # the penalty changes what is generated
+    m = Model.load(model.folder, dtype="float32", max_tokens_in_cache=1024)
+    assert m.engine.can_feed_from_device()
+    got = m.generate(prompts, 12, cfg, stop_ids=())
+    assert [g.tokens for g in got] == want
+    # one at a time (other batch sizes, other buffers) gives the same
+    got1 = m.generate(prompts, 12, cfg, stop_ids=(), max_batch=1)
+    assert [g.tokens for g in got1] == want
+
+
 def test_temperature_sampling_is_reproducible_and_batch_independent(model_factory):
     from rust_inference_b200 import Model, SamplerConfig
     model = model_factory("B", std=0.08)
