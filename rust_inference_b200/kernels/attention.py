@@ -8,13 +8,19 @@
 """
 from __future__ import annotations
 
+import functools
 import os
 
 import torch
 
 from . import ops
 
-N_SMS = 148
+
+@functools.lru_cache(maxsize=None)
+def _sm_count() -> int:
+    """SMs of the current device (148 on a B200)."""
+    return int(torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count)
+
 # RI_B200_PREFILL_ATTENTION=mma keeps the mma.sync prefill kernel (for comparisons)
 _PREFILL = os.environ.get("RI_B200_PREFILL_ATTENTION", "tcgen05")
 # RI_B200_DECODE_ATTENTION=cluster / cp_async / tma forces one of the decode kernels (default: by batch size)
@@ -27,7 +33,7 @@ def decode_splits(n_seqs: int, n_kv_heads: int, max_seq_len: int, page_size: int
     never more, so the grid is one wave; never more runs than the longest sequence has pages.
     Depends on the batch size and the cache geometry only, so a captured step keeps its grid."""
     pairs = max(1, n_seqs * n_kv_heads)
-    want = (2 * N_SMS) // pairs
+    want = (2 * _sm_count()) // pairs
     if os.environ.get("RI_B200_DECODE_SPLITS"):
         want = int(os.environ["RI_B200_DECODE_SPLITS"])
     return max(1, min(want, limit, -(-max_seq_len // page_size)))

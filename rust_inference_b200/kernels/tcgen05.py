@@ -9,7 +9,6 @@ import torch
 from . import build, ops
 from .ops import KernelError, _call, _need, _need_cuda, _p, _stream
 
-N_SMS = 148
 _status = None     # host-visible word a kernel writes when one of its bounded waits ran out
 _x_maps: dict = {}  # tensor maps of activation buffers, by (pointer, rows, K, token tile)
 

@@ -3,7 +3,11 @@
 This file rests on the formulas of yudono/rust-inference's CPU code: the crate is a
 binary with private modules that needs a Rust toolchain and crates from the network,
 neither of which exists here, so it cannot be imported or compiled for a golden run.
-Every function below cites the lines of the reference that it restates.
+Every function below cites the lines of the reference that it restates.  In place of a
+golden run of the reference, `tests/golden/` holds a second, independent statement of the
+same formulas (a scalar C++ program: loops, one token at a time, a cache), the logits it
+computes on two tiny models, and the script that made them; `tests/test_plain_impl.py`
+compares this file with them.
 
 It processes whole sequences, keeps no cache, has one function for each part and
 shares no code with the package under test: it only uses torch tensor arithmetic

@@ -130,3 +130,50 @@ def test_greedy_generate_stops_without_emitting(tmp_path):
     stop = out[2]
     cut = plain_impl.greedy_generate(m.weights, m.cfg, [5, 6, 7], 6, stop_ids=(stop,))
     assert cut == out[:out.index(stop)]
+
+
+# ----------------------------------------------------------------------------------------
+# A second statement of the same formulas: tests/golden/scalar_decoder.cpp (scalar loops, one token
+# at a time, a cache).  Its logits on the tiny configurations are stored beside it.
+# ----------------------------------------------------------------------------------------
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_plain_implementation_agrees_with_the_scalar_program(name):
+    import json
+    import os
+    import sys
+    import numpy as np
+    golden = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+    sys.path.insert(0, golden)
+    import make_golden
+    with open(os.path.join(golden, f"{name}.json")) as f:
+        meta = json.load(f)
+    want = torch.from_numpy(np.fromfile(os.path.join(golden, f"{name}.logits.f32"), dtype=np.float32)
+                            .reshape(meta["shape"]))
+    cfg, w = make_golden.tiny_weights(name)
+    assert make_golden.tokens_of(name, cfg.vocab_size) == meta["tokens"]
+    weights = {k: torch.from_numpy(v) for k, v in w.items()}
+    got = plain_impl.forward(weights, cfg.to_dict(), meta["tokens"])
+    assert got.shape == want.shape
+    err = ((got - want).abs().max() / want.abs().max()).item()
+    assert err <= 2e-5, err                                 # two orders of summation in float32
+
+
+def test_the_scalar_program_reproduces_its_stored_logits(tmp_path):
+    """Where a C++ compiler is at hand, build the scalar program and run it again."""
+    import json
+    import os
+    import shutil
+    import sys
+    import numpy as np
+    if shutil.which("g++") is None:
+        pytest.skip("no g++")
+    golden = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+    sys.path.insert(0, golden)
+    import make_golden
+    binary = make_golden.build(str(tmp_path))
+    cfg, w = make_golden.tiny_weights("A")
+    with open(os.path.join(golden, "A.json")) as f:
+        meta = json.load(f)
+    again = make_golden.run_scalar(binary, cfg, w, meta["tokens"], str(tmp_path))
+    want = np.fromfile(os.path.join(golden, "A.logits.f32"), dtype=np.float32).reshape(meta["shape"])
+    assert np.abs(again - want).max() <= 1e-6 * np.abs(want).max()
