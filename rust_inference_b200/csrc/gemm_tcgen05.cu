@@ -697,7 +697,7 @@ RI_API int ri_gemm_tcgen05_set_long_tile(int tn) {
 //  up to 128 tokens   one token tile, as narrow as the step allows.  Such steps stream weights:
 //                     measured in a replayed graph at 8 tokens, the o, q/k/v and down projections of
 //                     a 3584-wide model are fastest with about two CTAs per SM (7-10 pieces) and at
-//                     least 4 k-blocks per piece.
+//                     least 4 k-blocks per piece (more for wider steps, whose pieces end in more atomics).
 //  beyond, SiLU-gate  the token-major kernel, 128 tokens per tile.
 //  beyond, others     the feature-major kernel.  Measured at 192..4,096 tokens: a k-block takes about
 //                     as long whatever the tile's width (128..256), so what counts is how many rounds
@@ -714,8 +714,11 @@ RI_API int ri_gemm_tcgen05_plan(int n_tok, int n_feat, int K, int mode, int* til
     if (n_tok <= 128) {
         tn = n_tok <= 16 ? 16 : (n_tok + 15) / 16 * 16;
         if (can_split && feat_tiles < ctas) {
+            // every piece ends in tn x 128 atomic adds, so wider steps want longer pieces: at least a tenth of
+            // the tile's width in k-blocks (128 tokens, K = 3584: 4-5 pieces, 11 us, against 10 pieces, 13 us)
+            const int min_kb = tn / 10 > 4 ? (tn + 9) / 10 : 4;
             long long want = (2 * ctas) / feat_tiles;
-            if (want > total_kb / 4) want = total_kb / 4;
+            if (want > total_kb / min_kb) want = total_kb / min_kb;
             sp = want < 1 ? 1 : (int)want;
         }
     } else if (mode == 3) {
