@@ -89,3 +89,30 @@ def test_host_rng_is_a_uniform_in_open_closed_unit_interval():
     assert len(set(us)) > 990
     assert rng.uniform(1, 2, 3) == rng.uniform(1, 2, 3) != rng.uniform(1, 3, 2)
     assert all(u * 2 ** 24 == int(u * 2 ** 24) for u in us[:50])
+
+
+def test_bench_contract_without_a_gpu():
+    """`bench.py` for more than one GPU says so in one line and exits with 2; the reference arm prints
+    its `unavailable` line and exits with 0; the benchmark model is configs[2] of BASELINE.json."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    bench = os.path.join(root, "bench.py")
+    many = subprocess.run([sys.executable, bench, "--gpus", "2", "--steps", "2", "--warmup", "1"],
+                          capture_output=True, text=True)
+    assert many.returncode == 2 and len(many.stdout.strip().splitlines()) == 1
+    ref = subprocess.run([sys.executable, bench, "--impl", "reference", "--gpus", "1"], capture_output=True, text=True)
+    assert ref.returncode == 0
+    line = json.loads(ref.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and "unavailable" in line
+    sys.path.insert(0, root)
+    import bench as bench_module
+    m = bench_module.MODEL
+    assert (m["num_hidden_layers"], m["hidden_size"], m["num_attention_heads"], m["num_key_value_heads"],
+            m["head_dim"], m["intermediate_size"], m["vocab_size"]) == (28, 3584, 28, 4, 128, 18944, 152064)
+    with open(os.path.join(root, "BASELINE.json")) as f:
+        text = json.load(f)["configs"][2]
+    for number in ("28 layers", "hidden 3584", "28 heads", "4 kv heads", "head_dim 128", "18944", "152064"):
+        assert number in text
