@@ -427,15 +427,18 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         if (lane == 0) {
             const int* pages = page_table + (size_t)seq_slot[b] * max_pages;
             int issued = 0;
+            int page_next = pg_begin < pg_end ? pages[pg_begin] : 0;   // a page's number is fetched one turn ahead
             for (int pg = pg_begin; pg < pg_end; ++pg) {
                 const int j = pg - pg_begin, s = j % RING;
+                const int page_now = page_next;
+                if (pg + 1 < pg_end) page_next = pages[pg + 1];
                 if (pg == pg_hi - 1) wait_for_previous_kernels();      // the page the new key and value went to
                 if (!tc::mbar_wait(smem_u32(&empty_bar[s]), (uint32_t)((j / RING) & 1) ^ 1u) || abort_flag) {
                     tc::report(status, 21);
                     abort_flag = 1;
                     break;
                 }
-                const int row = (pages[pg] * n_kv_heads + kvh) * PAGE;
+                const int row = (page_now * n_kv_heads + kvh) * PAGE;
                 const uint32_t bar = smem_u32(&full_bar[s]);
                 tc::mbar_expect_tx(bar, 2 * TILE);
 #pragma unroll

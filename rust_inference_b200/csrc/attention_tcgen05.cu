@@ -170,8 +170,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             for (int a = 0; a < ATOMS; ++a)
                 tma_load_2d(q_smem + a * BM * 128, &map_q, smem_u32(&q_full), h * HD + a * 64, tok0 + q0);
             int k_issued = 0, v_issued = 0;
+            int page_next = pages[pg_begin];                        // a page's number is fetched one turn ahead
             for (int j = 0; j < n_pages; ++j) {
-                const int row = (pages[pg_begin + j] * n_kv_heads + kvh) * BN;
+                const int row = (page_next * n_kv_heads + kvh) * BN;
+                if (j + 1 < n_pages) page_next = pages[pg_begin + j + 1];
                 const int kb = j & 1;
                 if (!mbar_wait(smem_u32(&k_empty[kb]), (uint32_t)((j >> 1) & 1) ^ 1u) || abort_flag) {
                     report(status, ST_ATTN_PRODUCER); abort_flag = 1; break;
