@@ -156,6 +156,10 @@ __device__ __forceinline__ void softmax_update(float (*s)[4], float* m, float* l
 // ---------------------------------------------------------------------------------------------
 // decode: one token per sequence, split over runs of pages
 // ---------------------------------------------------------------------------------------------
+constexpr int MAX_CLUSTER_SPLITS = 8;                          // the portable cluster size
+constexpr int NBUF = 3;             // page buffers of the cp.async decode kernel: with three, a run of three pages is in
+                                    // flight before the kernel has even waited for its predecessor
+
 template <int HD, bool CLUSTER>
 __global__ void __launch_bounds__(THREADS)
 attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_ld, const __nv_bfloat16* __restrict__ kcache,
@@ -166,12 +170,13 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_ld, const __nv_bfl
                    __nv_bfloat16* __restrict__ out, int out_ld) {
     constexpr int TILE = PAGE * HD * 2;                 // bytes of one K or V page tile
     extern __shared__ __align__(128) uint8_t smem[];
-    // [2 buffers][K tile, V tile], then the Q tile [16][HD]
+    // [NBUF buffers][K tile, V tile], then the Q tile [16][HD], then (cluster form) what the peers send
     const uint32_t kv_base = smem_u32(smem);
-    const uint32_t q_tile = kv_base + 4 * TILE;
+    const uint32_t q_tile = kv_base + 2 * NBUF * TILE;
 
     const int b = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
     let_next_kernel_start();
+    if (CLUSTER) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");   // "this CTA runs": waited for before the merge
     // What the step fixed before its first kernel (lengths, slots, the page table) and the pages that
     // hold only older positions are written by no kernel of this step: they are read, and the first
     // page's copy is started, while the kernel before this one still runs.
@@ -192,18 +197,22 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_ld, const __nv_bfl
         load_tile_async<HD>(kv_base + (2 * buf + 1) * TILE, vcache + base, PAGE);
         cp_async_commit();
     };
-    // the page of the new token (the sequence's last) is still being written by the kernel before
-    const bool early = pg_begin < pg_end && pg_begin != pg_hi - 1;
-    if (early) issue(pg_begin, 0);
+    // up to NBUF pages are on their way before the wait; the page of the new token (the sequence's last) is
+    // still being written by the kernel before and has to stay behind it
+    const int n_pages = max(0, pg_end - pg_begin);
+    int issued = 0;
+    while (issued < n_pages && issued < NBUF && pg_begin + issued != pg_hi - 1) {
+        issue(pg_begin + issued, issued);
+        ++issued;
+    }
     wait_for_previous_kernels();          // q and the newest key and value come from the kernel before
     // Q rows: head kvh*n_rep + r for r < n_rep, zero above
     for (int idx = threadIdx.x; idx < 16 * (HD / 8); idx += THREADS) {
         const int r = idx / (HD / 8), c = idx % (HD / 8);
         uint4 v = make_uint4(0, 0, 0, 0);
         if (r < n_rep) v = *reinterpret_cast<const uint4*>(q + (size_t)token * q_ld + (size_t)(kvh * n_rep + r) * HD + c * 8);
-        *reinterpret_cast<uint4*>(smem + 4 * TILE + tile_off<HD>(r, c)) = v;
+        *reinterpret_cast<uint4*>(smem + 2 * NBUF * TILE + tile_off<HD>(r, c)) = v;
     }
-    if (pg_begin < pg_end && !early) issue(pg_begin, 0);
     __syncthreads();                                      // Q tile written
 
     uint32_t qf[HD / 16][4];
@@ -220,13 +229,15 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_ld, const __nv_bfl
     for (int t = 0; t < HD / 8; ++t) o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.f;
 
     for (int pg = pg_begin; pg < pg_end; ++pg) {
-        const int buf = (pg - pg_begin) & 1;
-        if (pg + 1 < pg_end) {
-            issue(pg + 1, buf ^ 1);
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
+        const int i = pg - pg_begin, buf = i % NBUF;
+        // page j goes to buffer j % NBUF, which the barrier at the end of page j - NBUF has set free
+        while (issued < n_pages && issued <= i + NBUF - 1) {
+            issue(pg_begin + issued, issued % NBUF);
+            ++issued;
         }
+        // the copies complete in the order they were issued: all but the ones behind this page's
+        const int behind = issued - i - 1;
+        if (behind >= 2) cp_async_wait<2>(); else if (behind == 1) cp_async_wait<1>(); else cp_async_wait<0>();
         __syncthreads();                                  // this page's tiles have landed for everyone
         const uint32_t ktile = kv_base + (2 * buf) * TILE, vtile = ktile + TILE;
         const int kbase = warp * 16;                      // this warp's 16 keys of the page
@@ -267,9 +278,17 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_ld, const __nv_bfl
         sml[((warp * 16 + g + 8) << 1) + 1] = l[1];
     }
     __syncthreads();
-    // the CTA's merged partial result for the cluster: [n_rep][HD] and [n_rep][2], behind the warps' areas
-    float* fo = sml + 4 * 16 * 2;
-    float* fml = fo + 16 * HD;
+    // cluster form: what the peers send lies behind the Q tile, outside anything a CTA still works on
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    const int chunk = (n_rep * HD + n_splits - 1) / n_splits;
+    float* recv_o = reinterpret_cast<float*>(smem + 2 * NBUF * TILE + 16 * HD * 2);   // [n_splits][chunk]
+    float* recv_ml = recv_o + 16 * HD + MAX_CLUSTER_SPLITS;                           // [n_splits][16][2]
+    if (CLUSTER) {
+        // every CTA of the cluster has arrived at the barrier near its start by now: all of them exist, so
+        // their shared memory may be written
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    }
     for (int idx = threadIdx.x; idx < n_rep * HD; idx += THREADS) {
         const int r = idx / HD, d = idx % HD;
         float M = -INFINITY;
@@ -286,11 +305,17 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_ld, const __nv_bfl
         }
         const int h = kvh * n_rep + r;
         if (CLUSTER) {
-            fo[idx] = acc;
-            if (d == 0) {
-                fml[2 * r] = M;
-                fml[2 * r + 1] = L;
-            }
+            // The splits of this (sequence, kv head) are the CTAs of one cluster (its z extent).  Output idx is
+            // merged by CTA idx / chunk: every CTA sends its partial value there, and its row statistics to
+            // everyone, with plain stores into the peers' shared memory; nothing is read remotely.
+            const int owner = idx / chunk;
+            cluster.map_shared_rank(recv_o, owner)[split * chunk + (idx - owner * chunk)] = acc;
+            if (d == 0)
+                for (int sp = 0; sp < n_splits; ++sp) {
+                    float* ml = cluster.map_shared_rank(recv_ml, sp) + (split * 16 + r) * 2;
+                    ml[0] = M;
+                    ml[1] = L;
+                }
         } else if (n_splits == 1) {
             out[(size_t)token * out_ld + (size_t)h * HD + d] = __float2bfloat16_rn(acc / L);
         } else {
@@ -303,32 +328,24 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_ld, const __nv_bfl
         }
     }
     if (CLUSTER) {
-        // The splits of this (sequence, kv head) are the CTAs of one cluster (its z extent).  After the
-        // barrier each merges its slice of the n_rep * HD outputs over all peers by log-sum-exp, reading
-        // their partial results through distributed shared memory, and writes the final rows.
-        namespace cg = cooperative_groups;
-        cg::cluster_group cluster = cg::this_cluster();
-        cluster.sync();
-        const int total = n_rep * HD;
-        const int chunk = (total + n_splits - 1) / n_splits;
-        const int lo = split * chunk, hi = min(total, lo + chunk);
+        cluster.sync();                                   // everything sent has arrived
+        const int lo = split * chunk, hi = min(n_rep * HD, lo + chunk);
         for (int idx = lo + (int)threadIdx.x; idx < hi; idx += THREADS) {
             const int r = idx / HD, d = idx % HD;
             float M = -INFINITY;
-            for (int sp = 0; sp < n_splits; ++sp) M = fmaxf(M, cluster.map_shared_rank(fml, sp)[2 * r]);
+            for (int sp = 0; sp < n_splits; ++sp) M = fmaxf(M, recv_ml[(sp * 16 + r) * 2]);
             float L = 0.f, acc = 0.f;
             for (int sp = 0; sp < n_splits; ++sp) {
-                const float* pml = cluster.map_shared_rank(fml, sp);
-                const float ms = pml[2 * r];
+                const float ms = recv_ml[(sp * 16 + r) * 2];
                 if (ms != -INFINITY) {
                     const float f = expf(ms - M);
-                    L += f * pml[2 * r + 1];
-                    acc += f * cluster.map_shared_rank(fo, sp)[idx];
+                    L += f * recv_ml[(sp * 16 + r) * 2 + 1];
+                    acc += f * recv_o[sp * chunk + (idx - lo)];
                 }
             }
             out[(size_t)token * out_ld + (size_t)(kvh * n_rep + r) * HD + d] = __float2bfloat16_rn(acc / L);
         }
-        cluster.sync();                                   // nobody leaves while a peer may still read its shared memory
+        // nobody reads or writes a peer's shared memory after that barrier: a CTA may leave when it is done
     }
 }
 
@@ -694,7 +711,7 @@ int launch_decode(const void* q, int q_ld, const void* kc, const void* vc, const
                   const int* seq_slot, const int* seq_len, const int* cu_seqlens, int n_seqs, int n_heads,
                   int n_kv_heads, float scale, int window, int n_splits, float* part_o, float* part_ml, void* out,
                   int out_ld, cudaStream_t stream) {
-    constexpr int SMEM = 4 * PAGE * HD * 2 + 16 * HD * 2;      // also covers the merge area 4*16*HD*4 + 512
+    constexpr int SMEM = 2 * NBUF * PAGE * HD * 2 + 16 * HD * 2;      // also covers the merge area 4*16*HD*4 + 512
     static_assert(4 * 16 * HD * 4 + 4 * 16 * 2 * 4 <= SMEM, "merge area must fit");
     static bool configured = false;
     if (!configured) {
@@ -718,15 +735,15 @@ int launch_decode(const void* q, int q_ld, const void* kc, const void* vc, const
 }
 
 // The splits of a (sequence, kv head) as one thread-block cluster that merges its own partial results.
-constexpr int MAX_CLUSTER_SPLITS = 8;                          // the portable cluster size
 
 template <int HD>
 int launch_decode_cluster(const void* q, int q_ld, const void* kc, const void* vc, const int* page_table, int max_pages,
                           const int* seq_slot, const int* seq_len, const int* cu_seqlens, int n_seqs, int n_heads,
                           int n_kv_heads, float scale, int window, int n_splits, void* out, int out_ld,
                           cudaStream_t stream) {
-    constexpr int SMEM = 4 * PAGE * HD * 2 + 16 * HD * 2;
-    static_assert((4 * 16 * HD + 4 * 16 * 2 + 16 * HD + 16 * 2) * 4 <= SMEM, "merge areas must fit");
+    // page buffers (the warps' merge area lies over them), the Q tile, and what the peers send
+    constexpr int SMEM = 2 * NBUF * PAGE * HD * 2 + 16 * HD * 2 + (16 * HD + MAX_CLUSTER_SPLITS + MAX_CLUSTER_SPLITS * 16 * 2) * 4;
+    static_assert((4 * 16 * HD + 4 * 16 * 2) * 4 <= 2 * NBUF * PAGE * HD * 2, "merge area must fit the page buffers");
     auto kernel = attn_decode_kernel<HD, true>;
     static bool configured = false;
     if (!configured) {
