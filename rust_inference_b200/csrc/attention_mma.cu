@@ -261,15 +261,16 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_ld, const __nv_bfl
     }
 
     // ---- merge the 4 warps (each saw a quarter of the keys) through shared memory ----
-    float* so = reinterpret_cast<float*>(smem);           // [4][16][HD]
-    float* sml = so + 4 * 16 * HD;                        // [4][16][2]
+    constexpr int SO_LD = HD + 4;                         // padded rows: the 8 rows a warp stores at once hit 8 bank groups
+    float* so = reinterpret_cast<float*>(smem);           // [4][16][SO_LD]
+    float* sml = so + 4 * 16 * SO_LD;                     // [4][16][2]
+    float* rowf = sml + 4 * 16 * 2;                       // [4][16]: exp(m_w - M) of each warp and row
+    float* rowML = rowf + 4 * 16;                         // [16][2]: the CTA's M and L of each row
 #pragma unroll
     for (int t = 0; t < HD / 8; ++t) {
         const int d = t * 8 + 2 * tq;
-        so[(warp * 16 + g) * HD + d] = o[t][0];
-        so[(warp * 16 + g) * HD + d + 1] = o[t][1];
-        so[(warp * 16 + g + 8) * HD + d] = o[t][2];
-        so[(warp * 16 + g + 8) * HD + d + 1] = o[t][3];
+        *reinterpret_cast<float2*>(so + (warp * 16 + g) * SO_LD + d) = make_float2(o[t][0], o[t][1]);
+        *reinterpret_cast<float2*>(so + (warp * 16 + g + 8) * SO_LD + d) = make_float2(o[t][2], o[t][3]);
     }
     if (tq == 0) {
         sml[((warp * 16 + g) << 1)] = m[0];
@@ -278,72 +279,89 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_ld, const __nv_bfl
         sml[((warp * 16 + g + 8) << 1) + 1] = l[1];
     }
     __syncthreads();
+    // a row's statistics once (not once per output element): its maximum over the warps, each warp's factor, its sum
+    if ((int)threadIdx.x < n_rep) {
+        const int r = threadIdx.x;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, sml[(w * 16 + r) << 1]);
+        float L = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float f = (M == -INFINITY) ? 0.f : expf(sml[(w * 16 + r) << 1] - M);
+            rowf[w * 16 + r] = f;
+            L += f * sml[((w * 16 + r) << 1) + 1];
+        }
+        rowML[2 * r] = M;
+        rowML[2 * r + 1] = L;
+    }
     // cluster form: what the peers send lies behind the Q tile, outside anything a CTA still works on
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
     const int chunk = (n_rep * HD + n_splits - 1) / n_splits;
     float* recv_o = reinterpret_cast<float*>(smem + 2 * NBUF * TILE + 16 * HD * 2);   // [n_splits][chunk]
     float* recv_ml = recv_o + 16 * HD + MAX_CLUSTER_SPLITS;                           // [n_splits][16][2]
+    float* comb = recv_ml + MAX_CLUSTER_SPLITS * 16 * 2;                              // [n_splits + 1][16]: factors, 1 / L
     if (CLUSTER) {
         // every CTA of the cluster has arrived at the barrier near its start by now: all of them exist, so
         // their shared memory may be written
         asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
     }
+    __syncthreads();                                      // row statistics written
+    if (CLUSTER && (int)threadIdx.x < n_rep) {
+        // this CTA's row statistics to every CTA of the cluster (plain stores into the peers' shared memory)
+        const int r = threadIdx.x;
+        for (int sp = 0; sp < n_splits; ++sp) {
+            float* ml = cluster.map_shared_rank(recv_ml, sp) + (split * 16 + r) * 2;
+            ml[0] = rowML[2 * r];
+            ml[1] = rowML[2 * r + 1];
+        }
+    }
     for (int idx = threadIdx.x; idx < n_rep * HD; idx += THREADS) {
         const int r = idx / HD, d = idx % HD;
-        float M = -INFINITY;
+        float acc = 0.f;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) M = fmaxf(M, sml[(w * 16 + r) << 1]);
-        float L = 0.f, acc = 0.f;
-        if (M != -INFINITY) {
-#pragma unroll
-            for (int w = 0; w < 4; ++w) {
-                const float f = expf(sml[(w * 16 + r) << 1] - M);
-                L += f * sml[((w * 16 + r) << 1) + 1];
-                acc += f * so[(w * 16 + r) * HD + d];
-            }
-        }
+        for (int w = 0; w < 4; ++w) acc += rowf[w * 16 + r] * so[(w * 16 + r) * SO_LD + d];
         const int h = kvh * n_rep + r;
         if (CLUSTER) {
             // The splits of this (sequence, kv head) are the CTAs of one cluster (its z extent).  Output idx is
-            // merged by CTA idx / chunk: every CTA sends its partial value there, and its row statistics to
-            // everyone, with plain stores into the peers' shared memory; nothing is read remotely.
+            // merged by CTA idx / chunk: every CTA sends its partial value there; nothing is read remotely.
             const int owner = idx / chunk;
             cluster.map_shared_rank(recv_o, owner)[split * chunk + (idx - owner * chunk)] = acc;
-            if (d == 0)
-                for (int sp = 0; sp < n_splits; ++sp) {
-                    float* ml = cluster.map_shared_rank(recv_ml, sp) + (split * 16 + r) * 2;
-                    ml[0] = M;
-                    ml[1] = L;
-                }
         } else if (n_splits == 1) {
-            out[(size_t)token * out_ld + (size_t)h * HD + d] = __float2bfloat16_rn(acc / L);
+            out[(size_t)token * out_ld + (size_t)h * HD + d] = __float2bfloat16_rn(acc / rowML[2 * r + 1]);
         } else {
             const size_t row = ((size_t)b * n_heads + h) * n_splits + split;
             part_o[row * HD + d] = acc;
             if (d == 0) {
-                part_ml[row * 2] = M;
-                part_ml[row * 2 + 1] = L;
+                part_ml[row * 2] = rowML[2 * r];
+                part_ml[row * 2 + 1] = rowML[2 * r + 1];
             }
         }
     }
     if (CLUSTER) {
         cluster.sync();                                   // everything sent has arrived
+        if ((int)threadIdx.x < n_rep) {
+            // a row's merge over the splits once: its maximum, each split's factor, one over its sum
+            const int r = threadIdx.x;
+            float M = -INFINITY;
+            for (int sp = 0; sp < n_splits; ++sp) M = fmaxf(M, recv_ml[(sp * 16 + r) * 2]);
+            float L = 0.f;
+            for (int sp = 0; sp < n_splits; ++sp) {
+                const float ms = recv_ml[(sp * 16 + r) * 2];
+                const float f = (ms == -INFINITY) ? 0.f : expf(ms - M);
+                comb[sp * 16 + r] = f;
+                L += f * recv_ml[(sp * 16 + r) * 2 + 1];
+            }
+            comb[n_splits * 16 + r] = 1.0f / L;
+        }
+        __syncthreads();
         const int lo = split * chunk, hi = min(n_rep * HD, lo + chunk);
         for (int idx = lo + (int)threadIdx.x; idx < hi; idx += THREADS) {
             const int r = idx / HD, d = idx % HD;
-            float M = -INFINITY;
-            for (int sp = 0; sp < n_splits; ++sp) M = fmaxf(M, recv_ml[(sp * 16 + r) * 2]);
-            float L = 0.f, acc = 0.f;
-            for (int sp = 0; sp < n_splits; ++sp) {
-                const float ms = recv_ml[(sp * 16 + r) * 2];
-                if (ms != -INFINITY) {
-                    const float f = expf(ms - M);
-                    L += f * recv_ml[(sp * 16 + r) * 2 + 1];
-                    acc += f * recv_o[sp * chunk + (idx - lo)];
-                }
-            }
-            out[(size_t)token * out_ld + (size_t)(kvh * n_rep + r) * HD + d] = __float2bfloat16_rn(acc / L);
+            float acc = 0.f;
+            for (int sp = 0; sp < n_splits; ++sp) acc += comb[sp * 16 + r] * recv_o[sp * chunk + (idx - lo)];
+            out[(size_t)token * out_ld + (size_t)(kvh * n_rep + r) * HD + d] = __float2bfloat16_rn(acc * comb[n_splits * 16 + r]);
         }
         // nobody reads or writes a peer's shared memory after that barrier: a CTA may leave when it is done
     }
@@ -517,16 +535,17 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     __syncthreads();                      // every page consumed, every copy landed: the ring is free
 
     // ---- merge the 4 compute warps (each saw a quarter of the keys) through shared memory ----
-    float* so = reinterpret_cast<float*>(smem);           // [4][16][HD]
-    float* sml = so + 4 * 16 * HD;                        // [4][16][2]
+    constexpr int SO_LD = HD + 4;                         // padded rows: the 8 rows a warp stores at once hit 8 bank groups
+    float* so = reinterpret_cast<float*>(smem);           // [4][16][SO_LD]
+    float* sml = so + 4 * 16 * SO_LD;                     // [4][16][2]
+    float* rowf = sml + 4 * 16 * 2;                       // [4][16]: exp(m_w - M) of each warp and row
+    float* rowML = rowf + 4 * 16;                         // [16][2]: M and L of each row
     if (warp < 4) {
 #pragma unroll
         for (int t = 0; t < HD / 8; ++t) {
             const int d = t * 8 + 2 * tq;
-            so[(warp * 16 + g) * HD + d] = o[t][0];
-            so[(warp * 16 + g) * HD + d + 1] = o[t][1];
-            so[(warp * 16 + g + 8) * HD + d] = o[t][2];
-            so[(warp * 16 + g + 8) * HD + d + 1] = o[t][3];
+            *reinterpret_cast<float2*>(so + (warp * 16 + g) * SO_LD + d) = make_float2(o[t][0], o[t][1]);
+            *reinterpret_cast<float2*>(so + (warp * 16 + g + 8) * SO_LD + d) = make_float2(o[t][2], o[t][3]);
         }
         if (tq == 0) {
             sml[((warp * 16 + g) << 1)] = m[0];
@@ -537,29 +556,37 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     }
     __syncthreads();
     if (abort_flag) return;
-    for (int idx = threadIdx.x; idx < n_rep * HD; idx += DECODE_TMA_THREADS) {
-        const int r = idx / HD, d = idx % HD;
+    // a row's statistics once (not once per output element)
+    if ((int)threadIdx.x < n_rep) {
+        const int r = threadIdx.x;
         float M = -INFINITY;
 #pragma unroll
         for (int w = 0; w < 4; ++w) M = fmaxf(M, sml[(w * 16 + r) << 1]);
-        float L = 0.f, acc = 0.f;
-        if (M != -INFINITY) {
+        float L = 0.f;
 #pragma unroll
-            for (int w = 0; w < 4; ++w) {
-                const float f = expf(sml[(w * 16 + r) << 1] - M);
-                L += f * sml[((w * 16 + r) << 1) + 1];
-                acc += f * so[(w * 16 + r) * HD + d];
-            }
+        for (int w = 0; w < 4; ++w) {
+            const float f = (M == -INFINITY) ? 0.f : expf(sml[(w * 16 + r) << 1] - M);
+            rowf[w * 16 + r] = f;
+            L += f * sml[((w * 16 + r) << 1) + 1];
         }
+        rowML[2 * r] = M;
+        rowML[2 * r + 1] = L;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < n_rep * HD; idx += DECODE_TMA_THREADS) {
+        const int r = idx / HD, d = idx % HD;
+        float acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) acc += rowf[w * 16 + r] * so[(w * 16 + r) * SO_LD + d];
         const int h = kvh * n_rep + r;
         if (n_splits == 1) {
-            out[(size_t)token * out_ld + (size_t)h * HD + d] = __float2bfloat16_rn(acc / L);
+            out[(size_t)token * out_ld + (size_t)h * HD + d] = __float2bfloat16_rn(acc / rowML[2 * r + 1]);
         } else {
             const size_t row = ((size_t)b * n_heads + h) * n_splits + split;
             part_o[row * HD + d] = acc;
             if (d == 0) {
-                part_ml[row * 2] = M;
-                part_ml[row * 2 + 1] = L;
+                part_ml[row * 2] = rowML[2 * r];
+                part_ml[row * 2 + 1] = rowML[2 * r + 1];
             }
         }
     }
@@ -711,8 +738,8 @@ int launch_decode(const void* q, int q_ld, const void* kc, const void* vc, const
                   const int* seq_slot, const int* seq_len, const int* cu_seqlens, int n_seqs, int n_heads,
                   int n_kv_heads, float scale, int window, int n_splits, float* part_o, float* part_ml, void* out,
                   int out_ld, cudaStream_t stream) {
-    constexpr int SMEM = 2 * NBUF * PAGE * HD * 2 + 16 * HD * 2;      // also covers the merge area 4*16*HD*4 + 512
-    static_assert(4 * 16 * HD * 4 + 4 * 16 * 2 * 4 <= SMEM, "merge area must fit");
+    constexpr int SMEM = 2 * NBUF * PAGE * HD * 2 + 16 * HD * 2;      // the merge area lies over the page buffers
+    static_assert((4 * 16 * (HD + 4) + 4 * 16 * 2 + 4 * 16 + 16 * 2) * 4 <= SMEM, "merge area must fit");
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
@@ -742,8 +769,9 @@ int launch_decode_cluster(const void* q, int q_ld, const void* kc, const void* v
                           int n_kv_heads, float scale, int window, int n_splits, void* out, int out_ld,
                           cudaStream_t stream) {
     // page buffers (the warps' merge area lies over them), the Q tile, and what the peers send
-    constexpr int SMEM = 2 * NBUF * PAGE * HD * 2 + 16 * HD * 2 + (16 * HD + MAX_CLUSTER_SPLITS + MAX_CLUSTER_SPLITS * 16 * 2) * 4;
-    static_assert((4 * 16 * HD + 4 * 16 * 2) * 4 <= 2 * NBUF * PAGE * HD * 2, "merge area must fit the page buffers");
+    constexpr int SMEM = 2 * NBUF * PAGE * HD * 2 + 16 * HD * 2 +
+                         (16 * HD + MAX_CLUSTER_SPLITS + MAX_CLUSTER_SPLITS * 16 * 2 + (MAX_CLUSTER_SPLITS + 1) * 16) * 4;
+    static_assert((4 * 16 * (HD + 4) + 4 * 16 * 2 + 4 * 16 + 16 * 2) * 4 <= 2 * NBUF * PAGE * HD * 2, "merge area must fit the page buffers");
     auto kernel = attn_decode_kernel<HD, true>;
     static bool configured = false;
     if (!configured) {
@@ -778,7 +806,7 @@ int launch_decode_tma(const CUtensorMap& mk, const CUtensorMap& mv, const void* 
                       int n_heads, int n_kv_heads, float scale, int window, int n_splits, float* part_o,
                       float* part_ml, void* out, int out_ld, int* status, cudaStream_t stream) {
     constexpr int SMEM = 2 * RING * PAGE * HD * 2 + 16 * HD * 2 + 1024;
-    static_assert(4 * 16 * HD * 4 + 4 * 16 * 2 * 4 <= 2 * RING * PAGE * HD * 2, "merge area must fit the ring");
+    static_assert((4 * 16 * (HD + 4) + 4 * 16 * 2 + 4 * 16 + 16 * 2) * 4 <= 2 * RING * PAGE * HD * 2, "merge area must fit the ring");
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attn_decode_tma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);

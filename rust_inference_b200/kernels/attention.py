@@ -49,9 +49,9 @@ def decode_plan(n_seqs: int, n_kv_heads: int, max_seq_len: int, page_size: int):
     64, 1,024 positions: 26.7 us against 40.9 us with cp.async)."""
     if _DECODE in ("auto", "cluster"):
         splits = decode_splits(n_seqs, n_kv_heads, max_seq_len, page_size, CLUSTER_SPLITS)
-        # measured at 1,024 positions: 1 sequence 6.0 us against 8.1 us with the merge kernel, 4: 7.4
-        # against 11.4, 8: 9.6 against 9.9, 16 (four splits): 12.2 against 11.3, 32 (two): 17.8 against 17.3
-        if splits >= (6 if _DECODE == "auto" else 2):
+        # measured at 1,024 positions: 1 sequence 5.3 us against 7.9 us with the merge kernel, 4: 6.3
+        # against 11.1, 8: 8.4 against 9.6, 16 (four splits): 10.9 against 10.7, 32 (two): 16.3 against 16.4
+        if splits >= 2:
             return "cluster", splits
     splits = decode_splits(n_seqs, n_kv_heads, max_seq_len, page_size)
     if _DECODE == "tma" or (_DECODE in ("auto", "cluster") and splits == 1):
