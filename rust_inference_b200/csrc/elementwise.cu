@@ -109,11 +109,54 @@ rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ w, con
     }
 }
 
+// Steps of many rows (prompts): one warp per row, the row in registers, no block-wide barrier; the
+// weights are read again by every warp (they stay in L1/L2).  CH float4s per lane: rows of up to 512 * CH.
+template <typename T, int CH>
+__global__ void __launch_bounds__(256)
+rmsnorm_warp_kernel(const float* __restrict__ x, const float* __restrict__ w, const int* __restrict__ rows,
+                    T* __restrict__ out, int n_rows, int n, float eps) {
+    const int lane = threadIdx.x & 31, n4 = n >> 2;
+    const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    let_next_kernel_start();
+    wait_for_previous_kernels();
+    if (r >= n_rows) return;
+    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * n);
+    float4 xv[CH];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < CH; ++j) {
+        const int i = lane + j * 32;
+        xv[j] = i < n4 ? xr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        ss += xv[j].x * xv[j].x + xv[j].y * xv[j].y + xv[j].z * xv[j].z + xv[j].w * xv[j].w;
+    }
+    ss = warp_sum(ss);
+    const float scale = 1.0f / sqrtf(ss / (float)n + eps);
+    T* o = out + (size_t)r * n;
+#pragma unroll
+    for (int j = 0; j < CH; ++j) {
+        const int i = lane + j * 32;
+        if (i < n4) {
+            const float4 wv = reinterpret_cast<const float4*>(w)[i];
+            store4<T>(o + 4 * i, xv[j].x * scale * wv.x, xv[j].y * scale * wv.y, xv[j].z * scale * wv.z,
+                      xv[j].w * scale * wv.w);
+        }
+    }
+}
+
 template <typename T>
 cudaError_t launch_rmsnorm(const float* x, const float* w, const int* rows, T* out, int n_rows, int n, float eps,
                            cudaStream_t stream) {
     const bool vec = n % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)out % 16 == 0;
     const int n4 = n / 4;
+    if (vec && n_rows >= 256 && n4 <= 32 * 64) {
+        // many rows: a warp per row (measured at 2,048 rows of 3584: 14-16 us with a block per row)
+        const int ch = (n4 + 31) / 32;
+        const int blocks = (n_rows + 7) / 8;
+        if (ch <= 8) return launch_dependent(rmsnorm_warp_kernel<T, 8>, blocks, 256, 0, stream, x, w, rows, out, n_rows, n, eps);
+        if (ch <= 16) return launch_dependent(rmsnorm_warp_kernel<T, 16>, blocks, 256, 0, stream, x, w, rows, out, n_rows, n, eps);
+        if (ch <= 32) return launch_dependent(rmsnorm_warp_kernel<T, 32>, blocks, 256, 0, stream, x, w, rows, out, n_rows, n, eps);
+        return launch_dependent(rmsnorm_warp_kernel<T, 64>, blocks, 256, 0, stream, x, w, rows, out, n_rows, n, eps);
+    }
     if (vec && n4 <= 4 * 1024) {
         // as many threads as float4s, rounded up to whole warps, at most 1024
         int threads = ((n4 + 31) / 32) * 32;

@@ -46,6 +46,26 @@ def test_rmsnorm(out_dtype, n, eps):
     assert torch.equal(picked, out[[8, 0, 3]])
 
 
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n_rows, n", [(300, 144), (257, 1000), (2048, 3584), (260, 5120), (256, 8192)])
+def test_rmsnorm_of_many_rows(out_dtype, n_rows, n):
+    """Steps of many rows take a kernel with one warp per row (and any width it cannot hold, another)."""
+    ops = _ops()
+    x = torch.randn(n_rows, n, device=DEV) * 2
+    x[7] *= 1e-3
+    w = torch.randn(n, device=DEV)
+    out = torch.empty(n_rows, n, device=DEV, dtype=out_dtype)
+    ops.rmsnorm(x, w, 1e-6, out)
+    pick = [0, 7, n_rows // 2, n_rows - 1]
+    want = plain_impl.rmsnorm(x[pick].double().cpu(), w.double().cpu(), 1e-6)
+    tol = 2e-6 if out_dtype == torch.float32 else 5e-3
+    assert ((out[pick].double().cpu() - want).abs() <= tol * want.abs().clamp_min(1e-3)).all()
+    # every row as the few-rows kernel computes it
+    few = torch.empty(8, n, device=DEV, dtype=out_dtype)
+    ops.rmsnorm(x[100:108].contiguous(), w, 1e-6, few)
+    assert (out[100:108].double() - few.double()).abs().max().item() <= tol * few.double().abs().max().item()
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("inter", [11, 176, 18944])
 def test_silu_mul(dtype, inter):
