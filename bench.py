@@ -28,6 +28,7 @@ import os
 import random
 import subprocess
 import sys
+import tempfile
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -84,11 +85,11 @@ class ClockSampler:
 
     def __init__(self):
         self.proc = None
-        self.path = os.path.join(ROOT, "gpurun_out", "bench_clocks.csv")
+        fd, self.path = tempfile.mkstemp(prefix="bench_clocks_", suffix=".csv")
+        os.close(fd)
 
     def start(self):
         try:
-            os.makedirs(os.path.dirname(self.path), exist_ok=True)
             self.out = open(self.path, "w")
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200"],
@@ -120,6 +121,10 @@ class ClockSampler:
                 for name, val in zip(names, parts[3:7]):
                     if val.lower().startswith("active"):
                         reasons.add(name)
+        try:
+            os.remove(self.path)
+        except OSError:
+            pass
         sm.sort()
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
                 "reasons": sorted(reasons), "samples": len(sm)}
