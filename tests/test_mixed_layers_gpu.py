@@ -241,3 +241,114 @@ def test_layers_that_differ_in_one_model(dtype, mixed_model):
     assert rel_err(torch.cat(rows[2]), _plain_logits(weights, others[1])) <= tol
     assert rel_err(torch.cat(rows[1]), _plain_logits(weights, others[0])[:len(others[0]) - 2]) <= tol
     eng.check_device_status()
+
+
+# ------------------------------------------------------------------------------------------
+# Another norm and another arrangement, defined here: a LayerNorm with a bias (mean subtracted), and
+# a block that feeds the same normalised input to the mixer and to the feed-forward and adds both
+# to the stream (h = x + mix(norm(x)) + ff(norm(x))).  Registered from outside the package, built
+# from a spec and stepped like any other model.
+# ------------------------------------------------------------------------------------------
+def _register_parallel():
+    from rust_inference_b200.config.registry import register_architecture
+    from rust_inference_b200.parts.base import Arrangement, Norm
+    from rust_inference_b200.parts.registry import register
+    from rust_inference_b200.parts.spec import LayerSpec, ModelSpec, PartSpec, TensorSpec, default_schedule
+
+    @register("norm", "toy_layernorm", replace=True)
+    class ToyLayerNorm(Norm):
+        graph_safe = True
+
+        def __init__(self, *, eps: float, hidden_size, dtype, device):
+            super().__init__(hidden_size=hidden_size, dtype=dtype, device=device)
+            self.eps = eps
+            self.weight = self.bias = None
+
+        def tensor_specs(self):
+            return {"weight": TensorSpec((self.hidden_size,), role="vector", init="ones"),
+                    "bias": TensorSpec((self.hidden_size,), role="vector")}
+
+        def set_tensors(self, tensors):
+            self.weight, self.bias = tensors["weight"], tensors["bias"]
+
+        def forward(self, x, out, rows=None):
+            src = x if rows is None else x[rows.long()]
+            mean = src.mean(dim=-1, keepdim=True)
+            var = ((src - mean) ** 2).mean(dim=-1, keepdim=True)
+            out.copy_(((src - mean) / torch.sqrt(var + self.eps) * self.weight + self.bias).to(out.dtype))
+            return out
+
+    @register("arrangement", "toy_parallel", replace=True)
+    class Parallel(Arrangement):
+        def forward(self, residual, ctx, cache_layer, writes_cache):
+            normed = ctx.buffer("normed", (residual.shape[0], residual.shape[1]), ctx.dtype)
+            self.mixer_norm.forward(residual, normed)
+            self.mixer.forward(normed, residual, ctx, cache_layer, writes_cache)
+            self.feed_forward.forward(normed, residual, ctx)       # the same input: the second norm is not used
+
+    def build(d):
+        rope = PartSpec("rope", {"head_dim": 64, "base": 1e4, "style": "half"})
+        norm = lambda p: PartSpec("toy_layernorm", {"eps": 1e-5}, prefix=p)
+        layers = tuple(LayerSpec(
+            prefix=f"h.{i}.", arrangement="toy_parallel",
+            mixer=PartSpec("gqa_attention", {"n_heads": 4, "n_kv_heads": 2, "head_dim": 64, "qkv_bias": True, "position": rope},
+                           prefix="attn."),
+            feed_forward=PartSpec("swiglu", {"intermediate_size": d["inter"]}, prefix="mlp."),
+            mixer_norm=norm("ln."), feed_forward_norm=norm("unused_ln.")) for i in range(2))
+        return ModelSpec(hidden_size=d["hidden"], vocab_size=d["vocab"], max_positions=256, layers=layers,
+                         schedule=default_schedule(2), final_norm=norm("ln_f."),
+                         embedding_name="wte.weight", head_name=None)
+
+    register_architecture("ToyParallelLM", lambda d: d, build, replace=True)
+
+
+def _plain_parallel(w, tokens, inter):
+    def layernorm(x, pre):
+        mean = x.mean(dim=-1, keepdim=True)
+        var = ((x - mean) ** 2).mean(dim=-1, keepdim=True)
+        return (x - mean) / torch.sqrt(var + 1e-5) * w[pre + "weight"] + w[pre + "bias"]
+    n = len(tokens)
+    h = plain_impl.embedding(w["wte.weight"], tokens)
+    cos, sin = plain_impl.rope_table(64, 1e4, n)
+    for i in range(2):
+        pre = f"h.{i}."
+        xn = layernorm(h, pre + "ln.")
+        a, _ = plain_impl.attention(xn, w, pre + "attn.", n_heads=4, n_kv_heads=2, head_dim=64, cos=cos, sin=sin,
+                                    rope_style="half")
+        h = h + a + plain_impl.swiglu(xn, w, pre + "mlp.")
+    return plain_impl.linear(layernorm(h, "ln_f."), w["wte.weight"])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_another_norm_and_another_arrangement(dtype, tmp_path):
+    from rust_inference_b200.config.registry import get_architecture, unregister_architecture
+    from rust_inference_b200.engine.engine import Engine
+    from rust_inference_b200.engine.model import declared_tensors
+    from rust_inference_b200.parts.registry import unregister
+    from rust_inference_b200.weights.loader import random_tensors
+    from rust_inference_b200.weights.safetensors_io import ModelFiles, write_safetensors
+    _register_parallel()
+    try:
+        cfg = {"architectures": ["ToyParallelLM"], "hidden": 136, "inter": 200, "vocab": 77}
+        folder = str(tmp_path / "parallel")
+        os.makedirs(folder)
+        with open(os.path.join(folder, "config.json"), "w") as f:
+            json.dump(cfg, f)
+        names = declared_tensors(get_architecture("ToyParallelLM").build_spec(cfg))
+        assert "h.0.ln.bias" in names and "h.1.unused_ln.weight" in names and "ln_f.bias" in names
+        write_safetensors(os.path.join(folder, "model.safetensors"), dict(random_tensors(names, 4, std=0.08)))
+        files = ModelFiles(folder)
+        weights = {n: files.tensor(n).float() for n in files.names()}
+        files.close()
+        eng = Engine.from_pretrained(folder, dtype=dtype, max_tokens=512)
+        toks = random_tokens(70, 77, seed=3)
+        want = _plain_parallel(weights, toks, 200)
+        s = eng.alloc_slot()
+        head = eng.step([s], [toks[:41]], "all").cpu()
+        tail = torch.cat([eng.step([s], [[t]], "last").cpu() for t in toks[41:]])
+        assert rel_err(torch.cat([head, tail]), want) <= (1e-4 if dtype == "float32" else 4e-2)
+        eng.check_device_status()
+    finally:
+        unregister("norm", "toy_layernorm")
+        unregister("arrangement", "toy_parallel")
+        unregister_architecture("ToyParallelLM")
