@@ -25,7 +25,17 @@
 //
 // The logits buffer is overwritten (it becomes the probabilities), as the reference
 // overwrites its logits slice.
+//
+// Two kernels compute the same thing.  `sample_kernel` gives a row to one thread block: any
+// vocabulary, any options.  `sample_cluster_kernel` gives a row to a thread-block cluster of eight,
+// each block taking a contiguous eighth of the row; the blocks exchange their maxima, sums and
+// candidates through distributed shared memory.  A block alone spends tens of microseconds on the
+// exponentials of a 150,000-entry row while 140 SMs idle at a batch of eight; the cluster is used for
+// large vocabularies whenever the options allow it (greedy, plain temperature, top-k up to 256 with or
+// without top-p).
 #include "common.cuh"
+
+#include <cooperative_groups.h>
 
 using namespace ri;
 
@@ -215,6 +225,104 @@ __device__ void finish_row(float* p, int n, const int* ids, int top_k, float top
     }
 }
 
+// The same for a compact list of at most THREADS candidates (ascending id order, ids in `ids`): an entry per
+// thread.  Instead of finding the thresholds by bisection, every thread counts its entry's place in the
+// descending order (ties by position, as a stable sort leaves them), which takes n steps and no block-wide
+// reduction; the k-th largest is the entry at place k - 1, and top-p keeps an entry while the entries before
+// it in that order have not reached p.  The draw is one thread's walk over the list in id order.
+__device__ void finish_short(const float* p, int n, const int* ids, int top_k, float top_p, float u, int* out, int* mirror,
+                             int r, float* fscratch, float* chunk_sum, int* chunk_cnt) {
+    const int tid = threadIdx.x;
+    float v = tid < n ? p[tid] : 0.f;
+    int place = 0;
+    for (int j = 0; j < n; ++j) {
+        const float o = p[j];
+        place += (o > v) || (o == v && j < tid);
+    }
+    // ---- top-k (sampler.rs:130-160): ties with the k-th largest are kept; the list is always renormalised ----
+    if (top_k > 0) {
+        if (top_k < n) {
+            if (tid < n && place == top_k - 1) fscratch[0] = v;
+            __syncthreads();
+            const float threshold = fscratch[0];
+            __syncthreads();
+            if (v < threshold) v = 0.f;
+        }
+        const float s = block_sum(v, fscratch);
+        if (s > 0.f) v *= 1.0f / s;
+    }
+    // ---- top-p (sampler.rs:163-196) ----
+    if (top_p > 0.f && top_p < 1.f) {
+        if (tid < n) { chunk_sum[tid] = v; chunk_cnt[tid] = place; }
+        __syncthreads();
+        float before = 0.f;
+        for (int j = 0; j < n; ++j)
+            if (chunk_cnt[j] < place) before += chunk_sum[j];
+        if (!(before < top_p)) v = 0.f;
+        __syncthreads();
+        const float s = block_sum(v, fscratch);
+        if (s > 0.f) v *= 1.0f / s;
+    }
+    // ---- draw (sampler.rs:199-210): first entry at which the running sum reaches u ----
+    __syncthreads();
+    if (tid < n) chunk_sum[tid] = v;
+    __syncthreads();
+    if (tid == 0) {
+        float run = 0.f;
+        int tok = -1, last = -1;
+        for (int j = 0; j < n && tok < 0; ++j) {
+            const float q = chunk_sum[j];
+            run += q;
+            if (q > 0.f) {
+                last = j;
+                if (run >= u) tok = j;
+            }
+        }
+        const int e = tok >= 0 ? tok : (last >= 0 ? last : n - 1);
+        store_token(out, mirror, r, ids[e]);
+    }
+}
+
+// Repetition penalty (sampler.rs:109-127) on the ids of [lo, hi): l > 0 ? l / penalty : l * penalty for each id
+// among the row's recent tokens and then the newest one, which may still be on the device only; an id that
+// occurs several times is penalised that often.  A thread per entry of the list: the first occurrence of an id
+// applies the penalty as often as the id occurs.  `list` holds THREADS ints; longer lists are walked by one thread.
+__device__ void apply_penalty(float* p, int lo, int hi, float penalty, const int* __restrict__ recent, int recent_ld,
+                              const int* __restrict__ recent_count, const int* newest, int r, int* list) {
+    const int tid = threadIdx.x;
+    const int n_recent = recent != nullptr ? recent_count[r] : 0;
+    const int n = n_recent + (newest != nullptr ? 1 : 0);
+    if (n <= THREADS) {
+        if (tid < n) list[tid] = tid < n_recent ? recent[(size_t)r * recent_ld + tid] : newest[r];
+        __syncthreads();
+        if (tid < n) {
+            const int id = list[tid];
+            if (id >= lo && id < hi) {
+                bool first = true;
+                int times = 0;
+                for (int j = 0; j < n; ++j) {
+                    const bool same = list[j] == id;
+                    first = first && !(same && j < tid);
+                    times += same;
+                }
+                if (first) {
+                    float v = p[id];
+                    for (int t = 0; t < times; ++t) v = v > 0.f ? v / penalty : v * penalty;
+                    p[id] = v;
+                }
+            }
+        }
+    } else if (tid == 0) {
+        for (int i = 0; i < n; ++i) {
+            const int id = i < n_recent ? recent[(size_t)r * recent_ld + i] : newest[r];
+            if (id >= lo && id < hi) {
+                if (p[id] > 0.f) p[id] /= penalty; else p[id] *= penalty;
+            }
+        }
+    }
+    __syncthreads();
+}
+
 __global__ void __launch_bounds__(THREADS)
 sample_kernel(float* __restrict__ logits, int vocab, int* out, float temperature, int top_k,
               float top_p, float penalty, const int* __restrict__ recent, int recent_ld,
@@ -235,21 +343,8 @@ sample_kernel(float* __restrict__ logits, int vocab, int* out, float temperature
     wait_for_previous_kernels();          // the logits come from the kernel before
     float* p = logits + (size_t)r * vocab;
 
-    // ---- repetition penalty (sampler.rs:109-127) ----
-    if (penalty != 1.0f && (recent != nullptr || newest != nullptr)) {
-        if (tid == 0) {
-            const int n = recent != nullptr ? recent_count[r] : 0;
-            for (int i = 0; i <= n; ++i) {
-                // the row's recent ids, then the newest one, which may still be on the device only
-                if (i == n && newest == nullptr) break;
-                const int id = i < n ? recent[(size_t)r * recent_ld + i] : newest[r];
-                if (id >= 0 && id < vocab) {
-                    if (p[id] > 0.f) p[id] /= penalty; else p[id] *= penalty;
-                }
-            }
-        }
-        __syncthreads();
-    }
+    if (penalty != 1.0f && (recent != nullptr || newest != nullptr))
+        apply_penalty(p, 0, vocab, penalty, recent, recent_ld, recent_count, newest, r, chunk_cnt);
 
     // ---- greedy (sampler.rs:81-83, math.rs:328-339): first maximum ----
     if (temperature <= 0.f) {
@@ -365,7 +460,8 @@ sample_kernel(float* __restrict__ logits, int vocab, int* out, float temperature
             int n = 0;
             for (int k = 0; k < WARPS; ++k) n += seg_count[k];
             __syncthreads();
-            finish_row(cand_p, n, cand_i, top_k, top_p, u, out, mirror, r, fscratch, iscratch, chunk_sum, chunk_cnt);
+            if (n <= THREADS) finish_short(cand_p, n, cand_i, top_k, top_p, u, out, mirror, r, fscratch, chunk_sum, chunk_cnt);
+            else finish_row(cand_p, n, cand_i, top_k, top_p, u, out, mirror, r, fscratch, iscratch, chunk_sum, chunk_cnt);
             return;
         }
         // too many ties for the list: the long way below handles any row
@@ -435,7 +531,265 @@ sample_kernel(float* __restrict__ logits, int vocab, int* out, float temperature
     finish_row(p, vocab, nullptr, top_k, top_p, u, out, mirror, r, fscratch, iscratch, chunk_sum, chunk_cnt);
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// A row per cluster.
+// ---------------------------------------------------------------------------------------------
+constexpr int CLUSTER = 8;
+constexpr int GROUPS = CLUSTER * WARPS;      // stretches of a row: one per warp of the cluster, in id order
+
+__global__ void __launch_bounds__(THREADS)
+sample_cluster_kernel(float* __restrict__ logits, int vocab, int per_cta, int* out, float temperature, int top_k,
+                      float top_p, float penalty, const int* __restrict__ recent, int recent_ld,
+                      const int* __restrict__ recent_count, unsigned long long seed, const int* __restrict__ row_stream,
+                      const int* __restrict__ row_counter, int counter_offset, int* __restrict__ mirror,
+                      const int* newest) {      // `newest` and `out` may be the same buffer: a row reads before it writes
+    namespace cg = cooperative_groups;
+    __shared__ float fscratch[33];
+    __shared__ int iscratch[33];
+    __shared__ float chunk_sum[THREADS];
+    __shared__ int chunk_cnt[THREADS];
+    __shared__ float cand_p[CAP];
+    __shared__ int cand_i[CAP];
+    __shared__ int seg_count[WARPS + 1];
+    __shared__ float warp_z[WARPS];
+    // written by the other blocks of the cluster
+    __shared__ float rx_wmax[GROUPS];
+    __shared__ float rx_sum[CLUSTER];
+    __shared__ int rx_cnt[CLUSTER];
+    __shared__ float rx_best[CLUSTER];
+    __shared__ int rx_best_i[CLUSTER];
+
+    cg::cluster_group cluster = cg::this_cluster();
+    const int rank = (int)cluster.block_rank();
+    const int r = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");   // "this block runs": waited for before the first exchange
+    if (tid == 0) seg_count[WARPS] = 0;                          // (the exchanges below make it visible in time)
+    let_next_kernel_start();
+    wait_for_previous_kernels();          // the logits come from the kernel before
+    float* p = logits + (size_t)r * vocab;
+    const int c_lo = min(vocab, rank * per_cta), c_hi = min(vocab, c_lo + per_cta);     // this block's part of the row
+
+    // every block goes through the list and changes the ids of its part
+    if (penalty != 1.0f && (recent != nullptr || newest != nullptr))
+        apply_penalty(p, c_lo, c_hi, penalty, recent, recent_ld, recent_count, newest, r, chunk_cnt);
+
+    // ---- greedy (sampler.rs:81-83, math.rs:328-339): first maximum ----
+    if (temperature <= 0.f) {
+        float best = -INFINITY;
+        int best_i = 0x7fffffff;
+        for (int i = c_lo + tid; i < c_hi; i += THREADS) {
+            const float v = p[i];
+            if (v > best) { best = v; best_i = i; }
+        }
+        const float m = block_max(best, fscratch);
+        int cand = (best == m) ? best_i : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) cand = min(cand, __shfl_xor_sync(0xffffffffu, cand, o));
+        __syncthreads();
+        if (lane == 0) iscratch[warp] = cand;
+        __syncthreads();
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        if (tid < 32) {
+            int t = iscratch[tid];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) t = min(t, __shfl_xor_sync(0xffffffffu, t, o));
+            if (tid == 0) {
+                cluster.map_shared_rank(rx_best, 0)[rank] = m;
+                cluster.map_shared_rank(rx_best_i, 0)[rank] = t;
+            }
+        }
+        cluster.sync();
+        if (rank == 0 && tid == 0) {
+            float bm = -INFINITY;
+            int bi = 0x7fffffff;
+            for (int c = 0; c < CLUSTER; ++c)                    // parts are in id order: a later one must be larger to win
+                if (rx_best[c] > bm && rx_best_i[c] != 0x7fffffff) { bm = rx_best[c]; bi = rx_best_i[c]; }
+            store_token(out, mirror, r, bi == 0x7fffffff ? 0 : bi);
+        }
+        return;
+    }
+
+    // ---- the maximum (the order of operations and the formulas are those of sample_kernel) ----
+    const int per = per_cta / WARPS;                             // a warp's stretch; a multiple of 32
+    const int w_lo = min(c_hi, c_lo + warp * per), w_hi = min(c_hi, w_lo + per);
+    float tmax = -INFINITY;
+    for (int i = w_lo + lane; i < w_hi; i += 32) tmax = fmaxf(tmax, p[i]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, o));
+    tmax = tmax / temperature;                                   // the largest x of this warp's stretch
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (lane < CLUSTER) cluster.map_shared_rank(rx_wmax, lane)[rank * WARPS + warp] = tmax;
+    const float u = uniform_open_closed(seed, (unsigned)row_stream[r], (unsigned)(row_counter[r] + counter_offset));
+    cluster.sync();
+    float m = -INFINITY;
+    for (int g = lane; g < GROUPS; g += 32) m = fmaxf(m, rx_wmax[g]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    const bool nucleus = top_p > 0.f && top_p < 1.f;
+    const bool shortlist = top_k > 0 && top_k < vocab;           // the host sends top_k <= GROUPS only
+
+    // ---- candidates for top-k: the k-th largest of the stretches' maxima is a lower bound of the k-th largest of
+    // the row; every id that reaches it (a shade lower: see sample_kernel) goes on the list ----
+    float tau = INFINITY;
+    if (shortlist) {
+        if (tid < GROUPS) {
+            const float mine = rx_wmax[tid];
+            int above = 0;
+            for (int j = 0; j < GROUPS; ++j) {
+                const float o = rx_wmax[j];
+                above += (o > mine) || (o == mine && j < tid);
+            }
+            if (above == top_k - 1) fscratch[0] = mine - (fabsf(mine - m) + 1.f) * 2e-6f;
+        }
+        __syncthreads();
+        tau = fscratch[0];
+        __syncthreads();
+    }
+
+    // ---- the sum, and the candidates in id order ----
+    int cnt = 0;
+    float lsum = 0.f;
+#pragma unroll 4
+    for (int base = w_lo; base < w_hi; base += 32) {
+        const int i = base + lane;
+        const float x = i < w_hi ? p[i] / temperature : -INFINITY;
+        lsum += expf(x - m);                                     // exp(-inf) = 0 past the end
+        if (shortlist) {
+            const bool take = x >= tau;
+            const unsigned mask = __ballot_sync(0xffffffffu, take);
+            if (mask) {
+                const int pos = cnt + __popc(mask & ((1u << lane) - 1u));
+                if (take && pos < SEG_CAP) {
+                    cand_p[warp * SEG_CAP + pos] = x;
+                    cand_i[warp * SEG_CAP + pos] = i;
+                }
+                cnt += __popc(mask);
+            }
+        }
+    }
+    const float wsum = warp_sum(lsum);
+    if (lane == 0) {
+        warp_z[warp] = wsum;
+        seg_count[warp] = cnt;
+        if (cnt > SEG_CAP) seg_count[WARPS] = 1;                 // a stretch with more candidates than it can hold
+    }
+    const float cta_z = block_sum(lsum, fscratch);               // (also makes the counts visible)
+    int n_mine = 0;
+    for (int k = 0; k < WARPS; ++k) n_mine += seg_count[k];
+    if (seg_count[WARPS]) n_mine = CAP + 1;                      // marks the overflow for every block
+    if (tid < CLUSTER) {
+        cluster.map_shared_rank(rx_sum, tid)[rank] = cta_z;
+        cluster.map_shared_rank(rx_cnt, tid)[rank] = n_mine;
+    }
+    cluster.sync();
+    float z = 0.f;
+    int n_all = 0, n_before = 0;
+    for (int c = 0; c < CLUSTER; ++c) {                          // fixed order: the same sums in every block
+        if (c == rank) n_before = n_all;
+        z += rx_sum[c];
+        n_all = min(CAP + 1, n_all + rx_cnt[c]);
+    }
+    const float inv_z = 1.0f / z;
+
+    if (!nucleus && !shortlist) {
+        // ---- plain temperature sampling: the block, then the warp, in whose part the running sum reaches u ----
+        int owner_cta = -1;
+        float run = 0.f, before_cta = 0.f;
+        for (int c = 0; c < CLUSTER; ++c) {
+            const float before = run;
+            run += rx_sum[c] * inv_z;
+            if (owner_cta < 0 && run >= u) { owner_cta = c; before_cta = before; }
+        }
+        if (owner_cta < 0) {
+            // rounding left the total just below u: the last id (sampler.rs:208-209)
+            if (rank == CLUSTER - 1 && tid == 0) store_token(out, mirror, r, vocab - 1);
+            return;
+        }
+        if (rank != owner_cta) return;
+        if (tid == 0) {
+            float wrun = before_cta;
+            int owner = -1;
+            for (int w = 0; w < WARPS; ++w) {
+                const float before = wrun;
+                wrun += warp_z[w] * inv_z;
+                if (owner < 0 && wrun >= u) { owner = w; fscratch[0] = before; }
+            }
+            iscratch[0] = owner;
+        }
+        __syncthreads();
+        int owner = iscratch[0];
+        float start = fscratch[0];
+        if (owner < 0) {                                         // the block's sum reached u, its warps' sums fell short by rounding
+            owner = WARPS - 1;
+            while (owner > 0 && min(c_hi, c_lo + owner * per) >= c_hi) --owner;
+            start = -1.f;                                        // walk the last stretch and take its last id with probability
+        }
+        if (warp == owner) {
+            float wrun = start < 0.f ? 0.f : start;
+            int tok = -1, last = -1;
+            for (int base = w_lo; base < w_hi && tok < 0; base += 32) {
+                const int i = base + lane;
+                const float pr = i < w_hi ? expf(p[i] / temperature - m) * inv_z : 0.f;
+                float incl = pr;                                 // inclusive prefix sum over the 32 lanes
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const float t = __shfl_up_sync(0xffffffffu, incl, o);
+                    if (lane >= o) incl += t;
+                }
+                const unsigned has = __ballot_sync(0xffffffffu, pr > 0.f);
+                if (has) last = base + 31 - __clz(has);
+                const unsigned hit = __ballot_sync(0xffffffffu, start >= 0.f && wrun + incl >= u && pr > 0.f);
+                if (hit) tok = base + __ffs(hit) - 1;
+                wrun += __shfl_sync(0xffffffffu, incl, 31);
+            }
+            if (lane == 0) store_token(out, mirror, r, tok >= 0 ? tok : (last >= 0 ? last : w_hi - 1));
+        }
+        return;
+    }
+
+    if (shortlist && n_all <= CAP) {
+        // ---- every block sends its candidates, as probabilities, to their place in the first block's list ----
+        float* dst_p = cluster.map_shared_rank(cand_p, 0);
+        int* dst_i = cluster.map_shared_rank(cand_i, 0);
+        float vals[CAP / THREADS];
+        int idxs[CAP / THREADS], dst[CAP / THREADS];
+#pragma unroll
+        for (int j = 0; j < CAP / THREADS; ++j) {
+            const int slot = tid + j * THREADS, w = slot / SEG_CAP, pos = slot % SEG_CAP;
+            dst[j] = -1;
+            if (pos < seg_count[w]) {
+                int off = n_before;
+                for (int k = 0; k < w; ++k) off += seg_count[k];
+                dst[j] = off + pos;
+                vals[j] = expf(cand_p[slot] - m) * inv_z;
+                idxs[j] = cand_i[slot];
+            }
+        }
+        cluster.sync();                                          // the first block has read its own list: it may be overwritten
+#pragma unroll
+        for (int j = 0; j < CAP / THREADS; ++j)
+            if (dst[j] >= 0) { dst_p[dst[j]] = vals[j]; dst_i[dst[j]] = idxs[j]; }
+        cluster.sync();
+        if (rank == 0) {
+            if (n_all <= THREADS) finish_short(cand_p, n_all, cand_i, top_k, top_p, u, out, mirror, r, fscratch, chunk_sum, chunk_cnt);
+            else finish_row(cand_p, n_all, cand_i, top_k, top_p, u, out, mirror, r, fscratch, iscratch, chunk_sum, chunk_cnt);
+        }
+        return;
+    }
+
+    // ---- the long way (more ties than the list holds): every block turns its part of the row into
+    // probabilities, the first one walks the whole row ----
+    for (int i = c_lo + tid; i < c_hi; i += THREADS) p[i] = expf(p[i] / temperature - m) * inv_z;
+    __threadfence();
+    cluster.sync();
+    if (rank == 0)
+        finish_row(p, vocab, nullptr, top_k, top_p, u, out, mirror, r, fscratch, iscratch, chunk_sum, chunk_cnt);
+}
+
 }  // namespace
+
+int g_cluster_min_vocab = 32768;
 
 // logits: float32 [rows, vocab], overwritten.  out: int32 [rows].
 // recent (may be null): int32 [rows, recent_ld] with recent_count[r] valid ids per row, oldest first.
@@ -462,10 +816,45 @@ RI_API int ri_sample(float* logits, int rows, int vocab, int* out, float tempera
             return fail("sample: the mirror is not pinned host memory that the device can write");
         }
     }
+    // A cluster per row when the row is long enough to be worth it and the options allow it: greedy, plain
+    // temperature, or a top-k that the stretches' maxima can bound (with or without top-p).
+    const bool no_top_k = top_k <= 0 || top_k >= vocab;
+    const bool plain = no_top_k && !(top_p > 0.f && top_p < 1.f);
+    const bool by_cluster = g_cluster_min_vocab > 0 && vocab >= g_cluster_min_vocab && rows <= 65535 &&
+                            (temperature <= 0.f || plain || (!no_top_k && top_k <= GROUPS));
+    if (by_cluster) {
+        // a block's part: an equal share rounded up so that each of its warps has whole groups of 32 ids
+        const int per_cta = ((vocab + CLUSTER - 1) / CLUSTER + THREADS - 1) / THREADS * THREADS;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(CLUSTER, rows);
+        cfg.blockDim = dim3(THREADS);
+        cfg.dynamicSmemBytes = 0;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = CLUSTER;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = pdl_enabled() ? 2 : 1;
+        cudaError_t e = cudaLaunchKernelEx(&cfg, sample_cluster_kernel, logits, vocab, per_cta, out, temperature, top_k, top_p,
+                                           penalty, recent, recent_ld, recent_count, seed, row_stream, row_counter,
+                                           counter_offset, mirror, newest);
+        return check_launch(e, "sample (cluster)");
+    }
     cudaError_t e = launch_dependent(sample_kernel, dim3(rows), dim3(THREADS), (size_t)0, stream, logits, vocab, out,
                                      temperature, top_k, top_p, penalty, recent, recent_ld, recent_count, seed,
                                      row_stream, row_counter, counter_offset, mirror, newest);
     return check_launch(e, "sample");
+}
+
+// Rows of at least this many entries are sampled by a cluster of blocks where the options allow it
+// (0: never).  For comparisons and tests.
+RI_API int ri_sample_set_cluster_min_vocab(int vocab) {
+    g_cluster_min_vocab = vocab < 0 ? 0 : vocab;
+    return 0;
 }
 
 RI_DEFINE_LAST_ERROR()

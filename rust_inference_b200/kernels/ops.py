@@ -214,6 +214,12 @@ def sample(logits: torch.Tensor, out: torch.Tensor, *, temperature: float, top_k
     return out
 
 
+def sample_cluster_min_vocab(vocab: int) -> None:
+    """Rows of at least `vocab` entries are sampled by a cluster of thread blocks where the options
+    allow it (0: never; the library's default is 32,768).  For comparisons and tests."""
+    load("sampling").ri_sample_set_cluster_min_vocab(c_int(vocab))
+
+
 def attention_mma_supports(head_dim: int, page_size: int, n_heads: int, n_kv_heads: int, decode: bool) -> bool:
     lib = load("attention_mma")
     return bool(lib.ri_attention_mma_supports(c_int(head_dim), c_int(page_size), c_int(n_heads),

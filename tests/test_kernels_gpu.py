@@ -462,6 +462,16 @@ def test_attention_finds_a_far_key(dtype):
             assert (out3.float().cpu() - c["ref"]).abs().max().item() <= tol * c["ref"].abs().max().item()
 
 
+@pytest.fixture(params=["a block per row", "a cluster per row"])
+def sampling_kernel(request):
+    """Every sampling test runs twice: with the kernel that gives a row to one thread block, and with the one
+    that gives it to a cluster of eight wherever the options allow it (whatever the size of the vocabulary)."""
+    ops = _ops()
+    ops.sample_cluster_min_vocab(0 if request.param == "a block per row" else 1)
+    yield request.param
+    ops.sample_cluster_min_vocab(32768)
+
+
 def _sample(logits, **kw):
     ops = _ops()
     rows = logits.shape[0]
@@ -473,7 +483,7 @@ def _sample(logits, **kw):
     return out.cpu().tolist()
 
 
-def test_sampling_greedy_first_maximum():
+def test_sampling_greedy_first_maximum(sampling_kernel):
     g = torch.Generator().manual_seed(0)
     logits = torch.randn(6, 152064, generator=g)
     logits[1, 777] = logits[1, 151000] = 50.0                 # a tie: the first wins (math.rs:328-339)
@@ -488,7 +498,7 @@ def test_sampling_greedy_first_maximum():
 
 
 @pytest.mark.parametrize("vocab", [5, 384, 1000, 152064])
-def test_sampling_temperature_matches_the_cdf(vocab):
+def test_sampling_temperature_matches_the_cdf(vocab, sampling_kernel):
     """The drawn token must be the one whose CDF interval holds u, up to rounding at the edges."""
     g = torch.Generator().manual_seed(vocab)
     rows, T, seed = 64, 0.7, 4
@@ -506,7 +516,7 @@ def test_sampling_temperature_matches_the_cdf(vocab):
             assert got[r] == plain_impl.draw(probs, u) or abs(cdf[got[r]].item() - u) < 1e-5 or abs(lo - u) < 1e-5
 
 
-def test_sampling_frequencies_follow_the_distribution():
+def test_sampling_frequencies_follow_the_distribution(sampling_kernel):
     probs = torch.tensor([0.5, 0.25, 0.125, 0.0625, 0.0625])
     n = 4000
     logits = probs.log()[None].repeat(n, 1)
@@ -515,7 +525,7 @@ def test_sampling_frequencies_follow_the_distribution():
     assert (freq - probs).abs().max().item() < 0.03
 
 
-def test_sampling_top_k_top_p_and_penalty_follow_the_reference():
+def test_sampling_top_k_top_p_and_penalty_follow_the_reference(sampling_kernel):
     g = torch.Generator().manual_seed(1)
     vocab, rows, seed = 500, 48, 7
     logits = torch.randn(rows, vocab, generator=g) * 2
@@ -545,11 +555,38 @@ def test_sampling_top_k_top_p_and_penalty_follow_the_reference():
                    recent_count=torch.tensor([1], dtype=torch.int32, device=DEV)) == [2]
 
 
+def test_sampling_penalises_an_id_as_often_as_it_occurs(sampling_kernel):
+    """The recent ids may name a token several times, and the newest one (on the device) may repeat one of
+    them: each occurrence applies the penalty again (sampler.rs:109-127).  Greedy leaves the penalised logits
+    in the buffer, which is compared entry by entry."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(5)
+    for vocab in (50, 40000):
+        rows = 5
+        logits = torch.randn(rows, vocab, generator=g) * 4
+        recent = torch.randint(0, vocab, (rows, 64), generator=g).int()
+        recent[:, 10:20] = recent[:, 0:1]                      # the first id another ten times
+        recent[:, 30] = recent[:, 31] = vocab - 1
+        counts = torch.tensor([64, 33, 0, 12, 64], dtype=torch.int32)
+        newest = recent[:, 0].clone()
+        newest[3] = 7
+        buf = logits.clone().to(DEV)
+        out = torch.empty(rows, dtype=torch.int32, device=DEV)
+        ops.sample(buf, out, temperature=0.0, penalty=1.3, recent=recent.to(DEV), recent_count=counts.to(DEV),
+                   newest=newest.to(DEV))
+        for r in range(rows):
+            hist = recent[r, :counts[r]].tolist() + [int(newest[r])]
+            want = plain_impl.repetition_penalty(logits[r], hist, 1.3, 10 ** 6)
+            assert torch.allclose(buf[r].cpu(), want, rtol=1e-6, atol=0), (vocab, r)
+            assert out[r].item() == plain_impl.argmax_first(want)
+
+
 @pytest.mark.parametrize("vocab, kw", [
     (152064, dict(top_k=40, top_p=0.95)), (152064, dict(top_k=1000)), (152064, dict(top_k=1024, top_p=0.5)),
-    (4099, dict(top_k=7)), (5, dict(top_k=3, top_p=0.9)), (37, dict(top_k=36)),
+    (4099, dict(top_k=7)), (5, dict(top_k=3, top_p=0.9)), (37, dict(top_k=36)), (152064, dict(top_k=256)),
+    (40001, dict(top_k=200, top_p=0.8)), (33000, dict(top_k=2)),
 ])
-def test_sampling_top_k_over_a_candidate_list(vocab, kw):
+def test_sampling_top_k_over_a_candidate_list(vocab, kw, sampling_kernel):
     """With top-k the kernel keeps a short list of candidates instead of walking the vocabulary for every
     threshold: the drawn token must lie where the plain filters put the uniform number."""
     g = torch.Generator().manual_seed(vocab)
@@ -568,7 +605,7 @@ def test_sampling_top_k_over_a_candidate_list(vocab, kw):
         assert lo - 2e-5 <= u <= cdf[got[r]].item() + 2e-5, (kw, r, got[r], u)
 
 
-def test_sampling_top_k_with_more_ties_than_the_list_holds():
+def test_sampling_top_k_with_more_ties_than_the_list_holds(sampling_kernel):
     """Rows in which thousands of ids tie with the k-th largest: every one of them is kept (sampler.rs:130-160
     keeps ties), the candidate list cannot hold them, and the kernel takes the long way."""
     vocab, rows, seed = 20000, 4, 3
