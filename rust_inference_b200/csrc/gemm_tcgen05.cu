@@ -8,7 +8,8 @@
 // and runs a narrower tile inside the next larger one).  So a decode step with a handful of tokens
 // still fills the 128-row MMA with weights, and a long step can take the tile width that leaves the
 // least idle tail in the last wave of its persistent grid.  The SiLU-gate projection of steps of more than 128
-// tokens takes the token-major kernel further down (128 tokens x 256 weight rows per tile).
+// tokens takes the token-major kernel further down (128 tokens x 256 weight rows per tile), and long steps
+// whose tiles fill the grid run token-major on pairs of SMs (tcgen05 cta_group::2, at the end of the device code).
 // Both operands are K-major, which is how the reference lays its matrices out
 // ([out, in] row-major, quant.rs:45-50) and how activations are packed.
 //
@@ -336,6 +337,70 @@ constexpr int TM_TOK = 128;                         // tokens per tile (MMA M)
 constexpr int TM_ROWS = 256;                        // rows of W per tile (MMA N)
 constexpr int TM_STAGE_BYTES = (TM_TOK + TM_ROWS) * BLOCK_K * 2;     // 48 KiB
 
+// The token-major epilogue of one tile: the thread's token (TMEM lane) times the tile's features, 16 at a time
+// from the accumulator at `trow` (SiLU-gate: gate values in the first 128 columns, up values in the second).
+template <bool DUAL, int MODE>
+__device__ __forceinline__ void tm_write_tile(uint32_t trow, int t, bool t_ok, int f0, int n_feat, bool aligned,
+                                              const float* __restrict__ bias, void* __restrict__ out_,
+                                              bool pieces = false) {     // MODE 2: other work items add to the same tile
+    constexpr int FEATS = DUAL ? TM_ROWS / 2 : TM_ROWS;
+#pragma unroll 1
+    for (int c0 = 0; c0 < FEATS; c0 += 16) {
+        if (f0 + c0 >= n_feat) break;                       // uniform over the warp
+        uint32_t v[16], u[16];
+        tmem_ld16(trow + c0, v);
+        if (DUAL) tmem_ld16(trow + TM_ROWS / 2 + c0, u);
+        tmem_wait_ld();
+        if (!t_ok) continue;
+        const size_t o0 = (size_t)t * n_feat + f0 + c0;
+        const bool whole = aligned && f0 + c0 + 16 <= n_feat;
+        float r[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const float a = __uint_as_float(v[j]);
+            if (MODE == 3) r[j] = silu_to_bf16(a) * __uint_as_float(u[j]);
+            else if (MODE == 2) r[j] = a;
+            else r[j] = a + ((bias != nullptr && f0 + c0 + j < n_feat) ? bias[f0 + c0 + j] : 0.f);
+        }
+        if (whole) {
+            if (MODE == 0 || MODE == 3) {
+                __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(out_) + o0;
+                uint4 lo, hi;
+                lo.x = pack_bf16x2(r[0], r[1]);  lo.y = pack_bf16x2(r[2], r[3]);
+                lo.z = pack_bf16x2(r[4], r[5]);  lo.w = pack_bf16x2(r[6], r[7]);
+                hi.x = pack_bf16x2(r[8], r[9]);  hi.y = pack_bf16x2(r[10], r[11]);
+                hi.z = pack_bf16x2(r[12], r[13]); hi.w = pack_bf16x2(r[14], r[15]);
+                *reinterpret_cast<uint4*>(dst) = lo;
+                *reinterpret_cast<uint4*>(dst + 8) = hi;
+            } else {
+                float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(out_) + o0);
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    float4 x = make_float4(r[4 * q4], r[4 * q4 + 1], r[4 * q4 + 2], r[4 * q4 + 3]);
+                    if (MODE == 2 && pieces) {           // four adds in one reduction, no value returned
+                        asm volatile("red.relaxed.gpu.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + q4), "f"(x.x),
+                                     "f"(x.y), "f"(x.z), "f"(x.w) : "memory");
+                        continue;
+                    }
+                    if (MODE == 2) {                     // K is not split: a plain read-add-write
+                        const float4 old = dst[q4];
+                        x.x += old.x; x.y += old.y; x.z += old.z; x.w += old.w;
+                    }
+                    dst[q4] = x;
+                }
+            }
+        } else {
+            for (int j = 0; j < 16; ++j)
+                if (f0 + c0 + j < n_feat) {
+                    if (MODE == 0 || MODE == 3) reinterpret_cast<__nv_bfloat16*>(out_)[o0 + j] = __float2bfloat16_rn(r[j]);
+                    else if (MODE == 1) reinterpret_cast<float*>(out_)[o0 + j] = r[j];
+                    else if (pieces) atomicAdd(reinterpret_cast<float*>(out_) + o0 + j, r[j]);
+                    else reinterpret_cast<float*>(out_)[o0 + j] += r[j];
+                }
+        }
+    }
+}
+
 template <bool DUAL, int MODE>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_w2,
@@ -499,55 +564,7 @@ gemm_tm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             const int t = t0 + lane_base + lane;
             const bool t_ok = t < n_tok;
             const uint32_t trow = tmem_base + ((uint32_t)lane_base << 16) + (uint32_t)(buf * TM_ROWS);
-#pragma unroll 1
-            for (int c0 = 0; c0 < FEATS; c0 += 16) {
-                if (f0 + c0 >= n_feat) break;                       // uniform over the warp
-                uint32_t v[16], u[16];
-                tmem_ld16(trow + c0, v);
-                if (DUAL) tmem_ld16(trow + TM_ROWS / 2 + c0, u);
-                tmem_wait_ld();
-                if (!t_ok) continue;
-                const size_t o0 = (size_t)t * n_feat + f0 + c0;
-                const bool whole = aligned && f0 + c0 + 16 <= n_feat;
-                float r[16];
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const float a = __uint_as_float(v[j]);
-                    if (MODE == 3) r[j] = silu_to_bf16(a) * __uint_as_float(u[j]);
-                    else if (MODE == 2) r[j] = a;
-                    else r[j] = a + ((bias != nullptr && f0 + c0 + j < n_feat) ? bias[f0 + c0 + j] : 0.f);
-                }
-                if (whole) {
-                    if (MODE == 0 || MODE == 3) {
-                        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(out_) + o0;
-                        uint4 lo, hi;
-                        lo.x = pack_bf16x2(r[0], r[1]);  lo.y = pack_bf16x2(r[2], r[3]);
-                        lo.z = pack_bf16x2(r[4], r[5]);  lo.w = pack_bf16x2(r[6], r[7]);
-                        hi.x = pack_bf16x2(r[8], r[9]);  hi.y = pack_bf16x2(r[10], r[11]);
-                        hi.z = pack_bf16x2(r[12], r[13]); hi.w = pack_bf16x2(r[14], r[15]);
-                        *reinterpret_cast<uint4*>(dst) = lo;
-                        *reinterpret_cast<uint4*>(dst + 8) = hi;
-                    } else {
-                        float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(out_) + o0);
-#pragma unroll
-                        for (int q4 = 0; q4 < 4; ++q4) {
-                            float4 x = make_float4(r[4 * q4], r[4 * q4 + 1], r[4 * q4 + 2], r[4 * q4 + 3]);
-                            if (MODE == 2) {                     // K is not split here: a plain read-add-write
-                                const float4 old = dst[q4];
-                                x.x += old.x; x.y += old.y; x.z += old.z; x.w += old.w;
-                            }
-                            dst[q4] = x;
-                        }
-                    }
-                } else {
-                    for (int j = 0; j < 16; ++j)
-                        if (f0 + c0 + j < n_feat) {
-                            if (MODE == 0 || MODE == 3) reinterpret_cast<__nv_bfloat16*>(out_)[o0 + j] = __float2bfloat16_rn(r[j]);
-                            else if (MODE == 1) reinterpret_cast<float*>(out_)[o0 + j] = r[j];
-                            else reinterpret_cast<float*>(out_)[o0 + j] += r[j];
-                        }
-                }
-            }
+            tm_write_tile<DUAL, MODE>(trow, t, t_ok, f0, n_feat, aligned, bias, out_);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&acc_empty[buf]));
@@ -559,6 +576,239 @@ gemm_tm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS)
+                     : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// The token-major product on pairs of SMs (tcgen05 cta_group::2), for long steps.
+//
+// Two CTAs of a cluster share one MMA of M = 256 tokens x N = 256 rows of W: each CTA holds 128 of
+// the tokens (its half of A, and its half of the accumulator in its own tensor memory) and 128 of the
+// W rows (its half of B; the tensor cores read the other half from the partner's shared memory).  A
+// CTA so brings 32 KiB per k-block from L2 instead of 48 for the same 128 x 256 x 64 multiply-adds,
+// which is what long steps are bound by (asking tiles into L2 ahead of time made them slower, not
+// faster), and its ring holds six stages instead of four.  For the SiLU-gate projection the first CTA
+// loads the gate rows and the second the up rows of the same 128 features.
+//
+// The first CTA of the pair issues the MMAs.  Both CTAs' TMA loads report to its `full` barrier; its
+// commits arrive at the `empty` and `acc_full` barriers of both (multicast); the epilogue warps of both
+// arrive at its `acc_empty` barrier.  Tensor memory is allocated and freed by both, as a pair.
+// ---------------------------------------------------------------------------------------------
+constexpr int PAIR_STAGE_BYTES = 2 * A_BYTES;       // 128 tokens + 128 W rows per CTA and k-block: 32 KiB
+constexpr int PAIR_TOK = 2 * TM_TOK;                // tokens per pair tile
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// The address, in the cluster's shared window, of the first CTA's copy of a shared variable of this CTA.
+__device__ __forceinline__ uint32_t in_first_cta(uint32_t local_addr) {
+    uint32_t a;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, 0;" : "=r"(a) : "r"(local_addr));
+    return a;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// A tile into this CTA's shared memory whose arrival is counted by a barrier of the pair's first CTA.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t cluster_bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(cluster_bar), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, bool accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"((uint32_t)accumulate)
+        : "memory");
+}
+// Arrives at the barrier at this address in both CTAs of the pair once the MMAs issued so far are done.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"((uint16_t)3) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+
+template <bool DUAL, int MODE>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_w2,
+                 const __grid_constant__ CUtensorMap map_x, const float* __restrict__ bias, void* __restrict__ out_,
+                 int n_tok, int n_feat, int K, int kb_per_split, int split_k, int stages, int* status) {
+    constexpr int FEATS = DUAL ? TM_ROWS / 2 : TM_ROWS;        // output features per tile
+    constexpr int TMEM_COLS = 2 * TM_ROWS;                     // two accumulator buffers
+    // D float32, A and B bf16, both K-major, N = 256, M = 256 over the pair
+    constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TM_ROWS >> 3) << 17) |
+                               ((uint32_t)(PAIR_TOK >> 4) << 24);
+
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[MAX_STAGES];     // used in the first CTA only
+    __shared__ __align__(8) uint64_t empty_bar[MAX_STAGES];
+    __shared__ __align__(8) uint64_t acc_full[2];
+    __shared__ __align__(8) uint64_t acc_empty[2];             // used in the first CTA only
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ volatile int abort_flag;
+
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int rank = (int)cluster_rank();                      // 0: issues the MMAs
+    const int pair = (int)blockIdx.x >> 1, n_pairs = (int)gridDim.x >> 1;
+    const int n_kb = (K + BLOCK_K - 1) / BLOCK_K;
+    const int n_tok_tiles = (n_tok + PAIR_TOK - 1) / PAIR_TOK, n_feat_tiles = (n_feat + FEATS - 1) / FEATS;
+    const int total_tiles = n_tok_tiles * n_feat_tiles * split_k;            // work items: tiles x pieces of K
+    const int my_tiles = (pair < total_tiles) ? (total_tiles - 1 - pair) / n_pairs + 1 : 0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; ++s) {
+            mbar_init(smem_u32(&full_bar[s]), 1);
+            mbar_init(smem_u32(&empty_bar[s]), 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(smem_u32(&acc_full[i]), 1);
+            mbar_init(smem_u32(&acc_empty[i]), 8);             // one arrival per epilogue warp of the pair
+        }
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
+                     "r"((uint32_t)TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    cluster_sync_all();                                        // the partner's barriers stand before anything arrives there
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+    const uint32_t full0 = smem_u32(&full_bar[0]), empty0 = smem_u32(&empty_bar[0]);
+    const uint32_t full0_first = in_first_cta(full0);
+    let_next_kernel_start();
+
+    // token tiles vary fastest, so pairs that run together share the weight rows in L2
+    auto tile_coords = [&](int i, int& f0, int& t0, int& kb_begin, int& kb_end) {
+        const int item = pair + i * n_pairs;
+        const int rest = item / n_tok_tiles, sp = rest / n_feat_tiles;
+        t0 = (item - rest * n_tok_tiles) * PAIR_TOK;
+        f0 = (rest - sp * n_feat_tiles) * FEATS;
+        kb_begin = sp * kb_per_split;
+        kb_end = min(n_kb, kb_begin + kb_per_split);             // > kb_begin by construction of the split
+    };
+
+    if (warp == 0) {
+        // ---------------- TMA producer (both CTAs) ----------------
+        if (lane == 0) {
+            int it = 0, s = 0;
+            uint32_t ph = 0;
+            bool alive = true;
+            wait_for_previous_kernels();                         // the activations come from the kernel before
+            // this CTA's half of the W rows: gate (first CTA) or up (second) rows of the tile's features, or the
+            // first or second 128 of its 256 features
+            const CUtensorMap* my_w = (DUAL && rank == 1) ? &map_w2 : &map_w;
+            const int w_off = DUAL ? 0 : rank * BLOCK_F;
+            for (int i = 0; i < my_tiles && alive; ++i) {
+                int f0, t0, kb_begin, kb_end;
+                tile_coords(i, f0, t0, kb_begin, kb_end);
+                if (abort_flag) break;
+                for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
+                    if (!mbar_wait(empty0 + 8u * s, ph ^ 1u)) {
+                        if (!abort_flag) report(status, ST_PRODUCER_TIMEOUT);
+                        abort_flag = 1;
+                        alive = false;
+                        break;
+                    }
+                    const uint32_t stage = smem_base + (uint32_t)s * PAIR_STAGE_BYTES;
+                    if (rank == 0) mbar_expect_tx(full0 + 8u * s, 2 * PAIR_STAGE_BYTES);       // both CTAs' bytes
+                    tma_load_2d_pair(stage, &map_x, full0_first + 8u * s, kb * BLOCK_K, t0 + rank * TM_TOK);
+                    tma_load_2d_pair(stage + A_BYTES, my_w, full0_first + 8u * s, kb * BLOCK_K, f0 + w_off);
+                    if (++s == stages) { s = 0; ph ^= 1u; }
+                }
+            }
+            // Do not leave while a copy into this CTA's shared memory may still be in flight: a stage whose
+            // `empty` barrier has completed again was read by the MMAs, so its copy had landed.
+            for (int j = 0; j < stages && it > 0; ++j) {
+                if (!mbar_wait(empty0 + 8u * s, ph ^ 1u)) {
+                    report(status, ST_DRAIN_TIMEOUT);
+                    break;
+                }
+                if (++s == stages) { s = 0; ph ^= 1u; }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer (first CTA) ----------------
+        if (lane == 0 && rank == 0) {
+            int s = 0;
+            uint32_t ph = 0;
+            bool alive = true;
+            const uint64_t desc_x0 = make_smem_desc(smem_base), desc_w0 = make_smem_desc(smem_base + A_BYTES);
+            for (int i = 0; i < my_tiles && alive; ++i) {
+                int f0, t0, kb_begin, kb_end;
+                tile_coords(i, f0, t0, kb_begin, kb_end);
+                const int buf = i & 1;
+                if (!mbar_wait(smem_u32(&acc_empty[buf]), ((uint32_t)(i >> 1) & 1u) ^ 1u)) {
+                    report(status, ST_MMA_TIMEOUT);
+                    abort_flag = 1;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t acc = tmem_base + (uint32_t)(buf * TM_ROWS);
+                for (int kb = kb_begin; kb < kb_end; ++kb) {
+                    if (!mbar_wait(full0 + 8u * s, ph)) {
+                        report(status, ST_MMA_TIMEOUT);
+                        abort_flag = 1;
+                        alive = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint64_t off = (uint64_t)((uint32_t)s * (uint32_t)(PAIR_STAGE_BYTES >> 4));
+#pragma unroll
+                    for (int k = 0; k < BLOCK_K / 16; ++k)
+                        umma_pair(acc, desc_x0 + off + 2 * k, desc_w0 + off + 2 * k, IDESC, kb > kb_begin || k > 0);
+                    umma_commit_pair(empty0 + 8u * s);           // frees the stage in both CTAs
+                    if (++s == stages) { s = 0; ph ^= 1u; }
+                }
+                umma_commit_pair(smem_u32(&acc_full[buf]));
+            }
+        }
+    } else {
+        // ---------------- epilogue (both CTAs): a thread owns a token, writes runs of 16 features ----------------
+        const int lane_base = (warp & 3) * 32;
+        const bool aligned = n_feat % 8 == 0;
+        const uint32_t acc_empty_first = in_first_cta(smem_u32(&acc_empty[0]));
+        wait_for_previous_kernels();
+        for (int i = 0; i < my_tiles; ++i) {
+            int f0, t0, kb_begin, kb_end;
+            tile_coords(i, f0, t0, kb_begin, kb_end);
+            const int buf = i & 1;
+            const bool landed = mbar_wait(smem_u32(&acc_full[buf]), (uint32_t)(i >> 1) & 1u);
+            if (!landed && lane == 0) {
+                report(status, ST_EPILOGUE_TIMEOUT);
+                abort_flag = 1;
+            }
+            tc_fence_after();
+            if (!landed || abort_flag) break;
+            const int t = t0 + rank * TM_TOK + lane_base + lane;
+            const bool t_ok = t < n_tok;
+            const uint32_t trow = tmem_base + ((uint32_t)lane_base << 16) + (uint32_t)(buf * TM_ROWS);
+            tm_write_tile<DUAL, MODE>(trow, t, t_ok, f0, n_feat, aligned, bias, out_, split_k > 1);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(acc_empty_first + 8u * (uint32_t)buf);
+        }
+    }
+
+    // nothing of the pair's tensor or shared memory is freed while the partner may still use it
+    tc_fence_before();
+    cluster_sync_all();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS)
                      : "memory");
     }
 }
@@ -658,6 +908,82 @@ int launch_tm(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& 
     return check_launch(e, "gemm_tcgen05 (token-major)");
 }
 
+int g_pair_min_tokens = 512;     // steps of at least this many tokens may run on pairs of SMs (0: never)
+bool g_pair_always = false;      // ... whatever their tiles make of the grid (tests)
+
+// Whether a product runs on pairs of SMs.  Measured on a 3584-wide model at 512, 2,048 and 8,192 tokens: where
+// the pair tiles fill the grid's rounds as well as the single-CTA tiles do, pairs are 2-5% faster (SiLU-gate
+// projection 367 -> 357 us at 2,048 tokens, q/k/v 218 -> 208 us at 8,192); where they leave a round half
+// empty (o and down projections: 112 tiles of 256 x 256 on 74 pairs) they lose up to 15%.  The adding epilogue
+// cannot split K here, so it stays with the single-CTA kernel.
+// Pieces of K for the adding epilogue on pairs: the count that leaves the busiest pair the fewest k-blocks,
+// with a dozen per work item for its epilogue and ramp.
+int pair_split(int n_tok, int n_feat, int K) {
+    const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
+    const long long tiles = (long long)((n_tok + PAIR_TOK - 1) / PAIR_TOK) * ((n_feat + TM_ROWS - 1) / TM_ROWS);
+    const long long pairs = sm_count() / 2;
+    long long best = -1;
+    int split = 1;
+    for (int sp = 1; sp <= 10 && (sp == 1 || total_kb / sp >= 8); ++sp) {
+        const long long cost = ((tiles * sp + pairs - 1) / pairs) * ((total_kb + sp - 1) / sp + 12);
+        if (best < 0 || cost < best) { best = cost; split = sp; }
+    }
+    return split;
+}
+
+bool on_pairs(int n_tok, int n_feat, int mode) {
+    if (g_pair_min_tokens <= 0 || n_tok < g_pair_min_tokens) return false;
+    if (g_pair_always) return true;
+    if (mode == 2) return false;
+    const long long feats = mode == 3 ? TM_ROWS / 2 : TM_ROWS;
+    const long long tiles = (long long)((n_tok + PAIR_TOK - 1) / PAIR_TOK) * ((n_feat + feats - 1) / feats);
+    const long long pairs = sm_count() / 2;
+    const long long rounds = (tiles + pairs - 1) / pairs;
+    return tiles * 100 >= rounds * pairs * 93;               // the last round at least ~93% full on average
+}
+
+template <bool DUAL, int MODE>
+int launch_pair(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx, const float* bias, void* out,
+                int n_tok, int n_feat, int K, int split_k, int* status, cudaStream_t stream) {
+    const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
+    if (split_k < 1 || MODE != 2) split_k = 1;
+    if (split_k > total_kb) split_k = total_kb;
+    const int kb_per_split = (total_kb + split_k - 1) / split_k;
+    split_k = (total_kb + kb_per_split - 1) / kb_per_split;          // no empty piece
+    int stages = SMEM_BUDGET / PAIR_STAGE_BYTES;
+    if (stages > MAX_STAGES) stages = MAX_STAGES;
+    if (stages > total_kb) stages = total_kb;
+    const size_t smem = (size_t)stages * PAIR_STAGE_BYTES + 1024;
+    auto kernel = gemm_pair_kernel<DUAL, MODE>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BUDGET + 1024);
+        if (e != cudaSuccess) return fail("gemm_tcgen05: cannot raise dynamic shared memory: %s", cudaGetErrorString(e));
+        configured = true;
+    }
+    constexpr int FEATS = DUAL ? TM_ROWS / 2 : TM_ROWS;
+    const long long total_tiles = (long long)((n_tok + PAIR_TOK - 1) / PAIR_TOK) * ((n_feat + FEATS - 1) / FEATS) * split_k;
+    if (total_tiles > 0x7fffffffLL) return fail("gemm_tcgen05: %lld tiles exceed the index range", total_tiles);
+    long long pairs = sm_count() / 2;
+    if (pairs > total_tiles) pairs = total_tiles;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(2 * pairs));
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, mw, mw2, mx, bias, out, n_tok, n_feat, K, kb_per_split, split_k, stages, status);
+    return check_launch(e, "gemm_tcgen05 (pairs of SMs)");
+}
+
 template <bool DUAL, int MODE>
 int pick_tile(int tn, const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx, const float* bias,
               void* out, int n_tok, int n_feat, int K, int split_k, int* status, cudaStream_t stream) {
@@ -673,6 +999,14 @@ int pick_tile(int tn, const CUtensorMap& mw, const CUtensorMap& mw2, const CUten
 }
 
 }  // namespace
+
+// Steps of at least n_tok tokens may run on pairs of SMs (0: never); with always != 0 they do, whatever
+// their tiles make of the grid.  For comparisons and tests; plans made before the call no longer hold.
+RI_API int ri_gemm_tcgen05_set_pairs(int n_tok, int always) {
+    g_pair_min_tokens = n_tok < 0 ? 0 : n_tok;
+    g_pair_always = always != 0;
+    return 0;
+}
 
 // Shared memory a CTA may use for its stage ring, in bytes (0 restores the defaults).  For tuning.
 RI_API int ri_gemm_tcgen05_set_smem_budget(int bytes) {
@@ -711,7 +1045,10 @@ RI_API int ri_gemm_tcgen05_plan(int n_tok, int n_feat, int K, int mode, int* til
     const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
     const bool can_split = mode == 2;
     int tn = 16, sp = 1;
-    if (n_tok <= 128) {
+    if (on_pairs(n_tok, n_feat, mode)) {
+        tn = TM_TOK;                                              // pairs of SMs: each CTA's box holds 128 tokens
+        if (mode == 2) sp = pair_split(n_tok, n_feat, K);
+    } else if (n_tok <= 128) {
         tn = n_tok <= 16 ? 16 : (n_tok + 15) / 16 * 16;
         if (can_split && feat_tiles < ctas) {
             // every piece ends in tn x 128 atomic adds, so wider steps want longer pieces: at least a tenth of
@@ -776,6 +1113,14 @@ RI_API int ri_gemm_tcgen05(const void* map_x, const void* map_w, const void* map
     const CUtensorMap& mx = *reinterpret_cast<const CUtensorMap*>(map_x);
     // Measured at 2,048 tokens of a 3584-wide model: the SiLU-gate projection runs at 1,334 TFLOP/s
     // token-major against 1,145 feature-major; q/k/v, o and down are 3-12% faster feature-major.
+    if (on_pairs(n_tok, n_feat, mode)) {
+        switch (mode) {
+            case 0: return launch_pair<false, 0>(mw, mw2, mx, bias, out, n_tok, n_feat, K, 1, status, stream);
+            case 1: return launch_pair<false, 1>(mw, mw2, mx, bias, out, n_tok, n_feat, K, 1, status, stream);
+            case 2: return launch_pair<false, 2>(mw, mw2, mx, bias, out, n_tok, n_feat, K, split_k, status, stream);
+            default: return launch_pair<true, 3>(mw, mw2, mx, bias, out, n_tok, n_feat, K, 1, status, stream);
+        }
+    }
     if (dual && n_tok > TM_TOK) return launch_tm<true, 3>(mw, mw2, mx, bias, out, n_tok, n_feat, K, status, stream);
     switch (mode) {
         case 0: return pick_tile<false, 0>(tn, mw, mw2, mx, bias, out, n_tok, n_feat, K, split_k, status, stream);

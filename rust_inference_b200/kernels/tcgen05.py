@@ -61,6 +61,14 @@ def plan(n_tok: int, n_feat: int, k: int, mode: int) -> tuple:
     return tile.value, split.value
 
 
+def set_pairs(min_tokens: int = 512, always: bool = False) -> None:
+    """Steps of at least `min_tokens` tokens may run on pairs of SMs (tcgen05 cta_group::2; 0: never);
+    with `always` they do, whatever their tiles make of the grid.  For comparisons and tests."""
+    build.load("gemm_tcgen05").ri_gemm_tcgen05_set_pairs(c_int(min_tokens), c_int(1 if always else 0))
+    plan.cache_clear()
+    _x_maps.clear()
+
+
 def token_tile(n_tok: int, n_feat: int, k: int, mode: int) -> int:
     return plan(n_tok, n_feat, k, mode)[0]
 

@@ -272,6 +272,47 @@ def test_gemm_tcgen05_token_tile_follows_the_grid(m, n, k):
     tcgen05.check_status()
 
 
+@pytest.mark.parametrize("m, n, k", [(512, 512, 256), (300, 1000, 520), (1111, 264, 72), (256, 3000, 64), (40, 384, 128),
+                                     (2048, 1184, 1096)])
+def test_gemm_tcgen05_on_pairs_of_sms(m, n, k):
+    """The same products with two CTAs sharing each MMA (tcgen05 cta_group::2: 256 tokens x 256 weight rows per
+    pair, each CTA loading half of both operands), forced on whatever the shape; ragged tokens, features and K."""
+    ops = _ops()
+    from rust_inference_b200.kernels import linear, tcgen05
+    tcgen05.set_pairs(1, always=True)
+    try:
+        assert tcgen05.plan(m, n, k, ops.EPI_STORE) == (128, 1)
+        x = (torch.randn(m, k, device=DEV) * 0.5).bfloat16()
+        w = linear.Weight((torch.randn(n, k, device=DEV) * 0.1).bfloat16())
+        w2 = linear.Weight((torch.randn(n, k, device=DEV) * 0.1).bfloat16())
+        bias = torch.randn(n, device=DEV)
+        ref = x.double() @ w.t.double().t()
+        ref2 = x.double() @ w2.t.double().t()
+        scale = ref.abs().max().item()
+        out32 = torch.full((m, n), 9.0, device=DEV)
+        tcgen05.gemm(x, w, out32, ops.EPI_STORE_F32)
+        assert (out32.double() - ref).abs().max().item() <= 1e-5 * scale
+        out = torch.empty(m, n, device=DEV, dtype=torch.bfloat16)
+        tcgen05.gemm(x, w, out, ops.EPI_STORE, bias=bias)
+        assert (out.double() - (ref + bias)).abs().max().item() <= 8e-3 * (scale + bias.abs().max().item())
+        act = torch.empty(m, n, device=DEV, dtype=torch.bfloat16)
+        tcgen05.gemm(x, w, act, ops.EPI_SILU_MUL, w2=w2)
+        want = plain_impl.silu(ref.float()).double() * ref2
+        assert (act.double() - want).abs().max().item() <= 8e-3 * (want.abs().max().item() + 1e-3)
+        # the adding epilogue stays with the single-CTA kernel, which can split K
+        res = torch.randn(m, n, device=DEV)
+        before = res.clone()
+        tcgen05.gemm(x, w, res, ops.EPI_RESIDUAL)
+        assert (res.double() - (before + ref)).abs().max().item() <= 1e-5 * (scale + 4)
+        torch.cuda.synchronize()
+        tcgen05.check_status()
+    finally:
+        tcgen05.set_pairs()
+    # by default only long steps whose tiles fill the pairs' rounds go there
+    assert tcgen05.plan(8, 3584, 3584, ops.EPI_STORE)[0] == 16
+    assert tcgen05.plan(2048, 18944, 3584, ops.EPI_SILU_MUL) == (128, 1)
+
+
 def test_gemm_tcgen05_refuses_what_it_cannot_do():
     from rust_inference_b200.kernels import linear, ops, tcgen05
     x = torch.zeros(4, 100, device=DEV, dtype=torch.bfloat16)
