@@ -146,6 +146,7 @@ def main() -> int:
     ap.add_argument("--prompt-min", type=int, default=PROMPT_MIN, help="shortest prompt of the decode runs")
     ap.add_argument("--prompt-max", type=int, default=PROMPT_MAX, help="longest prompt of the decode runs")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS)
+    ap.add_argument("--seq-len", type=int, default=CONTEXT, help="positions a sequence may reach (cache and rotary table)")
     ap.add_argument("--skip-points", action="store_true", help="skip the batch-1 and batch-64 points")
     ap.add_argument("--kernel", default=None, help="time ONE kernel at the benchmark model's sizes instead "
                     "(qkv, qkv_split, o_proj, gate_up, down, lm_head, attn_decode, attn_prefill, attn_prefill_mma, rmsnorm, rope)")
@@ -189,7 +190,10 @@ def main() -> int:
     cache_tokens = max(biggest * (-(-(prompt_max + total_steps) // 64) * 64), prefill_tokens + 64) + 4096
     torch.cuda.set_device(0)
     t0 = time.time()
-    model = Model.random(cfg, seed=0, dtype="bfloat16", device="cuda:0", max_seq_len=CONTEXT,
+    seq_len = max(args.seq_len, prompt_max + total_steps, prefill_tokens)
+    model_cfg["max_position_embeddings"] = max(model_cfg.get("max_position_embeddings", seq_len), seq_len)
+    cfg = config_from_dict(model_cfg)
+    model = Model.random(cfg, seed=0, dtype="bfloat16", device="cuda:0", max_seq_len=seq_len,
                          max_tokens_in_cache=cache_tokens)
     engine = model.engine
     print(f"[bench] model ready in {time.time() - t0:.1f} s; cache {engine.cache.bytes() / 1e9:.2f} GB",
@@ -287,7 +291,7 @@ def main() -> int:
 
     line = {
         "metric": f"decode tok/s @ batch {args.batch} ({SIZE_NAMES[args.sizes]} dense decoder, random bf16 weights, "
-                  f"8,192-position cache)",
+                  f"{seq_len:,}-position cache)",
         "value": main_run["tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
         "ms_per_step": main_run["ms_per_step"], "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random weights N(0, 0.02), seeded random token ids)",
@@ -297,7 +301,7 @@ def main() -> int:
             "hidden_size": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
             "head_dim": cfg.head_dim, "intermediate_size": cfg.intermediate_size, "vocab_size": cfg.vocab_size,
             "qkv_bias": cfg.attention_bias, "tied_embeddings": cfg.tie_word_embeddings,
-            "global_batch": args.batch, "seq_len": CONTEXT, "prompt_lengths": f"uniform {prompt_min}-{prompt_max}",
+            "global_batch": args.batch, "seq_len": seq_len, "prompt_lengths": f"uniform {prompt_min}-{prompt_max}",
             "mean_context": round(main_run["mean_ctx_tokens"] / args.batch, 1), "parallelism": "single GPU",
             "l2": "inputs larger than L2 (weights read once per step)", "peaks": peak_source,
         },
