@@ -6,6 +6,10 @@ from a static device buffer that is refilled before each replay and writes logit
 static buffer; its scratch buffers are private, so nothing it points to ever moves.
 Kernels size their grids from B and the cache geometry only, never from the current
 lengths, so one capture serves every step of that batch size.
+
+A batch size is captured only once it has been stepped a few times: a batch that loses a
+sequence at every step passes through many sizes once, and capturing each (a second pass over
+the model and a device synchronisation) would cost more than the launches it saves.
 """
 from __future__ import annotations
 
@@ -17,6 +21,9 @@ import torch
 
 from ..kernels import ops
 from .context import StepContext, Workspace, pack_step
+
+
+EAGER_STEPS = 2          # steps of a batch size that launch their kernels one by one before it is captured
 
 
 class DecodeGraph:
@@ -35,6 +42,7 @@ class DecodeGraph:
         self.workspace = Workspace(dev)
         self.graph = None
         self.launches = 0             # kernels one replay launches
+        self.eager_steps = 0
 
         def view(name):
             o, c = self.layout[name]
@@ -60,10 +68,13 @@ class DecodeGraph:
     def launch(self) -> torch.Tensor:
         """Run the step over whatever the static arrays hold; returns the static logits buffer."""
         if self.graph is None:
-            # once eagerly (compiles, sizes scratch, caches tensor maps), then capture
-            before = ops.launch_count()
-            self.engine.model.forward(self.ctx, self.engine.cache, self.logits)
-            self.launches = ops.launch_count() - before
+            if self.eager_steps < EAGER_STEPS:
+                # eagerly (the first time this also compiles, sizes scratch and caches tensor maps)
+                self.eager_steps += 1
+                before = ops.launch_count()
+                self.engine.model.forward(self.ctx, self.engine.cache, self.logits)
+                self.launches = ops.launch_count() - before
+                return self.logits
             torch.cuda.synchronize(self.engine.device)
             g = torch.cuda.CUDAGraph()
             collecting = gc.isenabled()
@@ -75,8 +86,6 @@ class DecodeGraph:
                 if collecting:
                     gc.enable()
             self.graph = g
-            # the eager run already produced this step's logits
-            return self.logits
         self.graph.replay()
         return self.logits
 
