@@ -191,11 +191,7 @@ class Engine:
             if decode and self.use_graphs:
                 # one token per sequence, logits for each: the captured step of this batch size
                 dev, _, _ = self._stage(slots, tokens, wants)
-                graph = self._graphs.get(len(slots))
-                if graph is None:
-                    from .graphs import DecodeGraph
-                    graph = self._graphs[len(slots)] = DecodeGraph(self, len(slots))
-                logits = graph.run(dev)
+                logits = self._graph_for(len(slots)).run(dev)
                 if not borrow:
                     logits = logits.clone()
             else:
@@ -209,6 +205,14 @@ class Engine:
             self.cache.commit(s, self.cache.length(s) + len(t))
         return logits
 
+    def _graph_for(self, n: int):
+        """The captured decode step of n sequences (made on first use; call with the device current)."""
+        graph = self._graphs.get(n)
+        if graph is None:
+            from .graphs import DecodeGraph
+            graph = self._graphs[n] = DecodeGraph(self, n)
+        return graph
+
     def can_feed_from_device(self) -> bool:
         """True if decode steps replay a captured graph, so a step can take its tokens from a
         device tensor (`step_from_device`)."""
@@ -217,26 +221,19 @@ class Engine:
     def decode_token_buffer(self, n: int) -> torch.Tensor:
         """The int32 [n] device buffer from which the captured decode step of n sequences reads its
         tokens: a sampler that writes there feeds `step_from_device` without a copy."""
-        from .graphs import DecodeGraph
         with torch.cuda.device(self.device):
-            graph = self._graphs.get(n)
-            if graph is None:
-                graph = self._graphs[n] = DecodeGraph(self, n)
-        return graph.ctx.token_ids
+            return self._graph_for(n).ctx.token_ids
 
     def step_from_device(self, slots: list, tokens_dev: torch.Tensor):
         """One decode step whose tokens (one per sequence, int32 [B]) are already on the device,
         for instance straight from the sampler: no host round trip between sampling and the next
         step.  Returns the step's logits [B, vocab] in a buffer the next step overwrites."""
-        from .graphs import DecodeGraph
         n = len(slots)
         if tokens_dev.numel() != n or tokens_dev.dtype != torch.int32:
             raise ValueError("step_from_device: one int32 token per sequence")
         with torch.cuda.device(self.device):
             dev, _, _ = self._stage(slots, [[0]] * n, [[0]] * n)
-            graph = self._graphs.get(n)
-            if graph is None:
-                graph = self._graphs[n] = DecodeGraph(self, n)
+            graph = self._graph_for(n)
             graph.load_meta(dev, keep_tokens=True)
             if tokens_dev.data_ptr() != graph.ctx.token_ids.data_ptr():       # else they are in place already
                 graph.ctx.token_ids.copy_(tokens_dev, non_blocking=True)
@@ -252,7 +249,6 @@ class Engine:
         The first step is fed `first_tokens`."""
         from ..sampling.params import SamplerConfig
         from ..kernels import ops
-        from .graphs import DecodeGraph
         cfg = sampler_config or SamplerConfig.plain(temperature=0.0)
         if cfg.uses_history:
             raise ValueError("decode_steps keeps no token history: use it without a repetition penalty")
@@ -263,9 +259,7 @@ class Engine:
         starts = [self.cache.length(s) for s in slots]
         self.cache.reserve([(s, st + n_steps) for s, st in zip(slots, starts)])
         with torch.cuda.device(self.device):
-            graph = self._graphs.get(n)
-            if graph is None:
-                graph = self._graphs[n] = DecodeGraph(self, n)
+            graph = self._graph_for(n)
             out = torch.empty((n_steps, n), dtype=torch.int32, device=self.device)
             streams = torch.arange(n, dtype=torch.int32, device=self.device)
             counters = torch.arange(n_steps, dtype=torch.int32, device=self.device).repeat_interleave(n).view(n_steps, n)
