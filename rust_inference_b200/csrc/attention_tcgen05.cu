@@ -15,7 +15,7 @@
 //                 when the true maximum exceeds it by more than 2^8, so P stays below 256 and the
 //                 accumulator is rescaled rarely (exactness is kept: the final division by the
 //                 row sum uses the same scaling).
-//   O += P V      P is written to shared memory as bf16 in the swizzled K-major layout and is the
+//   O += P V      P goes back to tensor memory as bf16, over the scores it was made from, and is the
 //                 A operand; the V page, [keys][head_dim] as the cache holds it, is the B operand
 //                 in MN-major form; O accumulates in tensor memory in float32.
 // Warp 0 issues the TMA loads, warp 1 the MMAs, warps 2-5 are the softmax rows.  There are two score
@@ -101,7 +101,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                                   ((uint32_t)(BM >> 4) << 24);
 
     // Everything lives in dynamic shared memory: the tiles (1024-byte aligned for the 128-byte swizzle) and,
-    // behind them, the barriers.  With head_dim 128 the tiles take 112 KiB and two CTAs share an SM only if
+    // behind them, the barriers.  With head_dim 128 the tiles take 96 KiB and two CTAs share an SM only if
     // nothing is spent on alignment: the kernel declares no static shared memory, so that the dynamic part
     // starts at the CTA's window, and checks that it fits.
     extern __shared__ uint8_t smem_raw[];
