@@ -148,14 +148,14 @@ class SequenceCache:
         total = sum(len(p) for p in added.values())
         if self.device.type != "cuda":
             for slot, pages in added.items():
-                have = len(self.pager._pages[slot])
+                have = self.pager.page_count(slot)
                 self.page_table_host[slot, have - len(pages):have] = pages
                 self.page_table[slot, have - len(pages):have] = torch.tensor(pages, dtype=torch.int32)
             return
         buf = self._staging(total)
         off = 0
         for slot, pages in added.items():
-            have = len(self.pager._pages[slot])
+            have = self.pager.page_count(slot)
             self.page_table_host[slot, have - len(pages):have] = pages
             buf[off:off + len(pages)] = torch.tensor(pages, dtype=torch.int32)
             self.page_table[slot, have - len(pages):have].copy_(buf[off:off + len(pages)], non_blocking=True)
@@ -166,3 +166,10 @@ class SequenceCache:
 
     def commit(self, slot: int, new_length: int) -> None:
         self.pager.set_length(slot, new_length)
+
+    def lengths(self, slots: list) -> list:
+        return self.pager.lengths(slots)
+
+    def advance(self, slots: list, counts: list) -> None:
+        """The end of a step: every slot's length moves on by the tokens it was given."""
+        self.pager.advance(slots, counts)

@@ -2,6 +2,7 @@
 from __future__ import annotations
 
 from dataclasses import dataclass, field
+from itertools import chain
 
 import numpy as np
 import torch
@@ -91,19 +92,36 @@ class StepContext:
         return self.workspace.get_zeroed(name, shape, dtype)
 
 
+_pack = None
+
+
+def _packer():
+    global _pack
+    if _pack is None:
+        from ctypes import c_int, c_longlong, c_void_p
+        from ..kernels import build
+        fn = build.load("host_runtime").ri_pack_step
+        fn.restype = c_longlong
+        fn.argtypes = [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p]
+        _pack = fn
+    return _pack
+
+
 def pack_step(starts: list, tokens: list, wants: list) -> tuple:
-    """Host side of a step: flatten B token lists into the int32 arrays of StepContext.
+    """Host side of a step: flatten B token lists into the int32 arrays of StepContext (the native
+    host runtime lays them out, `csrc/host_runtime.cpp`).
 
     starts[b]  positions already cached for sequence b
     tokens[b]  its new tokens
     wants[b]   indices into tokens[b] whose logits are wanted
     Returns (meta: np.int32 array, layout: dict name -> (offset, count), scalars: dict)."""
     n_seqs = len(tokens)
-    counts = [len(t) for t in tokens]
-    n_tokens = sum(counts)
-    cu = np.zeros(n_seqs + 1, dtype=np.int64)
-    np.cumsum(counts, out=cu[1:])
-    n_rows = sum(len(w) for w in wants)
+    counts = np.fromiter((len(t) for t in tokens), dtype=np.int32, count=n_seqs)
+    want_counts = np.fromiter((len(w) for w in wants), dtype=np.int32, count=n_seqs)
+    n_tokens, n_rows = int(counts.sum()), int(want_counts.sum())
+    flat = np.fromiter(chain.from_iterable(tokens), dtype=np.int32, count=n_tokens) if n_tokens else np.zeros(1, np.int32)
+    flat_wants = np.fromiter(chain.from_iterable(wants), dtype=np.int32, count=n_rows) if n_rows else np.zeros(1, np.int32)
+    start_arr = np.asarray(starts, dtype=np.int32).reshape(n_seqs)
     sizes = [("token_ids", n_tokens), ("token_pos", n_tokens), ("token_seq", n_tokens),
              ("seq_slot", n_seqs), ("seq_start", n_seqs), ("seq_len", n_seqs),
              ("cu_seqlens", n_seqs + 1), ("logit_rows", n_rows)]
@@ -112,31 +130,14 @@ def pack_step(starts: list, tokens: list, wants: list) -> tuple:
         layout[name] = (off, cnt)
         off += cnt
     meta = np.zeros(max(off, 1), dtype=np.int32)
-
-    def view(name):
-        o, c = layout[name]
-        return meta[o:o + c]
-
-    ids, pos, seq = view("token_ids"), view("token_pos"), view("token_seq")
-    rows = view("logit_rows")
-    r = 0
-    for b in range(n_seqs):
-        lo, hi = int(cu[b]), int(cu[b + 1])
-        ids[lo:hi] = tokens[b]
-        pos[lo:hi] = np.arange(starts[b], starts[b] + counts[b], dtype=np.int32)
-        seq[lo:hi] = b
-        for w in wants[b]:
-            if not (0 <= w < counts[b]):
-                raise ValueError(f"sequence {b}: wanted place {w} is outside its {counts[b]} tokens")
-            rows[r] = lo + w
-            r += 1
-    view("seq_start")[:] = starts
-    view("seq_len")[:] = [s + c for s, c in zip(starts, counts)]
-    view("cu_seqlens")[:] = cu
+    sc = np.zeros(3, dtype=np.int32)
+    rc = _packer()(n_seqs, start_arr.ctypes.data, counts.ctypes.data, flat.ctypes.data, None, want_counts.ctypes.data,
+                   flat_wants.ctypes.data, meta.ctypes.data, meta.size, sc.ctypes.data)
+    if rc < 0:
+        from ..kernels import build
+        raise ValueError(build.load("host_runtime").ri_last_error().decode())
     scalars = {
         "n_tokens": n_tokens, "n_seqs": n_seqs, "n_logit_rows": n_rows,
-        "max_new": max(counts) if counts else 0,
-        "max_len": max((s + c for s, c in zip(starts, counts)), default=0),
-        "all_single": bool(counts) and all(c == 1 for c in counts),
+        "max_new": int(sc[0]), "max_len": int(sc[1]), "all_single": bool(sc[2]),
     }
     return meta, layout, scalars

@@ -145,7 +145,7 @@ class Engine:
     def _stage(self, slots, tokens, wants):
         """Reserve cache room for the step and put its int32 arrays on the device."""
         self._check_batch(slots, tokens, wants)
-        starts = [self.cache.length(s) for s in slots]
+        starts = self.cache.lengths(slots)
         self.cache.reserve([(s, st + len(t)) for s, st, t in zip(slots, starts, tokens)])
         meta, layout, sc = pack_step(starts, tokens, wants)
         o, c = layout["seq_slot"]
@@ -201,8 +201,7 @@ class Engine:
                 except Exception:
                     self.workspace.rezero()          # accumulators a failed step may have left dirty
                     raise
-        for s, t in zip(slots, tokens):
-            self.cache.commit(s, self.cache.length(s) + len(t))
+        self.cache.advance(slots, [len(t) for t in tokens])
         return logits
 
     def _graph_for(self, n: int):
@@ -238,8 +237,7 @@ class Engine:
             if tokens_dev.data_ptr() != graph.ctx.token_ids.data_ptr():       # else they are in place already
                 graph.ctx.token_ids.copy_(tokens_dev, non_blocking=True)
             logits = graph.launch()
-        for s in slots:
-            self.cache.commit(s, self.cache.length(s) + 1)
+        self.cache.advance(slots, [1] * len(slots))
         return logits
 
     def decode_steps(self, slots: list, first_tokens: list, n_steps: int, sampler_config=None) -> torch.Tensor:
@@ -256,7 +254,7 @@ class Engine:
             raise RuntimeError("decode_steps replays a captured step; this model has a part that is not graph_safe")
         n = len(slots)
         self._check_batch(slots, [[t] for t in first_tokens], [[0]] * n)
-        starts = [self.cache.length(s) for s in slots]
+        starts = self.cache.lengths(slots)
         self.cache.reserve([(s, st + n_steps) for s, st in zip(slots, starts)])
         with torch.cuda.device(self.device):
             graph = self._graph_for(n)
@@ -274,6 +272,5 @@ class Engine:
                 ops.sample(logits, graph.ctx.token_ids, temperature=cfg.temperature, top_k=cfg.top_k,
                            top_p=cfg.top_p, seed=cfg.seed, row_stream=streams, row_counter=counters[i])
                 out[i].copy_(graph.ctx.token_ids, non_blocking=True)
-        for s, st in zip(slots, starts):
-            self.cache.commit(s, st + n_steps)
+        self.cache.advance(slots, [n_steps] * len(slots))
         return out

@@ -1,9 +1,11 @@
-"""Compiling the CUDA sources for sm_100a and loading them.
+"""Compiling the native sources and loading them.
 
-Each file under `csrc/` becomes one shared library with a plain C ABI, compiled by nvcc
-the first time something needs it and kept beside the sources (`csrc/_build/`), so a
-model only compiles the kernels it runs.  There is no other implementation behind these
-libraries: if one cannot be built or loaded, the caller gets the error.
+Each file under `csrc/` becomes one shared library with a plain C ABI, compiled the first
+time something needs it and kept beside the sources (`csrc/_build/`), so a model only
+compiles the kernels it runs: the CUDA sources by nvcc for sm_100a, the host runtime
+(`host_runtime.cpp`: cache books, step packing) by the C++ compiler.  There is no other
+implementation behind these libraries: if one cannot be built or loaded, the caller gets
+the error.
 """
 from __future__ import annotations
 
@@ -28,12 +30,16 @@ MODULES = {
     "gemm_tcgen05": "gemm_tcgen05.cu",
     "attention_mma": "attention_mma.cu",
     "attention_tcgen05": "attention_tcgen05.cu",
+    "host_runtime": "host_runtime.cpp",
 }
 
 NVCC_FLAGS = [
     "-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
     "-shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
 ]
+
+
+CXX_FLAGS = ["-std=c++17", "-O2", "-shared", "-fPIC", "-fvisibility=hidden"]
 
 
 class KernelBuildError(RuntimeError):
@@ -49,6 +55,13 @@ def _nvcc() -> str:
         if cand and os.path.isfile(cand):
             return cand
     raise KernelBuildError("nvcc not found: the sm_100a kernels cannot be compiled (set NVCC or PATH)")
+
+
+def _cxx() -> str:
+    for cand in (os.environ.get("CXX"), shutil.which("g++"), shutil.which("c++"), shutil.which("clang++")):
+        if cand and os.path.isfile(cand):
+            return cand
+    raise KernelBuildError("no C++ compiler found: the host runtime cannot be compiled (set CXX or PATH)")
 
 
 def _build_dir() -> str:
@@ -68,8 +81,9 @@ def _build_dir() -> str:
 
 def _source_digest(src: str) -> str:
     h = hashlib.sha256()
-    h.update(" ".join(NVCC_FLAGS).encode())
-    for name in [src] + sorted(f for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))):
+    h.update(" ".join(NVCC_FLAGS if src.endswith(".cu") else CXX_FLAGS).encode())
+    headers = sorted(f for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))) if src.endswith(".cu") else []
+    for name in [src] + headers:
         with open(os.path.join(CSRC, name), "rb") as f:
             h.update(name.encode())
             h.update(f.read())
@@ -103,11 +117,13 @@ def build(module: str, *, force: bool = False, verbose: bool = True) -> str:
                 with open(stamp) as f:
                     if f.read().strip() == digest:
                         return out
-            nvcc = _nvcc()
             tmp = out + f".{os.getpid()}.tmp"
-            cmd = [nvcc] + NVCC_FLAGS + ["-I", CSRC, "-o", tmp, src_path]
+            if src.endswith(".cu"):
+                cmd = [_nvcc()] + NVCC_FLAGS + ["-I", CSRC, "-o", tmp, src_path]
+            else:
+                cmd = [_cxx()] + CXX_FLAGS + ["-o", tmp, src_path]
             if verbose:
-                _say(f"compiling {src} for sm_100a ...")
+                _say(f"compiling {src}" + (" for sm_100a ..." if src.endswith(".cu") else " ..."))
             t0 = time.time()
             proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
             last = t0
@@ -122,7 +138,7 @@ def build(module: str, *, force: bool = False, verbose: bool = True) -> str:
             if proc.returncode != 0:
                 if os.path.exists(tmp):
                     os.remove(tmp)
-                raise KernelBuildError(f"nvcc failed on {src}:\n{' '.join(cmd)}\n{output}")
+                raise KernelBuildError(f"the compiler failed on {src}:\n{' '.join(cmd)}\n{output}")
             os.replace(tmp, out)
             with open(stamp, "w") as f:
                 f.write(digest)

@@ -80,6 +80,20 @@ def test_reserve_many_is_all_or_nothing():
     p.audit()
 
 
+def test_a_step_moves_all_its_slots_or_none():
+    p = SlotPager(3, 8, 64, 512)
+    a, b = p.alloc_slot(), p.alloc_slot()
+    p.reserve_many([(a, 100), (b, 10)])
+    p.advance([a, b], [100, 10])
+    assert p.lengths([b, a]) == [10, 100]
+    with pytest.raises(CacheError, match="exceeds its reserved pages"):
+        p.advance([a, b], [1, 60])                   # b has one page: 70 positions do not fit
+    assert p.lengths([a, b]) == [100, 10]            # a did not move either
+    with pytest.raises(CacheError, match="not in use"):
+        p.lengths([a, 2])
+    p.audit()
+
+
 def test_random_traffic_keeps_the_books():
     rng = random.Random(0)
     p = SlotPager(n_slots=5, n_pages=40, page_size=64, max_seq_len=1000)

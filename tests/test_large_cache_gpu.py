@@ -19,7 +19,7 @@ def test_pages_beyond_two_to_the_31_elements(dtype, tmp_path):
     eng = Engine.from_pretrained(m.folder, dtype=dtype, max_tokens=n_pages * 64, max_seq_len=1024, n_slots=4)
     pager = eng.cache.pager
     assert pager.n_pages == n_pages
-    pager._free_pages.reverse()                      # hand out the highest page numbers first
+    pager.prefer_high_pages()                        # hand out the highest page numbers first
     reqs = [random_tokens(n, m.cfg["vocab_size"], seed=n) for n in (300, 90)]
     want = [m.plain_logits(r) for r in reqs]
     tol = TOL[dtype]
