@@ -74,7 +74,10 @@ class SlotPager:
     def __del__(self):
         h, self._h = getattr(self, "_h", None), None
         if h:
-            self._rt.ri_pager_destroy(h)
+            try:
+                self._rt.ri_pager_destroy(h)
+            except Exception:          # the interpreter is shutting down and the library is gone
+                pass
 
     def _raise(self, code: int):
         msg = self._rt.ri_last_error().decode()
