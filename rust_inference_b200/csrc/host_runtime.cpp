@@ -314,3 +314,349 @@ RI_API int ri_pager_advance(void* h, int n, const int* slots, const int* counts)
     for (int i = 0; i < n; ++i) p->length[slots[i]] += counts[i];
     return 0;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Safetensors files: an 8-byte little-endian header length, a JSON header
+// {name: {"dtype", "shape", "data_offsets": [begin, end]}, "__metadata__": {..}} and the raw
+// little-endian data, which is mapped, not read.  The role is the one gguf.rs plays in the
+// reference (name -> type, shape, bytes; errors on a bad header: gguf.rs:255-341); the format
+// itself is the model folder's.
+// ---------------------------------------------------------------------------------------------
+#include <cctype>
+#include <cerrno>
+#include <cstring>
+#include <fcntl.h>
+#include <string>
+#include <sys/mman.h>
+#include <sys/stat.h>
+#include <unistd.h>
+#include <utility>
+
+namespace {
+
+struct StEntry {
+    std::string name, dtype;
+    std::vector<long long> shape;
+    long long begin = 0, end = 0;
+};
+
+struct StFile {
+    int fd = -1;
+    void* map = nullptr;
+    size_t size = 0, data_start = 0;
+    std::vector<StEntry> entries;
+    std::vector<std::pair<std::string, std::string>> metadata;
+};
+
+// The little of JSON that a header uses: objects, arrays, strings, integers, and any other value skipped.
+struct Json {
+    const char* s;
+    size_t n, i = 0;
+    std::string err;
+
+    bool bad(const char* what) {
+        if (err.empty()) err = std::string(what) + " at byte " + std::to_string(i);
+        return false;
+    }
+    void ws() {
+        while (i < n && (s[i] == ' ' || s[i] == '\t' || s[i] == '\n' || s[i] == '\r')) ++i;
+    }
+    bool eat(char c) {
+        ws();
+        if (i < n && s[i] == c) { ++i; return true; }
+        return false;
+    }
+    bool peek(char c) {
+        ws();
+        return i < n && s[i] == c;
+    }
+    static void utf8(std::string& out, unsigned cp) {
+        if (cp < 0x80) out += (char)cp;
+        else if (cp < 0x800) { out += (char)(0xC0 | (cp >> 6)); out += (char)(0x80 | (cp & 0x3F)); }
+        else if (cp < 0x10000) { out += (char)(0xE0 | (cp >> 12)); out += (char)(0x80 | ((cp >> 6) & 0x3F)); out += (char)(0x80 | (cp & 0x3F)); }
+        else { out += (char)(0xF0 | (cp >> 18)); out += (char)(0x80 | ((cp >> 12) & 0x3F)); out += (char)(0x80 | ((cp >> 6) & 0x3F)); out += (char)(0x80 | (cp & 0x3F)); }
+    }
+    bool hex4(unsigned& v) {
+        if (i + 4 > n) return bad("short \\u escape");
+        v = 0;
+        for (int k = 0; k < 4; ++k) {
+            const char c = s[i++];
+            v <<= 4;
+            if (c >= '0' && c <= '9') v |= (unsigned)(c - '0');
+            else if (c >= 'a' && c <= 'f') v |= (unsigned)(c - 'a' + 10);
+            else if (c >= 'A' && c <= 'F') v |= (unsigned)(c - 'A' + 10);
+            else return bad("bad \\u escape");
+        }
+        return true;
+    }
+    bool string(std::string& out) {
+        out.clear();
+        if (!eat('"')) return bad("expected a string");
+        while (i < n) {
+            const unsigned char c = (unsigned char)s[i++];
+            if (c == '"') return true;
+            if (c < 0x20) return bad("control character in a string");
+            if (c != '\\') { out += (char)c; continue; }
+            if (i >= n) break;
+            const char e = s[i++];
+            switch (e) {
+                case '"': out += '"'; break;
+                case '\\': out += '\\'; break;
+                case '/': out += '/'; break;
+                case 'b': out += '\b'; break;
+                case 'f': out += '\f'; break;
+                case 'n': out += '\n'; break;
+                case 'r': out += '\r'; break;
+                case 't': out += '\t'; break;
+                case 'u': {
+                    unsigned cp = 0;
+                    if (!hex4(cp)) return false;
+                    if (cp >= 0xD800 && cp < 0xDC00 && i + 6 <= n && s[i] == '\\' && s[i + 1] == 'u') {
+                        i += 2;
+                        unsigned lo;
+                        if (!hex4(lo)) return false;
+                        cp = 0x10000 + ((cp - 0xD800) << 10) + (lo - 0xDC00);
+                    }
+                    utf8(out, cp);
+                    break;
+                }
+                default: return bad("bad escape in a string");
+            }
+        }
+        return bad("unterminated string");
+    }
+    bool integer(long long& v) {
+        ws();
+        size_t j = i;
+        if (j < n && s[j] == '-') ++j;
+        if (j >= n || s[j] < '0' || s[j] > '9') return bad("expected an integer");
+        long long x = 0;
+        const bool neg = s[i] == '-';
+        for (; j < n && s[j] >= '0' && s[j] <= '9'; ++j) {
+            if (x > (0x7fffffffffffffffLL - 9) / 10) return bad("integer too large");
+            x = x * 10 + (s[j] - '0');
+        }
+        if (j < n && (s[j] == '.' || s[j] == 'e' || s[j] == 'E')) return bad("expected an integer");
+        i = j;
+        v = neg ? -x : x;
+        return true;
+    }
+    bool int_array(std::vector<long long>& out) {
+        out.clear();
+        if (!eat('[')) return bad("expected an array");
+        if (eat(']')) return true;
+        do {
+            long long v;
+            if (!integer(v)) return false;
+            out.push_back(v);
+        } while (eat(','));
+        return eat(']') || bad("expected ] or ,");
+    }
+    // any value, unread
+    bool skip(int depth = 0) {
+        if (depth > 64) return bad("nested too deeply");
+        ws();
+        if (i >= n) return bad("unexpected end");
+        const char c = s[i];
+        if (c == '"') { std::string t; return string(t); }
+        if (c == '{') {
+            ++i;
+            if (eat('}')) return true;
+            do {
+                std::string k;
+                if (!string(k) || !(eat(':') || bad("expected :")) || !skip(depth + 1)) return false;
+            } while (eat(','));
+            return eat('}') || bad("expected } or ,");
+        }
+        if (c == '[') {
+            ++i;
+            if (eat(']')) return true;
+            do {
+                if (!skip(depth + 1)) return false;
+            } while (eat(','));
+            return eat(']') || bad("expected ] or ,");
+        }
+        size_t j = i;
+        while (j < n && (isalnum((unsigned char)s[j]) || s[j] == '-' || s[j] == '+' || s[j] == '.')) ++j;
+        if (j == i) return bad("unexpected character");
+        const std::string tok(s + i, j - i);
+        const bool word = tok == "true" || tok == "false" || tok == "null";
+        const bool number = !word && (tok[0] == '-' || (tok[0] >= '0' && tok[0] <= '9'));
+        if (!word && !number) return bad("unexpected token");
+        i = j;
+        return true;
+    }
+};
+
+long long dtype_bytes(const std::string& d) {
+    if (d == "F32" || d == "I32") return 4;
+    if (d == "BF16" || d == "F16") return 2;
+    if (d == "I64") return 8;
+    return 0;                                  // not one this library reads
+}
+
+std::string shape_text(const std::vector<long long>& shape) {
+    std::string t = "[";
+    for (size_t k = 0; k < shape.size(); ++k) t += (k ? ", " : "") + std::to_string(shape[k]);
+    return t + "]";
+}
+
+void st_release(StFile* f) {
+    if (f->map) munmap(f->map, f->size);
+    if (f->fd >= 0) close(f->fd);
+    delete f;
+}
+
+}  // namespace
+
+// Opens and maps a file and reads its header; null with the reason in ri_last_error.
+RI_API void* ri_st_open(const char* path) {
+    StFile* f = new StFile;
+    auto give_up = [&](const std::string& why) -> void* {
+        fail(0, "%s: %s", path, why.c_str());
+        st_release(f);
+        return nullptr;
+    };
+    f->fd = open(path, O_RDONLY | O_CLOEXEC);
+    if (f->fd < 0) return give_up(strerror(errno));
+    struct stat st;
+    if (fstat(f->fd, &st) != 0) return give_up(strerror(errno));
+    f->size = (size_t)st.st_size;
+    if (f->size < 8) return give_up("too short to hold a safetensors header");
+    void* m = mmap(nullptr, f->size, PROT_READ, MAP_PRIVATE, f->fd, 0);
+    if (m == MAP_FAILED) return give_up(std::string("cannot map the file: ") + strerror(errno));
+    f->map = m;
+    const unsigned char* bytes = static_cast<const unsigned char*>(m);
+    unsigned long long hlen = 0;
+    for (int k = 7; k >= 0; --k) hlen = (hlen << 8) | bytes[k];
+    if (hlen == 0 || hlen > f->size - 8)
+        return give_up("header length " + std::to_string(hlen) + " does not fit a file of " + std::to_string(f->size) + " bytes");
+    f->data_start = 8 + (size_t)hlen;
+    const long long data_len = (long long)(f->size - f->data_start);
+
+    Json js{reinterpret_cast<const char*>(bytes + 8), (size_t)hlen, 0, std::string()};
+    auto bad_json = [&]() { return give_up("header is not valid JSON: " + js.err); };
+    js.ws();
+    if (js.i < js.n && js.s[js.i] != '{') {
+        if (!js.skip()) return bad_json();
+        return give_up("header must be a JSON object");
+    }
+    if (!js.eat('{')) { js.bad("expected {"); return bad_json(); }
+    if (!js.eat('}')) {
+        do {
+            std::string name;
+            if (!js.string(name) || !(js.eat(':') || js.bad("expected :"))) return bad_json();
+            if (name == "__metadata__") {
+                if (js.peek('{')) {
+                    js.eat('{');
+                    if (!js.eat('}')) {
+                        do {
+                            std::string k, v;
+                            if (!js.string(k) || !(js.eat(':') || js.bad("expected :"))) return bad_json();
+                            if (js.peek('"')) {
+                                if (!js.string(v)) return bad_json();
+                                f->metadata.emplace_back(k, v);
+                            } else if (!js.skip()) {
+                                return bad_json();
+                            }
+                        } while (js.eat(','));
+                        if (!js.eat('}')) { js.bad("expected } or ,"); return bad_json(); }
+                    }
+                } else if (!js.skip()) {
+                    return bad_json();
+                }
+                continue;
+            }
+            StEntry e;
+            e.name = name;
+            bool has_dtype = false, has_shape = false, has_offsets = false, malformed = false;
+            if (!js.peek('{')) {
+                if (!js.skip()) return bad_json();
+                malformed = true;
+            } else {
+                js.eat('{');
+                if (!js.eat('}')) {
+                    do {
+                        std::string k;
+                        if (!js.string(k) || !(js.eat(':') || js.bad("expected :"))) return bad_json();
+                        const size_t at = js.i;
+                        if (k == "dtype" && js.peek('"')) {
+                            if (!js.string(e.dtype)) return bad_json();
+                            has_dtype = true;
+                        } else if (k == "shape" && js.peek('[')) {
+                            if (js.int_array(e.shape)) has_shape = true;
+                            else { js.i = at; js.err.clear(); if (!js.skip()) return bad_json(); malformed = true; }
+                        } else if (k == "data_offsets" && js.peek('[')) {
+                            std::vector<long long> o;
+                            if (js.int_array(o) && o.size() == 2) { e.begin = o[0]; e.end = o[1]; has_offsets = true; }
+                            else { js.i = at; js.err.clear(); if (!js.skip()) return bad_json(); malformed = true; }
+                        } else {
+                            if (k == "dtype" || k == "shape" || k == "data_offsets") malformed = true;
+                            if (!js.skip()) return bad_json();
+                        }
+                    } while (js.eat(','));
+                    if (!js.eat('}')) { js.bad("expected } or ,"); return bad_json(); }
+                }
+            }
+            if (malformed || !has_dtype || !has_shape || !has_offsets) return give_up("malformed header entry for '" + name + "'");
+            const long long unit = dtype_bytes(e.dtype);
+            if (unit > 0) {
+                long long want = unit;
+                for (long long d : e.shape) {
+                    if (d < 0 || (d > 0 && want > 0x7fffffffffffffffLL / d)) return give_up("malformed header entry for '" + name + "'");
+                    want *= d;
+                }
+                if (e.end - e.begin != want)
+                    return give_up("'" + name + "' has " + std::to_string(e.end - e.begin) + " bytes, shape " + shape_text(e.shape) +
+                                   " of " + e.dtype + " needs " + std::to_string(want));
+            }
+            if (e.begin < 0 || e.end < e.begin || e.end > data_len)
+                return give_up("'" + name + "' data_offsets [" + std::to_string(e.begin) + ", " + std::to_string(e.end) +
+                               ") lie outside the " + std::to_string(data_len) + " data bytes");
+            f->entries.push_back(std::move(e));
+        } while (js.eat(','));
+        if (!js.eat('}')) { js.bad("expected } or ,"); return bad_json(); }
+    }
+    js.ws();
+    if (js.i != js.n) { js.bad("text after the header object"); return bad_json(); }
+    return f;
+}
+
+RI_API void ri_st_close(void* h) {
+    if (h) st_release(static_cast<StFile*>(h));
+}
+
+RI_API int ri_st_count(void* h) { return (int)static_cast<StFile*>(h)->entries.size(); }
+
+// Entry i: its name and dtype (UTF-8, valid until the file is closed), its shape, and where its bytes lie
+// among the data.
+RI_API int ri_st_entry(void* h, int i, const char** name, const char** dtype, int* ndim, const long long** shape,
+                       long long* begin, long long* end) {
+    StFile* f = static_cast<StFile*>(h);
+    if (i < 0 || i >= (int)f->entries.size()) return fail(-1, "no entry %d", i);
+    const StEntry& e = f->entries[i];
+    *name = e.name.c_str();
+    *dtype = e.dtype.c_str();
+    *ndim = (int)e.shape.size();
+    *shape = e.shape.data();
+    *begin = e.begin;
+    *end = e.end;
+    return 0;
+}
+
+// The mapped data (what data_offsets count from) and its length.
+RI_API const void* ri_st_data(void* h, long long* length) {
+    StFile* f = static_cast<StFile*>(h);
+    if (length) *length = (long long)(f->size - f->data_start);
+    return static_cast<const unsigned char*>(f->map) + f->data_start;
+}
+
+RI_API int ri_st_metadata_count(void* h) { return (int)static_cast<StFile*>(h)->metadata.size(); }
+
+RI_API int ri_st_metadata(void* h, int i, const char** key, const char** value) {
+    StFile* f = static_cast<StFile*>(h);
+    if (i < 0 || i >= (int)f->metadata.size()) return fail(-1, "no metadata entry %d", i);
+    *key = f->metadata[i].first.c_str();
+    *value = f->metadata[i].second.c_str();
+    return 0;
+}

@@ -11,9 +11,9 @@ float32, F16 is widened to float32 (exact), integer tensors become int32.
 from __future__ import annotations
 
 import json
-import mmap
 import os
 import struct
+from ctypes import POINTER, byref, c_char_p, c_int, c_longlong, c_ubyte, c_void_p
 
 import numpy as np
 import torch
@@ -34,46 +34,59 @@ _NAMES = {torch.float32: "F32", torch.bfloat16: "BF16", torch.float16: "F16",
           torch.int32: "I32", torch.int64: "I64"}
 
 
+_lib = None
+
+
+def _runtime():
+    global _lib
+    if _lib is None:
+        from ..kernels import build
+        lib = build.load("host_runtime")
+        lib.ri_st_open.restype = c_void_p
+        lib.ri_st_open.argtypes = [c_char_p]
+        lib.ri_st_close.restype = None
+        lib.ri_st_close.argtypes = [c_void_p]
+        lib.ri_st_count.argtypes = [c_void_p]
+        lib.ri_st_entry.argtypes = [c_void_p, c_int, POINTER(c_char_p), POINTER(c_char_p), POINTER(c_int),
+                                    POINTER(POINTER(c_longlong)), POINTER(c_longlong), POINTER(c_longlong)]
+        lib.ri_st_data.restype = c_void_p
+        lib.ri_st_data.argtypes = [c_void_p, POINTER(c_longlong)]
+        lib.ri_st_metadata_count.argtypes = [c_void_p]
+        lib.ri_st_metadata.argtypes = [c_void_p, c_int, POINTER(c_char_p), POINTER(c_char_p)]
+        _lib = lib
+    return _lib
+
+
 class SafetensorsFile:
-    """A memory-mapped safetensors file; `tensor(name)` copies nothing until asked."""
+    """A memory-mapped safetensors file; `tensor(name)` copies nothing until asked.  The native host
+    runtime (`csrc/host_runtime.cpp`) opens and maps the file and reads and checks its header."""
 
     def __init__(self, path: str):
         self.path = path
+        self._rt = _runtime()
+        self._h = c_void_p(self._rt.ri_st_open(os.fsencode(path)))
+        if not self._h:
+            raise WeightFileError(self._rt.ri_last_error().decode("utf-8", "replace"))
         try:
-            size = os.path.getsize(path)
-        except OSError as e:
-            raise WeightFileError(f"{path}: {e.strerror}") from None
-        if size < 8:
-            raise WeightFileError(f"{path}: too short to hold a safetensors header")
-        self._file = open(path, "rb")
-        (hlen,) = struct.unpack("<Q", self._file.read(8))
-        if hlen <= 0 or 8 + hlen > size:
-            raise WeightFileError(f"{path}: header length {hlen} does not fit a file of {size} bytes")
-        try:
-            header = json.loads(self._file.read(hlen).decode("utf-8"))
-        except (UnicodeDecodeError, json.JSONDecodeError) as e:
-            raise WeightFileError(f"{path}: header is not valid JSON: {e}") from None
-        if not isinstance(header, dict):
-            raise WeightFileError(f"{path}: header must be a JSON object")
-        self.metadata = header.pop("__metadata__", {}) or {}
-        self._data_start = 8 + hlen
-        data_len = size - self._data_start
-        self.entries: dict[str, dict] = {}
-        for name, e in header.items():
-            try:
-                dtype, shape, (begin, end) = e["dtype"], tuple(int(s) for s in e["shape"]), e["data_offsets"]
-            except (KeyError, TypeError, ValueError):
-                raise WeightFileError(f"{path}: malformed header entry for {name!r}") from None
-            if dtype in _DTYPES:
-                want = _DTYPES[dtype][1] * int(np.prod(shape, dtype=np.int64)) if shape else _DTYPES[dtype][1]
-                if end - begin != want:
-                    raise WeightFileError(
-                        f"{path}: {name!r} has {end - begin} bytes, shape {list(shape)} of {dtype} needs {want}")
-            if begin < 0 or end < begin or end > data_len:
-                raise WeightFileError(
-                    f"{path}: {name!r} data_offsets [{begin}, {end}) lie outside the {data_len} data bytes")
-            self.entries[name] = {"dtype": dtype, "shape": shape, "begin": begin, "end": end}
-        self._mmap = mmap.mmap(self._file.fileno(), 0, access=mmap.ACCESS_READ) if size else None
+            self.metadata = {}
+            key, value = c_char_p(), c_char_p()
+            for i in range(self._rt.ri_st_metadata_count(self._h)):
+                self._rt.ri_st_metadata(self._h, i, byref(key), byref(value))
+                self.metadata[key.value.decode("utf-8")] = value.value.decode("utf-8")
+            self.entries: dict[str, dict] = {}
+            name, dtype, ndim = c_char_p(), c_char_p(), c_int()
+            shape, begin, end = POINTER(c_longlong)(), c_longlong(), c_longlong()
+            for i in range(self._rt.ri_st_count(self._h)):
+                self._rt.ri_st_entry(self._h, i, byref(name), byref(dtype), byref(ndim), byref(shape), byref(begin),
+                                     byref(end))
+                self.entries[name.value.decode("utf-8")] = {
+                    "dtype": dtype.value.decode("utf-8"), "shape": tuple(int(shape[k]) for k in range(ndim.value)),
+                    "begin": begin.value, "end": end.value}
+        except UnicodeDecodeError:
+            self.close()
+            raise WeightFileError(f"{path}: header is not valid JSON: a name is not UTF-8") from None
+        length = c_longlong()
+        self._data = self._rt.ri_st_data(self._h, byref(length))
 
     def names(self):
         return list(self.entries)
@@ -88,13 +101,18 @@ class SafetensorsFile:
         return self.entries[name]["dtype"] in _DTYPES
 
     def tensor(self, name: str) -> torch.Tensor:
+        if not self._h:
+            raise WeightFileError(f"{self.path}: the file has been closed")
         e = self.entries[name]
         if e["dtype"] not in _DTYPES:
             raise WeightFileError(f"{self.path}: {name!r} has unsupported dtype {e['dtype']}")
         dtype, _ = _DTYPES[e["dtype"]]
         n_bytes = e["end"] - e["begin"]
-        raw = np.frombuffer(self._mmap, dtype=np.uint8, count=n_bytes, offset=self._data_start + e["begin"])
-        t = torch.from_numpy(raw.copy())       # one tensor at a time leaves the map
+        if n_bytes:
+            mapped = np.ctypeslib.as_array((c_ubyte * n_bytes).from_address(self._data + e["begin"]))
+            t = torch.from_numpy(mapped.copy())    # one tensor at a time leaves the map
+        else:
+            t = torch.empty(0, dtype=torch.uint8)
         t = t.view(dtype).reshape(e["shape"])
         if dtype == torch.float16:
             t = t.to(torch.float32)
@@ -103,10 +121,15 @@ class SafetensorsFile:
         return t
 
     def close(self):
-        if self._mmap is not None:
-            self._mmap.close()
-            self._mmap = None
-        self._file.close()
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            self._rt.ri_st_close(h)
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:              # the interpreter is shutting down and the library is gone
+            pass
 
 
 def write_safetensors(path: str, tensors: dict, metadata: dict | None = None) -> None:

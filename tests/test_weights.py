@@ -67,6 +67,37 @@ def test_bad_files(tmp_path):
         ModelFiles(str(tmp_path / "nowhere"))
 
 
+def test_headers_the_way_other_writers_make_them(tmp_path):
+    """Escapes and non-ASCII names, keys in any order, keys this library does not know, a dtype it does
+    not read, metadata that is null or holds other things than strings, a scalar: the header reader takes
+    what the format allows and only refuses what it must."""
+    p = tmp_path / "odd.safetensors"
+    name_json = r'bl\u00f6ck.\"q\"\\0\/\ud83d\ude00'         # as it stands in the header: JSON escapes, a surrogate pair
+    hdr = (r'{ "__metadata__": {"k": "v\n", "n": 3, "z": null},' + "\n" + ' "' + name_json + r'": {"data_offsets": [0, 8], '
+           r'"extra": [1, {"a": true}], "shape": [2], "dtype": "F32"}, "s": {"dtype": "I64", "shape": [], "data_offsets": [8, 16]}, '
+           r'"q": {"dtype": "F8_E4M3", "shape": [3], "data_offsets": [16, 19]} }').encode()
+    data = struct.pack("<2f", 1.5, -2.0) + struct.pack("<q", 7) + b"abc"
+    p.write_bytes(struct.pack("<Q", len(hdr)) + hdr + data)
+    f = SafetensorsFile(str(p))
+    want = json.loads(hdr)                                     # the interpreter's own JSON reader agrees on the names
+    want.pop("__metadata__")
+    assert set(f.names()) == set(want) and f.metadata == {"k": "v\n"}
+    odd = [n for n in f.names() if n.startswith("bl")][0]
+    assert odd == 'bl\u00f6ck."q"\\0/\U0001f600'
+    assert f.tensor(odd).tolist() == [1.5, -2.0] and f.shape(odd) == (2,)
+    assert f.tensor("s").dtype == torch.int32 and f.tensor("s").item() == 7 and f.shape("s") == ()
+    assert not f.supported("q") and f.dtype_name("q") == "F8_E4M3"
+    with pytest.raises(WeightFileError, match="unsupported dtype"):
+        f.tensor("q")
+    f.close()
+    for bad in (b'[1, 2]', b'{"w": 5}', b'{"w": {"dtype": "F32", "shape": [1.5], "data_offsets": [0, 4]}}',
+                b'{"w": {"dtype": "F32", "shape": [1]}}', b'{"w": {"dtype": "F32", "shape": [1], "data_offsets": [0, 4]}} x',
+                b'{"w": {"dtype": "F32", "shape": [1], "data_offsets": [0, 4, 8]}}'):
+        p.write_bytes(struct.pack("<Q", len(bad)) + bad + b"\0" * 8)
+        with pytest.raises(WeightFileError, match="JSON object|malformed|not valid JSON"):
+            SafetensorsFile(str(p))
+
+
 def test_declared_tensors_follow_the_config():
     cfg, spec = _spec("B")
     d = declared_tensors(spec)
