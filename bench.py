@@ -149,7 +149,7 @@ def main() -> int:
     ap.add_argument("--seq-len", type=int, default=CONTEXT, help="positions a sequence may reach (cache and rotary table)")
     ap.add_argument("--skip-points", action="store_true", help="skip the batch-1 and batch-64 points")
     ap.add_argument("--kernel", default=None, help="time ONE kernel at the benchmark model's sizes instead "
-                    "(qkv, qkv_split, o_proj, gate_up, down, lm_head, attn_decode, attn_prefill, attn_prefill_mma, rmsnorm, rope)")
+                    "(qkv, qkv_split, o_proj, gate_up, down, lm_head, sample, attn_decode, attn_prefill, attn_prefill_mma, rmsnorm, rope)")
     ap.add_argument("--tokens", type=int, default=8, help="with --kernel: tokens in the step")
     ap.add_argument("--context", type=int, default=1024, help="with --kernel: cached positions per sequence")
     ap.add_argument("--once", action="store_true", help="with --kernel: launch the workload once, untimed (for ncu)")

@@ -15,7 +15,7 @@ import math
 
 import torch
 
-KERNELS = ("qkv", "qkv_split", "o_proj", "gate_up", "down", "lm_head", "attn_decode", "attn_prefill",
+KERNELS = ("qkv", "qkv_split", "o_proj", "gate_up", "down", "lm_head", "sample", "attn_decode", "attn_prefill",
            "attn_prefill_mma", "rmsnorm", "rope")
 
 
@@ -73,6 +73,25 @@ def run(kernel: str, model: dict, tokens: int, context: int = 1024, eager_only: 
         launches = c
         flops = 2.0 * tokens * n * k * (2 if dual else 1)
         out.update(n=n, k=k, bytes=nbytes + tokens * k * 2, flops=flops)
+    elif kernel == "sample":
+        # the reference's default sampling (temperature 0.8, top-k 40, top-p 0.95, penalty 1.1 over 64 ids) on
+        # `tokens` rows of logits; the logits are overwritten, so every launch gets rows of its own
+        c = max(4, int(200e6 // (tokens * vocab * 4)) + 1)
+        rows = [torch.randn(tokens, vocab, device=dev) * 3 for _ in range(c)]
+        fresh = [r.clone() for r in rows]
+        toks = torch.empty(tokens, dtype=torch.int32, device=dev)
+        stream = torch.arange(tokens, dtype=torch.int32, device=dev)
+        counter = torch.zeros(tokens, dtype=torch.int32, device=dev)
+        recent = torch.randint(0, vocab, (tokens, 64), dtype=torch.int32, device=dev)
+        count = torch.full((tokens,), 64, dtype=torch.int32, device=dev)
+
+        def fn():
+            for i in range(c):
+                rows[i].copy_(fresh[i])
+                ops.sample(rows[i], toks, temperature=0.8, top_k=40, top_p=0.95, penalty=1.1, recent=recent,
+                           recent_count=count, seed=12345, row_stream=stream, row_counter=counter)
+        launches = c
+        out.update(bytes=tokens * vocab * 4, flops=0.0, note="each launch follows a copy that restores its logits")
     elif kernel == "rmsnorm":
         x = torch.randn(tokens, h, device=dev)
         w = torch.ones(h, device=dev)
