@@ -1,7 +1,7 @@
 """The Python entry point: load a model folder, generate from token ids."""
 from __future__ import annotations
 
-from .engine.engine import Engine
+from .engine.engine import Engine, resolve_max_seq_len
 from .engine.generate import GenerationResult, Generator
 from .sampling.params import SamplerConfig
 from .sampling.sampler import Sampler
@@ -24,18 +24,19 @@ class Model:
         max_tokens_in_cache: positions all live sequences may hold together (default: 8 sequences
         of max_seq_len, at most 65,536 positions)."""
         from .config.registry import load_spec
-        limit = load_spec(path)[1].max_positions
-        seq = min(max_seq_len or limit, limit)
+        seq = resolve_max_seq_len(max_seq_len, load_spec(path)[1].max_positions)
         if max_tokens_in_cache is None:
             max_tokens_in_cache = min(8 * seq, max(seq, 65536))
         return cls(Engine.from_pretrained(path, dtype=dtype, device=device, max_tokens=max_tokens_in_cache,
                                           max_seq_len=seq, n_slots=n_slots))
 
     @classmethod
-    def random(cls, config, *, seed: int = 0, std: float = 0.02, dtype: str = "bfloat16", device: str = "cuda",
-               max_seq_len: int | None = None, max_tokens_in_cache: int = 65536, n_slots: int | None = None) -> "Model":
-        """A model with random weights made on the device from a typed config and a seed."""
-        return cls(Engine.from_random(config, seed=seed, std=std, dtype=dtype, device=device,
+    def random(cls, config, *, seed: int = 0, std: float = 0.02, norm_std: float = 0.0, dtype: str = "bfloat16",
+               device: str = "cuda", max_seq_len: int | None = None, max_tokens_in_cache: int = 65536,
+               n_slots: int | None = None) -> "Model":
+        """A model with random weights made on the device from a typed config and a seed: matrices and
+        biases N(0, std), norm weights 1 + N(0, norm_std)."""
+        return cls(Engine.from_random(config, seed=seed, std=std, norm_std=norm_std, dtype=dtype, device=device,
                                       max_tokens=max_tokens_in_cache, max_seq_len=max_seq_len, n_slots=n_slots))
 
     def logits(self, tokens, want="all"):

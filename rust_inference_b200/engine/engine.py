@@ -9,6 +9,8 @@ passed by the caller (model.rs:361-363); here the position comes from the slot's
 """
 from __future__ import annotations
 
+from collections import OrderedDict
+
 import numpy as np
 import torch
 
@@ -37,6 +39,19 @@ def require_cuda(device) -> torch.device:
     if not torch.cuda.is_available():
         raise RuntimeError("no CUDA device is available; this library has no CPU path")
     return device
+
+
+def resolve_max_seq_len(asked: int | None, limit: int) -> int:
+    """The context length a run uses: the model's own (`max_position_embeddings`) unless a shorter
+    one is asked for, as `--max-seq-len` overrides it in the reference (model.rs:142-144).  A
+    longer one is an error: the model has no positions there."""
+    if asked is None:
+        return limit
+    if asked <= 0:
+        raise ValueError(f"max_seq_len must be positive, found {asked}")
+    if asked > limit:
+        raise ValueError(f"max_seq_len {asked} exceeds the model's max_position_embeddings {limit}")
+    return int(asked)
 
 
 class _PinnedRing:
@@ -70,11 +85,11 @@ class Engine:
                  n_slots: int | None = None, use_graphs: bool = True):
         self.model = model
         self.use_graphs = use_graphs and model.graph_safe()
-        self._graphs: dict = {}
+        self._graphs: OrderedDict = OrderedDict()       # batch size -> DecodeGraph, least recently used first
+        self._decode_logits = None                      # shared by batch sizes that have no graph yet
         self.device = require_cuda(model.device)
         self.dtype = model.dtype
-        limit = model.spec.max_positions
-        max_seq_len = min(max_seq_len or limit, limit)
+        max_seq_len = resolve_max_seq_len(max_seq_len, model.spec.max_positions)
         self.cache = SequenceCache(model.cache_requests(), max_tokens=max_tokens, max_seq_len=max_seq_len,
                                    dtype=model.dtype, device=self.device, n_slots=n_slots)
         self.max_seq_len = self.cache.max_seq_len
@@ -93,21 +108,22 @@ class Engine:
         device = require_cuda(device)
         config, spec = load_spec(model_dir)
         model = DecoderModel(spec, dtype=resolve_dtype(dtype), device=device)
-        model.load(read_model_tensors(model_dir, model.declared_tensors()))
+        model.load(read_model_tensors(model_dir, model.declared_tensors(), spec.ignored_tensors))
         eng = cls(model, max_tokens=max_tokens, max_seq_len=max_seq_len, n_slots=n_slots, use_graphs=use_graphs)
         eng.config = config
         return eng
 
     @classmethod
-    def from_random(cls, config, *, seed: int = 0, std: float = 0.02, dtype="bfloat16", device="cuda",
-                    max_tokens: int = 8192, max_seq_len: int | None = None,
+    def from_random(cls, config, *, seed: int = 0, std: float = 0.02, norm_std: float = 0.0, dtype="bfloat16",
+                    device="cuda", max_tokens: int = 8192, max_seq_len: int | None = None,
                     n_slots: int | None = None, use_graphs: bool = True) -> "Engine":
         """Random weights made on the device, without a folder (benchmarks)."""
         device = require_cuda(device)
         dtype = resolve_dtype(dtype)
         spec = get_architecture(config.architecture).build_spec(config)
         model = DecoderModel(spec, dtype=dtype, device=device)
-        model.load(random_tensors(model.declared_tensors(), seed, std=std, matrix_dtype=dtype, device=device))
+        model.load(random_tensors(model.declared_tensors(), seed, std=std, matrix_dtype=dtype, device=device,
+                                  norm_std=norm_std))
         eng = cls(model, max_tokens=max_tokens, max_seq_len=max_seq_len, n_slots=n_slots, use_graphs=use_graphs)
         eng.config = config
         return eng
@@ -191,7 +207,7 @@ class Engine:
             if decode and self.use_graphs:
                 # one token per sequence, logits for each: the captured step of this batch size
                 dev, _, _ = self._stage(slots, tokens, wants)
-                logits = self._graph_for(len(slots)).run(dev)
+                logits = self._graph_for(len(slots)).run(dev)      # cleans up after itself if it raises
                 if not borrow:
                     logits = logits.clone()
             else:
@@ -205,12 +221,25 @@ class Engine:
         return logits
 
     def _graph_for(self, n: int):
-        """The captured decode step of n sequences (made on first use; call with the device current)."""
+        """The captured decode step of n sequences (made on first use; call with the device current).
+        Only the most recently used batch sizes are kept."""
         graph = self._graphs.get(n)
         if graph is None:
-            from .graphs import DecodeGraph
+            from .graphs import MAX_SIZES, DecodeGraph
+            while len(self._graphs) >= MAX_SIZES:
+                self._graphs.popitem(last=False)
             graph = self._graphs[n] = DecodeGraph(self, n)
+        else:
+            self._graphs.move_to_end(n)
         return graph
+
+    def shared_decode_logits(self, n: int) -> torch.Tensor:
+        """float32 [n, vocab] for decode steps of batch sizes that have no buffer of their own yet; the
+        next step overwrites it."""
+        vocab = self.model.spec.vocab_size
+        if self._decode_logits is None or self._decode_logits.numel() < n * vocab:
+            self._decode_logits = torch.empty(n * vocab, dtype=torch.float32, device=self.device)
+        return self._decode_logits[:n * vocab].view(n, vocab)
 
     def can_feed_from_device(self) -> bool:
         """True if decode steps replay a captured graph, so a step can take its tokens from a

@@ -40,14 +40,38 @@ class _Live:
     history: list = field(default_factory=list)
 
 
+class CudaLoopDevice:
+    """The three things the look-ahead loop needs besides the engine and the sampler: host memory the
+    device can write into, a mark on the stream that the host can wait for, and picking rows out of a
+    token array.  A scripted stand-in (numpy arrays, marks that do nothing) lets the loop's decisions
+    be tested without a GPU."""
+
+    def host_buffer(self, n: int):
+        import torch
+        return torch.empty(n, dtype=torch.int32).pin_memory()
+
+    def mark(self):
+        import torch
+        ev = torch.cuda.Event()
+        ev.record()
+        return ev
+
+    def rows(self, tokens, keep: list):
+        """tokens[keep] as a new array on the same side (device or pinned host) as `tokens`."""
+        import torch
+        idx = torch.tensor(keep, dtype=torch.long, device=tokens.device)
+        return tokens[idx].contiguous()
+
+
 class Generator:
     """engine: alloc_slot(), free_slot(slot), step(slots, tokens, "last") -> logits,
                max_seq_len, cache.pager (for admission)
        sampler: sample(logits, streams, counters, histories) -> int tokens (device or host)"""
 
-    def __init__(self, engine, sampler, *, stop_ids=(), max_batch: int | None = None):
+    def __init__(self, engine, sampler, *, stop_ids=(), max_batch: int | None = None, device=None):
         self.engine = engine
         self.sampler = sampler
+        self.device = device or CudaLoopDevice()     # what the look-ahead loop needs of the device
         self.stop_ids = frozenset(int(s) for s in stop_ids)
         self.max_batch = max_batch
         self.step_times = None        # set to a list to record when each step's tokens reached the host
@@ -130,48 +154,50 @@ class Generator:
     def _run_batch_ahead(self, live, prompts, max_tokens, results, uses_history=False) -> None:
         """The same with one step of lookahead: while the host reads the tokens sampled by step i,
         step i+1 already runs on them."""
-        import torch
-        eng = self.engine
+        eng, dev = self.engine, self.device
 
-        # A few pinned buffers, taken in turn (at most two are awaited at any time).  The sampling
-        # kernel writes its tokens there as well as to the device, so the host needs no copy: it waits
-        # for the event recorded behind the kernel.
-        ring = [torch.empty(len(live), dtype=torch.int32).pin_memory() for _ in range(4)]
+        # A few host buffers the device can write to, taken in turn (at most two are awaited at any
+        # time).  The sampling kernel writes its tokens there as well as to the device, so the host
+        # needs no copy: it waits for the mark set behind the kernel.
+        ring = [dev.host_buffer(len(live)) for _ in range(4)]
         turn = [0]
+
+        def goes_on(s, drawn) -> bool:
+            """Will s certainly be stepped again after its next token (its drawn-th)?  Length limits are
+            known in advance; stop tokens are not."""
+            return drawn < max_tokens and s.prompt_length + drawn <= eng.max_seq_len
 
         def sample(logits, seqs, drawn, newest=None):
             host = ring[turn[0] % len(ring)][:len(seqs)]
             turn[0] += 1
-            # straight into the buffer the next step of this batch size reads its tokens from
-            out = eng.decode_token_buffer(len(seqs)) if hasattr(eng, "decode_token_buffer") else None
+            # straight into the buffer the next step of this batch size reads its tokens from, if the
+            # whole batch will be stepped again at this size
+            out = None
+            if hasattr(eng, "decode_token_buffer") and all(goes_on(s, d + 1) for s, d in zip(seqs, drawn)):
+                out = eng.decode_token_buffer(len(seqs))
             # With a repetition penalty the host's histories lack the token that was just fed (it has not
             # been read yet): the kernel takes that one from the device.  It reads `newest` before it writes
             # `out`, so the two may be the same buffer.
             tokens_dev = self.sampler.sample(logits, [s.index for s in seqs], drawn,
                                              [s.history for s in seqs] if uses_history else None,
                                              out=out, mirror=host, newest=newest if uses_history else None)
-            ev = torch.cuda.Event()
-            ev.record()
-            self.d2h_bytes += host.numel() * 4
-            return tokens_dev, (host, ev)
+            self.d2h_bytes += len(seqs) * 4
+            return tokens_dev, (host, dev.mark())
 
         logits = eng.step([s.slot for s in live], [list(prompts[s.index]) for s in live], "last", borrow=True)
         self.steps += 1
-        pending = (list(live),) + sample(logits, live, [len(s.tokens) for s in live])    # sequences, tokens on the device, (host copy, event)
+        pending = (list(live),) + sample(logits, live, [len(s.tokens) for s in live])    # sequences, tokens on the device, (host copy, mark)
         while pending is not None:
-            seqs, tokens_dev, (host, ev) = pending
-            # Who certainly goes on after the token just sampled (length limits are known; stop tokens are not)?
-            rows = [i for i, s in enumerate(seqs)
-                    if len(s.tokens) + 1 < max_tokens and s.prompt_length + len(s.tokens) + 1 <= eng.max_seq_len]
+            seqs, tokens_dev, (host, mark) = pending
+            rows = [i for i, s in enumerate(seqs) if goes_on(s, len(s.tokens) + 1)]
             nxt = None
             if rows:
                 ahead = [seqs[i] for i in rows]
-                feed_dev = tokens_dev if len(rows) == len(seqs) else tokens_dev[
-                    torch.tensor(rows, dtype=torch.long, device=tokens_dev.device)]
+                feed_dev = tokens_dev if len(rows) == len(seqs) else dev.rows(tokens_dev, rows)
                 logits = eng.step_from_device([s.slot for s in ahead], feed_dev)
                 self.steps += 1
                 nxt = (ahead,) + sample(logits, ahead, [len(s.tokens) + 1 for s in ahead], newest=feed_dev)
-            ev.synchronize()                                         # the earlier tokens; the step just launched keeps running
+            mark.synchronize()                                       # the earlier tokens; the step just launched keeps running
             if hasattr(eng, "check_device_status"):
                 eng.check_device_status()
             if self.step_times is not None:
@@ -184,15 +210,13 @@ class Generator:
                     s.history.append(int(tok))
             if nxt is not None and stopped:
                 # a sequence that sampled a stop token ran the step ahead for nothing: drop its row
-                ahead, sampled, (host2, ev2) = nxt
+                ahead, sampled, (host2, mark2) = nxt
                 keep = [i for i, s in enumerate(ahead) if id(s) not in stopped]
                 if not keep:
                     nxt = None
                 elif len(keep) < len(ahead):
-                    ev2.synchronize()
-                    idx = torch.tensor(keep, dtype=torch.long, device=sampled.device)
-                    nxt = ([ahead[i] for i in keep], sampled[idx].contiguous(),
-                           (host2[torch.tensor(keep, dtype=torch.long)].clone(), ev2))
+                    mark2.synchronize()
+                    nxt = ([ahead[i] for i in keep], dev.rows(sampled, keep), (dev.rows(host2, keep), mark2))
             pending = nxt
         live[:] = [s for s in live if s.slot >= 0]
 

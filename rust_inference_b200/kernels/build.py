@@ -30,6 +30,7 @@ MODULES = {
     "gemm_tcgen05": "gemm_tcgen05.cu",
     "attention_mma": "attention_mma.cu",
     "attention_tcgen05": "attention_tcgen05.cu",
+    "wait_probe": "wait_probe.cu",
     "host_runtime": "host_runtime.cpp",
 }
 

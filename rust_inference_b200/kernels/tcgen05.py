@@ -44,6 +44,16 @@ def check_status() -> None:
         raise KernelError(f"a tensor-core kernel gave up: {STATUS_TEXT.get(code, f'code {code}')}")
 
 
+def wait_probe(limit: int = 2000, code: int = 2, arrive_first: bool = False) -> None:
+    """Run the kernels' bounded wait (`mbar_wait`) on a barrier that nothing arrives at, with a limit
+    of `limit` polls: it runs out within microseconds, stores `code` in the status word as a kernel
+    that gave up would, and returns.  After a synchronisation `check_status()` raises that code's
+    text.  With arrive_first the barrier is complete before the wait, which then succeeds."""
+    st = status_word()
+    _call("wait_probe", "ri_wait_probe", c_int(limit), c_int(code), c_int(1 if arrive_first else 0),
+          c_void_p(st.data_ptr()), _stream())
+
+
 def supports(x: torch.Tensor, w) -> bool:
     """The kernel's alignment rule: bf16, K a multiple of 8 (16-byte rows for TMA)."""
     return x.dtype == torch.bfloat16 and w.t.dtype == torch.bfloat16 and w.k % 8 == 0 and w.k >= 8

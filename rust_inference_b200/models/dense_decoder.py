@@ -43,6 +43,9 @@ def build_spec(cfg: DenseDecoderConfig) -> ModelSpec:
         embedding_name="model.embed_tokens.weight",
         head_name=None if cfg.tie_word_embeddings else "lm_head.weight",
         stop_ids=tuple(cfg.eos_token_ids),
+        # a stored head beside tied embeddings is a copy of the embedding (the reference clones it,
+        # model.rs:221-226); old exports carry the rotary frequencies, which are made from the base here
+        ignored_tensors=(("lm_head.weight",) if cfg.tie_word_embeddings else ()) + ("*.rotary_emb.inv_freq",),
     )
 
 

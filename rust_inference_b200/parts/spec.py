@@ -54,6 +54,8 @@ class ModelSpec:
     embedding_name: str = "model.embed_tokens.weight"
     head_name: str | None = "lm_head.weight"      # None: tied to the embedding
     stop_ids: tuple = ()
+    # name patterns of tensors a folder may hold although the model does not read them
+    ignored_tensors: tuple = ()
 
     def cache_layers(self) -> int:
         return 1 + max(e.cache for e in self.schedule)

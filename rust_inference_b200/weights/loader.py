@@ -8,8 +8,10 @@ all missing tensors, all unexpected ones, every wrong shape and every unsupporte
 """
 from __future__ import annotations
 
+import fnmatch
 import json
 import os
+import warnings
 import zlib
 from typing import Iterator, Mapping
 
@@ -39,11 +41,18 @@ class WeightError(ValueError):
         super().__init__("\n".join(lines))
 
 
-def check_tensors(files: ModelFiles, expected: Mapping[str, TensorSpec]) -> None:
+def check_tensors(files: ModelFiles, expected: Mapping[str, TensorSpec], ignore=()) -> list:
+    """Compare the folder with the declaration; raises ONE `WeightError` for everything that is
+    wrong.  `ignore`: name patterns (fnmatch) of tensors a folder may hold although the model does
+    not use them (a stored head beside tied embeddings, rotary frequency tables of old exports):
+    the reference takes the tensors it needs by name and leaves the rest (model.rs:157-203).  They
+    are returned, and the caller warns; every other undeclared tensor stays an error."""
     have = set(files.names())
     want = set(expected)
     missing = sorted(want - have)
-    unexpected = sorted(have - want)
+    extra = sorted(have - want)
+    ignored = [n for n in extra if any(fnmatch.fnmatchcase(n, pat) for pat in ignore)]
+    unexpected = [n for n in extra if n not in set(ignored)]
     wrong_shape, bad_dtype = [], []
     for name in sorted(want & have):
         if tuple(files.shape(name)) != tuple(expected[name].shape):
@@ -54,15 +63,19 @@ def check_tensors(files: ModelFiles, expected: Mapping[str, TensorSpec]) -> None
             bad_dtype.append((name, files.dtype_name(name)))
     if missing or unexpected or wrong_shape or bad_dtype:
         raise WeightError(files.model_dir, missing, unexpected, wrong_shape, bad_dtype)
+    return ignored
 
 
-def read_model_tensors(model_dir: str, expected: Mapping[str, TensorSpec]) -> Iterator[tuple]:
+def read_model_tensors(model_dir: str, expected: Mapping[str, TensorSpec], ignore=()) -> Iterator[tuple]:
     """Check the folder against `expected`, then yield (name, tensor) one at a time, each in
     the precision it was stored in (bfloat16 stays bfloat16, 32-bit stays 32-bit, integer
-    tables int32)."""
+    tables int32).  Tensors that match `ignore` are left unread, with a warning."""
     files = ModelFiles(model_dir)
     try:
-        check_tensors(files, expected)
+        ignored = check_tensors(files, expected, ignore)
+        if ignored:
+            warnings.warn(f"{model_dir}: tensors the model does not use were left unread: " + ", ".join(ignored),
+                          stacklevel=2)
         for name in expected:
             yield name, files.tensor(name)
     finally:
@@ -79,9 +92,12 @@ def _tensor_seed(seed: int, name: str) -> int:
 
 
 def random_tensors(expected: Mapping[str, TensorSpec], seed: int, *, std: float = 0.02,
-                   matrix_dtype: torch.dtype = torch.bfloat16, device="cpu") -> Iterator[tuple]:
+                   matrix_dtype: torch.dtype = torch.bfloat16, device="cpu",
+                   norm_std: float = 0.0) -> Iterator[tuple]:
     """Yield (name, tensor): matrices ~ N(0, std) in `matrix_dtype`, biases ~ N(0, std) and
-    norm weights 1.0 in float32, integer tables zero."""
+    norm weights 1 + N(0, norm_std) in float32 (exactly 1.0 by default), integer tables zero.
+    With norm_std > 0 every norm weight differs from every other, so a test model shows a
+    norm weight that was swapped, dropped or skipped."""
     device = torch.device(device)
     for name, spec in expected.items():
         gen = torch.Generator(device=device)
@@ -90,6 +106,8 @@ def random_tensors(expected: Mapping[str, TensorSpec], seed: int, *, std: float 
             t = torch.zeros(spec.shape, dtype=torch.int32, device=device)
         elif spec.init == "ones":
             t = torch.ones(spec.shape, dtype=torch.float32, device=device)
+            if norm_std > 0.0:
+                t += torch.empty(spec.shape, dtype=torch.float32, device=device).normal_(0.0, norm_std, generator=gen)
         elif spec.init == "zeros":
             t = torch.zeros(spec.shape, dtype=torch.float32, device=device)
         elif spec.init == "normal":
@@ -102,7 +120,7 @@ def random_tensors(expected: Mapping[str, TensorSpec], seed: int, *, std: float 
 
 
 def write_random_model(model_dir: str, config, seed: int, *, std: float = 0.02,
-                       matrix_dtype: torch.dtype = torch.bfloat16) -> str:
+                       matrix_dtype: torch.dtype = torch.bfloat16, norm_std: float = 0.0) -> str:
     """Random-weights mode: make a model folder (config.json, model.safetensors) from a
     typed config and a seed.  Returns the folder."""
     from ..config.registry import get_architecture
@@ -112,7 +130,7 @@ def write_random_model(model_dir: str, config, seed: int, *, std: float = 0.02,
     spec = arch.build_spec(config)
     expected = declared_tensors(spec)
     os.makedirs(model_dir, exist_ok=True)
-    tensors = dict(random_tensors(expected, seed, std=std, matrix_dtype=matrix_dtype))
+    tensors = dict(random_tensors(expected, seed, std=std, matrix_dtype=matrix_dtype, norm_std=norm_std))
     write_safetensors(os.path.join(model_dir, "model.safetensors"), tensors,
                       metadata={"format": "pt", "seed": seed})
     with open(os.path.join(model_dir, "config.json"), "w", encoding="utf-8") as f:

@@ -81,18 +81,25 @@ class TinyModel:
         return plain_impl.forward(self.weights, self.cfg, tokens, **kw)
 
 
-def make_model(tmp_path, name, *, seed=0, std=0.05, matrix_dtype=torch.bfloat16, overrides=None):
+NORM_STD = 0.2      # norm weights of the test models are 1 + N(0, 0.2): no two alike, none equal to one
+
+
+def oracle_weights(folder, device="cpu") -> dict:
+    """The stored tensors, widened to float32, read with the `safetensors` package and not with the
+    library's own reader: a tensor the library mis-slices shows against the plain implementation."""
+    from safetensors.torch import load_file
+    return {n: t.float() for n, t in load_file(os.path.join(folder, "model.safetensors"), device=device).items()}
+
+
+def make_model(tmp_path, name, *, seed=0, std=0.05, matrix_dtype=torch.bfloat16, overrides=None, norm_std=NORM_STD):
     from rust_inference_b200 import config_from_dict, write_random_model
-    from rust_inference_b200.weights.safetensors_io import ModelFiles
     d = dict(TINY[name])
     if overrides:
         d.update(overrides)
     cfg = config_from_dict(d)
     folder = str(tmp_path / f"model_{name}_{seed}")
-    write_random_model(folder, cfg, seed=seed, std=std, matrix_dtype=matrix_dtype)
-    files = ModelFiles(folder)
-    weights = {n: files.tensor(n).float() for n in files.names()}
-    files.close()
+    write_random_model(folder, cfg, seed=seed, std=std, matrix_dtype=matrix_dtype, norm_std=norm_std)
+    weights = oracle_weights(folder)
     with open(os.path.join(folder, "config.json")) as f:
         cfg_dict = json.load(f)
     return TinyModel(folder, cfg_dict, weights)

@@ -23,6 +23,7 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
 
 CASES = {"A": dict(seed=0, n_tokens=23, token_seed=1), "B": dict(seed=2, n_tokens=31, token_seed=3)}
 STD = 0.08
+NORM_STD = 0.2          # norm weights 1 + N(0, 0.2): a swapped or skipped norm weight changes the logits
 
 
 def tiny_weights(name):
@@ -35,7 +36,8 @@ def tiny_weights(name):
     from rust_inference_b200.weights.loader import random_tensors
     cfg = config_from_dict(TINY[name])
     spec = get_architecture(cfg.architecture).build_spec(cfg)
-    tensors = dict(random_tensors(declared_tensors(spec), CASES[name]["seed"], std=STD, matrix_dtype=torch.float32))
+    tensors = dict(random_tensors(declared_tensors(spec), CASES[name]["seed"], std=STD, matrix_dtype=torch.float32,
+                                  norm_std=NORM_STD))
     return cfg, {k: v.float().numpy() for k, v in tensors.items()}
 
 
@@ -87,7 +89,7 @@ def main():
             logits = run_scalar(binary, cfg, w, tokens, tmp)
             logits.astype(np.float32).tofile(os.path.join(HERE, f"{name}.logits.f32"))
             with open(os.path.join(HERE, f"{name}.json"), "w") as f:
-                json.dump({"config": name, "weights_seed": CASES[name]["seed"], "std": STD, "tokens": tokens,
+                json.dump({"config": name, "weights_seed": CASES[name]["seed"], "std": STD, "norm_std": NORM_STD, "tokens": tokens,
                            "shape": list(logits.shape)}, f)
             print(f"{name}: {logits.shape}, |logits| max {np.abs(logits).max():.4f}")
 

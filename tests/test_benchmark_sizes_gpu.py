@@ -8,7 +8,7 @@ import os
 import pytest
 import torch
 
-from conftest import TOL, random_tokens, rel_err
+from conftest import TOL, oracle_weights, random_tokens, rel_err
 
 pytestmark = pytest.mark.gpu
 
@@ -23,12 +23,9 @@ SIZES = {
 @pytest.fixture(scope="module")
 def big_model(tmp_path_factory):
     from rust_inference_b200 import config_from_dict, write_random_model
-    from rust_inference_b200.weights.safetensors_io import ModelFiles
     folder = str(tmp_path_factory.mktemp("big") / "model")
-    write_random_model(folder, config_from_dict(SIZES), seed=5, std=0.02)
-    files = ModelFiles(folder)
-    weights = {n: files.tensor(n).float().cuda() for n in files.names()}
-    files.close()
+    write_random_model(folder, config_from_dict(SIZES), seed=5, std=0.02, norm_std=0.2)
+    weights = oracle_weights(folder, device="cuda")
     with open(os.path.join(folder, "config.json")) as f:
         cfg = json.load(f)
     return folder, cfg, weights

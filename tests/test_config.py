@@ -125,3 +125,16 @@ def test_register_a_new_architecture():
         assert config_from_dict({"architectures": ["ToyForCausalLM"]}) == {"architectures": ["ToyForCausalLM"]}
     finally:
         unregister_architecture("ToyForCausalLM")
+
+
+def test_max_seq_len_may_shorten_the_context_but_not_lengthen_it():
+    """--max-seq-len overrides the model's context length (model.rs:142-144); beyond
+    max_position_embeddings the model has no positions, which is an error here."""
+    from rust_inference_b200.engine.engine import resolve_max_seq_len
+    assert resolve_max_seq_len(None, 2048) == 2048
+    assert resolve_max_seq_len(64, 2048) == 64
+    assert resolve_max_seq_len(2048, 2048) == 2048
+    with pytest.raises(ValueError, match="exceeds the model's max_position_embeddings 2048"):
+        resolve_max_seq_len(4096, 2048)
+    with pytest.raises(ValueError, match="positive"):
+        resolve_max_seq_len(0, 2048)

@@ -1,8 +1,14 @@
-"""The generation loop's decisions, with a scripted engine and sampler (no GPU)."""
+"""The generation loop's decisions, with a scripted engine and sampler (no GPU).
+
+Every test runs over both loops: the plain one (step, sample, read, decide) and the one every real
+engine takes, which looks one step ahead (`Generator._run_batch_ahead`): there the engine can feed a
+step from the device, the sampler writes into a host buffer and the loop waits for a mark.  The
+stand-ins below are numpy arrays and marks that do nothing."""
+import numpy as np
 import pytest
 
 from rust_inference_b200.cache.pager import SlotPager
-from rust_inference_b200.engine.generate import Generator
+from rust_inference_b200.engine.generate import Generator as _Generator
 
 
 class FakeCache:
@@ -33,6 +39,45 @@ class FakeEngine:
         return ("logits", len(slots))
 
 
+class AheadEngine(FakeEngine):
+    """The same books, plus what lets the loop look ahead: a step fed from a 'device' array."""
+
+    def __init__(self, *a, **k):
+        super().__init__(*a, **k)
+        self.token_buffers = {}
+        self.fed_in_place = 0
+
+    def can_feed_from_device(self):
+        return True
+
+    def decode_token_buffer(self, n):
+        return self.token_buffers.setdefault(n, np.zeros(n, dtype=np.int32))
+
+    def step_from_device(self, slots, tokens_dev):
+        assert len(tokens_dev) == len(slots)
+        if tokens_dev is self.token_buffers.get(len(slots)):
+            self.fed_in_place += 1
+        return self.step(slots, [[int(t)] for t in tokens_dev], "last")
+
+
+class FakeMark:
+    waited = 0
+
+    def synchronize(self):
+        FakeMark.waited += 1
+
+
+class FakeLoopDevice:
+    def host_buffer(self, n):
+        return np.full(n, -1, dtype=np.int32)
+
+    def mark(self):
+        return FakeMark()
+
+    def rows(self, tokens, keep):
+        return np.asarray(tokens)[list(keep)].copy()
+
+
 class ScriptedSampler:
     """token = script(request index, how many it has drawn)."""
 
@@ -40,13 +85,36 @@ class ScriptedSampler:
         self.script = script
         self.seen = []
 
-    def sample(self, logits, streams, counters, histories):
+    def sample(self, logits, streams, counters, histories=None, out=None, mirror=None, newest=None):
         self.seen.append((list(streams), list(counters)))
-        return [self.script(s, c) for s, c in zip(streams, counters)]
+        toks = [self.script(s, c) for s, c in zip(streams, counters)]
+        if out is None and mirror is None:
+            return toks                                   # the plain loop reads what is returned
+        dev = out if out is not None else np.zeros(len(toks), dtype=np.int32)
+        dev[:] = toks
+        if mirror is not None:
+            mirror[:] = toks
+        return dev
 
 
-def test_unequal_prompts_start_together_then_one_token_each():
-    eng = FakeEngine()
+@pytest.fixture(params=["plain", "ahead"])
+def loop(request):
+    return request.param
+
+
+ENGINES = {"plain": FakeEngine, "ahead": AheadEngine}
+
+
+def make_engine(loop, *a, base=None, **k):
+    return ENGINES[loop](*a, **k)
+
+
+def Generator(engine, sampler, **k):
+    return _Generator(engine, sampler, device=FakeLoopDevice(), **k)
+
+
+def test_unequal_prompts_start_together_then_one_token_each(loop):
+    eng = make_engine(loop)
     gen = Generator(eng, ScriptedSampler(lambda s, c: 100 + 10 * s + c))
     res = gen.generate([[1, 2, 3], [4] * 70, [7]], max_tokens=3)
     assert [r.tokens for r in res] == [[100, 101, 102], [110, 111, 112], [120, 121, 122]]
@@ -61,28 +129,41 @@ def test_unequal_prompts_start_together_then_one_token_each():
     assert eng.cache.pager.free_slot_count() == 4 and eng.cache.pager.free_page_count() == 16
 
 
-def test_stop_token_ends_early_is_not_emitted_and_frees_the_slot():
-    eng = FakeEngine()
+def test_stop_token_ends_early_is_not_emitted_and_frees_the_slot(loop):
+    eng = make_engine(loop)
     sampler = ScriptedSampler(lambda s, c: 9 if (s == 1 and c == 1) else 5)
     gen = Generator(eng, sampler, stop_ids=[9])
     res = gen.generate([[1], [2], [3]], max_tokens=4)
     assert res[1].tokens == [5] and res[1].finish_reason == "stop"
     assert res[0].tokens == [5, 5, 5, 5] and res[0].finish_reason == "length"
-    # after sequence 1 stopped, the batch shrank to the two others
-    assert [len(c[0]) for c in eng.calls] == [3, 3, 2, 2]
-    assert sampler.seen[2][0] == [0, 2]
+    if loop == "plain":
+        # after sequence 1 stopped, the batch shrank to the two others
+        assert [len(c[0]) for c in eng.calls] == [3, 3, 2, 2]
+        assert sampler.seen[2][0] == [0, 2]
+    else:
+        # one step ahead: when the stop token is read, the step that feeds it already runs (three
+        # rows); its row is dropped and the stop token is fed no further
+        assert [len(c[0]) for c in eng.calls] == [3, 3, 3, 2]
+        assert eng.calls[2][1] == [[5], [9], [5]] and eng.calls[3][1] == [[5], [5]]
+        assert sampler.seen[2][0] == [0, 1, 2] and sampler.seen[3][0] == [0, 2]
+    assert res[2].tokens == [5, 5, 5, 5]
     eng.cache.pager.audit()
+    assert eng.cache.pager.free_slot_count() == 4
 
 
-def test_stop_at_the_first_token():
-    eng = FakeEngine()
+def test_stop_at_the_first_token(loop):
+    eng = make_engine(loop)
     gen = Generator(eng, ScriptedSampler(lambda s, c: 9), stop_ids=[9])
     res = gen.generate([[1, 2]], max_tokens=8)
-    assert res[0].tokens == [] and res[0].finish_reason == "stop" and len(eng.calls) == 1
+    assert res[0].tokens == [] and res[0].finish_reason == "stop"
+    # the loop that looks ahead has fed the stop token once before it read it
+    assert len(eng.calls) == (1 if loop == "plain" else 2)
+    eng.cache.pager.audit()
+    assert eng.cache.pager.free_slot_count() == 4
 
 
-def test_batches_follow_one_another_and_reuse_slots():
-    eng = FakeEngine(n_slots=2, n_pages=16)
+def test_batches_follow_one_another_and_reuse_slots(loop):
+    eng = make_engine(loop, n_slots=2, n_pages=16)
     gen = Generator(eng, ScriptedSampler(lambda s, c: 5))
     res = gen.generate([[i + 1] * (i + 1) for i in range(5)], max_tokens=2)
     assert len(res) == 5 and all(r.tokens == [5, 5] for r in res)
@@ -94,9 +175,9 @@ def test_batches_follow_one_another_and_reuse_slots():
     assert eng.cache.pager.free_slot_count() == 2
 
 
-def test_admission_counts_pages_for_the_whole_generation():
+def test_admission_counts_pages_for_the_whole_generation(loop):
     # 4 pages of 64: a prompt of 60 with up to 10 more needs 2 pages, so only 2 requests fit at once
-    eng = FakeEngine(n_slots=4, n_pages=4)
+    eng = make_engine(loop, n_slots=4, n_pages=4)
     gen = Generator(eng, ScriptedSampler(lambda s, c: 5))
     res = gen.generate([[1] * 60] * 3, max_tokens=10)
     assert all(len(r.tokens) == 10 for r in res)
@@ -104,8 +185,8 @@ def test_admission_counts_pages_for_the_whole_generation():
     eng.cache.pager.audit()
 
 
-def test_a_request_that_cannot_fit_is_an_error():
-    eng = FakeEngine(n_slots=2, n_pages=1)
+def test_a_request_that_cannot_fit_is_an_error(loop):
+    eng = make_engine(loop, n_slots=2, n_pages=1)
     gen = Generator(eng, ScriptedSampler(lambda s, c: 5))
     with pytest.raises(RuntimeError, match="does not fit"):
         gen.generate([[1] * 100], max_tokens=4)
@@ -113,8 +194,8 @@ def test_a_request_that_cannot_fit_is_an_error():
     assert eng.cache.pager.free_slot_count() == 2
 
 
-def test_max_seq_len_ends_with_length():
-    eng = FakeEngine(n_slots=1, n_pages=8, max_seq_len=70)
+def test_max_seq_len_ends_with_length(loop):
+    eng = make_engine(loop, n_slots=1, n_pages=8, max_seq_len=70)
     gen = Generator(eng, ScriptedSampler(lambda s, c: 5))
     res = gen.generate([[1] * 68], max_tokens=50)
     # positions 68 and 69 can still be fed; the token sampled after position 69 has nowhere to go
@@ -124,8 +205,8 @@ def test_max_seq_len_ends_with_length():
         gen.generate([[1] * 71], max_tokens=1)
 
 
-def test_edge_cases():
-    eng = FakeEngine()
+def test_edge_cases(loop):
+    eng = make_engine(loop)
     gen = Generator(eng, ScriptedSampler(lambda s, c: 5))
     with pytest.raises(ValueError, match="empty prompt"):
         gen.generate([[1], []], max_tokens=2)
@@ -134,14 +215,14 @@ def test_edge_cases():
     assert gen.generate([], max_tokens=3) == []
 
 
-def test_max_batch_limits_a_wave():
-    eng = FakeEngine(n_slots=4)
+def test_max_batch_limits_a_wave(loop):
+    eng = make_engine(loop, n_slots=4)
     gen = Generator(eng, ScriptedSampler(lambda s, c: 5), max_batch=1)
     gen.generate([[1], [2], [3]], max_tokens=1)
     assert [len(c[0]) for c in eng.calls] == [1, 1, 1]
 
 
-def test_slots_are_freed_when_a_step_raises():
+def test_slots_are_freed_when_a_step_raises(loop):
     class Boom(FakeEngine):
         def step(self, *a, **k):
             if len(self.calls) == 1:
@@ -156,17 +237,90 @@ def test_slots_are_freed_when_a_step_raises():
     assert eng.cache.pager.free_slot_count() == 4
 
 
-def test_history_reaches_the_sampler_when_the_penalty_is_on():
+def test_history_reaches_the_sampler_when_the_penalty_is_on(loop):
     from rust_inference_b200 import SamplerConfig
 
     class HistSampler(ScriptedSampler):
         params = SamplerConfig(repetition_penalty=1.3)
 
-        def sample(self, logits, streams, counters, histories):
+        def sample(self, logits, streams, counters, histories=None, out=None, mirror=None, newest=None):
             self.hist = [list(h) for h in histories]
-            return super().sample(logits, streams, counters, histories)
+            self.newest = None if newest is None else [int(t) for t in newest]
+            return super().sample(logits, streams, counters, histories, out=out, mirror=mirror, newest=newest)
 
-    eng = FakeEngine()
+    eng = make_engine(loop)
     s = HistSampler(lambda st, c: 50 + c)
     Generator(eng, s).generate([[1, 2, 3]], max_tokens=3)
-    assert s.hist == [[1, 2, 3, 50, 51]]            # prompt and generated tokens (model.rs:357, :364, :440)
+    if loop == "plain":
+        assert s.hist == [[1, 2, 3, 50, 51]]        # prompt and generated tokens (model.rs:357, :364, :440)
+    else:
+        # the newest token has not reached the host when the next one is sampled: the sampler is given
+        # it on the device, and the host's history holds the ones before
+        assert s.hist == [[1, 2, 3, 50]] and s.newest == [51]
+
+
+# ----------------------------------------------------------------------------------------
+# Cases of the loop that looks ahead
+# ----------------------------------------------------------------------------------------
+def test_two_sequences_stop_in_the_same_step(loop):
+    eng = make_engine(loop)
+    gen = Generator(eng, ScriptedSampler(lambda s, c: 9 if (s in (0, 2) and c == 2) else 40 + s), stop_ids=[9])
+    res = gen.generate([[1], [2, 2], [3, 3, 3], [4]], max_tokens=5)
+    assert [r.tokens for r in res] == [[40, 40], [41] * 5, [42, 42], [43] * 5]
+    assert [r.finish_reason for r in res] == ["stop", "length", "stop", "length"]
+    sizes = [len(c[0]) for c in eng.calls]
+    assert sizes == ([4, 4, 4, 2, 2] if loop == "plain" else [4, 4, 4, 4, 2])
+    assert 9 not in [t for c in eng.calls[-1:] for toks in c[1] for t in toks]
+    eng.cache.pager.audit()
+    assert eng.cache.pager.free_slot_count() == 4 and eng.cache.pager.free_page_count() == 16
+
+
+def test_every_sequence_stops_while_a_step_is_in_flight(loop):
+    eng = make_engine(loop, n_slots=2)
+    gen = Generator(eng, ScriptedSampler(lambda s, c: 9 if c == 1 else 7), stop_ids=[9])
+    res = gen.generate([[1], [2], [3]], max_tokens=6)            # two batches on two slots
+    assert [r.tokens for r in res] == [[7], [7], [7]] and all(r.finish_reason == "stop" for r in res)
+    sizes = [len(c[0]) for c in eng.calls]
+    # plain: prefill + one decode step per batch; ahead: one more step per batch, run for nothing
+    assert sizes == ([2, 2, 1, 1] if loop == "plain" else [2, 2, 2, 1, 1, 1])
+    eng.cache.pager.audit()
+    assert eng.cache.pager.free_slot_count() == 2 and eng.cache.pager.free_page_count() == 16
+
+
+def test_one_ends_at_max_seq_len_a_step_before_another_stops(loop):
+    eng = make_engine(loop, n_slots=2, n_pages=8, max_seq_len=70)
+    # request 0 (prompt 67) can be fed at positions 67, 68, 69: it ends by length with its 4th token;
+    # request 1 samples a stop token as its 5th
+    gen = Generator(eng, ScriptedSampler(lambda s, c: 9 if (s == 1 and c == 4) else 20 + s), stop_ids=[9])
+    res = gen.generate([[1] * 67, [2] * 3], max_tokens=30)
+    assert res[0].tokens == [20] * 4 and res[0].finish_reason == "length"
+    assert res[1].tokens == [21] * 4 and res[1].finish_reason == "stop"
+    sizes = [len(c[0]) for c in eng.calls]
+    # the sequence that ends by length is never stepped beyond its last position in either loop
+    assert sizes == ([2, 2, 2, 2, 1] if loop == "plain" else [2, 2, 2, 2, 1, 1])
+    assert max(len(t) for c in eng.calls[1:] for t in c[1]) == 1
+    eng.cache.pager.audit()
+    assert eng.cache.pager.free_slot_count() == 2
+
+
+def test_tokens_are_fed_in_place_while_the_whole_batch_goes_on():
+    eng = AheadEngine()
+    gen = Generator(eng, ScriptedSampler(lambda s, c: 9 if (s == 0 and c == 3) else 5), stop_ids=[9])
+    res = gen.generate([[1], [2]], max_tokens=6)
+    assert res[0].tokens == [5, 5, 5] and res[1].tokens == [5] * 6
+    # steps of two rows were fed from the buffer the sampler wrote into (no gather, no copy); once a row
+    # had been dropped, the single row that was left was gathered once, then fed in place again
+    assert eng.fed_in_place >= 4
+    # nothing asks for a token buffer of a size that is never stepped: the last sample of the batch
+    # (and the first sample, of one row after the stop) writes to a buffer of its own
+    assert set(eng.token_buffers) <= {1, 2}
+    eng.cache.pager.audit()
+
+
+def test_the_last_sample_of_a_batch_takes_no_token_buffer():
+    eng = AheadEngine()
+    Generator(eng, ScriptedSampler(lambda s, c: 5)).generate([[1], [2], [3]], max_tokens=1)
+    assert eng.token_buffers == {}                               # one sample, no step after it
+    eng2 = AheadEngine()
+    Generator(eng2, ScriptedSampler(lambda s, c: 5)).generate([[1], [2], [3]], max_tokens=3)
+    assert set(eng2.token_buffers) == {3}

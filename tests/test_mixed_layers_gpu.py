@@ -19,7 +19,7 @@ import pytest
 import torch
 
 import plain_impl
-from conftest import random_tokens, rel_err
+from conftest import oracle_weights, random_tokens, rel_err
 
 pytestmark = pytest.mark.gpu
 
@@ -161,7 +161,7 @@ def mixed_model(tmp_path_factory):
     from rust_inference_b200.engine.model import declared_tensors
     from rust_inference_b200.parts.registry import unregister
     from rust_inference_b200.weights.loader import random_tensors
-    from rust_inference_b200.weights.safetensors_io import ModelFiles, write_safetensors
+    from rust_inference_b200.weights.safetensors_io import write_safetensors
     _register_parts()
     _register_architecture()
     folder = str(tmp_path_factory.mktemp("mixed") / "model")
@@ -170,13 +170,11 @@ def mixed_model(tmp_path_factory):
     with open(os.path.join(folder, "config.json"), "w") as f:
         json.dump(cfg, f)
     names = declared_tensors(get_architecture("ToyMixedLM").build_spec(cfg))
-    tensors = dict(random_tensors(names, 3, std=0.08))
+    tensors = dict(random_tensors(names, 3, std=0.08, norm_std=0.2))
     # a decisive router: the best expert of a token must not hang on bfloat16's rounding of its input
     tensors["model.layers.2.moe.router.weight"] *= 6.0
     write_safetensors(os.path.join(folder, "model.safetensors"), tensors)
-    files = ModelFiles(folder)
-    weights = {n: files.tensor(n).float() for n in files.names()}
-    files.close()
+    weights = oracle_weights(folder)
     yield folder, weights
     unregister("feed_forward", "toy_routed")
     unregister("mixer", "toy_position_add")
@@ -326,7 +324,7 @@ def test_another_norm_and_another_arrangement(dtype, tmp_path):
     from rust_inference_b200.engine.model import declared_tensors
     from rust_inference_b200.parts.registry import unregister
     from rust_inference_b200.weights.loader import random_tensors
-    from rust_inference_b200.weights.safetensors_io import ModelFiles, write_safetensors
+    from rust_inference_b200.weights.safetensors_io import write_safetensors
     _register_parallel()
     try:
         cfg = {"architectures": ["ToyParallelLM"], "hidden": 136, "inter": 200, "vocab": 77}
@@ -336,10 +334,8 @@ def test_another_norm_and_another_arrangement(dtype, tmp_path):
             json.dump(cfg, f)
         names = declared_tensors(get_architecture("ToyParallelLM").build_spec(cfg))
         assert "h.0.ln.bias" in names and "h.1.unused_ln.weight" in names and "ln_f.bias" in names
-        write_safetensors(os.path.join(folder, "model.safetensors"), dict(random_tensors(names, 4, std=0.08)))
-        files = ModelFiles(folder)
-        weights = {n: files.tensor(n).float() for n in files.names()}
-        files.close()
+        write_safetensors(os.path.join(folder, "model.safetensors"), dict(random_tensors(names, 4, std=0.08, norm_std=0.2)))
+        weights = oracle_weights(folder)
         eng = Engine.from_pretrained(folder, dtype=dtype, max_tokens=512)
         toks = random_tokens(70, 77, seed=3)
         want = _plain_parallel(weights, toks, 200)

@@ -229,7 +229,7 @@ def test_toy_mixer_with_state_registers_builds_and_steps(dtype, tmp_path):
         spec = get_architecture("ToyStateLM").build_spec(cfg)
         names = declared_tensors(spec)
         assert "l0.toy.mix.weight" in names and "l1.attn.q_proj.weight" in names and "l2.toy.mix.weight" in names
-        write_safetensors(os.path.join(folder, "model.safetensors"), dict(random_tensors(names, 0, std=0.1)))
+        write_safetensors(os.path.join(folder, "model.safetensors"), dict(random_tensors(names, 0, std=0.1, norm_std=0.2)))
         eng = Engine.from_pretrained(folder, dtype=dtype, max_tokens=1024, n_slots=3)
         reqs = eng.model.cache_requests()
         assert isinstance(reqs[0], StateRequest) and isinstance(reqs[1], KVRequest) and reqs[0] == reqs[2]

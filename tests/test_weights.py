@@ -180,6 +180,68 @@ def test_bias_and_tied_head_must_match_the_config(tmp_path):
     with pytest.raises(WeightError) as e:
         list(read_model_tensors(folder, declared_tensors(spec)))
     assert e.value.unexpected == ["lm_head.weight", "model.layers.0.self_attn.q_proj.bias"]
+    # with the architecture's own list of tensors a folder may carry unused, the stored head of a tied
+    # model is left unread with a warning; the bias the config rules out stays an error
+    assert spec.ignored_tensors == ("lm_head.weight", "*.rotary_emb.inv_freq")
+    with pytest.raises(WeightError) as e:
+        list(read_model_tensors(folder, declared_tensors(spec), spec.ignored_tensors))
+    assert e.value.unexpected == ["model.layers.0.self_attn.q_proj.bias"]
+
+
+def test_a_folder_may_carry_tensors_the_model_does_not_read(tmp_path):
+    """A stored head beside tied embeddings and the rotary frequency tables of old exports: the
+    reference takes what it needs by name and leaves the rest (model.rs:157-203)."""
+    cfg, spec = _spec("A")
+    folder = write_random_model(str(tmp_path / "m"), cfg, seed=0)
+
+    def change(t):
+        t["lm_head.weight"] = t["model.embed_tokens.weight"].clone()
+        t["model.layers.1.self_attn.rotary_emb.inv_freq"] = torch.ones(32)
+    _rewrite(folder, change)
+    expected = declared_tensors(spec)
+    with pytest.warns(UserWarning, match="lm_head.weight.*rotary_emb.inv_freq"):
+        got = dict(read_model_tensors(folder, expected, spec.ignored_tensors))
+    assert set(got) == set(expected)
+    # an untied model must have its head: nothing is ignorable there
+    cfg_b, spec_b = _spec("B")
+    assert "lm_head.weight" not in spec_b.ignored_tensors
+
+
+def test_a_file_written_by_the_safetensors_package_loads(tmp_path):
+    """The other direction of the round trip: tensors made with torch, stored by the `safetensors`
+    package, fetched by name through the library's own reader."""
+    from safetensors.torch import save_file
+    cfg, spec = _spec("B")
+    expected = declared_tensors(spec)
+    g = torch.Generator().manual_seed(11)
+    tensors = {}
+    for i, (name, ts) in enumerate(expected.items()):
+        t = torch.randn(ts.shape, generator=g)
+        tensors[name] = t.bfloat16() if ts.role == "matrix" and i % 2 else t       # both stored precisions
+    folder = tmp_path / "pkg"
+    folder.mkdir()
+    save_file(tensors, str(folder / "model.safetensors"), metadata={"format": "pt"})
+    (folder / "config.json").write_text(json.dumps(cfg.to_dict()))
+    got = dict(read_model_tensors(str(folder), expected))
+    assert list(got) == list(expected)
+    for name, t in tensors.items():
+        assert got[name].dtype == t.dtype and torch.equal(got[name], t), name
+
+
+def test_norm_weights_of_test_models_are_all_different():
+    cfg, spec = _spec("B")
+    expected = declared_tensors(spec)
+    plain = dict(random_tensors(expected, 3, matrix_dtype=torch.float32))
+    assert all(torch.equal(t, torch.ones_like(t)) for n, t in plain.items() if n.endswith("norm.weight"))
+    varied = dict(random_tensors(expected, 3, matrix_dtype=torch.float32, norm_std=0.2))
+    norms = [t for n, t in varied.items() if n.endswith("norm.weight") or n.endswith("layernorm.weight")]
+    assert len(norms) == 2 * cfg.num_hidden_layers + 1
+    for i, a in enumerate(norms):
+        assert (a - 1).abs().mean() > 0.05
+        for b in norms[i + 1:]:
+            assert not torch.equal(a, b)
+    # matrices do not depend on norm_std
+    assert torch.equal(plain["model.layers.0.mlp.up_proj.weight"], varied["model.layers.0.mlp.up_proj.weight"])
 
 
 def test_unsupported_dtype_is_reported(tmp_path):
