@@ -39,16 +39,44 @@ class Model:
         return cls(Engine.from_random(config, seed=seed, std=std, norm_std=norm_std, dtype=dtype, device=device,
                                       max_tokens=max_tokens_in_cache, max_seq_len=max_seq_len, n_slots=n_slots))
 
-    def logits(self, tokens, want="all"):
+    def state_dict(self) -> dict:
+        """name -> tensor for every tensor of the model, under the weight file's names, as held on the
+        device (matrices in the run dtype, norm weights and biases float32; packed matrices as views
+        of their parts).  Handing these to a plain implementation gives it the very numbers the
+        engine computes with, without a folder on disk."""
+        return self.engine.model.state_dict()
+
+    def save_safetensors(self, folder: str) -> str:
+        """Write the model as a folder (config.json, model.safetensors) that `Model.load` reads back."""
+        import json
+        import os
+        from .weights.safetensors_io import write_safetensors
+        if self.config is None:
+            raise RuntimeError("save_safetensors: the model was built without a typed configuration")
+        os.makedirs(folder, exist_ok=True)
+        tensors = {name: t.detach().to("cpu") for name, t in self.state_dict().items()}
+        write_safetensors(os.path.join(folder, "model.safetensors"), tensors, metadata={"format": "pt"})
+        with open(os.path.join(folder, "config.json"), "w", encoding="utf-8") as f:
+            json.dump(self.config.to_dict(), f, indent=2)
+        return folder
+
+    def logits(self, tokens, want="all", layer_stats: list | None = None):
         """float32 logits [wanted, vocab] of one list of token ids run whole, as one step of the
         engine (the reference computes them for every position, transformer.rs:89-97).  `want`:
         "all", "last", or a list of positions among the tokens.  The sequence's slot is given
-        back afterwards."""
+        back afterwards.  `layer_stats`: a list that receives (label, {min, max, mean, first}) of the
+        hidden vector at position 0 after every layer and after the final norm, which the reference
+        prints in debug builds (transformer.rs:80-96)."""
+        from .engine.model import LayerProbe
+        probe = LayerProbe([0]) if layer_stats is not None else None
         slot = self.engine.alloc_slot()
         try:
-            return self.engine.step([slot], [list(tokens)], want if isinstance(want, str) else [list(want)])
+            out = self.engine.step([slot], [list(tokens)], want if isinstance(want, str) else [list(want)], probe=probe)
         finally:
             self.engine.free_slot(slot)
+        if probe is not None:
+            layer_stats.extend(probe.stats[0])
+        return out
 
     def generate(self, prompts, max_tokens: int = 512, sampler_config: SamplerConfig | None = None,
                  stop_ids=None, max_batch: int | None = None, record_step_times: bool = False) -> list:

@@ -14,8 +14,10 @@
 //    the library carries it until the process exits.  A call needs
 //    n_seqs * n_heads * n_splits * (head_dim + 2) floats; a larger call is refused with an
 //    error message (ri_last_error), nothing is launched.
-//  * The first call on a device looks up the array's device address (once per device, with
-//    that device current).  Make that first call outside any stream capture.
+//  * The first call on a device looks up the array's device address and raises the kernel's
+//    shared-memory limit (each once per device, with that device current; several devices in
+//    one process each get their own).  Make that first call outside any stream capture.  Host
+//    threads may make first calls at the same time: the per-device records are atomic.
 //  * All calls share the one array, and it keeps what the last call left in it.  The kernel
 //    writes every partial slot it later reads (empty splits included), so nothing has to be
 //    cleared between calls.  Two calls that overlap on the GPU (different streams, no

@@ -740,12 +740,8 @@ int launch_decode(const void* q, int q_ld, const void* kc, const void* vc, const
                   int out_ld, cudaStream_t stream) {
     constexpr int SMEM = 2 * NBUF * PAGE * HD * 2 + 16 * HD * 2;      // the merge area lies over the page buffers
     static_assert((4 * 16 * (HD + 4) + 4 * 16 * 2 + 4 * 16 + 16 * 2) * 4 <= SMEM, "merge area must fit");
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
-        if (e != cudaSuccess) return fail("attention: cannot raise dynamic shared memory: %s", cudaGetErrorString(e));
-        configured = true;
-    }
+    static PerDeviceOnce configured;       // per device: the attribute belongs to a device's copy of the kernel
+    if (int rc = raise_dynamic_smem(attn_decode_kernel<HD, false>, SMEM, configured, "attention")) return rc;
     dim3 grid(n_seqs, n_kv_heads, n_splits);
     cudaError_t e = launch_dependent(
         attn_decode_kernel<HD, false>, grid, dim3(THREADS), (size_t)SMEM, stream, (const __nv_bfloat16*)q, q_ld,
@@ -773,12 +769,8 @@ int launch_decode_cluster(const void* q, int q_ld, const void* kc, const void* v
                          (16 * HD + MAX_CLUSTER_SPLITS + MAX_CLUSTER_SPLITS * 16 * 2 + (MAX_CLUSTER_SPLITS + 1) * 16) * 4;
     static_assert((4 * 16 * (HD + 4) + 4 * 16 * 2 + 4 * 16 + 16 * 2) * 4 <= 2 * NBUF * PAGE * HD * 2, "merge area must fit the page buffers");
     auto kernel = attn_decode_kernel<HD, true>;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
-        if (e != cudaSuccess) return fail("attention: cannot raise dynamic shared memory: %s", cudaGetErrorString(e));
-        configured = true;
-    }
+    static PerDeviceOnce configured;       // per device: the attribute belongs to a device's copy of the kernel
+    if (int rc = raise_dynamic_smem(kernel, SMEM, configured, "attention")) return rc;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(n_seqs, n_kv_heads, n_splits);
     cfg.blockDim = dim3(THREADS);
@@ -807,12 +799,8 @@ int launch_decode_tma(const CUtensorMap& mk, const CUtensorMap& mv, const void* 
                       float* part_ml, void* out, int out_ld, int* status, cudaStream_t stream) {
     constexpr int SMEM = 2 * RING * PAGE * HD * 2 + 16 * HD * 2 + 1024;
     static_assert((4 * 16 * (HD + 4) + 4 * 16 * 2 + 4 * 16 + 16 * 2) * 4 <= 2 * RING * PAGE * HD * 2, "merge area must fit the ring");
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_tma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
-        if (e != cudaSuccess) return fail("attention: cannot raise dynamic shared memory: %s", cudaGetErrorString(e));
-        configured = true;
-    }
+    static PerDeviceOnce configured;       // per device: the attribute belongs to a device's copy of the kernel
+    if (int rc = raise_dynamic_smem(attn_decode_tma_kernel<HD>, SMEM, configured, "attention")) return rc;
     dim3 grid(n_seqs, n_kv_heads, n_splits);
     cudaError_t e = launch_dependent(
         attn_decode_tma_kernel<HD>, grid, dim3(DECODE_TMA_THREADS), (size_t)SMEM, stream, mk, mv, (const __nv_bfloat16*)q,
@@ -833,12 +821,8 @@ int launch_prefill(const void* q, int q_ld, const void* kc, const void* vc, cons
                    const int* seq_slot, const int* seq_start, const int* cu_seqlens, int n_seqs, int max_new,
                    int n_heads, int n_kv_heads, float scale, int window, void* out, int out_ld, cudaStream_t stream) {
     constexpr int SMEM = 4 * PAGE * HD * 2 + 64 * HD * 2;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
-        if (e != cudaSuccess) return fail("attention: cannot raise dynamic shared memory: %s", cudaGetErrorString(e));
-        configured = true;
-    }
+    static PerDeviceOnce configured;       // per device: the attribute belongs to a device's copy of the kernel
+    if (int rc = raise_dynamic_smem(attn_prefill_kernel<HD>, SMEM, configured, "attention")) return rc;
     dim3 grid((max_new + 63) / 64, n_heads, n_seqs);
     cudaError_t e = launch_dependent(
         attn_prefill_kernel<HD>, grid, dim3(THREADS), (size_t)SMEM, stream, (const __nv_bfloat16*)q, q_ld,
@@ -956,7 +940,9 @@ static __device__ __align__(256) float g_decode_static_scratch[RI_DECODE_STATIC_
 
 namespace {
 constexpr int MAX_DEVICES = 64;
-float* g_decode_static_ptr[MAX_DEVICES] = {nullptr};
+// One address per device, looked up on that device's first call.  Atomic: two host threads that make a
+// device's first call together both store the same address.
+std::atomic<float*> g_decode_static_ptr[MAX_DEVICES];
 
 // The device address of the scratch array on the current device; looked up on the first call.
 int decode_static_scratch(float** ptr) {
@@ -964,14 +950,14 @@ int decode_static_scratch(float** ptr) {
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return fail("attention_decode_static: cudaGetDevice failed: %s", cudaGetErrorString(e));
     if (dev < 0 || dev >= MAX_DEVICES) return fail("attention_decode_static: device %d is out of range", dev);
-    if (g_decode_static_ptr[dev] == nullptr) {
-        float* p = nullptr;
+    float* p = g_decode_static_ptr[dev].load(std::memory_order_acquire);
+    if (p == nullptr) {
         e = cudaGetSymbolAddress((void**)&p, g_decode_static_scratch);
         if (e != cudaSuccess || p == nullptr)
             return fail("attention_decode_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
-        g_decode_static_ptr[dev] = p;
+        g_decode_static_ptr[dev].store(p, std::memory_order_release);
     }
-    *ptr = g_decode_static_ptr[dev];
+    *ptr = p;
     return 0;
 }
 }  // namespace

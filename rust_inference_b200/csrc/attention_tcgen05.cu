@@ -384,12 +384,8 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
     constexpr int TILES = ATOMS * BM * 128 + 4 * ATOMS * BN * 128;
     constexpr int SMEM = TILES + (HD >= 128 ? 256 : 1024 + 256);
     auto kernel = attn_prefill_tc_kernel<HD>;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
-        if (e != cudaSuccess) return fail("attention_tcgen05: cannot raise dynamic shared memory: %s", cudaGetErrorString(e));
-        configured = true;
-    }
+    static PerDeviceOnce configured;       // per device: the attribute belongs to a device's copy of the kernel
+    if (int rc = raise_dynamic_smem(kernel, SMEM, configured, "attention_tcgen05")) return rc;
     // blocks are handed out x fastest: every head and sequence of the longest query tiles first, the short
     // tiles last, so the causal triangle's tail is filled with small pieces
     dim3 grid(n_heads, n_seqs, (max_new + BM - 1) / BM);

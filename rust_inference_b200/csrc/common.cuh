@@ -12,6 +12,7 @@
 #include <stdio.h>
 #include <stdarg.h>
 #include <stdlib.h>
+#include <atomic>
 
 #define RI_API extern "C" __attribute__((visibility("default")))
 
@@ -140,6 +141,27 @@ inline cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 bl
 inline int check_launch(cudaError_t e, const char* what) {
     if (e != cudaSuccess) return fail("%s: launch failed: %s", what, cudaGetErrorString(e));
     return check_launch(what);
+}
+
+// A kernel's limit of dynamic shared memory is an attribute of ONE device's copy of the kernel.  This
+// remembers, per device, that it has been raised: a bit per device (0..63), set with an atomic OR, so
+// every device a process uses is configured once, whichever host thread gets there first (two threads
+// that race both set the same value).  Devices beyond 63 are configured at every call.
+struct PerDeviceOnce {
+    std::atomic<unsigned long long> done{0ull};
+};
+
+template <typename Kernel>
+inline int raise_dynamic_smem(Kernel kernel, int bytes, PerDeviceOnce& once, const char* what) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail("%s: cudaGetDevice failed: %s", what, cudaGetErrorString(e));
+    const bool tracked = dev >= 0 && dev < 64;
+    if (tracked && ((once.done.load(std::memory_order_acquire) >> dev) & 1ull)) return 0;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e != cudaSuccess) return fail("%s: cannot raise dynamic shared memory: %s", what, cudaGetErrorString(e));
+    if (tracked) once.done.fetch_or(1ull << dev, std::memory_order_release);
+    return 0;
 }
 
 }  // namespace ri

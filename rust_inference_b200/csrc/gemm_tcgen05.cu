@@ -864,12 +864,8 @@ int launch(int tn, const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensor
     int kb_per_split = (total_kb + split_k - 1) / split_k;
     split_k = (total_kb + kb_per_split - 1) / kb_per_split;          // no empty split
     auto kernel = gemm_tc_kernel<TN, DUAL, MODE>;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BUDGET + 1024);
-        if (e != cudaSuccess) return fail("gemm_tcgen05: cannot raise dynamic shared memory: %s", cudaGetErrorString(e));
-        configured = true;
-    }
+    static PerDeviceOnce configured;       // per device: the attribute belongs to a device's copy of the kernel
+    if (int rc = raise_dynamic_smem(kernel, SMEM_BUDGET + 1024, configured, "gemm_tcgen05")) return rc;
     const long long total_tiles = (long long)((n_tok + tn - 1) / tn) * ((n_feat + BLOCK_F - 1) / BLOCK_F) * split_k;
     if (total_tiles > 0x7fffffffLL) return fail("gemm_tcgen05: %lld tiles exceed the index range", total_tiles);
     // a persistent grid: as many CTAs as fit the GPU at once (two per SM when the ring is small and
@@ -892,12 +888,8 @@ int launch_tm(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& 
     if (stages > total_kb) stages = total_kb;
     const size_t smem = (size_t)stages * TM_STAGE_BYTES + 1024;
     auto kernel = gemm_tm_kernel<DUAL, MODE>;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BUDGET + 1024);
-        if (e != cudaSuccess) return fail("gemm_tcgen05: cannot raise dynamic shared memory: %s", cudaGetErrorString(e));
-        configured = true;
-    }
+    static PerDeviceOnce configured;       // per device: the attribute belongs to a device's copy of the kernel
+    if (int rc = raise_dynamic_smem(kernel, SMEM_BUDGET + 1024, configured, "gemm_tcgen05")) return rc;
     constexpr int FEATS = DUAL ? TM_ROWS / 2 : TM_ROWS;
     const long long total_tiles = (long long)((n_tok + TM_TOK - 1) / TM_TOK) * ((n_feat + FEATS - 1) / FEATS);
     if (total_tiles > 0x7fffffffLL) return fail("gemm_tcgen05: %lld tiles exceed the index range", total_tiles);
@@ -955,12 +947,8 @@ int launch_pair(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap
     if (stages > total_kb) stages = total_kb;
     const size_t smem = (size_t)stages * PAIR_STAGE_BYTES + 1024;
     auto kernel = gemm_pair_kernel<DUAL, MODE>;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BUDGET + 1024);
-        if (e != cudaSuccess) return fail("gemm_tcgen05: cannot raise dynamic shared memory: %s", cudaGetErrorString(e));
-        configured = true;
-    }
+    static PerDeviceOnce configured;       // per device: the attribute belongs to a device's copy of the kernel
+    if (int rc = raise_dynamic_smem(kernel, SMEM_BUDGET + 1024, configured, "gemm_tcgen05")) return rc;
     constexpr int FEATS = DUAL ? TM_ROWS / 2 : TM_ROWS;
     const long long total_tiles = (long long)((n_tok + PAIR_TOK - 1) / PAIR_TOK) * ((n_feat + FEATS - 1) / FEATS) * split_k;
     if (total_tiles > 0x7fffffffLL) return fail("gemm_tcgen05: %lld tiles exceed the index range", total_tiles);

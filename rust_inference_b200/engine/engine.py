@@ -187,7 +187,7 @@ class Engine:
             page_size=self.cache.page_size, dtype=self.dtype, device=self.device, workspace=self.workspace,
             host_slots=sc["host"][0], host_starts=sc["host"][1], host_counts=sc["host"][2])
 
-    def step(self, slots: list, tokens: list, wants="last", borrow: bool = False):
+    def step(self, slots: list, tokens: list, wants="last", borrow: bool = False, probe=None):
         """Run one step.
 
         slots[b]   cache slot of sequence b (from `alloc_slot`)
@@ -195,7 +195,10 @@ class Engine:
         wants      "last", "all", "none", or per sequence a list of places among its tokens
         Returns float32 logits [wanted places, vocab] on the device, in the order of the
         sequences and of their places; None if nothing is wanted.  With borrow=True the result
-        may be a buffer that the next step overwrites (the generation loop consumes it at once)."""
+        may be a buffer that the next step overwrites (the generation loop consumes it at once).
+        `probe`: an `engine.model.LayerProbe` that records the hidden state's statistics after every
+        layer for chosen rows of the packed tokens (a debugging aid; the step then runs kernel by
+        kernel, never as a captured graph)."""
         if wants == "last":
             wants = [[len(t) - 1] for t in tokens]
         elif wants == "all":
@@ -204,7 +207,7 @@ class Engine:
             wants = [[] for _ in tokens]
         decode = all(len(t) == 1 for t in tokens) and all(w == [0] for w in wants)
         with torch.cuda.device(self.device):
-            if decode and self.use_graphs:
+            if decode and self.use_graphs and probe is None:
                 # one token per sequence, logits for each: the captured step of this batch size
                 dev, _, _ = self._stage(slots, tokens, wants)
                 logits = self._graph_for(len(slots)).run(dev)      # cleans up after itself if it raises
@@ -213,7 +216,7 @@ class Engine:
             else:
                 ctx = self.make_context(slots, tokens, wants)
                 try:
-                    logits = self.model.forward(ctx, self.cache)
+                    logits = self.model.forward(ctx, self.cache, probe=probe)
                 except Exception:
                     self.workspace.rezero()          # accumulators a failed step may have left dirty
                     raise

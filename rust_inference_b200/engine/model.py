@@ -36,6 +36,32 @@ class _Layer:
             yield self.spec.prefix + getattr(self.spec, role).prefix, part
 
 
+class LayerProbe:
+    """The reference's debug probe (transformer.rs:80-96: min, max, mean and the first four values
+    of the hidden vector after every layer and after the final norm, at position 0) for chosen rows
+    of a step's packed tokens.  `stats[row]` is a list of (label, dict) in the order the layers ran:
+    "L0", "L1", ... (one per schedule entry), then "FNL"."""
+
+    def __init__(self, rows):
+        self.rows = [int(r) for r in rows]
+        self.stats = {r: [] for r in self.rows}
+
+    def record(self, label: str, hidden: torch.Tensor, picked: bool = False) -> None:
+        x = hidden if picked else hidden[self.rows]
+        x = x.float()
+        summary = torch.stack([x.amin(dim=1), x.amax(dim=1), x.sum(dim=1) / x.shape[1]], dim=1).cpu()
+        first = x[:, :4].cpu()
+        for i, r in enumerate(self.rows):
+            self.stats[r].append((label, {"min": float(summary[i, 0]), "max": float(summary[i, 1]),
+                                          "mean": float(summary[i, 2]), "first": [float(v) for v in first[i]]}))
+
+    @staticmethod
+    def format(label: str, s: dict) -> str:
+        """One line in the reference's layout (transformer.rs:84-85)."""
+        return (f"  [{label}] min={s['min']:9.4f} max={s['max']:9.4f} mean={s['mean']:9.4f} h0..3="
+                + ",".join(f"{v:.4f}" for v in s["first"]))
+
+
 class DecoderModel:
     def __init__(self, spec: ModelSpec, *, dtype: torch.dtype, device):
         if dtype not in (torch.float32, torch.bfloat16):
@@ -127,6 +153,23 @@ class DecoderModel:
         if self.spec.head_name is None:
             self.head = linear.Weight(self.embedding)      # tied: the same storage, no copy
 
+    def state_dict(self) -> dict:
+        """Every tensor of the model under the name the weight file gives it, as the model holds it
+        on the device (matrices in the run dtype, vectors float32): what the parts packed together
+        (q, k and v in one matrix) comes back apart, as views.  A tied head is not listed: it is the
+        embedding.  The reference has no counterpart (it only reads, model.rs:157-203)."""
+        out = {self.spec.embedding_name: self.embedding}
+        for prefix, part in self._named_parts():
+            for local, t in part.get_tensors().items():
+                out[prefix + local] = t
+        if self.spec.head_name is not None:
+            out[self.spec.head_name] = self.head.t
+        declared = self.declared_tensors()
+        if set(out) != set(declared):
+            raise RuntimeError("state_dict: the parts returned other tensors than they declared: "
+                               f"{sorted(set(out) ^ set(declared))}")
+        return {name: out[name] for name in declared}
+
     def graph_safe(self) -> bool:
         """True if every part can run inside a captured CUDA graph."""
         return all(getattr(part, "graph_safe", True) for _, part in self._named_parts())
@@ -154,14 +197,22 @@ class DecoderModel:
         return total
 
     # ---- the step --------------------------------------------------------------
-    def forward(self, ctx, cache, logits_out: torch.Tensor | None = None):
+    def forward(self, ctx, cache, logits_out: torch.Tensor | None = None, probe: "LayerProbe | None" = None):
         """Run the step's tokens through the scheduled layers; returns float32 logits
-        [wanted rows, vocab] (None when nothing is wanted)."""
+        [wanted rows, vocab] (None when nothing is wanted).  `probe` (a debugging aid, never
+        inside a captured step) records statistics of the hidden state after every layer."""
         h = self.spec.hidden_size
         residual = ctx.buffer("residual", (ctx.n_tokens, h), torch.float32)
         ops.embed_gather(self.embedding, ctx.token_ids, residual)
-        for layer, cache_index, writes in self.schedule:
+        for run, (layer, cache_index, writes) in enumerate(self.schedule):
             self.layers[layer].block.forward(residual, ctx, cache.layer(cache_index), writes)
+            if probe is not None:
+                probe.record(f"L{run}", residual)
+        if probe is not None:
+            rows = torch.tensor(probe.rows, dtype=torch.int32, device=self.device)
+            normed = torch.empty((len(probe.rows), h), dtype=self.dtype, device=self.device)
+            self.final_norm.forward(residual, normed, rows=rows)
+            probe.record("FNL", normed, picked=True)
         if ctx.n_logit_rows == 0:
             return None
         normed = ctx.buffer("head_in", (ctx.n_logit_rows, h), self.dtype)

@@ -57,6 +57,16 @@ class GQAttention(Mixer):
                 [tensors["q_proj.bias"], tensors["k_proj.bias"], tensors["v_proj.bias"]], dim=0).contiguous()
         self.w_o = linear.Weight(tensors["o_proj.weight"])
 
+    def get_tensors(self):
+        q, kv = self.q_dim, self.kv_dim
+        w = self.w_qkv.t
+        out = {"q_proj.weight": w[:q], "k_proj.weight": w[q:q + kv], "v_proj.weight": w[q + kv:],
+               "o_proj.weight": self.w_o.t}
+        if self.qkv_bias:
+            b = self.b_qkv
+            out.update({"q_proj.bias": b[:q], "k_proj.bias": b[q:q + kv], "v_proj.bias": b[q + kv:]})
+        return out
+
     def prepare(self, max_positions):
         self.position.prepare(max_positions)
 

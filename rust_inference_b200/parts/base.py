@@ -37,6 +37,14 @@ class Part:
         if tensors:
             raise NotImplementedError
 
+    def get_tensors(self) -> dict:
+        """The inverse of `set_tensors`: local tensor name -> tensor as it was received (views into
+        whatever the part packed them into), for `DecoderModel.state_dict()`.  A part without
+        tensors has nothing to return; one with tensors must say how to take its packing apart."""
+        if self.tensor_specs():
+            raise NotImplementedError(f"{type(self).__name__} does not un-pack its tensors (get_tensors)")
+        return {}
+
     def prepare(self, max_positions: int) -> None:
         """Called once the largest position is known (tables and the like)."""
 

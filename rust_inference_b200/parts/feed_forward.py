@@ -29,6 +29,9 @@ class SwiGLU(FeedForward):
         self.w_up = linear.Weight(tensors["up_proj.weight"])
         self.w_down = linear.Weight(tensors["down_proj.weight"])
 
+    def get_tensors(self):
+        return {"gate_proj.weight": self.w_gate.t, "up_proj.weight": self.w_up.t, "down_proj.weight": self.w_down.t}
+
     def forward(self, x, residual, ctx):
         act = ctx.buffer("ffn_act", (x.shape[0], self.intermediate_size), self.dtype)
         # gate and up in one pass over x, SiLU-gate in the epilogue (mlp.rs:35-43)

@@ -25,5 +25,8 @@ class RMSNorm(Norm):
     def set_tensors(self, tensors):
         self.weight = tensors["weight"]
 
+    def get_tensors(self):
+        return {"weight": self.weight}
+
     def forward(self, x, out, rows=None):
         return ops.rmsnorm(x, self.weight, self.eps, out, rows)

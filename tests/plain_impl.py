@@ -191,13 +191,23 @@ def resolve_config(cfg: dict) -> dict:
     return c
 
 
-def forward(weights: dict, cfg: dict, tokens, schedule=None, dtype=torch.float32) -> torch.Tensor:
+def row_stats(row: torch.Tensor) -> dict:
+    """min, max, mean and the first four values of one hidden vector, as the reference's debug
+    probe prints them for position 0 (transformer.rs:80-86, :90-96)."""
+    return {"min": float(row.min()), "max": float(row.max()), "mean": float(row.sum() / row.numel()),
+            "first": [float(v) for v in row[:4]]}
+
+
+def forward(weights: dict, cfg: dict, tokens, schedule=None, dtype=torch.float32, stats=None,
+            stats_position: int = 0) -> torch.Tensor:
     """Logits [n, vocab] at every position of one sequence (transformer.rs:63-98):
     embedding row, the layers in order, final RMSNorm, lm_head (the embedding matrix
     when tied, model.rs:221-226).
 
     `schedule` is the list of layers to run, as (weights_layer, reads_cache_of) pairs;
-    the default is each layer once, in order, with its own keys and values."""
+    the default is each layer once, in order, with its own keys and values.
+    `stats`: a list that receives (label, row_stats) of the hidden vector at `stats_position`
+    after every layer ("L0", "L1", ...) and after the final norm ("FNL")."""
     c = resolve_config(cfg)
     p = {k: v.to(dtype) for k, v in weights.items()}
     n = len(tokens)
@@ -212,7 +222,11 @@ def forward(weights: dict, cfg: dict, tokens, schedule=None, dtype=torch.float32
         kv_from = produced[reads] if reads is not None else None
         h, kv = block(h, p, layer, c, cos, sin, kv_from=kv_from)
         produced[run_idx] = kv
+        if stats is not None:
+            stats.append((f"L{run_idx}", row_stats(h[stats_position])))
     h = rmsnorm(h, p["model.norm.weight"], c["rms_norm_eps"])
+    if stats is not None:
+        stats.append(("FNL", row_stats(h[stats_position])))
     head = p["model.embed_tokens.weight"] if c["tie_word_embeddings"] else p["lm_head.weight"]
     return linear(h, head)
 

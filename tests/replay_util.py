@@ -130,4 +130,6 @@ def worst_error(trace: Trace, outputs: dict, plain: dict) -> tuple:
             err = float((got[i] - want).abs().max() / want.abs().max())
             if not err <= worst[0]:
                 worst = (err, step, rid, pos)
+    from conftest import note_error
+    note_error(worst[0])
     return worst

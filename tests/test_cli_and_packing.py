@@ -116,3 +116,22 @@ def test_bench_contract_without_a_gpu():
         text = json.load(f)["configs"][2]
     for number in ("28 layers", "hidden 3584", "28 heads", "4 kv heads", "head_dim 128", "18944", "152064"):
         assert number in text
+
+
+def test_flags_of_the_random_weights_mode(tmp_path):
+    cfg = tmp_path / "config.json"
+    cfg.write_text("{}")
+    a = parse_args(["--random-config", str(cfg), "--weights-seed", "7", "--random-prompts", "3:5:9", "--slots", "2",
+                    "--print-logits-topk", "4", "--dump-layer-stats"])
+    assert a["random_config"] == str(cfg) and a["weights_seed"] == 7 and a["random_prompts"] == (3, 5, 9)
+    assert a["slots"] == 2 and a["logits_topk"] == 4 and a["layer_stats"] and a["model"] is None
+    for argv, word in [
+        (["--random-config", str(cfg)], "--prompt is required"),
+        (["--random-config", str(cfg), "--model", str(tmp_path), "--prompt", "1"], "exclude each other"),
+        (["--random-config", str(tmp_path / "none.json"), "--prompt", "1"], "not found"),
+        (["--model", str(tmp_path), "--random-prompts", "3:9:5"], "Invalid --random-prompts"),
+        (["--model", str(tmp_path), "--random-prompts", "x"], "Invalid --random-prompts"),
+        (["--model", str(tmp_path), "--prompt", "1", "--slots", "0"], "Invalid --slots"),
+    ]:
+        with pytest.raises(CliError, match=word):
+            parse_args(argv)

@@ -260,3 +260,73 @@ def test_the_order_of_layers_is_data(dtype, model_factory):
         head = eng.step([slot], [toks[:50]], "all").cpu()
         tail = torch.cat([eng.step([slot], [[t]], "last").cpu() for t in toks[50:]])
         assert rel_err(torch.cat([head, tail]), want) <= TOL[dtype], label
+
+
+def test_a_failed_decode_step_leaves_no_dirty_accumulator(model_factory, monkeypatch):
+    """A bf16 decode step of a model this wide adds the pieces of its K-split q/k/v projection onto a
+    float32 accumulator that the rotary kernel consumes and zeroes again.  If a step fails between the
+    two, the accumulator must not keep the leftovers: the failure is injected on the host (the rotary
+    kernel's Python face raises before it launches), in each phase of a batch size's life: on the
+    engine's shared scratch, on the size's own scratch, during the capture, and in a replayed graph's
+    neighbour (an eager prefill step)."""
+    from rust_inference_b200.kernels import ops, tcgen05
+    model = model_factory("E", std=0.05)
+    eng = _engine(model, "bfloat16")
+    assert tcgen05.plan(1, 8 * 64 + 2 * 2 * 64, 512, ops.EPI_RESIDUAL)[1] > 1     # the projection is split over K
+    toks = random_tokens(60, model.cfg["vocab_size"], seed=8)
+    want = model.plain_logits(toks)
+    s = eng.alloc_slot()
+    eng.step([s], [toks[:40]], "none")
+    real = ops.rope_cache_write_acc
+    state = {"fail": False, "calls": 0}
+
+    def flaky(*a, **k):
+        state["calls"] += 1
+        if state["fail"]:
+            raise RuntimeError("injected")
+        return real(*a, **k)
+
+    monkeypatch.setattr(ops, "rope_cache_write_acc", flaky)
+    pos = 40
+    # decode steps of this batch size, in order: the 1st and 2nd run on the engine's shared scratch, the
+    # 3rd on the size's own, the 4th is captured; after an abandoned capture the next step captures again
+    for nth, outcome in enumerate(["fail", "ok", "fail", "fail", "ok", "ok", "ok"], start=1):
+        if outcome == "fail":
+            state["fail"] = True
+            with pytest.raises(RuntimeError, match="injected"):
+                eng.step([s], [[toks[pos]]], "last")
+            state["fail"] = False
+            assert eng.cache.length(s) == pos                  # the failed step did not count
+            assert eng._graphs[1].graph is None
+            continue
+        got = eng.step([s], [[toks[pos]]], "last")[0]
+        assert rel_err(got, want[pos]) <= TOL["bfloat16"], nth
+        pos += 1
+    assert eng._graphs[1].graph is not None                    # the size did get its graph in the end
+    assert state["calls"] > 0                                  # the path under test did run
+    # an eager step of several tokens that fails, then the same step again
+    state["fail"] = True
+    with pytest.raises(RuntimeError, match="injected"):
+        eng.step([s], [toks[pos:pos + 5]], "all")
+    state["fail"] = False
+    got = eng.step([s], [toks[pos:pos + 5]], "all")
+    assert rel_err(got, want[pos:pos + 5]) <= TOL["bfloat16"]
+    eng.check_device_status()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_random_model_saved_and_loaded_again(dtype, tmp_path):
+    """`Model.random` makes its weights on the device; `state_dict()` hands them to the plain
+    implementation without a folder, and `save_safetensors` writes a folder that loads to the same logits."""
+    from conftest import TINY
+    from rust_inference_b200 import Model, config_from_dict
+    cfg = config_from_dict(TINY["B"])
+    m = Model.random(cfg, seed=12, std=0.08, norm_std=0.2, dtype=dtype, max_tokens_in_cache=512)
+    toks = random_tokens(40, cfg.vocab_size, seed=1)
+    weights = {n: t.float().cpu() for n, t in m.state_dict().items()}
+    want = plain_impl.forward(weights, cfg.to_dict(), toks)
+    got = m.logits(toks)
+    assert rel_err(got, want) <= TOL[dtype]
+    folder = m.save_safetensors(str(tmp_path / "saved"))
+    again = Model.load(folder, dtype=dtype, max_tokens_in_cache=512).logits(toks)
+    assert rel_err(again, got) <= (1e-6 if dtype == "float32" else 2e-2)

@@ -278,3 +278,18 @@ def test_sharded_folder(tmp_path):
     json.dump({"weight_map": weight_map}, open(os.path.join(folder, "model.safetensors.index.json"), "w"))
     got = dict(read_model_tensors(folder, declared_tensors(spec)))
     assert all(torch.equal(got[n], tensors[n]) for n in names)
+
+
+def test_state_dict_takes_the_packing_apart():
+    """The model keeps q, k and v in one matrix; `state_dict()` gives every tensor back under the weight
+    file's name with the values it was loaded with (8 tensors per layer without biases, 11 with)."""
+    from rust_inference_b200.engine.model import DecoderModel
+    for name in ("A", "B"):
+        cfg, spec = _spec(name)
+        model = DecoderModel(spec, dtype=torch.float32, device="cpu")
+        src = dict(random_tensors(model.declared_tensors(), 5, matrix_dtype=torch.float32, norm_std=0.2))
+        model.load(src.items())
+        sd = model.state_dict()
+        assert list(sd) == list(src)
+        assert all(torch.equal(sd[k], src[k]) for k in src)
+        assert ("lm_head.weight" in sd) == (not cfg.tie_word_embeddings)
