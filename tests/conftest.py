@@ -62,7 +62,10 @@ TINY = {
 }
 
 # bf16 runs are compared with the plain float32 implementation holding the same bf16 weights:
-# what differs is the rounding of activations, the cache and the outputs.
+# what differs is the rounding of activations, the cache and the outputs.  Observed on a B200 over all
+# tests of the tiny models (2-3 layers): float32 at most 1.1e-5 (typically 1e-6); bfloat16 0.4e-2 to
+# 1.7e-2, and 2.8e-2 for the head_dim-24 model drawn with std 0.1.  Rounding noise grows with depth (see
+# tests/test_full_depth_gpu.py, which takes its bfloat16 bound from the plain implementation itself).
 TOL = {"float32": 1e-4, "bfloat16": 4e-2}
 
 

@@ -100,9 +100,17 @@ def softmax_rows(s: torch.Tensor) -> torch.Tensor:
     return e * (1.0 / e.sum(dim=-1, keepdim=True))
 
 
+def stored(x: torch.Tensor, store_dtype) -> torch.Tensor:
+    """x as it reads back after being kept in `store_dtype` (None: unchanged).  The arithmetic of
+    this file is float32 throughout, as the reference's is; this only restates what keeping
+    activations and the cache in bfloat16 between two operations does to the numbers, so that a
+    test can tell how much of a bfloat16 run's distance from float32 is storage rounding."""
+    return x if store_dtype is None else x.to(store_dtype).to(x.dtype)
+
+
 def attention(x: torch.Tensor, p: dict, prefix: str, *, n_heads: int, n_kv_heads: int,
               head_dim: int, cos: torch.Tensor, sin: torch.Tensor, rope_style: str,
-              window: int | None = None, kv_from: tuple | None = None):
+              window: int | None = None, kv_from: tuple | None = None, store_dtype=None):
     """Grouped-query attention over one whole sequence (attention.rs:54-124).
 
     q = Wq x + bq, k = Wk x + bk, v = Wv x + bv (:66-76); rope on every q head and
@@ -125,10 +133,12 @@ def attention(x: torch.Tensor, p: dict, prefix: str, *, n_heads: int, n_kv_heads
         v = v.view(n, n_kv_heads, head_dim)
         k = torch.stack([rope_apply(k[:, h], cos[:n], sin[:n], rope_style)
                          for h in range(n_kv_heads)], dim=1)
+        k, v = stored(k, store_dtype), stored(v, store_dtype)          # the cache
     else:
         k, v = kv_from
     q = torch.stack([rope_apply(q[:, h], cos[:n], sin[:n], rope_style)
                      for h in range(n_heads)], dim=1)
+    q = stored(q, store_dtype)
     n_rep = n_heads // n_kv_heads
     scale = 1.0 / math.sqrt(float(head_dim))
     out = torch.zeros(n, n_heads, head_dim, dtype=x.dtype, device=x.device)
@@ -140,7 +150,8 @@ def attention(x: torch.Tensor, p: dict, prefix: str, *, n_heads: int, n_kv_heads
         kvh = h // n_rep
         s = (q[:, h] @ k[:, kvh].t()) * scale
         s = s.masked_fill(~visible, float("-inf"))
-        out[:, h] = softmax_rows(s) @ v[:, kvh]
+        out[:, h] = stored(softmax_rows(s), store_dtype) @ v[:, kvh]
+    out = stored(out, store_dtype)
     y = linear(out.reshape(n, n_heads * head_dim), p[prefix + "o_proj.weight"])
     return y, (k, v)
 
@@ -153,25 +164,26 @@ def silu(x: torch.Tensor) -> torch.Tensor:
     return torch.where(x >= 0, pos, neg)
 
 
-def swiglu(x: torch.Tensor, p: dict, prefix: str) -> torch.Tensor:
+def swiglu(x: torch.Tensor, p: dict, prefix: str, store_dtype=None) -> torch.Tensor:
     """down( silu(gate x) * (up x) ), no biases   (mlp.rs:31-46)."""
     g = silu(linear(x, p[prefix + "gate_proj.weight"]))
     u = linear(x, p[prefix + "up_proj.weight"])
-    return linear(g * u, p[prefix + "down_proj.weight"])
+    return linear(stored(g * u, store_dtype), p[prefix + "down_proj.weight"])
 
 
-def block(x: torch.Tensor, p: dict, layer: int, cfg: dict, cos, sin, kv_from=None):
-    """x + attn(norm(x)), then + mlp(norm(.))   (transformer.rs:20-48)."""
+def block(x: torch.Tensor, p: dict, layer: int, cfg: dict, cos, sin, kv_from=None, store_dtype=None):
+    """x + attn(norm(x)), then + mlp(norm(.))   (transformer.rs:20-48).  The residual stream stays
+    float32 whatever `store_dtype` is."""
     pre = f"model.layers.{layer}."
     eps = cfg["rms_norm_eps"]
-    xn = rmsnorm(x, p[pre + "input_layernorm.weight"], eps)
+    xn = stored(rmsnorm(x, p[pre + "input_layernorm.weight"], eps), store_dtype)
     a, kv = attention(xn, p, pre + "self_attn.", n_heads=cfg["num_attention_heads"],
                       n_kv_heads=cfg["num_key_value_heads"], head_dim=cfg["head_dim"],
                       cos=cos, sin=sin, rope_style=cfg.get("rope_style", "half"),
-                      kv_from=kv_from)
+                      kv_from=kv_from, store_dtype=store_dtype)
     h1 = x + a
-    xn2 = rmsnorm(h1, p[pre + "post_attention_layernorm.weight"], eps)
-    return h1 + swiglu(xn2, p, pre + "mlp."), kv
+    xn2 = stored(rmsnorm(h1, p[pre + "post_attention_layernorm.weight"], eps), store_dtype)
+    return h1 + swiglu(xn2, p, pre + "mlp.", store_dtype), kv
 
 
 # ----------------------------------------------------------------------------
@@ -199,7 +211,7 @@ def row_stats(row: torch.Tensor) -> dict:
 
 
 def forward(weights: dict, cfg: dict, tokens, schedule=None, dtype=torch.float32, stats=None,
-            stats_position: int = 0) -> torch.Tensor:
+            stats_position: int = 0, store_dtype=None) -> torch.Tensor:
     """Logits [n, vocab] at every position of one sequence (transformer.rs:63-98):
     embedding row, the layers in order, final RMSNorm, lm_head (the embedding matrix
     when tied, model.rs:221-226).
@@ -207,7 +219,9 @@ def forward(weights: dict, cfg: dict, tokens, schedule=None, dtype=torch.float32
     `schedule` is the list of layers to run, as (weights_layer, reads_cache_of) pairs;
     the default is each layer once, in order, with its own keys and values.
     `stats`: a list that receives (label, row_stats) of the hidden vector at `stats_position`
-    after every layer ("L0", "L1", ...) and after the final norm ("FNL")."""
+    after every layer ("L0", "L1", ...) and after the final norm ("FNL").
+    `store_dtype`: keep what passes from one operation to the next (normalised input, rotated q and
+    k, v, probabilities, attention output, gated activation) in this dtype, see `stored`."""
     c = resolve_config(cfg)
     p = {k: v.to(dtype) for k, v in weights.items()}
     n = len(tokens)
@@ -220,11 +234,11 @@ def forward(weights: dict, cfg: dict, tokens, schedule=None, dtype=torch.float32
     produced = {}
     for run_idx, (layer, reads) in enumerate(schedule):
         kv_from = produced[reads] if reads is not None else None
-        h, kv = block(h, p, layer, c, cos, sin, kv_from=kv_from)
+        h, kv = block(h, p, layer, c, cos, sin, kv_from=kv_from, store_dtype=store_dtype)
         produced[run_idx] = kv
         if stats is not None:
             stats.append((f"L{run_idx}", row_stats(h[stats_position])))
-    h = rmsnorm(h, p["model.norm.weight"], c["rms_norm_eps"])
+    h = stored(rmsnorm(h, p["model.norm.weight"], c["rms_norm_eps"]), store_dtype)
     if stats is not None:
         stats.append(("FNL", row_stats(h[stats_position])))
     head = p["model.embed_tokens.weight"] if c["tie_word_embeddings"] else p["lm_head.weight"]

@@ -133,3 +133,15 @@ def worst_error(trace: Trace, outputs: dict, plain: dict) -> tuple:
     from conftest import note_error
     note_error(worst[0])
     return worst
+
+
+def top_k_disagreements(trace: Trace, outputs: dict, plain: dict, k: int, tol: float) -> list:
+    """Rows whose k largest logits are not the plain implementation's, among the rows where the plain
+    order is decided by more than the tolerance could move it: [(step, request id, position)]."""
+    from conftest import top_k_agrees
+    bad = []
+    for step, rows in trace.expect.items():
+        for i, (rid, pos) in enumerate(rows):
+            if not top_k_agrees(outputs[step][i], plain[rid][pos], k, tol):
+                bad.append((step, rid, pos))
+    return bad

@@ -45,9 +45,14 @@ def full_model():
     torch.backends.cuda.matmul.allow_tf32 = False               # the oracle computes in true float32
     try:
         want = [plain_impl.forward(weights, SIZES, r).cpu() for r in reqs]
+        # the same float32 arithmetic with everything that passes between two operations kept in
+        # bfloat16: how far storage rounding alone moves the logits at this depth
+        rounded = [plain_impl.forward(weights, SIZES, r, store_dtype=torch.bfloat16).cpu() for r in reqs]
     finally:
         torch.backends.cuda.matmul.allow_tf32 = old
-    yield spec, weights, reqs, want
+    storage_error = max(rel_err(a, b) for a, b in zip(rounded, want))
+    del rounded
+    yield spec, weights, reqs, want, storage_error
     weights.clear()
     torch.cuda.empty_cache()
 
@@ -56,11 +61,16 @@ def full_model():
 def test_twenty_eight_layers_in_every_cutting(dtype, full_model):
     from rust_inference_b200.engine.engine import Engine
     from rust_inference_b200.engine.model import DecoderModel
-    spec, weights, reqs, want = full_model
+    spec, weights, reqs, want, storage_error = full_model
     model = DecoderModel(spec, dtype=torch.float32 if dtype == "float32" else torch.bfloat16, device="cuda")
     model.load(weights.items())
     eng = Engine(model, max_tokens=4096)
-    tol = TOL[dtype]
+    # float32: the library's bound.  bfloat16: rounding noise adds up over the layers (it grows with the
+    # square root of the depth: 0.011 at one layer of these sizes, 0.048 at 28), so the bound is taken
+    # from the plain implementation itself: one and a half times what bfloat16 storage alone costs it
+    # on these very requests.  A kernel fault shows as a multiple of that, and in float32 at 1e-4.
+    tol = TOL[dtype] if dtype == "float32" else 1.5 * storage_error
+    assert 0.02 < storage_error < 0.08
     observed = {}
 
     def check(got, w, what):
@@ -122,5 +132,6 @@ def test_twenty_eight_layers_in_every_cutting(dtype, full_model):
         check(out[2:3], want[2][33 + step:34 + step], "both batches, decode")
     eng.check_device_status()
     eng.cache.pager.audit()
-    print(f"\nobserved worst relative errors, 28 layers, {dtype}: "
+    print(f"\nbound {tol:.2e} (bfloat16 storage alone moves the plain logits by {storage_error:.2e}); "
+          f"observed worst relative errors, 28 layers, {dtype}: "
           + ", ".join(f"{k}: {v:.2e}" for k, v in observed.items()))

@@ -20,6 +20,7 @@ import torch
 
 import plain_impl
 from conftest import oracle_weights, random_tokens, rel_err
+from conftest import rel_err as _rel_err
 
 pytestmark = pytest.mark.gpu
 
@@ -125,8 +126,11 @@ def _register_architecture():
     register_architecture("ToyMixedLM", lambda d: d, build, replace=True)
 
 
-def _plain_logits(w: dict, tokens, dtype=torch.float32):
-    """The same stack from the plain implementation's parts, one whole sequence."""
+def _plain_logits(w: dict, tokens, dtype=torch.float32, margins: list | None = None):
+    """The same stack from the plain implementation's parts, one whole sequence.  `margins` receives,
+    per position, how far the routed layer's best expert leads the second best (difference of their
+    router logits over the largest |logit|): a choice that hangs on less than bfloat16's rounding of
+    the router's input is no test of a bfloat16 run."""
     p = {k: v.to(dtype) for k, v in w.items()}
     n = len(tokens)
     h = plain_impl.embedding(p["model.embed_tokens.weight"], tokens)
@@ -143,7 +147,11 @@ def _plain_logits(w: dict, tokens, dtype=torch.float32):
         h = h + a
         xn = plain_impl.rmsnorm(h, p[pre + "post_attention_layernorm.weight"], L["eps"])
         if "experts" in L:
-            probs = plain_impl.softmax_rows(plain_impl.linear(xn.float(), w[pre + "moe.router.weight"].float().to(h.device)))
+            router_logits = plain_impl.linear(xn.float(), w[pre + "moe.router.weight"].float().to(h.device))
+            probs = plain_impl.softmax_rows(router_logits)
+            if margins is not None:
+                top = router_logits.topk(2, dim=-1).values
+                margins.extend(((top[:, 0] - top[:, 1]) / router_logits.abs().amax(dim=-1)).tolist())
             out = torch.zeros_like(h)
             for t in range(n):
                 e = plain_impl.argmax_first(probs[t])
@@ -194,7 +202,22 @@ def test_layers_that_differ_in_one_model(dtype, mixed_model):
 
     tol = 1e-4 if dtype == "float32" else 4e-2
     toks = random_tokens(100, VOCAB, seed=11)
-    want = _plain_logits(weights, toks)
+
+    def plain(tokens):
+        """(logits, rows to compare): in bfloat16 only the positions whose expert is chosen by a clear
+        margin; no layer after the routed one mixes positions, so the others do not disturb them."""
+        margins = []
+        logits = _plain_logits(weights, tokens, margins=margins)
+        decided = torch.tensor(margins) > 0.05 if dtype == "bfloat16" else torch.ones(len(tokens), dtype=torch.bool)
+        assert decided.float().mean() > 0.7
+        return logits, decided
+
+    def rel_err(got, pair, upto=None, start=0):
+        logits, decided = pair
+        rows = decided[start:upto]
+        return _rel_err(got[rows], logits[start:upto][rows])
+
+    want = plain(toks)
     # whole, then the last 32 one by one
     s = eng.alloc_slot()
     whole = eng.step([s], [toks], "all").cpu()
@@ -212,7 +235,7 @@ def test_layers_that_differ_in_one_model(dtype, mixed_model):
         unwindowed = _plain_logits(weights, toks)
     finally:
         LAYERS[1]["window"] = saved
-    assert rel_err(unwindowed[60:], want[60:]) > 10 * tol
+    assert _rel_err(unwindowed[60:], want[0][60:]) > 10 * tol
 
     # a batch of unequal lengths; the shortest ends first and its slot is used again
     others = [random_tokens(n, VOCAB, seed=20 + n) for n in (9, 37)]
@@ -233,11 +256,11 @@ def test_layers_that_differ_in_one_model(dtype, mixed_model):
             again = eng.alloc_slot()
             assert again == slots[1]
             fresh = eng.step([again], [toks[:30]], "all").cpu()
-            assert rel_err(fresh, want[:30]) <= tol
+            assert rel_err(fresh, want, upto=30) <= tol
             eng.free_slot(again)
-    assert rel_err(torch.cat(rows[0]), want[:50]) <= tol
-    assert rel_err(torch.cat(rows[2]), _plain_logits(weights, others[1])) <= tol
-    assert rel_err(torch.cat(rows[1]), _plain_logits(weights, others[0])[:len(others[0]) - 2]) <= tol
+    assert rel_err(torch.cat(rows[0]), want, upto=50) <= tol
+    assert rel_err(torch.cat(rows[2]), plain(others[1])) <= tol
+    assert rel_err(torch.cat(rows[1]), plain(others[0]), upto=len(others[0]) - 2) <= tol
     eng.check_device_status()
 
 

@@ -177,3 +177,15 @@ def test_the_scalar_program_reproduces_its_stored_logits(tmp_path):
     again = make_golden.run_scalar(binary, cfg, w, meta["tokens"], str(tmp_path))
     want = np.fromfile(os.path.join(golden, "A.logits.f32"), dtype=np.float32).reshape(meta["shape"])
     assert np.abs(again - want).max() <= 1e-6 * np.abs(want).max()
+
+
+def test_storage_rounding_is_an_option_and_off_by_default(tmp_path):
+    """`store_dtype` restates what keeping activations in bfloat16 between operations costs; without it
+    nothing is rounded, and with float32 it is the identity."""
+    m = make_model(tmp_path, "B", std=0.08)
+    toks = list(range(3, 40))
+    plain = plain_impl.forward(m.weights, m.cfg, toks)
+    assert torch.equal(plain_impl.forward(m.weights, m.cfg, toks, store_dtype=torch.float32), plain)
+    rounded = plain_impl.forward(m.weights, m.cfg, toks, store_dtype=torch.bfloat16)
+    err = ((rounded - plain).abs().amax(dim=1) / plain.abs().amax(dim=1)).max().item()
+    assert 1e-4 < err < 3e-2, err

@@ -5,7 +5,7 @@ import pytest
 import torch
 
 from conftest import TOL, random_tokens
-from replay_util import batches, last_decoded, run_trace, whole, worst_error
+from replay_util import batches, last_decoded, run_trace, top_k_disagreements, whole, worst_error
 
 pytestmark = pytest.mark.gpu
 
@@ -32,6 +32,7 @@ def test_replay_modes(name, dtype, model_factory, tmp_path):
         err, step, rid, pos = worst_error(trace, out, plain)
         assert err <= TOL[dtype], (f"{name} {dtype} {mode}: rel err {err:.3e} at step {step}, request {rid}, "
                                    f"position {pos} (of {len(reqs[rid]) if rid else '?'})")
+        assert top_k_disagreements(trace, out, plain, 5, TOL[dtype]) == [], f"{name} {dtype} {mode}: top-5"
 
 
 @pytest.mark.parametrize("name", ["C", "D"])
