@@ -9,7 +9,6 @@ from __future__ import annotations
 
 import torch
 
-from ..kernels import linear, ops
 from ..parts.registry import lookup
 from ..parts.spec import ModelSpec, TensorSpec
 
@@ -20,20 +19,33 @@ def _build(category: str, part_spec, *, hidden_size, dtype, device):
 
 
 class _Layer:
+    """The parts of one layer, built for the roles its arrangement declares."""
+
     def __init__(self, layer_spec, *, hidden_size, dtype, device):
         self.spec = layer_spec
+        arrangement = lookup("arrangement", layer_spec.arrangement)
+        roles = dict(arrangement.ROLES)
+        given = set(layer_spec.parts)
+        unknown = sorted(given - set(roles))
+        missing = sorted(set(roles) - given - set(arrangement.OPTIONAL))
+        if unknown or missing:
+            raise ValueError(
+                f"layer {layer_spec.prefix!r}: arrangement {layer_spec.arrangement!r} has the roles {sorted(roles)}"
+                + (f"; missing: {missing}" if missing else "") + (f"; not a role of it: {unknown}" if unknown else ""))
         kw = dict(hidden_size=hidden_size, dtype=dtype, device=device)
-        self.parts = {
-            "mixer": _build("mixer", layer_spec.mixer, **kw),
-            "feed_forward": _build("feed_forward", layer_spec.feed_forward, **kw),
-            "mixer_norm": _build("norm", layer_spec.mixer_norm, **kw),
-            "feed_forward_norm": _build("norm", layer_spec.feed_forward_norm, **kw),
-        }
-        self.block = lookup("arrangement", layer_spec.arrangement)(**self.parts)
+        self.parts = {role: _build(roles[role], layer_spec.parts[role], **kw) for role in roles if role in given}
+        owners = [role for role in self.parts if roles[role] == "mixer"]
+        if len(owners) > 1:
+            raise ValueError(f"layer {layer_spec.prefix!r}: {owners} would share one cache layer; a layer has one mixer")
+        self.cache_owner = self.parts[owners[0]] if owners else None
+        self.block = arrangement(**self.parts)
+
+    def cache_request(self):
+        return self.cache_owner.cache_request() if self.cache_owner is not None else None
 
     def named_parts(self):
         for role, part in self.parts.items():
-            yield self.spec.prefix + getattr(self.spec, role).prefix, part
+            yield self.spec.prefix + self.spec.parts[role].prefix, part
 
 
 class LayerProbe:
@@ -70,10 +82,10 @@ class DecoderModel:
         self.dtype = dtype
         self.device = torch.device(device)
         kw = dict(hidden_size=spec.hidden_size, dtype=dtype, device=device)
+        self._embedding_spec, self._head_spec = spec.embedding_part(), spec.head_part()
+        self.embedding = _build("embedding", self._embedding_spec, **kw)
         self.layers = [_Layer(ls, **kw) for ls in spec.layers]
-        self.final_norm = _build("norm", spec.final_norm, **kw)
-        self.embedding = None
-        self.head = None
+        self.head = _build("head", self._head_spec, **kw)
 
         # the schedule: who writes which cache layer
         seen = set()
@@ -84,7 +96,7 @@ class DecoderModel:
                 raise ValueError(f"schedule names layer {entry.layer}, the model has {len(self.layers)}")
             writes = entry.cache not in seen
             seen.add(entry.cache)
-            request = self.layers[entry.layer].parts["mixer"].cache_request()
+            request = self.layers[entry.layer].cache_request()
             if writes:
                 self._cache_requests[entry.cache] = request
             elif request != self._cache_requests[entry.cache]:
@@ -95,18 +107,18 @@ class DecoderModel:
 
     # ---- tensors -----------------------------------------------------------
     def _named_parts(self):
+        yield self._embedding_spec.prefix, self.embedding
         for layer in self.layers:
             yield from layer.named_parts()
-        yield self.spec.final_norm.prefix, self.final_norm
+        yield self._head_spec.prefix, self.head
 
     def declared_tensors(self) -> dict:
-        v, h = self.spec.vocab_size, self.spec.hidden_size
-        out = {self.spec.embedding_name: TensorSpec((v, h))}
+        out = {}
         for prefix, part in self._named_parts():
             for local, ts in part.tensor_specs().items():
+                if prefix + local in out:
+                    raise ValueError(f"two parts declare the tensor {prefix + local!r}")
                 out[prefix + local] = ts
-        if self.spec.head_name is not None:
-            out[self.spec.head_name] = TensorSpec((v, h))
         return out
 
     def _place(self, t: torch.Tensor, ts: TensorSpec) -> torch.Tensor:
@@ -136,34 +148,30 @@ class DecoderModel:
                 raise ValueError(f"{name}: expected shape {list(ts.shape)}, found {list(t.shape)}")
             placed = self._place(t, ts)
             got.add(name)
-            if name == self.spec.embedding_name:
-                self.embedding = placed
-            elif name == self.spec.head_name:
-                self.head = linear.Weight(placed)
-            else:
-                part, local = owners[name]
-                bucket = pending.setdefault(id(part), (part, {}))[1]
-                bucket[local] = placed
-                if len(bucket) == counts[id(part)]:
-                    part.set_tensors(bucket)
-                    del pending[id(part)]
+            part, local = owners[name]
+            bucket = pending.setdefault(id(part), (part, {}))[1]
+            bucket[local] = placed
+            if len(bucket) == counts[id(part)]:
+                part.set_tensors(bucket)
+                del pending[id(part)]
         missing = sorted(set(declared) - got)
         if missing:
             raise KeyError(f"model is missing tensors: {', '.join(missing)}")
-        if self.spec.head_name is None:
-            self.head = linear.Weight(self.embedding)      # tied: the same storage, no copy
+        if self.head.wants_tie:
+            table = self.embedding.table()
+            if table is None:
+                raise ValueError("the head is tied to the embedding, which has no table to share")
+            self.head.tie(table)                          # the same storage, no copy
 
     def state_dict(self) -> dict:
         """Every tensor of the model under the name the weight file gives it, as the model holds it
         on the device (matrices in the run dtype, vectors float32): what the parts packed together
         (q, k and v in one matrix) comes back apart, as views.  A tied head is not listed: it is the
         embedding.  The reference has no counterpart (it only reads, model.rs:157-203)."""
-        out = {self.spec.embedding_name: self.embedding}
+        out = {}
         for prefix, part in self._named_parts():
             for local, t in part.get_tensors().items():
                 out[prefix + local] = t
-        if self.spec.head_name is not None:
-            out[self.spec.head_name] = self.head.t
         declared = self.declared_tensors()
         if set(out) != set(declared):
             raise RuntimeError("state_dict: the parts returned other tensors than they declared: "
@@ -187,41 +195,37 @@ class DecoderModel:
         is held in (the embedding table only counts when it is also the head, or when asked)."""
         total = 0
         item = 4 if self.dtype == torch.float32 else 2
+        skip = set()
+        if not include_embedding and not self.head.wants_tie:
+            skip = {self._embedding_spec.prefix + local for local in self.embedding.tensor_specs()}
         for name, ts in self.declared_tensors().items():
             n = 1
             for d in ts.shape:
                 n *= d
-            if name == self.spec.embedding_name and not include_embedding and self.spec.head_name is not None:
+            if name in skip:
                 continue
             total += n * (item if ts.role == "matrix" else 4)
         return total
 
     # ---- the step --------------------------------------------------------------
     def forward(self, ctx, cache, logits_out: torch.Tensor | None = None, probe: "LayerProbe | None" = None):
-        """Run the step's tokens through the scheduled layers; returns float32 logits
-        [wanted rows, vocab] (None when nothing is wanted).  `probe` (a debugging aid, never
-        inside a captured step) records statistics of the hidden state after every layer."""
-        h = self.spec.hidden_size
-        residual = ctx.buffer("residual", (ctx.n_tokens, h), torch.float32)
-        ops.embed_gather(self.embedding, ctx.token_ids, residual)
+        """Run the step's tokens: the embedding part fills the float32 hidden stream, the scheduled
+        layers add to it, the head part turns the wanted rows into float32 logits [wanted rows, vocab]
+        (None when nothing is wanted).  `probe` (a debugging aid, never inside a captured step)
+        records statistics of the hidden state after every layer."""
+        residual = ctx.buffer("residual", (ctx.n_tokens, self.spec.hidden_size), torch.float32)
+        self.embedding.forward(ctx, residual)
         for run, (layer, cache_index, writes) in enumerate(self.schedule):
             self.layers[layer].block.forward(residual, ctx, cache.layer(cache_index), writes)
             if probe is not None:
                 probe.record(f"L{run}", residual)
         if probe is not None:
-            rows = torch.tensor(probe.rows, dtype=torch.int32, device=self.device)
-            normed = torch.empty((len(probe.rows), h), dtype=self.dtype, device=self.device)
-            self.final_norm.forward(residual, normed, rows=rows)
-            probe.record("FNL", normed, picked=True)
+            normed = self.head.normalised(residual, torch.tensor(probe.rows, dtype=torch.int32, device=self.device))
+            if normed is not None:
+                probe.record("FNL", normed, picked=True)
         if ctx.n_logit_rows == 0:
             return None
-        normed = ctx.buffer("head_in", (ctx.n_logit_rows, h), self.dtype)
-        self.final_norm.forward(residual, normed, rows=ctx.logit_rows)
-        if logits_out is None:
-            logits_out = torch.empty((ctx.n_logit_rows, self.spec.vocab_size), dtype=torch.float32,
-                                     device=self.device)
-        linear.logits(normed, self.head, logits_out, ctx)
-        return logits_out
+        return self.head.forward(residual, ctx, logits_out)
 
 
 def declared_tensors(spec: ModelSpec) -> dict:

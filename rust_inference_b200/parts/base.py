@@ -82,14 +82,52 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
-class Arrangement:
-    """How a layer's parts are wired.  Built from the already-built parts."""
+class Embedding(Part):
+    """Token ids -> the float32 hidden stream."""
 
-    def __init__(self, *, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, feed_forward_norm: Norm):
-        self.mixer = mixer
-        self.feed_forward = feed_forward
-        self.mixer_norm = mixer_norm
-        self.feed_forward_norm = feed_forward_norm
+    def forward(self, ctx, residual: torch.Tensor) -> None:
+        """Fill residual (float32 [T, hidden]) for the step's tokens (`ctx.token_ids`, `ctx.token_pos`)."""
+        raise NotImplementedError
+
+    def table(self) -> torch.Tensor | None:
+        """The [vocab, hidden] matrix a tied head may share (None: nothing to share)."""
+        return None
+
+
+class Head(Part):
+    """The hidden stream -> float32 logits, on the wanted rows only."""
+
+    wants_tie = False         # True: the head has no matrix of its own and is given the embedding's
+
+    def tie(self, table: torch.Tensor) -> None:
+        raise NotImplementedError
+
+    def forward(self, residual: torch.Tensor, ctx, logits_out: torch.Tensor | None = None) -> torch.Tensor:
+        """float32 [ctx.n_logit_rows, vocab] for the rows `ctx.logit_rows` of the stream."""
+        raise NotImplementedError
+
+    def normalised(self, residual: torch.Tensor, rows: torch.Tensor) -> torch.Tensor | None:
+        """What the head's own norm makes of the given rows, for the layer probe (None: no norm)."""
+        return None
+
+    def matrix_bytes(self) -> int:
+        """Bytes of the projection matrix a step reads (shared or not)."""
+        return 0
+
+
+class Arrangement:
+    """How a layer's parts are wired.  Built from the already-built parts, one per role.
+
+    ROLES maps each role the arrangement has to the category its part is looked up in; a layer spec
+    must give exactly these roles (those in OPTIONAL may be left out and are then None).  At most
+    one role may be of category "mixer": its part owns the layer's cache."""
+
+    ROLES = {"mixer": "mixer", "feed_forward": "feed_forward", "mixer_norm": "norm", "feed_forward_norm": "norm"}
+    OPTIONAL: tuple = ()
+
+    def __init__(self, **parts):
+        for role in self.ROLES:
+            setattr(self, role, parts.get(role))
 
     def forward(self, residual: torch.Tensor, ctx, cache_layer, writes_cache: bool) -> None:
         raise NotImplementedError

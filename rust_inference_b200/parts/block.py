@@ -8,7 +8,9 @@ from .registry import register
 @register("arrangement", "pre_norm")
 class PreNorm(Arrangement):
     """h1 = x + mixer(norm(x)); h2 = h1 + ff(norm(h1)): the un-normalised stream is carried
-    (transformer.rs:31-47)."""
+    (transformer.rs:31-47).  Roles: mixer, feed_forward, mixer_norm, feed_forward_norm."""
+
+    ROLES = {"mixer": "mixer", "feed_forward": "feed_forward", "mixer_norm": "norm", "feed_forward_norm": "norm"}
 
     def forward(self, residual, ctx, cache_layer, writes_cache):
         normed = ctx.buffer("normed", (residual.shape[0], residual.shape[1]), ctx.dtype)

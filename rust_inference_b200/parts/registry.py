@@ -9,12 +9,14 @@ Interfaces (see `parts.base`):
   position encoding PositionEncoding
   mixer             Mixer
   feed-forward      FeedForward
-  arrangement       Arrangement (how norms, mixer, feed-forward and residuals are wired)
+  arrangement       Arrangement (how norms, mixer, feed-forward and residuals are wired; declares its roles)
+  embedding         Embedding (token ids -> hidden stream)
+  head              Head (hidden stream -> logits)
 """
 from __future__ import annotations
 
 _REGISTRIES: dict[str, dict] = {
-    "norm": {}, "position": {}, "mixer": {}, "feed_forward": {}, "arrangement": {},
+    "norm": {}, "position": {}, "mixer": {}, "feed_forward": {}, "arrangement": {}, "embedding": {}, "head": {},
 }
 
 
@@ -50,4 +52,4 @@ def kinds(category: str) -> list[str]:
 
 
 def _ensure_builtin() -> None:
-    from . import norm, rope, attention, feed_forward, block  # noqa: F401
+    from . import norm, rope, attention, feed_forward, block, embedding, head  # noqa: F401
