@@ -11,12 +11,21 @@ in 128..2048, in a cache of 8,192 positions per sequence.  A step is one decode 
   value     decoded tokens per second over K timed decode steps, timed on the device
             (sampling on the device, each token fed to the next step without a host trip)
   e2e       the same through the Python entry point (`Model.generate`): host token ids in,
-            host token ids out, every step with its host-to-device copy of the step's arrays
-            from pinned memory and a device-to-host read of the sampled tokens
+            host token ids out.  Every step's sampled tokens are read by the host (written to
+            pinned memory by the step itself); what a step needs from the host goes up from
+            pinned memory: the prompts, the arrays of a batch whenever its composition changes,
+            new page-table entries.  While the same sequences go on a step's input token and
+            positions are produced on the device, so the measured host-to-device bytes per step
+            are few.  `ms_per_step_median` / `_worst` are taken from the host's clock, token to token.
   prefill   one 2,048-token prompt in one step
   roofline  bytes the decode step must read (every weight once, the cache of the live
             sequences) / step time, against the measured copy bandwidth
-  points    decode tokens per second at batch 1 and batch 64
+  points    decode tokens per second at batch 1 and batch 64 (their contexts and fractions of
+            the copy bandwidth under `points_detail`)
+
+The prompts' prefill runs the GPU into its power cap, and for some tens of milliseconds afterwards
+decode steps take up to a tenth longer.  Every decode measurement therefore runs SETTLE_STEPS untimed
+decode steps after its prefill, then the W warm-up steps, then the K timed ones.
 
 Prints ONE JSON line.  Only one GPU is used: for --gpus > 1 it says so and exits with 2.
 """
@@ -61,6 +70,7 @@ SIZE_NAMES = {"qwen2.5-7b": "Qwen2.5-7B-sized", "llama3-8b": "Llama-3-8B-sized",
 CONTEXT = 8192
 PROMPT_MIN, PROMPT_MAX = 128, 2048
 PREFILL_TOKENS = 2048
+SETTLE_STEPS = 32
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
 
@@ -185,7 +195,7 @@ def main() -> int:
     cfg = config_from_dict(model_cfg)
     n_layers = cfg.num_hidden_layers
 
-    total_steps = warmup + steps + 2
+    total_steps = SETTLE_STEPS + warmup + steps + 2
     biggest = 64 if not args.skip_points else args.batch
     cache_tokens = max(biggest * (-(-(prompt_max + total_steps) // 64) * 64), prefill_tokens + 64) + 4096
     torch.cuda.set_device(0)
@@ -215,7 +225,7 @@ def main() -> int:
         for i in range(0, batch, 8):                       # prompts in groups, to bound scratch memory
             engine.step(slots[i:i + 8], prompts[i:i + 8], "none")
         first = [p[-1] for p in prompts]
-        toks = engine.decode_steps(slots, first, warmup, greedy)
+        toks = engine.decode_steps(slots, first, SETTLE_STEPS + warmup, greedy)
         torch.cuda.synchronize()
         launches0 = ops.launch_count()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -225,37 +235,37 @@ def main() -> int:
         torch.cuda.synchronize()
         engine.check_device_status()
         ms = e0.elapsed_time(e1)
-        graph = engine._graphs[batch]
-        launches = steps * (graph.launches + 1)            # the captured kernels plus the sampler
+        graph = engine.decode_graph(batch, greedy)
+        launches = steps * graph.launches                  # the captured kernels: model, sampler, the move to the next position
         ctx_tokens = sum(engine.cache.length(s) for s in slots) - batch * steps / 2.0
         for s in slots:
             engine.free_slot(s)
+        step_bytes = weight_bytes + ctx_tokens * kv_bytes_per_token
         return {"tok_s": batch * steps / (ms * 1e-3), "ms_per_step": ms / steps, "launches": launches,
-                "mean_ctx_tokens": ctx_tokens}
+                "mean_ctx_tokens": ctx_tokens, "gb_s": step_bytes / (ms / steps * 1e-3) / 1e9}
 
     clocks = ClockSampler()
     clocks.start()
 
     main_run = device_decode(args.batch, seed=1)
-    step_s = main_run["ms_per_step"] * 1e-3
-    step_bytes = weight_bytes + main_run["mean_ctx_tokens"] * kv_bytes_per_token
-    achieved_gbs = step_bytes / step_s / 1e9
+    achieved_gbs = main_run["gb_s"]
 
     # ---- end to end through the Python entry point ----
     prompts = make_prompts(args.batch, seed=1)
-    results = model.generate(prompts, max_tokens=warmup + steps + 1, sampler_config=greedy, stop_ids=(),
+    lead = SETTLE_STEPS + warmup
+    results = model.generate(prompts, max_tokens=lead + steps + 1, sampler_config=greedy, stop_ids=(),
                              record_step_times=True)
     times = model.last_stats["step_times"]
     # times[0] is the prefill step; times[i] the i-th decode step's tokens on the host
-    e2e_s = times[warmup + steps] - times[warmup]
+    e2e_s = times[lead + steps] - times[lead]
     e2e_tok_s = args.batch * steps / e2e_s
-    from rust_inference_b200.engine.context import pack_step
-    step_arrays = pack_step([0] * args.batch, [[0]] * args.batch, [[0]] * args.batch)[0]
-    # every decode step copies its arrays from pinned memory; the sampler's rows (stream, counter) go
-    # up once per batch and stay on the device while the same sequences advance together
-    h2d_per_step = step_arrays.nbytes
-    d2h_per_step = args.batch * 4                               # the sampled tokens, written to pinned host memory by the kernel
-    assert all(len(r.tokens) == warmup + steps + 1 for r in results)
+    gaps = sorted((times[i + 1] - times[i]) * 1e3 for i in range(lead, lead + steps))
+    # what went up from pinned memory during the whole call (prompts, the batch's arrays, new page-table
+    # entries), averaged over its steps; the sampled tokens come down every step, written to pinned host
+    # memory by the step itself
+    h2d_per_step = model.last_stats["h2d_bytes"] / max(1, model.last_stats["steps"])
+    d2h_per_step = args.batch * 4
+    assert all(len(r.tokens) == lead + steps + 1 for r in results)
 
     # ---- prefill of 2,048 tokens ----
     rng = random.Random(7)
@@ -281,11 +291,13 @@ def main() -> int:
     prefill = {"value": t / (pre * 1e-3), "tokens": t, "ms": pre,
                "frac": flops / (pre * 1e-3) / (peaks["bf16_tflops"] * 1e12)}
 
-    points = {}
+    points, points_detail = {}, {}
     if not args.skip_points:
         for b in (1, 64):
             r = device_decode(b, seed=100 + b)
             points[f"decode_b{b}"] = r["tok_s"]
+            points_detail[f"decode_b{b}"] = {"ms_per_step": r["ms_per_step"], "mean_context": round(r["mean_ctx_tokens"] / b, 1),
+                                             "gb_s": r["gb_s"], "frac": r["gb_s"] / peaks["hbm_gbs"]}
     engine.check_device_status()
     clock_info = clocks.stop()
 
@@ -304,14 +316,17 @@ def main() -> int:
             "global_batch": args.batch, "seq_len": seq_len, "prompt_lengths": f"uniform {prompt_min}-{prompt_max}",
             "mean_context": round(main_run["mean_ctx_tokens"] / args.batch, 1), "parallelism": "single GPU",
             "l2": "inputs larger than L2 (weights read once per step)", "peaks": peak_source,
+            "settle_steps": SETTLE_STEPS,
         },
         "e2e": {"value": e2e_tok_s, "unit": "tok/s", "h2d_bytes_per_step": round(h2d_per_step, 1),
-                "d2h_bytes_per_step": d2h_per_step},
+                "d2h_bytes_per_step": d2h_per_step, "ms_per_step_median": gaps[len(gaps) // 2],
+                "ms_per_step_worst": gaps[-1]},
         "gpu_launches": main_run["launches"],
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": achieved_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": achieved_gbs / peaks["hbm_gbs"]},
         "points": points,
+        "points_detail": points_detail,
         "clocks": clock_info,
     }
     print(json.dumps(line))

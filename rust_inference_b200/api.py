@@ -90,11 +90,15 @@ class Model:
         cfg = sampler_config or SamplerConfig()
         if stop_ids is None:
             stop_ids = self.engine.model.spec.stop_ids
-        gen = Generator(self.engine, Sampler(cfg, self.engine.device), stop_ids=stop_ids, max_batch=max_batch)
+        sampler = Sampler(cfg, self.engine.device)
+        gen = Generator(self.engine, sampler, stop_ids=stop_ids, max_batch=max_batch)
         if record_step_times:
             gen.step_times = []
-        h2d0 = self.engine.h2d_bytes
+        h2d0 = self.engine.h2d_bytes + self.engine.cache.h2d_bytes
         results = gen.generate(batch, max_tokens)
-        self.last_stats = {"steps": gen.steps, "h2d_bytes": self.engine.h2d_bytes - h2d0,
+        # everything that went up from pinned host memory: the steps' arrays (prompts among them), new
+        # page-table entries, the sampler's per-row arrays; and the sampled tokens that came down
+        h2d = self.engine.h2d_bytes + self.engine.cache.h2d_bytes - h2d0 + sampler.h2d_bytes
+        self.last_stats = {"steps": gen.steps, "h2d_bytes": h2d,
                            "d2h_bytes": gen.d2h_bytes, "step_times": gen.step_times}
         return results[0] if single else results

@@ -80,6 +80,7 @@ class SequenceCache:
         self._stage_bufs = [None] * 4
         self._stage_events = [None] * 4
         self._stage_turn = 0
+        self.h2d_bytes = 0             # bytes of page-table entries copied to the device so far
 
         # group layers by their needs
         self.groups: dict = {}
@@ -146,6 +147,7 @@ class SequenceCache:
         if not added:
             return
         total = sum(len(p) for p in added.values())
+        self.h2d_bytes += 4 * total
         if self.device.type != "cuda":
             for slot, pages in added.items():
                 have = self.pager.page_count(slot)

@@ -525,6 +525,50 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
     out[idx] = from_f32<T>(silu_f32(to_f32<T>(row[i])) * to_f32<T>(row[inter + i]));
 }
 
+// ---------------------------------------------------------------------------------------
+// The end of a decode step of n sequences (one token each): every sequence is one position
+// longer, so the step's int32 arrays move on by one and the next step of the same sequences
+// needs nothing from the host.  token_pos, seq_start and seq_len each grow by 1; token_ids
+// already hold what the sampler drew.  Optionally (null pointers switch a part off): the
+// sampler's per-row draw counters grow by 1; the drawn tokens are copied into slot
+// (*turn % host_slots) of a ring in pinned host memory and into slot (*turn % log_slots) of a
+// ring on the device; then *turn grows by 1.  One thread block; it runs last in the step.
+// ---------------------------------------------------------------------------------------
+__global__ void advance_decode_kernel(int* __restrict__ token_pos, int* __restrict__ seq_start,
+                                      int* __restrict__ seq_len, int n, const int* __restrict__ token_ids,
+                                      int* __restrict__ draw_counter, int* __restrict__ turn,
+                                      int* __restrict__ host_ring, int host_slots, int* __restrict__ log_ring,
+                                      int log_slots) {
+    let_next_kernel_start();
+    wait_for_previous_kernels();          // every kernel of the step has read the arrays; the sampler has written the tokens
+    const int t = turn ? *turn : 0;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        token_pos[i] += 1;
+        seq_start[i] += 1;
+        seq_len[i] += 1;
+        if (draw_counter) draw_counter[i] += 1;
+        if (host_ring || log_ring) {
+            const int tok = token_ids[i];
+            if (host_ring) host_ring[(size_t)(t % host_slots) * n + i] = tok;
+            if (log_ring) log_ring[(size_t)(t % log_slots) * n + i] = tok;
+        }
+    }
+    if (host_ring) __threadfence_system();
+    __syncthreads();                      // everyone has read *turn
+    if (threadIdx.x == 0 && turn) *turn = t + 1;
+}
+
+RI_API int ri_advance_decode(int* token_pos, int* seq_start, int* seq_len, int n, const int* token_ids,
+                             int* draw_counter, int* turn, int* host_ring, int host_slots, int* log_ring,
+                             int log_slots, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if ((host_ring && host_slots < 1) || (log_ring && log_slots < 1)) return fail("advance_decode: a ring needs at least one slot");
+    if ((host_ring || log_ring) && (!turn || !token_ids)) return fail("advance_decode: rings need the turn counter and the tokens");
+    cudaError_t e = launch_dependent(advance_decode_kernel, dim3(1), dim3(256), (size_t)0, stream, token_pos, seq_start,
+                                     seq_len, n, token_ids, draw_counter, turn, host_ring, host_slots, log_ring, log_slots);
+    return check_launch(e, "advance_decode");
+}
+
 RI_API int ri_silu_mul(const void* gu, void* out, int dtype, int n_tokens, int inter, cudaStream_t stream) {
     const size_t total = (size_t)n_tokens * inter;
     if (total == 0) return 0;

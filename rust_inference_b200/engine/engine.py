@@ -223,18 +223,23 @@ class Engine:
         self.cache.advance(slots, [len(t) for t in tokens])
         return logits
 
-    def _graph_for(self, n: int):
-        """The captured decode step of n sequences (made on first use; call with the device current).
-        Only the most recently used batch sizes are kept."""
-        graph = self._graphs.get(n)
+    def _graph_for(self, n: int, sampler=None):
+        """The captured decode step of n sequences, with the sampler inside it if one is given (made
+        on first use; call with the device current).  Only the most recently used ones are kept."""
+        key = (n, sampler)
+        graph = self._graphs.get(key)
         if graph is None:
             from .graphs import MAX_SIZES, DecodeGraph
             while len(self._graphs) >= MAX_SIZES:
                 self._graphs.popitem(last=False)
-            graph = self._graphs[n] = DecodeGraph(self, n)
+            graph = self._graphs[key] = DecodeGraph(self, n, sampler)
         else:
-            self._graphs.move_to_end(n)
+            self._graphs.move_to_end(key)
         return graph
+
+    def decode_graph(self, n: int, sampler=None):
+        """The decode step of n sequences as the engine holds it (None if it has not been used yet)."""
+        return self._graphs.get((n, sampler))
 
     def shared_decode_logits(self, n: int) -> torch.Tensor:
         """float32 [n, vocab] for decode steps of batch sizes that have no buffer of their own yet; the
@@ -249,28 +254,76 @@ class Engine:
         device tensor (`step_from_device`)."""
         return self.use_graphs
 
-    def decode_token_buffer(self, n: int) -> torch.Tensor:
+    def decode_token_buffer(self, n: int, sampler=None) -> torch.Tensor:
         """The int32 [n] device buffer from which the captured decode step of n sequences reads its
         tokens: a sampler that writes there feeds `step_from_device` without a copy."""
         with torch.cuda.device(self.device):
-            return self._graph_for(n).ctx.token_ids
+            return self._graph_for(n, sampler).ctx.token_ids
+
+    def _enter_decode(self, graph, slots: list, streams=None, counters=None) -> None:
+        """Reserve a position for every sequence and make the graph's static arrays describe this step.
+        When the step before was of the same sequences the arrays are already there (that step moved
+        them on), and nothing is copied; otherwise they come from the host, together with the
+        sampler's streams and draw counters if the step samples.  The token ids are left as they are."""
+        n = len(slots)
+        if len(set(slots)) != n:
+            raise ValueError("step: a slot appears twice in one batch")
+        starts = self.cache.lengths(slots)
+        self.cache.reserve([(s, st + 1) for s, st in zip(slots, starts)])
+        if graph.rows is not None:
+            streams, counters = list(streams), list(counters)
+        if graph.holds(slots, starts, streams, counters):
+            return
+        meta, layout, _ = pack_step(starts, [[0]] * n, [[0]] * n)
+        o, c = layout["seq_slot"]
+        meta[o:o + c] = slots
+        if graph.rows is not None:
+            if len(streams) != n or len(counters) != n:
+                raise ValueError("a step that samples needs a stream and a draw counter per sequence")
+            meta = np.concatenate([meta, np.asarray(streams, dtype=np.int32), np.asarray(counters, dtype=np.int32)])
+        dev = self._ring.stage(meta, self.device)
+        self.h2d_bytes += meta.nbytes
+        graph.load_meta(dev, keep_tokens=True, slots=slots, starts=starts, streams=streams, counters=counters)
+
+    def _feed(self, graph, tokens_dev: torch.Tensor) -> None:
+        if tokens_dev.numel() != graph.n_seqs or tokens_dev.dtype != torch.int32:
+            raise ValueError("a decode step takes one int32 token per sequence")
+        if tokens_dev.data_ptr() != graph.ctx.token_ids.data_ptr():       # else they are in place already
+            graph.ctx.token_ids.copy_(tokens_dev, non_blocking=True)
 
     def step_from_device(self, slots: list, tokens_dev: torch.Tensor):
         """One decode step whose tokens (one per sequence, int32 [B]) are already on the device,
         for instance straight from the sampler: no host round trip between sampling and the next
         step.  Returns the step's logits [B, vocab] in a buffer the next step overwrites."""
-        n = len(slots)
-        if tokens_dev.numel() != n or tokens_dev.dtype != torch.int32:
-            raise ValueError("step_from_device: one int32 token per sequence")
         with torch.cuda.device(self.device):
-            dev, _, _ = self._stage(slots, [[0]] * n, [[0]] * n)
-            graph = self._graph_for(n)
-            graph.load_meta(dev, keep_tokens=True)
-            if tokens_dev.data_ptr() != graph.ctx.token_ids.data_ptr():       # else they are in place already
-                graph.ctx.token_ids.copy_(tokens_dev, non_blocking=True)
+            graph = self._graph_for(len(slots))
+            self._enter_decode(graph, slots)
+            self._feed(graph, tokens_dev)
             logits = graph.launch()
         self.cache.advance(slots, [1] * len(slots))
         return logits
+
+    def can_sample_in_step(self, sampler_config) -> bool:
+        """True if decode steps can hold this sampler (`step_and_sample_from_device`): captured steps,
+        and options that need no token history."""
+        return self.use_graphs and not sampler_config.uses_history
+
+    def step_and_sample_from_device(self, slots: list, tokens_dev: torch.Tensor, sampler_config, streams: list,
+                                    counters: list):
+        """One decode step AND the sampling of its logits as one captured graph: feeds tokens_dev (int32
+        [B] on the device), samples one token per sequence with `sampler_config` (row b draws its
+        counters[b]-th number of stream streams[b]).  Returns (tokens on the device, the same in pinned
+        host memory): the device buffer is the one the next step of these sequences reads, so passing it
+        back costs nothing; the host buffer is valid once the step has finished (record an event behind
+        this call and wait for it) and is reused four steps later.  While the same sequences go on, a
+        step costs the host one graph launch: positions and draw counters move on on the device."""
+        with torch.cuda.device(self.device):
+            graph = self._graph_for(len(slots), sampler_config)
+            self._enter_decode(graph, slots, streams, counters)
+            self._feed(graph, tokens_dev)
+            graph.launch()
+        self.cache.advance(slots, [1] * len(slots))
+        return graph.ctx.token_ids, graph.last_tokens_host()
 
     def decode_steps(self, slots: list, first_tokens: list, n_steps: int, sampler_config=None) -> torch.Tensor:
         """Device-resident decoding: n_steps steps of one token per sequence in which each
@@ -278,31 +331,31 @@ class Engine:
         stop check in between.  Returns the sampled tokens, int32 [n_steps, B], on the device.
         The first step is fed `first_tokens`."""
         from ..sampling.params import SamplerConfig
-        from ..kernels import ops
+        from .graphs import LOG_RING
         cfg = sampler_config or SamplerConfig.plain(temperature=0.0)
         if cfg.uses_history:
             raise ValueError("decode_steps keeps no token history: use it without a repetition penalty")
-        if not self.model.graph_safe():
-            raise RuntimeError("decode_steps replays a captured step; this model has a part that is not graph_safe")
+        if not self.use_graphs:
+            raise RuntimeError("decode_steps replays a captured step; this engine runs without graphs "
+                               "(a part of the model is not graph_safe, or graphs were switched off)")
         n = len(slots)
         self._check_batch(slots, [[t] for t in first_tokens], [[0]] * n)
         starts = self.cache.lengths(slots)
-        self.cache.reserve([(s, st + n_steps) for s, st in zip(slots, starts)])
+        self.cache.reserve([(s, st + n_steps) for s, st in zip(slots, starts)])      # all or nothing, up front
+        streams = list(range(n))
+        pieces = []
         with torch.cuda.device(self.device):
-            graph = self._graph_for(n)
-            out = torch.empty((n_steps, n), dtype=torch.int32, device=self.device)
-            streams = torch.arange(n, dtype=torch.int32, device=self.device)
-            counters = torch.arange(n_steps, dtype=torch.int32, device=self.device).repeat_interleave(n).view(n_steps, n)
-            for i in range(n_steps):
-                meta, layout, _ = pack_step([st + i for st in starts], [[t] for t in first_tokens], [[0]] * n)
-                o, c = layout["seq_slot"]
-                meta[o:o + c] = slots
-                dev = self._ring.stage(meta, self.device)
-                self.h2d_bytes += meta.nbytes
-                graph.load_meta(dev, keep_tokens=i > 0)
-                logits = graph.launch()
-                ops.sample(logits, graph.ctx.token_ids, temperature=cfg.temperature, top_k=cfg.top_k,
-                           top_p=cfg.top_p, seed=cfg.seed, row_stream=streams, row_counter=counters[i])
-                out[i].copy_(graph.ctx.token_ids, non_blocking=True)
-        self.cache.advance(slots, [n_steps] * len(slots))
-        return out
+            graph = self._graph_for(n, cfg)
+            first = torch.tensor(first_tokens, dtype=torch.int32).pin_memory().to(self.device, non_blocking=True)
+            done = 0
+            while done < n_steps:
+                run = min(LOG_RING, n_steps - done)
+                for i in range(run):
+                    self._enter_decode(graph, slots, streams, [done + i] * n)
+                    if done + i == 0:
+                        self._feed(graph, first)
+                    graph.launch()
+                    self.cache.advance(slots, [1] * n)
+                pieces.append(graph.logged_tokens(run))
+                done += run
+        return pieces[0] if len(pieces) == 1 else torch.cat(pieces)

@@ -167,6 +167,11 @@ class Generator:
             known in advance; stop tokens are not."""
             return drawn < max_tokens and s.prompt_length + drawn <= eng.max_seq_len
 
+        # A sampler that needs no token history can live inside the captured decode step: one graph
+        # launch then runs the model, samples, and moves the step's arrays on for the next launch.
+        in_step = self.sampler.params if (hasattr(eng, "can_sample_in_step") and hasattr(self.sampler, "params")
+                                          and eng.can_sample_in_step(self.sampler.params)) else None
+
         def sample(logits, seqs, drawn, newest=None):
             host = ring[turn[0] % len(ring)][:len(seqs)]
             turn[0] += 1
@@ -174,7 +179,7 @@ class Generator:
             # whole batch will be stepped again at this size
             out = None
             if hasattr(eng, "decode_token_buffer") and all(goes_on(s, d + 1) for s, d in zip(seqs, drawn)):
-                out = eng.decode_token_buffer(len(seqs))
+                out = eng.decode_token_buffer(len(seqs), in_step) if in_step is not None else eng.decode_token_buffer(len(seqs))
             # With a repetition penalty the host's histories lack the token that was just fed (it has not
             # been read yet): the kernel takes that one from the device.  It reads `newest` before it writes
             # `out`, so the two may be the same buffer.
@@ -194,9 +199,16 @@ class Generator:
             if rows:
                 ahead = [seqs[i] for i in rows]
                 feed_dev = tokens_dev if len(rows) == len(seqs) else dev.rows(tokens_dev, rows)
-                logits = eng.step_from_device([s.slot for s in ahead], feed_dev)
+                drawn = [len(s.tokens) + 1 for s in ahead]
+                if in_step is not None:
+                    sampled, host2 = eng.step_and_sample_from_device([s.slot for s in ahead], feed_dev, in_step,
+                                                                     [s.index for s in ahead], drawn)
+                    self.d2h_bytes += len(ahead) * 4
+                    nxt = (ahead, sampled, (host2, dev.mark()))
+                else:
+                    logits = eng.step_from_device([s.slot for s in ahead], feed_dev)
+                    nxt = (ahead,) + sample(logits, ahead, drawn, newest=feed_dev)
                 self.steps += 1
-                nxt = (ahead,) + sample(logits, ahead, [len(s.tokens) + 1 for s in ahead], newest=feed_dev)
             mark.synchronize()                                       # the earlier tokens; the step just launched keeps running
             if hasattr(eng, "check_device_status"):
                 eng.check_device_status()

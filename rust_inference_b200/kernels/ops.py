@@ -214,6 +214,32 @@ def sample(logits: torch.Tensor, out: torch.Tensor, *, temperature: float, top_k
     return out
 
 
+def advance_decode(token_pos: torch.Tensor, seq_start: torch.Tensor, seq_len: torch.Tensor, token_ids: torch.Tensor,
+                   *, draw_counter: torch.Tensor | None = None, turn: torch.Tensor | None = None,
+                   host_ring: torch.Tensor | None = None, log_ring: torch.Tensor | None = None) -> None:
+    """The end of a decode step: positions, starts and lengths (int32 [n] each) grow by one in
+    place.  Optionally the sampler's draw counters grow by one, and the step's tokens are copied
+    into slot (turn % slots) of `host_ring` (pinned int32 [slots, n]) and of `log_ring` (device int32
+    [slots, n]); `turn` (device int32 [1]) then grows by one."""
+    n = token_pos.numel()
+    _need_cuda(token_pos, seq_start, seq_len, token_ids, draw_counter, turn, log_ring)
+    for t in (token_pos, seq_start, seq_len, token_ids, draw_counter, turn, log_ring):
+        _need(t is None or (t.dtype == torch.int32 and t.is_contiguous()), "advance_decode: arrays must be int32")
+    _need(seq_start.numel() == n and seq_len.numel() == n and token_ids.numel() >= n
+          and (draw_counter is None or draw_counter.numel() >= n), "advance_decode: one entry per sequence")
+    if host_ring is not None:
+        _need(host_ring.device.type == "cpu" and host_ring.is_pinned() and host_ring.dtype == torch.int32
+              and host_ring.is_contiguous() and host_ring.ndim == 2 and host_ring.shape[1] == n,
+              "advance_decode: host_ring must be pinned int32 [slots, n]")
+    if log_ring is not None:
+        _need(log_ring.ndim == 2 and log_ring.shape[1] == n, "advance_decode: log_ring must be int32 [slots, n]")
+    _need((host_ring is None and log_ring is None) or turn is not None, "advance_decode: rings need the turn counter")
+    _call("elementwise", "ri_advance_decode", _p(token_pos), _p(seq_start), _p(seq_len), c_int(n), _p(token_ids),
+          _p(draw_counter), _p(turn), c_void_p(host_ring.data_ptr() if host_ring is not None else 0),
+          c_int(host_ring.shape[0] if host_ring is not None else 0), _p(log_ring),
+          c_int(log_ring.shape[0] if log_ring is not None else 0), _stream())
+
+
 def sample_cluster_min_vocab(vocab: int) -> None:
     """Rows of at least `vocab` entries are sampled by a cluster of thread blocks where the options
     allow it (0: never; the library's default is 32,768).  For comparisons and tests."""

@@ -23,6 +23,7 @@ class Sampler:
         self._rows_key = None
         self._rows_dev = None
         self._rows_counters = None
+        self.h2d_bytes = 0                # bytes of per-row arrays copied to the device so far
 
     def _stage(self, meta: np.ndarray) -> torch.Tensor:
         """The per-row int32 arrays to the device, through pinned memory (no blocking copy)."""
@@ -35,6 +36,7 @@ class Sampler:
             buf = torch.empty(max(256, 2 * meta.size), dtype=torch.int32).pin_memory()
             self._pinned[i] = buf
         buf[:meta.size].copy_(torch.from_numpy(meta.reshape(-1)))
+        self.h2d_bytes += meta.nbytes
         dev = buf[:meta.size].to(self.device, non_blocking=True)
         ev = torch.cuda.Event()
         ev.record()

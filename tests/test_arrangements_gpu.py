@@ -282,7 +282,7 @@ def test_toy_roles_model_in_every_cutting_with_captured_state_updates(dtype, rol
     s = eng.alloc_slot()                                        # the same slot: its state starts from zero again
     head = eng.step([s], [toks[:58]], "all").cpu()
     tail = torch.cat([eng.step([s], [[t]], "last").cpu() for t in toks[58:]])
-    assert eng._graphs[1].graph is not None                     # the late steps replayed a captured graph
+    assert eng.decode_graph(1).graph is not None                     # the late steps replayed a captured graph
     assert rel_err(torch.cat([head, tail]), want) <= tol
     eng.free_slot(s)
     # an unequal batch; the shortest ends early, its slot is taken again by a new request while the others go on

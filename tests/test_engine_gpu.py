@@ -297,12 +297,12 @@ def test_a_failed_decode_step_leaves_no_dirty_accumulator(model_factory, monkeyp
                 eng.step([s], [[toks[pos]]], "last")
             state["fail"] = False
             assert eng.cache.length(s) == pos                  # the failed step did not count
-            assert eng._graphs[1].graph is None
+            assert eng.decode_graph(1).graph is None
             continue
         got = eng.step([s], [[toks[pos]]], "last")[0]
         assert rel_err(got, want[pos]) <= TOL["bfloat16"], nth
         pos += 1
-    assert eng._graphs[1].graph is not None                    # the size did get its graph in the end
+    assert eng.decode_graph(1).graph is not None                    # the size did get its graph in the end
     assert state["calls"] > 0                                  # the path under test did run
     # an eager step of several tokens that fails, then the same step again
     state["fail"] = True

@@ -43,7 +43,7 @@ def test_eighty_sequences_decode_together(name, dtype, model_factory):
             worst = max(worst, rel_err(got[i], w))
             assert top_k_agrees(got[i], w, 5, TOL[dtype]), (step, i)
         assert worst <= TOL[dtype], (step, worst)
-    graph = eng._graphs[N_SEQS]
+    graph = eng.decode_graph(N_SEQS)
     assert graph.graph is not None and graph.eager_steps >= 3           # the last steps were replays
     eng.check_device_status()
     eng.cache.pager.audit()
