@@ -60,6 +60,34 @@ class AheadEngine(FakeEngine):
         return self.step(slots, [[int(t)] for t in tokens_dev], "last")
 
 
+class InStepEngine(AheadEngine):
+    """An engine whose decode steps hold the sampler: one call runs the step and samples, and hands back
+    the tokens on the 'device' (the buffer the next step reads) and in 'pinned host' memory."""
+
+    def __init__(self, script, *a, **k):
+        super().__init__(*a, **k)
+        self.script = script
+        self.sampled_in_step = []
+        self.host_ring = {}
+
+    def can_sample_in_step(self, params):
+        return not params.uses_history
+
+    def decode_token_buffer(self, n, sampler=None):
+        return self.token_buffers.setdefault(n, np.zeros(n, dtype=np.int32))
+
+    def step_and_sample_from_device(self, slots, tokens_dev, params, streams, counters):
+        self.step_from_device(slots, tokens_dev)
+        self.sampled_in_step.append((list(streams), list(counters)))
+        toks = [self.script(s, c) for s, c in zip(streams, counters)]
+        dev = self.decode_token_buffer(len(slots))
+        dev[:] = toks
+        ring = self.host_ring.setdefault(len(slots), [np.zeros(len(slots), dtype=np.int32) for _ in range(4)])
+        host = ring[len(self.sampled_in_step) % 4]
+        host[:] = toks
+        return dev, host
+
+
 class FakeMark:
     waited = 0
 
@@ -97,19 +125,28 @@ class ScriptedSampler:
         return dev
 
 
-@pytest.fixture(params=["plain", "ahead"])
+@pytest.fixture(params=["plain", "ahead", "in_step"])
 def loop(request):
+    """plain: step, sample, read, decide.  ahead: one step of lookahead, the sampler called after each
+    step.  in_step: lookahead with the sampler inside the engine's decode step."""
     return request.param
 
 
 ENGINES = {"plain": FakeEngine, "ahead": AheadEngine}
 
 
-def make_engine(loop, *a, base=None, **k):
+def make_engine(loop, *a, **k):
+    if loop == "in_step":
+        return InStepEngine(None, *a, **k)          # the script comes with the sampler (see Generator below)
     return ENGINES[loop](*a, **k)
 
 
 def Generator(engine, sampler, **k):
+    if isinstance(engine, InStepEngine):
+        from rust_inference_b200 import SamplerConfig
+        engine.script = sampler.script
+        if not hasattr(sampler, "params"):
+            sampler.params = SamplerConfig.plain(0.0)
     return _Generator(engine, sampler, device=FakeLoopDevice(), **k)
 
 
@@ -145,7 +182,10 @@ def test_stop_token_ends_early_is_not_emitted_and_frees_the_slot(loop):
         # rows); its row is dropped and the stop token is fed no further
         assert [len(c[0]) for c in eng.calls] == [3, 3, 3, 2]
         assert eng.calls[2][1] == [[5], [9], [5]] and eng.calls[3][1] == [[5], [5]]
-        assert sampler.seen[2][0] == [0, 1, 2] and sampler.seen[3][0] == [0, 2]
+        # who was sampled: after the prompts' step the sampler object; in the in_step loop every later
+        # sample happens inside the engine's step
+        seen = [x[0] for x in sampler.seen] + [x[0] for x in getattr(eng, "sampled_in_step", [])]
+        assert seen == [[0, 1, 2], [0, 1, 2], [0, 1, 2], [0, 2]]
     assert res[2].tokens == [5, 5, 5, 5]
     eng.cache.pager.audit()
     assert eng.cache.pager.free_slot_count() == 4
@@ -301,6 +341,23 @@ def test_one_ends_at_max_seq_len_a_step_before_another_stops(loop):
     assert max(len(t) for c in eng.calls[1:] for t in c[1]) == 1
     eng.cache.pager.audit()
     assert eng.cache.pager.free_slot_count() == 2
+
+
+def test_in_step_sampling_takes_streams_and_draw_numbers_from_the_loop():
+    eng = InStepEngine(None)
+    sampler = ScriptedSampler(lambda s, c: 100 * s + c)
+    res = Generator(eng, sampler).generate([[1], [2, 2]], max_tokens=4)
+    assert [r.tokens for r in res] == [[0, 1, 2, 3], [100, 101, 102, 103]]
+    assert sampler.seen == [([0, 1], [0, 0])]                      # the sampler object only after the prompts
+    assert eng.sampled_in_step == [([0, 1], [1, 1]), ([0, 1], [2, 2]), ([0, 1], [3, 3])]
+    assert eng.fed_in_place == 3                                   # every step read its tokens where the last one left them
+    # with a token history the sampler cannot live in the step: the loop calls it after every step
+    from rust_inference_b200 import SamplerConfig
+    eng2 = InStepEngine(None)
+    s2 = ScriptedSampler(lambda s, c: 7)
+    s2.params = SamplerConfig(repetition_penalty=1.3)
+    Generator(eng2, s2).generate([[1]], max_tokens=3)
+    assert eng2.sampled_in_step == [] and len(s2.seen) == 3
 
 
 def test_tokens_are_fed_in_place_while_the_whole_batch_goes_on():
