@@ -578,9 +578,17 @@ sample_cluster_kernel(float* __restrict__ logits, int vocab, int per_cta, int* o
     if (temperature <= 0.f) {
         float best = -INFINITY;
         int best_i = 0x7fffffff;
-        for (int i = c_lo + tid; i < c_hi; i += THREADS) {
-            const float v = p[i];
-            if (v > best) { best = v; best_i = i; }
+        // eight loads in flight per thread: the walk is bound by the latency of its loads, not by their number
+        for (int i0 = c_lo + tid; i0 < c_hi; i0 += THREADS * 8) {
+            float v[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const int i = i0 + k * THREADS;
+                v[k] = i < c_hi ? p[i] : -INFINITY;
+            }
+#pragma unroll
+            for (int k = 0; k < 8; ++k)                            // ids ascend with k: a later one must be larger to win
+                if (v[k] > best) { best = v[k]; best_i = i0 + k * THREADS; }
         }
         const float m = block_max(best, fscratch);
         int cand = (best == m) ? best_i : 0x7fffffff;
@@ -614,7 +622,16 @@ sample_cluster_kernel(float* __restrict__ logits, int vocab, int per_cta, int* o
     const int per = per_cta / WARPS;                             // a warp's stretch; a multiple of 32
     const int w_lo = min(c_hi, c_lo + warp * per), w_hi = min(c_hi, w_lo + per);
     float tmax = -INFINITY;
-    for (int i = w_lo + lane; i < w_hi; i += 32) tmax = fmaxf(tmax, p[i]);
+    for (int i0 = w_lo + lane; i0 < w_hi; i0 += 32 * 8) {        // eight loads in flight per thread
+        float v[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const int i = i0 + k * 32;
+            v[k] = i < w_hi ? p[i] : -INFINITY;
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) tmax = fmaxf(tmax, v[k]);
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, o));
     tmax = tmax / temperature;                                   // the largest x of this warp's stretch

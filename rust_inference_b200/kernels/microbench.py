@@ -2,6 +2,7 @@
 
     python bench.py --kernel gate_up --tokens 8
     python bench.py --kernel attn_decode --tokens 64 --context 1024
+    python bench.py --kernel step_parts --tokens 8      # what each kind of kernel costs INSIDE a decode step
 
 The operand that a step streams (weights, or the cache) is rotated over enough copies to
 exceed L2, and the launches are replayed from a CUDA graph so that host launch cost is
@@ -16,7 +17,7 @@ import math
 import torch
 
 KERNELS = ("qkv", "qkv_split", "o_proj", "gate_up", "down", "lm_head", "sample", "attn_decode", "attn_prefill",
-           "attn_prefill_mma", "rmsnorm", "rope")
+           "attn_prefill_mma", "rmsnorm", "rope", "step_parts")
 
 
 def _graph_time(fn, launches_per_replay: int, reps: int = 10) -> float:
@@ -180,9 +181,102 @@ def run(kernel: str, model: dict, tokens: int, context: int = 1024, eager_only: 
     return out
 
 
+def step_parts(model: dict, batch: int, prompt_min: int = 128, prompt_max: int = 2048) -> dict:
+    """What each kind of kernel costs inside a decode step of `batch` sequences of the whole model: the
+    captured step (model, greedy sampler, move to the next position) is timed as it is and again with
+    one kind of kernel left out; the difference is that kind's share with everything that overlaps it
+    (programmatic dependent launch, tails and ramps) counted as it falls.  Results are microseconds
+    per step; the step without a kernel computes nothing meaningful and is only timed."""
+    import random
+    from ..api import Model
+    from ..config.registry import config_from_dict
+    from ..engine.context import pack_step
+    from ..engine.graphs import DecodeGraph
+    from ..parts import attention as attention_part
+    from ..sampling.params import SamplerConfig
+    from . import ops, tcgen05
+
+    cfg = config_from_dict(dict(model))
+    m = Model.random(cfg, seed=0, dtype="bfloat16", max_seq_len=8192, max_tokens_in_cache=batch * 2304 + 4096)
+    eng = m.engine
+    rng = random.Random(1)
+    prompts = [[rng.randrange(cfg.vocab_size) for _ in range(rng.randint(prompt_min, prompt_max))] for _ in range(batch)]
+    slots = [eng.alloc_slot() for _ in prompts]
+    for i in range(0, batch, 8):
+        eng.step(slots[i:i + 8], prompts[i:i + 8], "none")
+    starts = eng.cache.lengths(slots)
+    # every replay moves the step's positions on by one: room for all of them
+    eng.cache.reserve([(s, st + 64) for s, st in zip(slots, starts)])
+    meta, layout, _ = pack_step(starts, [[5]] * batch, [[0]] * batch)
+    o, c = layout["seq_slot"]
+    meta[o:o + c] = slots
+    rows = torch.cat([torch.arange(batch, dtype=torch.int32), torch.zeros(batch, dtype=torch.int32)])
+    meta_dev = torch.cat([torch.from_numpy(meta), rows]).cuda()
+    greedy = SamplerConfig.plain(0.0)
+
+    def time_step(sampler=greedy, reps=30):
+        g = DecodeGraph(eng, batch, sampler)
+        for _ in range(4):                                  # three steps kernel by kernel, then the capture
+            g.load_meta(meta_dev)
+            g.launch()
+        torch.cuda.synchronize()
+        for _ in range(5):
+            g.graph.replay()
+        g.load_meta(meta_dev)                               # back to the first position
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            g.graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / reps
+
+    def without(patches):
+        saved = [(obj, attr, getattr(obj, attr)) for obj, attr, _ in patches]
+        for obj, attr, new in patches:
+            setattr(obj, attr, new)
+        try:
+            return time_step()
+        finally:
+            for obj, attr, old in saved:
+                setattr(obj, attr, old)
+
+    real_gemm = tcgen05.gemm
+
+    def gemm_except(skip):
+        def gemm(x, w, out, mode, ctx=None, bias=None, w2=None, split_k=None):
+            return out if skip(w, mode) else real_gemm(x, w, out, mode, ctx, bias=bias, w2=w2, split_k=split_k)
+        return gemm
+
+    noop = lambda *a, **k: None
+    qd, kvd, h, inter = cfg.q_dim, cfg.kv_dim, cfg.hidden_size, cfg.intermediate_size
+    full = time_step()
+    out = {"kernel": "step_parts", "tokens": batch, "layers": cfg.num_hidden_layers, "step_us": full, "without_us": {}}
+    cases = {
+        "sampler": lambda: time_step(sampler=None),
+        "attention": lambda: without([(attention_part.attn_kernels, "attention", noop)]),
+        "rope_cache_write": lambda: without([(ops, "rope_cache_write_acc", noop), (ops, "rope_cache_write", noop)]),
+        "rmsnorm": lambda: without([(ops, "rmsnorm", lambda x, w, eps, out, rows=None: out)]),
+        "qkv_gemm": lambda: without([(tcgen05, "gemm", gemm_except(lambda w, mode: w.n == qd + 2 * kvd and w.k == h))]),
+        "o_gemm": lambda: without([(tcgen05, "gemm", gemm_except(lambda w, mode: w.n == h and w.k == qd and mode == ops.EPI_RESIDUAL))]),
+        "gate_up_gemm": lambda: without([(tcgen05, "gemm", gemm_except(lambda w, mode: mode == ops.EPI_SILU_MUL))]),
+        "down_gemm": lambda: without([(tcgen05, "gemm", gemm_except(lambda w, mode: w.k == inter))]),
+        "lm_head": lambda: without([(tcgen05, "gemm", gemm_except(lambda w, mode: mode == ops.EPI_STORE_F32))]),
+        "mixer (norm, qkv, rope, attention, o)": lambda: without([(attention_part.GQAttention, "forward", noop)]),
+    }
+    for name, run in cases.items():
+        out["without_us"][name] = run()
+    out["share_us"] = {name: full - t for name, t in out["without_us"].items()}
+    tcgen05.check_status()
+    return out
+
+
 def main(kernel: str, model: dict, tokens: int, context: int, eager_only: bool = False) -> int:
     if kernel not in KERNELS:
         print(f"unknown kernel {kernel!r}; choose from {', '.join(KERNELS)}")
         return 2
+    if kernel == "step_parts":
+        print(json.dumps(step_parts(model, tokens)))
+        return 0
     print(json.dumps(run(kernel, model, tokens, context, eager_only)))
     return 0
