@@ -66,7 +66,29 @@ OTHER_SIZES = {
         "tie_word_embeddings": False, "max_position_embeddings": 32768,
     },
 }
-SIZE_NAMES = {"qwen2.5-7b": "Qwen2.5-7B-sized", "llama3-8b": "Llama-3-8B-sized", "qwen2.5-32b": "Qwen2.5-32B-sized"}
+# the sizes the reference's README quotes its own (4-bit, CPU, batch 1) decode latencies for
+OTHER_SIZES.update({
+    "qwen2-0.5b": {
+        "architectures": ["Qwen2ForCausalLM"], "hidden_size": 896, "num_hidden_layers": 24,
+        "num_attention_heads": 14, "num_key_value_heads": 2, "head_dim": 64, "intermediate_size": 4864,
+        "vocab_size": 151936, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "attention_bias": True,
+        "tie_word_embeddings": True, "max_position_embeddings": 32768,
+    },
+    "qwen2-1.5b": {
+        "architectures": ["Qwen2ForCausalLM"], "hidden_size": 1536, "num_hidden_layers": 28,
+        "num_attention_heads": 12, "num_key_value_heads": 2, "head_dim": 128, "intermediate_size": 8960,
+        "vocab_size": 151936, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "attention_bias": True,
+        "tie_word_embeddings": True, "max_position_embeddings": 32768,
+    },
+    "qwen2.5-3b": {
+        "architectures": ["Qwen2ForCausalLM"], "hidden_size": 2048, "num_hidden_layers": 36,
+        "num_attention_heads": 16, "num_key_value_heads": 2, "head_dim": 128, "intermediate_size": 11008,
+        "vocab_size": 151936, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "attention_bias": True,
+        "tie_word_embeddings": True, "max_position_embeddings": 32768,
+    },
+})
+SIZE_NAMES = {"qwen2.5-7b": "Qwen2.5-7B-sized", "llama3-8b": "Llama-3-8B-sized", "qwen2.5-32b": "Qwen2.5-32B-sized",
+              "qwen2-0.5b": "Qwen2-0.5B-sized", "qwen2-1.5b": "Qwen2-1.5B-sized", "qwen2.5-3b": "Qwen2.5-3B-sized"}
 CONTEXT = 8192
 PROMPT_MIN, PROMPT_MAX = 128, 2048
 PREFILL_TOKENS = 2048

@@ -39,6 +39,19 @@ class Model:
         return cls(Engine.from_random(config, seed=seed, std=std, norm_std=norm_std, dtype=dtype, device=device,
                                       max_tokens=max_tokens_in_cache, max_seq_len=max_seq_len, n_slots=n_slots))
 
+    def memory(self) -> dict:
+        """Bytes the model holds on the device and what a decode step has to read of them: the weights
+        (every declared tensor once), the weights a step reads (the embedding table only when it is also
+        the head), the cache as allocated, and the cache bytes one position of one sequence adds."""
+        eng = self.engine
+        item = 4 if eng.dtype.itemsize == 4 else 2
+        per_position = 0
+        for req in eng.model.cache_requests():
+            if req is not None and hasattr(req, "n_kv_heads"):
+                per_position += 2 * req.n_kv_heads * req.head_dim * item
+        return {"weight_bytes": eng.model.weight_bytes(), "weight_bytes_per_step": eng.model.weight_bytes(False),
+                "cache_bytes": eng.cache.bytes(), "cache_bytes_per_position": per_position}
+
     def state_dict(self) -> dict:
         """name -> tensor for every tensor of the model, under the weight file's names, as held on the
         device (matrices in the run dtype, norm weights and biases float32; packed matrices as views
@@ -81,7 +94,8 @@ class Model:
     def generate(self, prompts, max_tokens: int = 512, sampler_config: SamplerConfig | None = None,
                  stop_ids=None, max_batch: int | None = None, record_step_times: bool = False) -> list:
         """prompts: a list of token-id lists (or one list of ints).  Returns one
-        `GenerationResult` per prompt.  stop_ids defaults to the model's eos ids
+        `GenerationResult` per prompt; `last_stats` then holds the call's counts (steps, prompt and
+        generated tokens, seconds, tokens per second, bytes copied up and down).  stop_ids defaults to the model's eos ids
         (config.json `eos_token_id`); a sampled stop id ends its sequence and is not returned
         (model.rs:383-387).  Defaults follow the reference: max_tokens 512 (main.rs:65),
         `SamplerConfig()` (sampler.rs:37-48)."""
@@ -94,11 +108,17 @@ class Model:
         gen = Generator(self.engine, sampler, stop_ids=stop_ids, max_batch=max_batch)
         if record_step_times:
             gen.step_times = []
+        import time
         h2d0 = self.engine.h2d_bytes + self.engine.cache.h2d_bytes
+        t0 = time.perf_counter()
         results = gen.generate(batch, max_tokens)
+        seconds = time.perf_counter() - t0
         # everything that went up from pinned host memory: the steps' arrays (prompts among them), new
         # page-table entries, the sampler's per-row arrays; and the sampled tokens that came down
         h2d = self.engine.h2d_bytes + self.engine.cache.h2d_bytes - h2d0 + sampler.h2d_bytes
-        self.last_stats = {"steps": gen.steps, "h2d_bytes": h2d,
-                           "d2h_bytes": gen.d2h_bytes, "step_times": gen.step_times}
+        n_out = sum(len(r.tokens) for r in results)
+        self.last_stats = {"steps": gen.steps, "h2d_bytes": h2d, "d2h_bytes": gen.d2h_bytes,
+                           "step_times": gen.step_times, "seconds": seconds,
+                           "prompt_tokens": sum(len(p) for p in batch), "generated_tokens": n_out,
+                           "tokens_per_second": n_out / seconds if seconds > 0 else 0.0}
         return results[0] if single else results

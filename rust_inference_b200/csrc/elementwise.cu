@@ -526,6 +526,57 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
 }
 
 // ---------------------------------------------------------------------------------------
+// Load-time helpers: a change of precision, and seeded normal numbers for the random-weights mode.
+// ---------------------------------------------------------------------------------------
+template <typename TI, typename TO>
+__global__ void cast_kernel(const TI* __restrict__ in, TO* __restrict__ out, size_t n) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = from_f32<TO>(to_f32<TI>(in[i]));      // bf16 -> float32 is exact; float32 -> bf16 rounds to nearest even
+}
+
+RI_API int ri_cast(const void* in, int in_dtype, void* out, int out_dtype, long long n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    if (in_dtype == RI_F32 && out_dtype == RI_BF16)
+        cast_kernel<float, __nv_bfloat16><<<blocks, 256, 0, stream>>>((const float*)in, (__nv_bfloat16*)out, (size_t)n);
+    else if (in_dtype == RI_BF16 && out_dtype == RI_F32)
+        cast_kernel<__nv_bfloat16, float><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)in, (float*)out, (size_t)n);
+    else
+        return fail("cast: from dtype %d to dtype %d is not a change between float32 and bfloat16", in_dtype, out_dtype);
+    return check_launch("cast");
+}
+
+__device__ __forceinline__ unsigned long long fill_mix64(unsigned long long z) {
+    z += 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+
+// Element i of a tensor keyed `key` is mean + std * sqrt(-2 ln u1) * cos(2 pi u2), with u1 in (0, 1] and
+// u2 in [0, 1) the upper and the next 24 bits of mix64(key ^ mix64(i)): the same number whatever the
+// launch shape, the device or the order tensors are made in.
+template <typename T>
+__global__ void fill_normal_kernel(T* __restrict__ out, size_t n, unsigned long long key, float mean, float std) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const unsigned long long z = fill_mix64(key ^ fill_mix64((unsigned long long)i));
+    const float u1 = (float)((z >> 40) + 1ull) * (1.0f / 16777216.0f);
+    const float u2 = (float)((z >> 16) & 0xFFFFFFull) * (1.0f / 16777216.0f);
+    out[i] = from_f32<T>(mean + std * sqrtf(-2.0f * logf(u1)) * cospif(2.0f * u2));
+}
+
+RI_API int ri_fill_normal(void* out, int dtype, long long n, unsigned long long key, float mean, float std,
+                          cudaStream_t stream) {
+    if (n <= 0) return 0;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    if (dtype == RI_F32) fill_normal_kernel<float><<<blocks, 256, 0, stream>>>((float*)out, (size_t)n, key, mean, std);
+    else if (dtype == RI_BF16) fill_normal_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((__nv_bfloat16*)out, (size_t)n, key, mean, std);
+    else return fail("fill_normal: unknown dtype %d", dtype);
+    return check_launch("fill_normal");
+}
+
+// ---------------------------------------------------------------------------------------
 // The end of a decode step of n sequences (one token each): every sequence is one position
 // longer, so the step's int32 arrays move on by one and the next step of the same sequences
 // needs nothing from the host.  token_pos, seq_start and seq_len each grow by 1; token_ids

@@ -121,11 +121,22 @@ class DecoderModel:
                 out[prefix + local] = ts
         return out
 
+    def _to(self, t: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+        """t on the model's device in `dtype`: the copy up in the stored precision, the change of
+        precision on the device (bfloat16 <-> float32 by the library's own kernel)."""
+        t = t.to(device=self.device).contiguous()
+        if t.dtype == dtype:
+            return t
+        if self.device.type == "cuda" and {t.dtype, dtype} == {torch.float32, torch.bfloat16}:
+            from ..kernels import ops
+            return ops.cast(t, dtype)
+        return t.to(dtype)
+
     def _place(self, t: torch.Tensor, ts: TensorSpec) -> torch.Tensor:
         if ts.role == "matrix":
-            return t.to(device=self.device, dtype=self.dtype).contiguous()
+            return self._to(t, self.dtype)
         if ts.role == "vector":
-            return t.to(device=self.device, dtype=torch.float32).contiguous()
+            return self._to(t, torch.float32)
         if ts.role == "table":
             return t.to(device=self.device, dtype=torch.int32).contiguous()
         raise ValueError(f"unknown tensor role {ts.role!r}")

@@ -214,6 +214,26 @@ def sample(logits: torch.Tensor, out: torch.Tensor, *, temperature: float, top_k
     return out
 
 
+def cast(src: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """src (float32 or bfloat16, contiguous, on the device) in the other of the two precisions."""
+    _need_cuda(src)
+    _need(src.is_contiguous(), "cast: contiguous tensors only")
+    out = torch.empty(src.shape, dtype=dtype, device=src.device)
+    _call("elementwise", "ri_cast", _p(src), c_int(dtype_code(src.dtype)), _p(out), c_int(dtype_code(dtype)),
+          c_longlong(src.numel()), _stream())
+    return out
+
+
+def fill_normal(out: torch.Tensor, key: int, mean: float = 0.0, std: float = 1.0) -> torch.Tensor:
+    """out[i] = mean + std * z_i with z_i a standard normal number that depends on (key, i) only
+    (`sampling.rng.normal` restates it on the host).  out: float32 or bfloat16, contiguous, on the device."""
+    _need_cuda(out)
+    _need(out.is_contiguous(), "fill_normal: contiguous tensors only")
+    _call("elementwise", "ri_fill_normal", _p(out), c_int(dtype_code(out.dtype)), c_longlong(out.numel()),
+          c_ulonglong(key & 0xFFFFFFFFFFFFFFFF), c_float(mean), c_float(std), _stream())
+    return out
+
+
 def advance_decode(token_pos: torch.Tensor, seq_start: torch.Tensor, seq_len: torch.Tensor, token_ids: torch.Tensor,
                    *, draw_counter: torch.Tensor | None = None, turn: torch.Tensor | None = None,
                    host_ring: torch.Tensor | None = None, log_ring: torch.Tensor | None = None) -> None:

@@ -22,3 +22,13 @@ def uniform(seed: int, stream: int, counter: int) -> float:
     """u in (0, 1], a multiple of 2^-24."""
     z = _mix64((seed & _M) ^ _mix64(((stream & 0xFFFFFFFF) << 32) | (counter & 0xFFFFFFFF)))
     return ((z >> 40) + 1) / 16777216.0
+
+
+def normal(key: int, index: int) -> float:
+    """The standard normal number `ops.fill_normal` gives element `index` of a tensor keyed `key`
+    (Box-Muller on two 24-bit uniforms of one 64-bit hash), in double precision."""
+    import math
+    z = _mix64((key & _M) ^ _mix64(index & _M))
+    u1 = ((z >> 40) + 1) / 16777216.0
+    u2 = ((z >> 16) & 0xFFFFFF) / 16777216.0
+    return math.sqrt(-2.0 * math.log(u1)) * math.cos(2.0 * math.pi * u2)

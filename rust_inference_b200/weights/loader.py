@@ -99,6 +99,9 @@ def random_tensors(expected: Mapping[str, TensorSpec], seed: int, *, std: float 
     With norm_std > 0 every norm weight differs from every other, so a test model shows a
     norm weight that was swapped, dropped or skipped."""
     device = torch.device(device)
+    if device.type == "cuda":
+        yield from _random_tensors_on_device(expected, seed, std, matrix_dtype, device, norm_std)
+        return
     for name, spec in expected.items():
         gen = torch.Generator(device=device)
         gen.manual_seed(_tensor_seed(seed, name))
@@ -116,6 +119,30 @@ def random_tensors(expected: Mapping[str, TensorSpec], seed: int, *, std: float 
             raise ValueError(f"{name}: unknown init {spec.init!r}")
         if spec.role == "matrix":
             t = t.to(matrix_dtype)
+        yield name, t
+
+
+def _random_tensors_on_device(expected, seed, std, matrix_dtype, device, norm_std) -> Iterator[tuple]:
+    """The same on a CUDA device, filled by the library's own kernel: element i of a tensor is a
+    function of (seed, tensor name, i) alone (`sampling.rng.normal` restates it), written in the
+    precision the tensor is kept in.  The numbers are not those of the host generator above; a model
+    made here is handed to a plain implementation through `state_dict()`."""
+    from ..kernels import ops
+    for name, spec in expected.items():
+        key = _tensor_seed(seed, name)
+        if spec.role == "table":
+            t = torch.zeros(spec.shape, dtype=torch.int32, device=device)
+        elif spec.init == "zeros":
+            t = torch.zeros(spec.shape, dtype=torch.float32, device=device)
+        elif spec.init == "ones":
+            t = torch.ones(spec.shape, dtype=torch.float32, device=device)
+            if norm_std > 0.0:
+                ops.fill_normal(t, key, mean=1.0, std=norm_std)
+        elif spec.init == "normal":
+            t = torch.empty(spec.shape, dtype=matrix_dtype if spec.role == "matrix" else torch.float32, device=device)
+            ops.fill_normal(t, key, mean=0.0, std=std)
+        else:
+            raise ValueError(f"{name}: unknown init {spec.init!r}")
         yield name, t
 
 

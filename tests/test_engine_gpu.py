@@ -129,6 +129,12 @@ def test_greedy_generation_through_the_entry_point(model_factory):
             assert g.tokens == w[:w.index(stop)] and g.finish_reason == "stop"
         else:
             assert g.tokens == w and g.finish_reason == "length"
+    st = m.last_stats
+    assert st["generated_tokens"] == sum(len(g.tokens) for g in got) and st["prompt_tokens"] == 5 + 11 + 17 + 1
+    assert st["tokens_per_second"] > 0 and st["steps"] >= 1 and st["d2h_bytes"] > 0 and st["h2d_bytes"] > 0
+    mem = m.memory()
+    assert mem["cache_bytes_per_position"] == 2 * 2 * 2 * 64 * 4            # 2 layers x (K, V) x 2 kv heads x 64 x float32
+    assert mem["weight_bytes"] == mem["weight_bytes_per_step"]              # tied: the embedding is also the head
     # more requests than slots: batches follow one another
     m2 = Model.load(model.folder, dtype="float32", max_tokens_in_cache=256, n_slots=2)
     got = m2.generate(prompts, 8, SamplerConfig.plain(0.0), stop_ids=())
@@ -327,6 +333,14 @@ def test_a_random_model_saved_and_loaded_again(dtype, tmp_path):
     want = plain_impl.forward(weights, cfg.to_dict(), toks)
     got = m.logits(toks)
     assert rel_err(got, want) <= TOL[dtype]
+    # the device-made weights are a function of (seed, tensor name, element) that the host can restate
+    import zlib
+    from rust_inference_b200.sampling import rng
+    name = "model.layers.1.mlp.down_proj.weight"
+    key = (12 * 1_000_003 + zlib.crc32(name.encode())) % (2 ** 63 - 1)
+    got_w = m.state_dict()[name].float().flatten().cpu()
+    for i in (0, 5, got_w.numel() - 1):
+        assert abs(float(got_w[i]) - 0.08 * rng.normal(key, i)) <= (1e-6 if dtype == "float32" else 1e-3)
     folder = m.save_safetensors(str(tmp_path / "saved"))
     again = Model.load(folder, dtype=dtype, max_tokens_in_cache=512).logits(toks)
     assert rel_err(again, got) <= (1e-6 if dtype == "float32" else 2e-2)

@@ -662,3 +662,63 @@ def test_sampling_top_k_with_more_ties_than_the_list_holds(sampling_kernel):
         cdf = torch.cumsum(p, dim=0)
         lo = cdf[got[r] - 1].item() if got[r] > 0 else 0.0
         assert lo - 2e-5 <= u <= cdf[got[r]].item() + 2e-5, (r, got[r], u)
+
+
+# ----------------------------------------------------------------------------------------
+# load-time kernels and the step's own bookkeeping kernel
+# ----------------------------------------------------------------------------------------
+@pytest.mark.parametrize("n", [1, 255, 256, 100_003])
+def test_cast_between_the_two_precisions(n):
+    ops = _ops()
+    x = torch.randn(n, device=DEV) * 100
+    x[0] = 1.00390625                                    # exactly between two bfloat16 values: ties go to even
+    down = ops.cast(x, torch.bfloat16)
+    assert down.dtype == torch.bfloat16 and torch.equal(down, x.to(torch.bfloat16))
+    up = ops.cast(down, torch.float32)
+    assert up.dtype == torch.float32 and torch.equal(up, down.float())       # widening is exact
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_fill_normal_is_a_function_of_key_and_index(dtype):
+    ops = _ops()
+    key = 0x1234_5678_9ABC_DEF0
+    out = torch.empty(3, 1001, dtype=dtype, device=DEV)
+    ops.fill_normal(out, key, mean=1.0, std=0.2)
+    flat = out.float().flatten().cpu()
+    for i in (0, 1, 2, 1000, 1001, 3002):
+        want = 1.0 + 0.2 * rng.normal(key, i)
+        tol = 1e-5 if dtype == torch.float32 else 8e-3
+        assert abs(float(flat[i]) - want) <= tol, i
+    again = torch.empty(3003, dtype=dtype, device=DEV)
+    ops.fill_normal(again, key, mean=1.0, std=0.2)
+    assert torch.equal(again.flatten(), out.flatten())                   # the shape does not matter
+    other = torch.empty(3003, dtype=dtype, device=DEV)
+    ops.fill_normal(other, key + 1, mean=1.0, std=0.2)
+    assert not torch.equal(other, again)
+    big = torch.empty(1 << 20, device=DEV)
+    ops.fill_normal(big, 7)
+    assert abs(float(big.mean())) < 5e-3 and abs(float(big.std()) - 1.0) < 5e-3
+    assert float(big.abs().max()) < 6.0                                  # 24-bit uniforms: |z| <= 5.77
+
+
+def test_advance_decode_moves_a_step_on():
+    ops = _ops()
+    n = 300
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    pos, start, length = i32(list(range(n))), i32(list(range(n))), i32([i + 1 for i in range(n)])
+    toks = i32([7 * i % 1000 for i in range(n)])
+    counter, turn = i32([3] * n), i32([0])
+    host = torch.full((4, n), -1, dtype=torch.int32).pin_memory()
+    log = torch.full((8, n), -1, dtype=torch.int32, device=DEV)
+    for step in range(6):
+        toks += 1
+        ops.advance_decode(pos, start, length, toks, draw_counter=counter, turn=turn, host_ring=host, log_ring=log)
+    torch.cuda.synchronize()
+    assert pos.tolist() == [i + 6 for i in range(n)] and start.tolist() == pos.tolist()
+    assert length.tolist() == [i + 7 for i in range(n)] and counter.tolist() == [9] * n and turn.item() == 6
+    final = toks.cpu()
+    assert torch.equal(host[5 % 4], final) and torch.equal(host[4 % 4], final - 1)     # the ring's last two slots
+    assert torch.equal(log[5].cpu(), final) and torch.equal(log[0].cpu(), final - 5)
+    # without the optional parts only the three arrays move
+    ops.advance_decode(pos, start, length, toks)
+    assert pos[0].item() == 7 and turn.item() == 6
