@@ -12,6 +12,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <vector>
+#include <unordered_set>
 
 #define RI_API extern "C" __attribute__((visibility("default")))
 
@@ -228,6 +229,171 @@ RI_API int ri_pager_audit(void* h) {
         if (slot_seen[s] != 1) return fail(-1, "slot accounting broken: a slot is lost or held twice");
         if (!p->live[s] && (!p->pages[s].empty() || p->length[s] != 0))
             return fail(-1, "free slot %d still holds pages or a length", s);
+    }
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// The generation loop's books: what every request has generated so far and whether it goes on.
+//
+// The reference's loop serves one prompt (model.rs:332-478): it samples, breaks BEFORE emitting when
+// the token is a stop id (model.rs:383-387), emits, and runs at most max_tokens iterations
+// (model.rs:373); it keeps every token of prompt and generation for the repetition window
+// (model.rs:357, :364, :440).  Here the same rules are kept per request of a batch, with one change:
+// a sequence that has no position left in the cache ends with reason "length" instead of a panic
+// (kv_cache.rs:54-59).  The loop in Python launches steps and reads tokens; every decision about a
+// request is made here.
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+enum Finish { GEN_LIVE = 0, GEN_STOP = 1, GEN_LENGTH = 2 };
+
+struct GenRequest {
+    int prompt_len = 0;
+    int finished = GEN_LIVE;
+    std::vector<int> tokens;      // generated, stop ids not among them
+    std::vector<int> history;     // prompt and generated tokens, kept only when a sampler wants them
+};
+
+struct GenBooks {
+    int max_tokens, max_seq_len;
+    bool keep_history;
+    std::unordered_set<int> stop_ids;
+    std::vector<GenRequest> reqs;
+
+    // Will the request certainly be stepped again after its `drawn`-th token?  Length limits are known
+    // in advance; stop tokens are not.
+    bool goes_on(const GenRequest& r, int drawn) const {
+        return drawn < max_tokens && r.prompt_len + drawn <= max_seq_len;
+    }
+};
+
+GenBooks* as_books(void* p) { return static_cast<GenBooks*>(p); }
+
+int check_request(const GenBooks* g, int i) {
+    if (i < 0 || i >= (int)g->reqs.size()) return fail(-1, "request %d does not exist (0..%d)", i, (int)g->reqs.size() - 1);
+    return 0;
+}
+
+}  // namespace
+
+RI_API void* ri_gen_create(int max_tokens, int max_seq_len, const int* stop_ids, int n_stop, int keep_history) {
+    if (max_seq_len <= 0) {
+        fail(0, "max_seq_len must be positive");
+        return nullptr;
+    }
+    GenBooks* g = new GenBooks{max_tokens, max_seq_len, keep_history != 0, {}, {}};
+    for (int i = 0; i < n_stop; ++i) g->stop_ids.insert(stop_ids[i]);
+    return g;
+}
+
+RI_API void ri_gen_destroy(void* h) { delete as_books(h); }
+
+// A new request; returns its index.
+RI_API int ri_gen_add(void* h, const int* prompt, int prompt_len) {
+    GenBooks* g = as_books(h);
+    if (prompt_len <= 0) return fail(-1, "request %d: empty prompt", (int)g->reqs.size());
+    if (prompt_len > g->max_seq_len)
+        return fail(-2, "request %d: prompt of %d tokens exceeds max_seq_len %d", (int)g->reqs.size(), prompt_len, g->max_seq_len);
+    GenRequest r;
+    r.prompt_len = prompt_len;
+    if (g->keep_history) r.history.assign(prompt, prompt + prompt_len);
+    g->reqs.push_back(std::move(r));
+    return (int)g->reqs.size() - 1;
+}
+
+// How many requests, starting at `first`, fit the cache together: every admitted request has pages for
+// its prompt plus all the tokens it may generate, so a batch never runs out of room half way.
+// max_batch <= 0: no limit.  Returns the count (>= 1), or a negative code if even one does not fit.
+RI_API int ri_gen_admit(void* h, void* pager, int first, int max_batch) {
+    GenBooks* g = as_books(h);
+    Pager* p = as_pager(pager);
+    long long free_pages = (long long)p->free_pages.size(), free_slots = (long long)p->free_slots.size();
+    int n = 0;
+    while (first + n < (int)g->reqs.size()) {
+        if (max_batch > 0 && n >= max_batch) break;
+        const int length = std::min(g->reqs[first + n].prompt_len + g->max_tokens, g->max_seq_len);
+        const int need = (length + p->page_size - 1) / p->page_size;
+        if (need > free_pages || free_slots == 0) break;
+        free_pages -= need;
+        free_slots -= 1;
+        ++n;
+    }
+    if (n == 0 && first < (int)g->reqs.size())
+        return fail(-3, "request %d (prompt of %d tokens, up to %d more) does not fit the cache even alone", first,
+                    g->reqs[first].prompt_len, g->max_tokens);
+    return n;
+}
+
+// flags[i] = 1 if request idx[i] will certainly be stepped again after its drawn[i]-th token.  Returns how many.
+RI_API int ri_gen_goes_on(void* h, int n, const int* idx, const int* drawn, int* flags) {
+    GenBooks* g = as_books(h);
+    int count = 0;
+    for (int i = 0; i < n; ++i) {
+        if (int rc = check_request(g, idx[i])) return rc;
+        flags[i] = g->goes_on(g->reqs[idx[i]], drawn[i]) ? 1 : 0;
+        count += flags[i];
+    }
+    return count;
+}
+
+// Books one sampled token per listed request.  status[i]: 0 the request goes on (the token is to be fed),
+// 1 it sampled a stop id (not emitted, not fed back), 2 it ends by length (the token is its last).
+// Returns how many go on.
+RI_API int ri_gen_book(void* h, int n, const int* idx, const int* tokens, int* status) {
+    GenBooks* g = as_books(h);
+    int going = 0;
+    for (int i = 0; i < n; ++i) {
+        if (int rc = check_request(g, idx[i])) return rc;
+        GenRequest& r = g->reqs[idx[i]];
+        if (r.finished != GEN_LIVE) return fail(-4, "request %d has ended already", idx[i]);
+        if (g->stop_ids.count(tokens[i])) {
+            r.finished = GEN_STOP;
+        } else {
+            r.tokens.push_back(tokens[i]);
+            if (g->keep_history) r.history.push_back(tokens[i]);
+            const int made = (int)r.tokens.size();
+            if (made >= g->max_tokens || r.prompt_len + made > g->max_seq_len) r.finished = GEN_LENGTH;   // no position left to feed it at
+        }
+        status[i] = r.finished;
+        going += r.finished == GEN_LIVE;
+    }
+    return going;
+}
+
+RI_API int ri_gen_token_count(void* h, int i) {
+    GenBooks* g = as_books(h);
+    if (int rc = check_request(g, i)) return rc;
+    return (int)g->reqs[i].tokens.size();
+}
+
+RI_API int ri_gen_finish(void* h, int i) {
+    GenBooks* g = as_books(h);
+    if (int rc = check_request(g, i)) return rc;
+    return g->reqs[i].finished;
+}
+
+// The request's generated tokens into out[0..cap); returns how many there are.
+RI_API int ri_gen_tokens(void* h, int i, int* out, int cap) {
+    GenBooks* g = as_books(h);
+    if (int rc = check_request(g, i)) return rc;
+    const std::vector<int>& t = g->reqs[i].tokens;
+    for (int k = 0; k < (int)t.size() && k < cap; ++k) out[k] = t[k];
+    return (int)t.size();
+}
+
+// The last `keep` ids of each listed request's history (prompt and generated tokens) as rows of
+// `width` ints, left-aligned, with their counts: what the sampler's repetition window is filled from.
+RI_API int ri_gen_recent(void* h, int n, const int* idx, int keep, int width, int* counts, int* rows) {
+    GenBooks* g = as_books(h);
+    if (!g->keep_history) return fail(-5, "these books keep no history");
+    if (keep > width) return fail(-6, "a row of %d ids cannot hold %d", width, keep);
+    for (int i = 0; i < n; ++i) {
+        if (int rc = check_request(g, idx[i])) return rc;
+        const std::vector<int>& hist = g->reqs[idx[i]].history;
+        const int take = std::max(0, std::min(keep, (int)hist.size()));
+        counts[i] = take;
+        for (int k = 0; k < take; ++k) rows[(size_t)i * width + k] = hist[hist.size() - take + k];
     }
     return 0;
 }

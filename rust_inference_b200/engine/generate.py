@@ -12,6 +12,10 @@ next step is launched with the sampled tokens fed on the device, and the host re
 tokens of the step before while it runs.  Which sequences end by length is known in advance;
 a sequence that turns out to have sampled a stop token has simply run one step for nothing.
 
+The loop here launches steps and reads tokens; what every request has generated, whether it goes on
+and which requests fit the cache together is kept and decided by the native host runtime
+(`engine/books.py` over `csrc/host_runtime.cpp`).
+
 Kept from the reference: a sampled stop token ends the sequence and is not emitted
 (model.rs:383-387); at most max_tokens tokens are generated (model.rs:373).  Changed: a
 sequence that reaches the cache's max_seq_len ends with reason "length" instead of the
@@ -21,7 +25,9 @@ nothing will follow (the reference runs one, model.rs:431-438).
 from __future__ import annotations
 
 import time
-from dataclasses import dataclass, field
+from dataclasses import dataclass
+
+from .books import LIVE, REASONS, GenerationBooks
 
 
 @dataclass
@@ -33,11 +39,10 @@ class GenerationResult:
 
 @dataclass
 class _Live:
-    index: int                    # which request
+    index: int                    # which request (its tokens and history are in the books)
     slot: int
     prompt_length: int
-    tokens: list = field(default_factory=list)
-    history: list = field(default_factory=list)
+    drawn: int = 0                # tokens sampled for it so far, read or not
 
 
 class CudaLoopDevice:
@@ -78,54 +83,30 @@ class Generator:
         self.steps = 0                # model steps run (prefill and decode)
         self.d2h_bytes = 0            # bytes of sampled tokens read back
 
-    # ---- admission: which requests start together ---------------------------------
-    def _admit(self, prompts, first: int, max_tokens: int) -> int:
-        """How many requests, starting at `first`, fit the cache together.  Every admitted
-        request has pages for its prompt plus all the tokens it may generate, so a batch
-        never runs out of room half way."""
-        pager = self.engine.cache.pager
-        page = pager.page_size
-        free_pages, free_slots = pager.free_page_count(), pager.free_slot_count()
-        n = 0
-        while first + n < len(prompts):
-            if self.max_batch is not None and n >= self.max_batch:
-                break
-            length = min(len(prompts[first + n]) + max_tokens, self.engine.max_seq_len)
-            need = -(-length // page)
-            if need > free_pages or free_slots == 0:
-                break
-            free_pages -= need
-            free_slots -= 1
-            n += 1
-        if n == 0:
-            raise RuntimeError(
-                f"request {first} (prompt of {len(prompts[first])} tokens, up to {max_tokens} more) "
-                f"does not fit the cache even alone")
-        return n
-
     def _to_host(self, tokens) -> list:
         if hasattr(tokens, "cpu"):
             tokens = tokens.cpu()
             self.d2h_bytes += tokens.numel() * tokens.element_size()
         return [int(t) for t in (tokens.tolist() if hasattr(tokens, "tolist") else tokens)]
 
-    def _finish_or_keep(self, s, tok, max_tokens, results) -> bool:
-        """Book one sampled token of sequence s; returns True if s goes on."""
-        reason = None
-        if tok in self.stop_ids:
-            reason = "stop"                                          # not emitted, not fed back
-        else:
-            s.tokens.append(tok)
-            if len(s.tokens) >= max_tokens:
-                reason = "length"
-            elif s.prompt_length + len(s.tokens) > self.engine.max_seq_len:
-                reason = "length"                                    # no position left to feed it at
-        if reason is None:
-            return True
-        results[s.index] = GenerationResult(s.tokens, reason, s.prompt_length)
-        self.engine.free_slot(s.slot)                                # the slot is free for the next batch
-        s.slot = -1
-        return False
+    def _histories(self, seqs, keep=None):
+        """The sampler's view of each sequence's past: the last ids of prompt and generated tokens."""
+        window = getattr(getattr(self.sampler, "params", None), "repetition_window", 64)
+        return self.books.recent([s.index for s in seqs], window if keep is None else keep)
+
+    def _book(self, seqs, tokens, results) -> list:
+        """Book one sampled token per sequence; returns the sequences that go on.  One that ends gives
+        its result and its slot back at once."""
+        status = self.books.book([s.index for s in seqs], tokens)
+        still = []
+        for s, st in zip(seqs, status):
+            if st == LIVE:
+                still.append(s)
+                continue
+            results[s.index] = GenerationResult(self.books.tokens(s.index), REASONS[st], s.prompt_length)
+            self.engine.free_slot(s.slot)                            # the slot is free for the next batch
+            s.slot = -1
+        return still
 
     def _run_batch(self, live, prompts, max_tokens, results, uses_history) -> None:
         """Step, sample, read the tokens, decide, step again."""
@@ -134,20 +115,17 @@ class Generator:
             logits = self.engine.step([s.slot for s in live], feed, "last", borrow=True)
             self.steps += 1
             sampled = self._to_host(self.sampler.sample(
-                logits, [s.index for s in live], [len(s.tokens) for s in live],
-                [s.history for s in live] if uses_history else None))
+                logits, [s.index for s in live], [s.drawn for s in live],
+                self._histories(live) if uses_history else None))
             if hasattr(self.engine, "check_device_status"):
                 self.engine.check_device_status()
             if self.step_times is not None:
                 self.step_times.append(time.perf_counter())
-            still, feed = [], []
-            for s, tok in zip(list(live), sampled):
-                if self._finish_or_keep(s, tok, max_tokens, results):
-                    if uses_history:
-                        s.history.append(tok)
-                    still.append(s)
-                    feed.append([tok])
-            live[:] = still
+            for s in live:
+                s.drawn += 1
+            fed = dict(zip((id(s) for s in live), sampled))
+            live[:] = self._book(live, sampled, results)
+            feed = [[fed[id(s)]] for s in live]
             if not live:
                 return
 
@@ -162,10 +140,7 @@ class Generator:
         ring = [dev.host_buffer(len(live)) for _ in range(4)]
         turn = [0]
 
-        def goes_on(s, drawn) -> bool:
-            """Will s certainly be stepped again after its next token (its drawn-th)?  Length limits are
-            known in advance; stop tokens are not."""
-            return drawn < max_tokens and s.prompt_length + drawn <= eng.max_seq_len
+        books = self.books
 
         # A sampler that needs no token history can live inside the captured decode step: one graph
         # launch then runs the model, samples, and moves the step's arrays on for the next launch.
@@ -178,31 +153,41 @@ class Generator:
             # straight into the buffer the next step of this batch size reads its tokens from, if the
             # whole batch will be stepped again at this size
             out = None
-            if hasattr(eng, "decode_token_buffer") and all(goes_on(s, d + 1) for s, d in zip(seqs, drawn)):
+            if hasattr(eng, "decode_token_buffer") and all(books.goes_on([s.index for s in seqs], [d + 1 for d in drawn])):
                 out = eng.decode_token_buffer(len(seqs), in_step) if in_step is not None else eng.decode_token_buffer(len(seqs))
             # With a repetition penalty the host's histories lack the token that was just fed (it has not
             # been read yet): the kernel takes that one from the device.  It reads `newest` before it writes
             # `out`, so the two may be the same buffer.
-            tokens_dev = self.sampler.sample(logits, [s.index for s in seqs], drawn,
-                                             [s.history for s in seqs] if uses_history else None,
+            # (the host's histories then give one id fewer, so that the window holds the same ids)
+            hist = None
+            if uses_history:
+                window = getattr(self.sampler.params, "repetition_window", 64)
+                hist = self._histories(seqs, window - 1 if (newest is not None and window > 0) else window)
+            tokens_dev = self.sampler.sample(logits, [s.index for s in seqs], drawn, hist,
                                              out=out, mirror=host, newest=newest if uses_history else None)
+            for s in seqs:
+                s.drawn += 1
             self.d2h_bytes += len(seqs) * 4
             return tokens_dev, (host, dev.mark())
 
         logits = eng.step([s.slot for s in live], [list(prompts[s.index]) for s in live], "last", borrow=True)
         self.steps += 1
-        pending = (list(live),) + sample(logits, live, [len(s.tokens) for s in live])    # sequences, tokens on the device, (host copy, mark)
+        pending = (list(live),) + sample(logits, live, [s.drawn for s in live])    # sequences, tokens on the device, (host copy, mark)
         while pending is not None:
             seqs, tokens_dev, (host, mark) = pending
-            rows = [i for i, s in enumerate(seqs) if goes_on(s, len(s.tokens) + 1)]
+            # who certainly goes on after the token just sampled (its drawn-th)?
+            flags = books.goes_on([s.index for s in seqs], [s.drawn for s in seqs])
+            rows = [i for i, on in enumerate(flags) if on]
             nxt = None
             if rows:
                 ahead = [seqs[i] for i in rows]
                 feed_dev = tokens_dev if len(rows) == len(seqs) else dev.rows(tokens_dev, rows)
-                drawn = [len(s.tokens) + 1 for s in ahead]
+                drawn = [s.drawn for s in ahead]
                 if in_step is not None:
                     sampled, host2 = eng.step_and_sample_from_device([s.slot for s in ahead], feed_dev, in_step,
                                                                      [s.index for s in ahead], drawn)
+                    for s in ahead:
+                        s.drawn += 1
                     self.d2h_bytes += len(ahead) * 4
                     nxt = (ahead, sampled, (host2, dev.mark()))
                 else:
@@ -214,12 +199,8 @@ class Generator:
                 eng.check_device_status()
             if self.step_times is not None:
                 self.step_times.append(time.perf_counter())
-            stopped = set()
-            for s, tok in zip(seqs, host.tolist()):
-                if not self._finish_or_keep(s, int(tok), max_tokens, results):
-                    stopped.add(id(s))
-                elif uses_history:
-                    s.history.append(int(tok))
+            going = self._book(seqs, host.tolist(), results)
+            stopped = {id(s) for s in seqs} - {id(s) for s in going}
             if nxt is not None and stopped:
                 # a sequence that sampled a stop token ran the step ahead for nothing: drop its row
                 ahead, sampled, (host2, mark2) = nxt
@@ -234,23 +215,19 @@ class Generator:
 
     # ---- the loop ---------------------------------------------------------------------
     def generate(self, prompts: list, max_tokens: int) -> list:
-        for i, p in enumerate(prompts):
-            if len(p) == 0:
-                raise ValueError(f"request {i}: empty prompt")
-            if len(p) > self.engine.max_seq_len:
-                raise ValueError(f"request {i}: prompt of {len(p)} tokens exceeds max_seq_len "
-                                 f"{self.engine.max_seq_len}")
         results: list = [None] * len(prompts)
+        uses_history = getattr(getattr(self.sampler, "params", None), "uses_history", False)
+        self.books = books = GenerationBooks(max_tokens, self.engine.max_seq_len, self.stop_ids, uses_history)
+        for p in prompts:
+            books.add(p)                                             # refuses an empty or over-long prompt
         if max_tokens <= 0:
             return [GenerationResult([], "length", len(p)) for p in prompts]
-        uses_history = getattr(getattr(self.sampler, "params", None), "uses_history", False)
         nxt = 0
         while nxt < len(prompts):
-            count = self._admit(prompts, nxt, max_tokens)
+            count = books.admit(self.engine.cache.pager, nxt, self.max_batch)
             live = []
             for i in range(nxt, nxt + count):
-                live.append(_Live(index=i, slot=self.engine.alloc_slot(), prompt_length=len(prompts[i]),
-                                  history=list(prompts[i]) if uses_history else []))
+                live.append(_Live(index=i, slot=self.engine.alloc_slot(), prompt_length=len(prompts[i])))
             nxt += count
             lookahead = (hasattr(self.sampler, "sample")
                          and getattr(self.engine, "can_feed_from_device", lambda: False)())
