@@ -843,8 +843,6 @@ int sm_count() {
     return n;
 }
 
-int g_smem_budget = 0;       // 0: the default for the tile; set through ri_gemm_tcgen05_set_smem_budget
-
 template <int TN, bool DUAL, int MODE>
 int launch(int tn, const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx, const float* bias, void* out,
            int n_tok, int n_feat, int K, int split_k, int* status, cudaStream_t stream) {
@@ -852,8 +850,7 @@ int launch(int tn, const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensor
     const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
     // Small token tiles (decode) leave room for a second CTA on the SM, so that the next kernel's
     // CTAs can settle in and prefetch their weights while this one drains.
-    int budget = g_smem_budget > 0 ? g_smem_budget : (3 * STAGE_BYTES <= 108 * 1024 && TN <= 64 ? 108 * 1024 : SMEM_BUDGET);
-    if (budget > SMEM_BUDGET) budget = SMEM_BUDGET;
+    const int budget = (3 * STAGE_BYTES <= 108 * 1024 && TN <= 64) ? 108 * 1024 : SMEM_BUDGET;
     int stages = budget / STAGE_BYTES;
     if (stages > MAX_STAGES) stages = MAX_STAGES;
     if (stages > total_kb) stages = total_kb;
@@ -996,22 +993,6 @@ RI_API int ri_gemm_tcgen05_set_pairs(int n_tok, int always) {
     return 0;
 }
 
-// Shared memory a CTA may use for its stage ring, in bytes (0 restores the defaults).  For tuning.
-RI_API int ri_gemm_tcgen05_set_smem_budget(int bytes) {
-    g_smem_budget = bytes;
-    return 0;
-}
-
-int g_long_tile = 0;         // 0: pick by the grid; set through ri_gemm_tcgen05_set_long_tile
-
-// Token tile of steps of more than 128 tokens in the feature-major kernel: a multiple of 16 in
-// 128..256, or 0 to let the grid decide.  For tuning.
-RI_API int ri_gemm_tcgen05_set_long_tile(int tn) {
-    if (tn != 0 && (tn < 128 || tn > 256 || tn % 16)) return fail("gemm_tcgen05: no long tile of %d tokens", tn);
-    g_long_tile = tn;
-    return 0;
-}
-
 // How a product of n_tok tokens, n_feat features and inner size K is cut: the token tile (rows of the
 // activation box, written to *tile) and, for the residual epilogue (mode 2, the only one that can
 // add partial sums), over how many pieces K is split (*split; 1 for the other modes).
@@ -1053,7 +1034,6 @@ RI_API int ri_gemm_tcgen05_plan(int n_tok, int n_feat, int K, int mode, int* til
         long long best_cost = -1;
         const int max_split = can_split ? (total_kb / 4 < 10 ? (total_kb / 4 < 1 ? 1 : total_kb / 4) : 10) : 1;
         for (int t = 128; t <= 256; t += 16) {
-            if (g_long_tile && t != g_long_tile) continue;
             const long long tiles = (long long)((n_tok + t - 1) / t) * feat_tiles;
             for (int s = 1; s <= max_split; ++s) {
                 const long long items = tiles * s;

@@ -41,7 +41,11 @@ def decode_splits(n_seqs: int, n_kv_heads: int, max_seq_len: int, page_size: int
 
 def decode_plan(n_seqs: int, n_kv_heads: int, max_seq_len: int, page_size: int):
     """Which decode kernel a step of n_seqs sequences takes, and into how many runs of pages it
-    cuts a sequence: ("cluster" | "tma" | "cp_async", splits).
+    cuts a sequence: ("cluster" | "tma" | "cp_async", splits).  Left to itself it answers "cluster"
+    (2..8 runs) while a step's sequences x kv heads leave SMs idle, and "tma" with one run per
+    sequence beyond; "cp_async" (runs merged through scratch by a second kernel) is only taken when
+    RI_B200_DECODE_ATTENTION asks for it: it is the kernel of the allocation-free entry point and
+    the comparison for the other two.
 
     Split runs are merged inside the kernel when the splits of a (sequence, kv head) fit a
     thread-block cluster: no scratch round trip and no second kernel.  Large batches are not
