@@ -326,7 +326,8 @@ __device__ void apply_penalty(float* p, int lo, int hi, float penalty, const int
 __global__ void __launch_bounds__(THREADS)
 sample_kernel(float* __restrict__ logits, int vocab, int* out, float temperature, int top_k,
               float top_p, float penalty, const int* __restrict__ recent, int recent_ld,
-              const int* __restrict__ recent_count, unsigned long long seed, const int* __restrict__ row_stream,
+              const int* __restrict__ recent_count, unsigned long long seed, const unsigned long long* __restrict__ seed_ptr,
+              const int* __restrict__ row_stream,
               const int* __restrict__ row_counter, int counter_offset, int* __restrict__ mirror,
               const int* newest) {      // `newest` and `out` may be the same buffer: a row reads before it writes
     __shared__ float fscratch[33];
@@ -388,6 +389,7 @@ sample_kernel(float* __restrict__ logits, int vocab, int* out, float temperature
     }
     tmax = tmax / temperature;                               // the largest x this thread saw
     const float m = block_max(tmax, fscratch);
+    if (seed_ptr != nullptr) seed = *seed_ptr;                   // a seed kept on the device (a captured step's)
     const float u = uniform_open_closed(seed, (unsigned)row_stream[r], (unsigned)(row_counter[r] + counter_offset));
     // the second pass is made warp by warp over contiguous stretches of the row, so that what it finds keeps
     // the order of the ids
@@ -541,7 +543,8 @@ constexpr int GROUPS = CLUSTER * WARPS;      // stretches of a row: one per warp
 __global__ void __launch_bounds__(THREADS)
 sample_cluster_kernel(float* __restrict__ logits, int vocab, int per_cta, int* out, float temperature, int top_k,
                       float top_p, float penalty, const int* __restrict__ recent, int recent_ld,
-                      const int* __restrict__ recent_count, unsigned long long seed, const int* __restrict__ row_stream,
+                      const int* __restrict__ recent_count, unsigned long long seed, const unsigned long long* __restrict__ seed_ptr,
+              const int* __restrict__ row_stream,
                       const int* __restrict__ row_counter, int counter_offset, int* __restrict__ mirror,
                       const int* newest) {      // `newest` and `out` may be the same buffer: a row reads before it writes
     namespace cg = cooperative_groups;
@@ -637,6 +640,7 @@ sample_cluster_kernel(float* __restrict__ logits, int vocab, int per_cta, int* o
     tmax = tmax / temperature;                                   // the largest x of this warp's stretch
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
     if (lane < CLUSTER) cluster.map_shared_rank(rx_wmax, lane)[rank * WARPS + warp] = tmax;
+    if (seed_ptr != nullptr) seed = *seed_ptr;                   // a seed kept on the device (a captured step's)
     const float u = uniform_open_closed(seed, (unsigned)row_stream[r], (unsigned)(row_counter[r] + counter_offset));
     cluster.sync();
     float m = -INFINITY;
@@ -815,10 +819,12 @@ int g_cluster_min_vocab = 32768;
 // mirror (may be null): int32 [rows] in host memory the device can write; receives the tokens too.
 // newest (may be null): int32 [rows] on the device, one more recent id per row (the token of the step
 // before, which the host may not have read yet); penalised after the ids of `recent`.
+// seed_dev (may be null): a 64-bit seed on the device that takes the place of `seed` (a captured step
+// keeps its seed there, so that another seed needs no other capture).
 RI_API int ri_sample(float* logits, int rows, int vocab, int* out, float temperature, int top_k, float top_p,
                      float penalty, const int* recent, int recent_ld, const int* recent_count,
                      unsigned long long seed, const int* row_stream, const int* row_counter, int counter_offset,
-                     int* mirror, const int* newest, cudaStream_t stream) {
+                     int* mirror, const int* newest, const unsigned long long* seed_dev, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (vocab <= 0) return fail("sample: vocabulary of %d", vocab);
     if (penalty <= 0.f) return fail("sample: repetition penalty %f must be positive", penalty);
@@ -857,12 +863,12 @@ RI_API int ri_sample(float* logits, int rows, int vocab, int* out, float tempera
         cfg.attrs = attr;
         cfg.numAttrs = pdl_enabled() ? 2 : 1;
         cudaError_t e = cudaLaunchKernelEx(&cfg, sample_cluster_kernel, logits, vocab, per_cta, out, temperature, top_k, top_p,
-                                           penalty, recent, recent_ld, recent_count, seed, row_stream, row_counter,
+                                           penalty, recent, recent_ld, recent_count, seed, seed_dev, row_stream, row_counter,
                                            counter_offset, mirror, newest);
         return check_launch(e, "sample (cluster)");
     }
     cudaError_t e = launch_dependent(sample_kernel, dim3(rows), dim3(THREADS), (size_t)0, stream, logits, vocab, out,
-                                     temperature, top_k, top_p, penalty, recent, recent_ld, recent_count, seed,
+                                     temperature, top_k, top_p, penalty, recent, recent_ld, recent_count, seed, seed_dev,
                                      row_stream, row_counter, counter_offset, mirror, newest);
     return check_launch(e, "sample");
 }

@@ -9,6 +9,7 @@ passed by the caller (model.rs:361-363); here the position comes from the slot's
 """
 from __future__ import annotations
 
+import dataclasses
 from collections import OrderedDict
 
 import numpy as np
@@ -223,23 +224,28 @@ class Engine:
         self.cache.advance(slots, [len(t) for t in tokens])
         return logits
 
+    @staticmethod
+    def _graph_key(n: int, sampler):
+        # the seed lives on the device beside the draw counters: steps that differ in it share a capture
+        return (n, None if sampler is None else dataclasses.replace(sampler, seed=0))
+
     def _graph_for(self, n: int, sampler=None):
         """The captured decode step of n sequences, with the sampler inside it if one is given (made
         on first use; call with the device current).  Only the most recently used ones are kept."""
-        key = (n, sampler)
+        key = self._graph_key(n, sampler)
         graph = self._graphs.get(key)
         if graph is None:
             from .graphs import MAX_SIZES, DecodeGraph
             while len(self._graphs) >= MAX_SIZES:
                 self._graphs.popitem(last=False)
-            graph = self._graphs[key] = DecodeGraph(self, n, sampler)
+            graph = self._graphs[key] = DecodeGraph(self, n, key[1])
         else:
             self._graphs.move_to_end(key)
         return graph
 
     def decode_graph(self, n: int, sampler=None):
         """The decode step of n sequences as the engine holds it (None if it has not been used yet)."""
-        return self._graphs.get((n, sampler))
+        return self._graphs.get(self._graph_key(n, sampler))
 
     def shared_decode_logits(self, n: int) -> torch.Tensor:
         """float32 [n, vocab] for decode steps of batch sizes that have no buffer of their own yet; the
@@ -260,7 +266,7 @@ class Engine:
         with torch.cuda.device(self.device):
             return self._graph_for(n, sampler).ctx.token_ids
 
-    def _enter_decode(self, graph, slots: list, streams=None, counters=None) -> None:
+    def _enter_decode(self, graph, slots: list, streams=None, counters=None, seed=None) -> None:
         """Reserve a position for every sequence and make the graph's static arrays describe this step.
         When the step before was of the same sequences the arrays are already there (that step moved
         them on), and nothing is copied; otherwise they come from the host, together with the
@@ -272,7 +278,7 @@ class Engine:
         self.cache.reserve([(s, st + 1) for s, st in zip(slots, starts)])
         if graph.rows is not None:
             streams, counters = list(streams), list(counters)
-        if graph.holds(slots, starts, streams, counters):
+        if graph.holds(slots, starts, streams, counters, seed):
             return
         meta, layout, _ = pack_step(starts, [[0]] * n, [[0]] * n)
         o, c = layout["seq_slot"]
@@ -280,10 +286,13 @@ class Engine:
         if graph.rows is not None:
             if len(streams) != n or len(counters) != n:
                 raise ValueError("a step that samples needs a stream and a draw counter per sequence")
-            meta = np.concatenate([meta, np.asarray(streams, dtype=np.int32), np.asarray(counters, dtype=np.int32)])
+            seed_words = np.asarray([int(seed) & 0xFFFFFFFFFFFFFFFF], dtype=np.uint64).view(np.int32)
+            meta = np.concatenate([meta, np.asarray(streams, dtype=np.int32), np.asarray(counters, dtype=np.int32),
+                                   seed_words])
         dev = self._ring.stage(meta, self.device)
         self.h2d_bytes += meta.nbytes
-        graph.load_meta(dev, keep_tokens=True, slots=slots, starts=starts, streams=streams, counters=counters)
+        graph.load_meta(dev, keep_tokens=True, slots=slots, starts=starts, streams=streams, counters=counters,
+                        seed=seed)
 
     def _feed(self, graph, tokens_dev: torch.Tensor) -> None:
         if tokens_dev.numel() != graph.n_seqs or tokens_dev.dtype != torch.int32:
@@ -319,7 +328,7 @@ class Engine:
         step costs the host one graph launch: positions and draw counters move on on the device."""
         with torch.cuda.device(self.device):
             graph = self._graph_for(len(slots), sampler_config)
-            self._enter_decode(graph, slots, streams, counters)
+            self._enter_decode(graph, slots, streams, counters, sampler_config.seed)
             self._feed(graph, tokens_dev)
             graph.launch()
         self.cache.advance(slots, [1] * len(slots))
@@ -351,7 +360,7 @@ class Engine:
             while done < n_steps:
                 run = min(LOG_RING, n_steps - done)
                 for i in range(run):
-                    self._enter_decode(graph, slots, streams, [done + i] * n)
+                    self._enter_decode(graph, slots, streams, [done + i] * n, cfg.seed)
                     if done + i == 0:
                         self._feed(graph, first)
                     graph.launch()

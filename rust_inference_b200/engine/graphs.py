@@ -63,11 +63,13 @@ class DecodeGraph:
         self.eager_steps = 0
         self.held = None              # [slots, lengths before the step, streams, draw counters] the static arrays describe now
         self.turn = 0                 # steps run: the host's copy of the device counter that picks the ring slots
-        self.rows = self.turn_dev = self.host_ring = self.log = None
+        self.rows = self.turn_dev = self.host_ring = self.log = self.seed_dev = None
         if sampler is not None:
             if sampler.uses_history:
                 raise ValueError("a step can only hold a sampler that needs no token history")
-            self.rows = torch.zeros(2 * n_seqs, dtype=torch.int32, device=dev)        # streams, then draw counters
+            # streams, then draw counters, then the seed (64 bits): another seed needs no other capture
+            self.rows = torch.zeros(2 * n_seqs + 2, dtype=torch.int32, device=dev)
+            self.seed_dev = self.rows[2 * n_seqs:].view(torch.int64)
             self.turn_dev = torch.zeros(1, dtype=torch.int32, device=dev)
             self.host_ring = torch.zeros((HOST_RING, n_seqs), dtype=torch.int32).pin_memory()
             self.log = torch.zeros((LOG_RING, n_seqs), dtype=torch.int32, device=dev)
@@ -85,16 +87,16 @@ class DecodeGraph:
             device=dev, workspace=engine.workspace, extras={"graph": True})
 
     # ---- what the static arrays hold ------------------------------------------------------
-    def holds(self, slots: list, starts: list, streams=None, counters=None) -> bool:
+    def holds(self, slots: list, starts: list, streams=None, counters=None, seed=None) -> bool:
         """True if the static arrays already describe a step of these slots at these lengths, drawing
         these numbers (the step before moved them on), so nothing has to come from the host."""
         h = self.held
         if h is None or h[0] != slots or h[1] != starts:
             return False
-        return self.rows is None or (h[2] == streams and h[3] == counters)
+        return self.rows is None or (h[2] == streams and h[3] == counters and h[4] == seed)
 
     def load_meta(self, meta_dev: torch.Tensor, keep_tokens: bool = False, slots=None, starts=None,
-                  streams=None, counters=None) -> None:
+                  streams=None, counters=None, seed=None) -> None:
         """Refill the static arrays from this step's arrays (device, `pack_step` layout, followed by the
         sampler's streams and draw counters if the step samples).  With keep_tokens the token ids
         already in the static buffer stay (the sampler wrote them)."""
@@ -104,13 +106,13 @@ class DecodeGraph:
         else:
             self.static_meta.copy_(meta_dev[:m], non_blocking=True)
         if self.rows is not None:
-            if meta_dev.numel() < m + 2 * n:
-                raise ValueError("a step that samples needs its streams and draw counters after the step's arrays")
-            self.rows.copy_(meta_dev[m:m + 2 * n], non_blocking=True)
+            if meta_dev.numel() < m + 2 * n + 2:
+                raise ValueError("a step that samples needs its streams, draw counters and seed after the step's arrays")
+            self.rows.copy_(meta_dev[m:m + 2 * n + 2], non_blocking=True)
         self.held = None
         if slots is not None:
             self.held = [list(slots), list(starts), list(streams) if streams is not None else None,
-                         list(counters) if counters is not None else None]
+                         list(counters) if counters is not None else None, seed]
 
     # ---- running ------------------------------------------------------------------------------
     def _step(self, logits: torch.Tensor) -> None:
@@ -120,9 +122,10 @@ class DecodeGraph:
         if self.sampler is not None:
             p = self.sampler
             ops.sample(logits, ctx.token_ids, temperature=p.temperature, top_k=p.top_k, top_p=p.top_p, penalty=1.0,
-                       seed=p.seed, row_stream=self.rows[:n], row_counter=self.rows[n:], counter_offset=0)
+                       seed=0, seed_dev=self.seed_dev, row_stream=self.rows[:n], row_counter=self.rows[n:2 * n],
+                       counter_offset=0)
         ops.advance_decode(ctx.token_pos, ctx.seq_start, ctx.seq_len, ctx.token_ids,
-                           draw_counter=self.rows[n:] if self.rows is not None else None, turn=self.turn_dev,
+                           draw_counter=self.rows[n:2 * n] if self.rows is not None else None, turn=self.turn_dev,
                            host_ring=self.host_ring, log_ring=self.log)
 
     def _eager(self, logits: torch.Tensor) -> torch.Tensor:

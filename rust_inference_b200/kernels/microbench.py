@@ -210,7 +210,7 @@ def step_parts(model: dict, batch: int, prompt_min: int = 128, prompt_max: int =
     meta, layout, _ = pack_step(starts, [[5]] * batch, [[0]] * batch)
     o, c = layout["seq_slot"]
     meta[o:o + c] = slots
-    rows = torch.cat([torch.arange(batch, dtype=torch.int32), torch.zeros(batch, dtype=torch.int32)])
+    rows = torch.cat([torch.arange(batch, dtype=torch.int32), torch.zeros(batch + 2, dtype=torch.int32)])   # streams, draw counters, seed
     meta_dev = torch.cat([torch.from_numpy(meta), rows]).cuda()
     greedy = SamplerConfig.plain(0.0)
 

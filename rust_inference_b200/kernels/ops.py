@@ -190,10 +190,14 @@ def sample(logits: torch.Tensor, out: torch.Tensor, *, temperature: float, top_k
            penalty: float = 1.0, recent: torch.Tensor | None = None, recent_count: torch.Tensor | None = None,
            seed: int = 0, row_stream: torch.Tensor | None = None,
            row_counter: torch.Tensor | None = None, counter_offset: int = 0,
-           mirror: torch.Tensor | None = None, newest: torch.Tensor | None = None) -> torch.Tensor:
+           mirror: torch.Tensor | None = None, newest: torch.Tensor | None = None,
+           seed_dev: torch.Tensor | None = None) -> torch.Tensor:
     """One token per row of float32 logits [R, V] (overwritten).  out: int32 [R].  `mirror`: a
     pinned int32 host tensor [R] that receives the tokens as well (the kernel writes it directly).
-    `newest`: int32 [R] on the device, one more recent id per row for the repetition penalty."""
+    `newest`: int32 [R] on the device, one more recent id per row for the repetition penalty.
+    `seed_dev`: int64 [1] on the device, a seed that takes the place of `seed` (read when the kernel runs)."""
+    _need(seed_dev is None or (seed_dev.is_cuda and seed_dev.dtype == torch.int64 and seed_dev.numel() >= 1),
+          "sample: seed_dev must be int64 [1] on the device")
     _need_cuda(logits, out, recent, recent_count, row_stream, row_counter, newest)
     _need(newest is None or (newest.dtype == torch.int32 and newest.is_contiguous() and newest.numel() >= logits.shape[0]),
           "sample: newest must be int32 [R]")
@@ -210,7 +214,7 @@ def sample(logits: torch.Tensor, out: torch.Tensor, *, temperature: float, top_k
           c_int(top_k), c_float(top_p), c_float(penalty), _p(recent),
           c_int(recent.shape[1] if recent is not None else 0), _p(recent_count),
           c_ulonglong(seed & 0xFFFFFFFFFFFFFFFF), _p(row_stream), _p(row_counter), c_int(counter_offset),
-          c_void_p(mirror.data_ptr() if mirror is not None else 0), _p(newest), _stream())
+          c_void_p(mirror.data_ptr() if mirror is not None else 0), _p(newest), _p(seed_dev), _stream())
     return out
 
 

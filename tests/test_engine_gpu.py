@@ -195,6 +195,15 @@ def test_temperature_sampling_is_reproducible_and_batch_independent(model_factor
     assert [x.tokens for x in a] == [x.tokens for x in b]
     c = m.generate(prompts, 16, SamplerConfig.plain(temperature=0.7, seed=5), stop_ids=())
     assert [x.tokens for x in a] != [x.tokens for x in c]
+    # the seed lives on the device beside the draw counters: another seed took no other capture
+    assert m.engine.decode_graph(4, cfg) is m.engine.decode_graph(4, SamplerConfig.plain(temperature=0.7, seed=5))
+    assert m.engine.decode_graph(4, cfg).graph is not None
+    # a seed beyond 32 bits, checked against the host's restatement of the draw
+    from conftest import oracle_generate
+    big = SamplerConfig.plain(temperature=0.7, seed=0x1234_5678_9ABC_DEF1)
+    e = m.generate(prompts[:2], 6, big, stop_ids=())
+    for i, p in enumerate(prompts[:2]):
+        assert e[i].tokens == oracle_generate(model, p, 6, temperature=0.7, seed=big.seed, stream=i)
     # request 2 draws the same numbers when the batch is cut differently (one at a time)
     d = m.generate(prompts, 16, cfg, stop_ids=(), max_batch=1)
     assert [x.tokens for x in d] == [x.tokens for x in a]
