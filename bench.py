@@ -198,7 +198,7 @@ def main() -> int:
         return 2
     if args.kernel:
         from rust_inference_b200.kernels import microbench
-        return microbench.main(args.kernel, MODEL, args.tokens, args.context, args.once)
+        return microbench.main(args.kernel, OTHER_SIZES[args.sizes], args.tokens, args.context, args.once)
     warmup = max(3, args.warmup)
     steps = max(1, args.steps)
 
