@@ -293,3 +293,64 @@ def test_state_dict_takes_the_packing_apart():
         assert list(sd) == list(src)
         assert all(torch.equal(sd[k], src[k]) for k in src)
         assert ("lm_head.weight" in sd) == (not cfg.tie_word_embeddings)
+
+
+def test_malformed_files_are_refused_never_read_wrongly(tmp_path):
+    """The reader's header parser and its checks meet damaged files: bytes flipped, cut out or added
+    in the header, absurd numbers, deep nesting, a header cut short, offsets and shapes that do not fit
+    the data, a wrong header length, a body cut short.  Every file is either refused with
+    WeightFileError or read completely; a tensor that is read lies inside the file."""
+    import random
+    path = str(tmp_path / "x.safetensors")
+    write_safetensors(path, {"a.weight": torch.randn(4, 6), "b": torch.randn(3).bfloat16(),
+                             "c": torch.arange(5, dtype=torch.int32)}, metadata={"k": "v"})
+    raw = open(path, "rb").read()
+    (hlen,) = struct.unpack("<Q", raw[:8])
+    hdr = raw[8:8 + hlen]
+    rng = random.Random(0)
+    out = str(tmp_path / "m.safetensors")
+    loaded = refused = 0
+    for _ in range(700):
+        h = bytearray(hdr)
+        kind = rng.randrange(8)
+        if kind == 0:
+            for _ in range(rng.randint(1, 4)):
+                h[rng.randrange(len(h))] = rng.randrange(256)
+        elif kind == 1:
+            i = rng.randrange(len(h))
+            del h[i:i + rng.randint(1, 10)]
+        elif kind == 2:
+            i = rng.randrange(len(h))
+            h[i:i] = bytes(rng.choice(b'{}[]",:0123456789-eE.\\u ') for _ in range(rng.randint(1, 12)))
+        elif kind == 3:
+            h = bytearray(hdr.replace(b"24", str(rng.choice([0, -1, 2 ** 31, 2 ** 63, 2 ** 64, 10 ** 30])).encode(), 1))
+        elif kind == 4:
+            h = bytearray(b"[" * rng.randint(1, 5000))
+        elif kind == 5:
+            h = bytearray(b'{"a":' * rng.randint(1, 3000))
+        elif kind == 6:
+            h = bytearray(hdr[:rng.randrange(len(hdr))])
+        else:
+            j = json.loads(hdr)
+            k = rng.choice([k for k in j if k != "__metadata__"])
+            j[k]["data_offsets"] = [rng.randrange(-5, 200), rng.randrange(-5, 200)]
+            j[k]["shape"] = [rng.randrange(-2, 10) for _ in range(rng.randint(0, 4))]
+            h = bytearray(json.dumps(j).encode())
+        claimed = len(h) if rng.random() < 0.8 else rng.choice([0, 1, len(h) - 1, len(h) + 1, 2 ** 40, 2 ** 63])
+        body = raw[8 + hlen:] if rng.random() < 0.8 else raw[8 + hlen:][:rng.randrange(60)]
+        with open(out, "wb") as f:
+            f.write(struct.pack("<Q", claimed & (2 ** 64 - 1)) + bytes(h) + body)
+        try:
+            f = SafetensorsFile(out)
+        except WeightFileError:
+            refused += 1
+            continue
+        try:
+            for n in f.names():
+                t = f.tensor(n)                                        # a dtype the library does not read is refused here
+                assert t.numel() * t.element_size() <= 2 * len(body) + 8      # what was read lies inside the file (F16 widens)
+            loaded += 1
+        except WeightFileError:
+            refused += 1
+        f.close()
+    assert refused > 400 and loaded > 20
