@@ -4,6 +4,8 @@ from here and never become a model of anyone's:
   * a layer whose arrangement has no feed-forward (roles: mixer, mixer_norm);
   * a layer with four norms (a norm before and after the mixer and before and after the feed-forward);
   * an embedding that scales its rows and adds learned positions, and a head that caps its logits;
+  * another position encoding for the attention part: a rotation of only the first half of every head,
+    with its own base, written with device-side indexing into the paged cache;
   * a mixer with fixed-size state of its own that is safe to capture: its decode update reads the
     step's slots on the device, so decode steps replay a CUDA graph.
 
@@ -20,6 +22,7 @@ import plain_impl
 from conftest import TOL, oracle_weights, random_tokens, rel_err
 
 HIDDEN, VOCAB, MAX_POS, INTER = 128, 97, 256, 144
+ROTARY_DIMS, ROTARY_BASE = 32, 5000.0        # the toy position encoding rotates 32 of a head's 64 dimensions
 SCALE, CAP, DECAY, EPS = 1.5, 3.0, 0.8, 1e-5
 ATT = dict(n_heads=4, n_kv_heads=2, head_dim=64)
 
@@ -28,7 +31,7 @@ def _register():
     from rust_inference_b200.cache.sequence_cache import StateRequest
     from rust_inference_b200.config.registry import register_architecture
     from rust_inference_b200.kernels import linear, ops
-    from rust_inference_b200.parts.base import Arrangement, Embedding, Head, Mixer
+    from rust_inference_b200.parts.base import Arrangement, Embedding, Head, Mixer, PositionEncoding
     from rust_inference_b200.parts.registry import lookup, register
     from rust_inference_b200.parts.spec import LayerSpec, ModelSpec, PartSpec, TensorSpec, default_schedule
 
@@ -62,6 +65,43 @@ def _register():
                          lambda x, out: self.mixer.forward(x, out, ctx, cache_layer, writes_cache))
             self._branch(residual, ctx, self.feed_forward_norm, self.feed_forward_post_norm,
                          lambda x, out: self.feed_forward.forward(x, out, ctx))
+
+    @register("position", "toy_partial_rotary", replace=True)
+    class PartialRotary(PositionEncoding):
+        """Rotates the first `rotary_dims` dimensions of every q and k head (pairs (i, i + rotary_dims / 2),
+        angle position / base^(2i / rotary_dims)) and leaves the rest as they are; then stores k and v
+        at their positions in the paged cache.  Everything is indexed on the device (token positions,
+        slots, the page table), so it runs inside captured decode steps."""
+
+        def __init__(self, *, rotary_dims, base, hidden_size, dtype, device):
+            super().__init__(hidden_size=hidden_size, dtype=dtype, device=device)
+            self.rd, self.base = rotary_dims, base
+            self.cos = self.sin = None
+
+        def prepare(self, max_positions):
+            cos, sin = plain_impl.rope_table(self.rd, self.base, max_positions)
+            self.cos, self.sin = cos.to(self.device), sin.to(self.device)
+
+        def apply_and_store(self, qkv, ctx, cache_layer, *, n_heads, n_kv_heads, head_dim, write_kv):
+            t, half = qkv.shape[0], self.rd // 2
+            qd, kvd = n_heads * head_dim, n_kv_heads * head_dim
+            pos = ctx.token_pos.long()
+            c, s_ = self.cos[pos][:, None, :], self.sin[pos][:, None, :]
+            for lo, heads in ((0, n_heads), (qd, n_kv_heads)):
+                x = qkv[:, lo:lo + heads * head_dim].view(t, heads, head_dim)
+                a, b = x[..., :half].float(), x[..., half:self.rd].float()
+                lo_half, hi_half = a * c - b * s_, a * s_ + b * c        # both from the old values
+                x[..., :half] = lo_half.to(qkv.dtype)
+                x[..., half:self.rd] = hi_half.to(qkv.dtype)
+            if write_kv:
+                slot = ctx.seq_slot.long()[ctx.token_seq.long()]
+                page = ctx.page_table[slot, pos // ctx.page_size].long()
+                off = pos % ctx.page_size
+                heads = torch.arange(n_kv_heads, device=qkv.device)
+                k = qkv[:, qd:qd + kvd].view(t, n_kv_heads, head_dim)
+                v = qkv[:, qd + kvd:].view(t, n_kv_heads, head_dim)
+                cache_layer.k[page[:, None], heads[None, :], off[:, None]] = k
+                cache_layer.v[page[:, None], heads[None, :], off[:, None]] = v
 
     @register("embedding", "toy_scaled_positions", replace=True)
     class ScaledWithPositions(Embedding):
@@ -160,10 +200,11 @@ def _register():
     def build(d):
         norm = lambda p: PartSpec("rmsnorm", {"eps": EPS}, prefix=p)
         rope = PartSpec("rope", {"head_dim": ATT["head_dim"], "base": 1e4, "style": "half"})
-        attn = lambda: PartSpec("gqa_attention", dict(ATT, qkv_bias=False, position=rope), prefix="attn.")
+        partial = PartSpec("toy_partial_rotary", {"rotary_dims": ROTARY_DIMS, "base": ROTARY_BASE})
+        attn = lambda position=rope: PartSpec("gqa_attention", dict(ATT, qkv_bias=False, position=position), prefix="attn.")
         ff = PartSpec("swiglu", {"intermediate_size": INTER}, prefix="mlp.")
         layers = (
-            LayerSpec("l0.", "toy_mixer_only", mixer=attn(), mixer_norm=norm("n1.")),
+            LayerSpec("l0.", "toy_mixer_only", mixer=attn(partial), mixer_norm=norm("n1.")),
             LayerSpec("l1.", "toy_sandwich", mixer=attn(), feed_forward=ff, mixer_norm=norm("n1."),
                       mixer_post_norm=norm("n2."), feed_forward_norm=norm("n3."), feed_forward_post_norm=norm("n4.")),
             LayerSpec("l2.", "pre_norm", mixer=PartSpec("toy_decay_state", {"decay": DECAY}, prefix="state."),
@@ -182,9 +223,30 @@ def _unregister():
     from rust_inference_b200.config.registry import unregister_architecture
     from rust_inference_b200.parts.registry import unregister
     for category, kind in (("arrangement", "toy_mixer_only"), ("arrangement", "toy_sandwich"),
-                           ("embedding", "toy_scaled_positions"), ("head", "toy_capped"), ("mixer", "toy_decay_state")):
+                           ("embedding", "toy_scaled_positions"), ("head", "toy_capped"), ("mixer", "toy_decay_state"),
+                           ("position", "toy_partial_rotary")):
         unregister(category, kind)
     unregister_architecture("ToyRolesLM")
+
+
+def _plain_partial_rotary_attention(x, w, pre):
+    """Attention whose q and k heads are rotated in their first ROTARY_DIMS dimensions only."""
+    n, nh, nkv, hd = x.shape[0], ATT["n_heads"], ATT["n_kv_heads"], ATT["head_dim"]
+    cos, sin = plain_impl.rope_table(ROTARY_DIMS, ROTARY_BASE, n)
+
+    def heads(name, count):
+        y = plain_impl.linear(x, w[pre + name]).view(n, count, hd)
+        rot = torch.stack([plain_impl.rope_apply(y[:, h, :ROTARY_DIMS], cos, sin, "half") for h in range(count)], dim=1)
+        return torch.cat([rot, y[..., ROTARY_DIMS:]], dim=-1)
+
+    q, k = heads("q_proj.weight", nh), heads("k_proj.weight", nkv)
+    v = plain_impl.linear(x, w[pre + "v_proj.weight"]).view(n, nkv, hd)
+    visible = torch.ones(n, n, dtype=torch.bool).tril()
+    out = torch.zeros(n, nh, hd)
+    for h in range(nh):
+        s = (q[:, h] @ k[:, h // (nh // nkv)].t()) * (1.0 / math.sqrt(float(hd)))
+        out[:, h] = plain_impl.softmax_rows(s.masked_fill(~visible, float("-inf"))) @ v[:, h // (nh // nkv)]
+    return plain_impl.linear(out.reshape(n, nh * hd), w[pre + "o_proj.weight"])
 
 
 def _plain(w, toks):
@@ -193,7 +255,7 @@ def _plain(w, toks):
     att = lambda x, pre: plain_impl.attention(x, w, pre, cos=cos, sin=sin, rope_style="half", **ATT)[0]
     norm = lambda x, name: plain_impl.rmsnorm(x, w[name], EPS)
     h = plain_impl.embedding(w["tok.weight"], toks) * SCALE + w["tok.positions"][:n]
-    h = h + att(norm(h, "l0.n1.weight"), "l0.attn.")                                      # no feed-forward
+    h = h + _plain_partial_rotary_attention(norm(h, "l0.n1.weight"), w, "l0.attn.")       # no feed-forward; partial rotary
     h = h + norm(att(norm(h, "l1.n1.weight"), "l1.attn."), "l1.n2.weight")                # four norms
     h = h + norm(plain_impl.swiglu(norm(h, "l1.n3.weight"), w, "l1.mlp."), "l1.n4.weight")
     xn, s, mixed = norm(h, "l2.n1.weight"), torch.zeros(HIDDEN), []
