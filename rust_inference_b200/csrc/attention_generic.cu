@@ -54,7 +54,8 @@ attn_generic_kernel(const T* __restrict__ q, int q_ld, const T* __restrict__ kca
         float s = -INFINITY;
         __syncthreads();              // qs ready (first pass); ps / key_off free (later passes)
         if (j < n_keys) {
-            const int page = pages[j / page_size];
+            int page = pages[j / page_size];
+            if (!RI_IN_LIMIT(page, RI_LIMIT_PAGES, RI_CHECK_PAGE)) page = 0;      // checked build: recorded, read from a page that exists
             const size_t row = ((size_t)page * n_kv_heads + kvh) * page_size + (j % page_size);
             key_off[tid] = (int)row;  // rows fit in 31 bits: checked on the host
             const T* kr = kcache + row * hd;

@@ -192,7 +192,9 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_ld, const __nv_bfl
     const int pg_begin = pg_lo + split * per, pg_end = min(pg_hi, pg_begin + per);
 
     auto issue = [&](int pg, int buf) {
-        const size_t base = ((size_t)pages[pg] * n_kv_heads + kvh) * PAGE * HD;
+        int page = pages[pg];
+        if (!RI_BLOCK_IN_LIMIT(page, RI_LIMIT_PAGES, RI_CHECK_PAGE)) page = 0;    // checked build: recorded, read from a page that exists
+        const size_t base = ((size_t)page * n_kv_heads + kvh) * PAGE * HD;
         load_tile_async<HD>(kv_base + (2 * buf) * TILE, kcache + base, PAGE);
         load_tile_async<HD>(kv_base + (2 * buf + 1) * TILE, vcache + base, PAGE);
         cp_async_commit();
@@ -658,7 +660,9 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_ld, const __nv_bf
         *reinterpret_cast<uint4*>(smem + 4 * TILE + tile_off<HD>(r, c)) = v;
     }
     auto issue = [&](int pg, int buf) {
-        const size_t base = ((size_t)pages[pg] * n_kv_heads + kvh) * PAGE * HD;
+        int page = pages[pg];
+        if (!RI_BLOCK_IN_LIMIT(page, RI_LIMIT_PAGES, RI_CHECK_PAGE)) page = 0;    // checked build: recorded, read from a page that exists
+        const size_t base = ((size_t)page * n_kv_heads + kvh) * PAGE * HD;
         load_tile_async<HD>(kv_base + (2 * buf) * TILE, kcache + base, PAGE);
         load_tile_async<HD>(kv_base + (2 * buf + 1) * TILE, vcache + base, PAGE);
         cp_async_commit();

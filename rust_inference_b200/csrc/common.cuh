@@ -166,5 +166,62 @@ inline int raise_dynamic_smem(Kernel kernel, int bytes, PerDeviceOnce& once, con
 
 }  // namespace ri
 
+// ---------------------------------------------------------------------------------------
+// The checked build (-DRI_CHECK_BOUNDS; `RI_B200_CHECK_BOUNDS=1` makes the Python side compile and load
+// it from a folder of its own).  Kernels that reach memory through a table (a token id into the
+// embedding, a slot and a page number into the cache) compare the index with its limit first.  An index
+// outside is recorded in the library (which check, the index, the limit: the first one; and how many
+// there were) and the access is skipped or bent to a safe place: the kernel finishes, nothing faults,
+// and the host reads the record with `ri_bounds_report`.  Limits that the kernels are not given as
+// arguments (vocabulary, slots, pages) are set once per library with `ri_bounds_set_limits`; a limit of
+// 0 is not checked.  In the ordinary build every check is the constant `true` and costs nothing.
+// ---------------------------------------------------------------------------------------
+enum { RI_LIMIT_VOCAB = 0, RI_LIMIT_SLOTS = 1, RI_LIMIT_PAGES = 2 };
+enum { RI_CHECK_TOKEN_ID = 1, RI_CHECK_SLOT = 2, RI_CHECK_PAGE_INDEX = 3, RI_CHECK_PAGE = 4 };
+
+#ifdef RI_CHECK_BOUNDS
+namespace ri {
+__device__ int g_limits[3];
+__device__ int g_bounds[4];        // {check, index, limit} of the first index outside its range, and their number
+
+// `record`: whether this thread writes the record (an index that every thread of a block checks alike is
+// recorded by its first thread only, so that the count is of indices, not of threads).
+__device__ __forceinline__ bool in_range(long long i, long long limit, int check, bool record) {
+    if (limit <= 0 || (i >= 0 && i < limit)) return true;
+    if (record && atomicAdd(&g_bounds[3], 1) == 0) {
+        g_bounds[0] = check;
+        g_bounds[1] = (int)i;
+        g_bounds[2] = (int)limit;
+    }
+    return false;
+}
+}  // namespace ri
+#define RI_IN_LIMIT(i, which, check) ri::in_range((long long)(i), (long long)ri::g_limits[which], check, true)
+#define RI_BLOCK_IN_RANGE(i, limit, check) ri::in_range((long long)(i), (long long)(limit), check, threadIdx.x == 0)
+#define RI_BLOCK_IN_LIMIT(i, which, check) \
+    ri::in_range((long long)(i), (long long)ri::g_limits[which], check, threadIdx.x == 0)
+#define RI_DEFINE_BOUNDS()                                                                                     \
+    RI_API int ri_bounds_set_limits(int vocab, int slots, int pages) {                                         \
+        const int v[3] = {vocab, slots, pages};                                                                \
+        cudaError_t e = cudaMemcpyToSymbol(ri::g_limits, v, sizeof(v));                                        \
+        return e == cudaSuccess ? 0 : ri::fail("bounds: cannot set the limits: %s", cudaGetErrorString(e));   \
+    }                                                                                                          \
+    /* out[0..4): check, index, limit, count; the record is cleared.  Synchronises the device. */              \
+    RI_API int ri_bounds_report(int* out) {                                                                    \
+        const int zero[4] = {0, 0, 0, 0};                                                                      \
+        cudaError_t e = cudaMemcpyFromSymbol(out, ri::g_bounds, 4 * sizeof(int));                              \
+        if (e == cudaSuccess) e = cudaMemcpyToSymbol(ri::g_bounds, zero, sizeof(zero));                        \
+        return e == cudaSuccess ? 0 : ri::fail("bounds: cannot read the record: %s", cudaGetErrorString(e));  \
+    }
+#else
+#define RI_IN_LIMIT(i, which, check) true
+#define RI_BLOCK_IN_RANGE(i, limit, check) true
+#define RI_BLOCK_IN_LIMIT(i, which, check) true
+#define RI_DEFINE_BOUNDS()                                                                                     \
+    RI_API int ri_bounds_set_limits(int, int, int) { return ri::fail("this library is not a checked build"); } \
+    RI_API int ri_bounds_report(int*) { return ri::fail("this library is not a checked build"); }
+#endif
+
 #define RI_DEFINE_LAST_ERROR() \
+    RI_DEFINE_BOUNDS()         \
     RI_API const char* ri_last_error() { return ri::error_buffer(); }

@@ -16,8 +16,13 @@ __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __re
     const int t = blockIdx.x;
     let_next_kernel_start();
     wait_for_previous_kernels();          // the ids may come from the previous step's sampler
-    const T* row = table + (size_t)ids[t] * hidden;
+    const int id = ids[t];
     float* o = out + (size_t)t * hidden;
+    if (!RI_BLOCK_IN_LIMIT(id, RI_LIMIT_VOCAB, RI_CHECK_TOKEN_ID)) {           // checked build: recorded, the row left zero
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = 0.f;
+        return;
+    }
+    const T* row = table + (size_t)id * hidden;
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_f32<T>(row[i]);
 }
 
@@ -216,8 +221,14 @@ __global__ void rope_cache_write_kernel(T* __restrict__ qkv, int ld, const float
     size_t cache_base = 0;
     if (write_kv) {
         const int slot = seq_slot[token_seq[t]];
-        const int page = page_table[(size_t)slot * max_pages + pos / page_size];
-        cache_base = ((size_t)page * n_kv_heads * page_size + (pos % page_size)) * hd;
+        // checked build: a slot, a page index or a page outside its range is recorded and nothing is written
+        if (!RI_BLOCK_IN_LIMIT(slot, RI_LIMIT_SLOTS, RI_CHECK_SLOT) || !RI_BLOCK_IN_RANGE(pos / page_size, max_pages, RI_CHECK_PAGE_INDEX)) {
+            write_kv = 0;
+        } else {
+            const int page = page_table[(size_t)slot * max_pages + pos / page_size];
+            if (!RI_BLOCK_IN_LIMIT(page, RI_LIMIT_PAGES, RI_CHECK_PAGE)) write_kv = 0;
+            cache_base = ((size_t)page * n_kv_heads * page_size + (pos % page_size)) * hd;
+        }
     }
     const size_t head_stride = (size_t)page_size * hd;
 
@@ -287,8 +298,14 @@ __global__ void rope_cache_write_vec_kernel(__nv_bfloat16* __restrict__ qkv, int
     size_t cache_base = 0;
     if (write_kv) {
         const int slot = seq_slot[token_seq[t]];
-        const int page = page_table[(size_t)slot * max_pages + pos / page_size];
-        cache_base = ((size_t)page * n_kv_heads * page_size + (pos % page_size)) * hd;
+        // checked build: a slot, a page index or a page outside its range is recorded and nothing is written
+        if (!RI_BLOCK_IN_LIMIT(slot, RI_LIMIT_SLOTS, RI_CHECK_SLOT) || !RI_BLOCK_IN_RANGE(pos / page_size, max_pages, RI_CHECK_PAGE_INDEX)) {
+            write_kv = 0;
+        } else {
+            const int page = page_table[(size_t)slot * max_pages + pos / page_size];
+            if (!RI_BLOCK_IN_LIMIT(page, RI_LIMIT_PAGES, RI_CHECK_PAGE)) write_kv = 0;
+            cache_base = ((size_t)page * n_kv_heads * page_size + (pos % page_size)) * hd;
+        }
     }
     const size_t head_stride = (size_t)page_size * hd;
     wait_for_previous_kernels();          // the projections come from the previous kernel
@@ -409,8 +426,14 @@ __global__ void rope_cache_write_acc_kernel(float* __restrict__ acc, int ld, con
     size_t cache_base = 0;
     if (write_kv) {
         const int slot = seq_slot[token_seq[t]];
-        const int page = page_table[(size_t)slot * max_pages + pos / page_size];
-        cache_base = ((size_t)page * n_kv_heads * page_size + (pos % page_size)) * hd;
+        // checked build: a slot, a page index or a page outside its range is recorded and nothing is written
+        if (!RI_BLOCK_IN_LIMIT(slot, RI_LIMIT_SLOTS, RI_CHECK_SLOT) || !RI_BLOCK_IN_RANGE(pos / page_size, max_pages, RI_CHECK_PAGE_INDEX)) {
+            write_kv = 0;
+        } else {
+            const int page = page_table[(size_t)slot * max_pages + pos / page_size];
+            if (!RI_BLOCK_IN_LIMIT(page, RI_LIMIT_PAGES, RI_CHECK_PAGE)) write_kv = 0;
+            cache_base = ((size_t)page * n_kv_heads * page_size + (pos % page_size)) * hd;
+        }
     }
     const size_t head_stride = (size_t)page_size * hd;
 

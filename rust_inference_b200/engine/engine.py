@@ -98,6 +98,9 @@ class Engine:
         self.workspace = Workspace(self.device)
         self._ring = _PinnedRing()
         self.h2d_bytes = 0          # bytes of step inputs copied to the device so far
+        from ..kernels import ops
+        if ops.checked_build():          # limits the kernels are not given as arguments (the last engine made sets them)
+            ops.bounds_set_limits(model.spec.vocab_size, self.cache.n_slots, self.cache.n_pages)
 
     # ---- construction ----------------------------------------------------------
     @classmethod
@@ -137,11 +140,18 @@ class Engine:
         self.cache.free_slot(slot)
 
     def check_device_status(self) -> None:
-        """Raise if a kernel gave up on a bounded wait since the last check.  Meaningful after a
-        synchronisation point (a device-to-host read of the step's result)."""
+        """Raise if a kernel gave up on a bounded wait since the last check (meaningful after a
+        synchronisation point: a device-to-host read of the step's result); in the checked build
+        (RI_B200_CHECK_BOUNDS=1) also if a kernel met an index outside its table."""
         if self.dtype == torch.bfloat16:
             from ..kernels import tcgen05
             tcgen05.check_status()
+        from ..kernels import ops
+        if ops.checked_build():
+            found = ops.bounds_report()
+            if found:
+                raise ops.KernelError("the checked build found indices outside their tables: " + "; ".join(
+                    f"{lib}: {what} ({index}, limit {limit}; {count} in all)" for lib, what, index, limit, count in found))
 
     # ---- the step ------------------------------------------------------------------
     def _check_batch(self, slots, tokens, wants):

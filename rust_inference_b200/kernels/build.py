@@ -42,6 +42,13 @@ NVCC_FLAGS = [
 
 CXX_FLAGS = ["-std=c++17", "-O2", "-shared", "-fPIC", "-fvisibility=hidden"]
 
+# RI_B200_CHECK_BOUNDS=1: the checked build of the kernels (indices that reach memory through a table are
+# compared with their limits, recorded and skipped when outside: `csrc/common.cuh`).  It is compiled into
+# and loaded from a folder of its own, beside the ordinary libraries.
+CHECKED = os.environ.get("RI_B200_CHECK_BOUNDS", "") == "1"
+if CHECKED:
+    NVCC_FLAGS = NVCC_FLAGS + ["-DRI_CHECK_BOUNDS"]
+
 
 class KernelBuildError(RuntimeError):
     pass
@@ -67,6 +74,8 @@ def _cxx() -> str:
 
 def _build_dir() -> str:
     d = os.environ.get("RI_B200_BUILD_DIR") or os.path.join(CSRC, "_build")
+    if CHECKED:
+        d = os.path.join(d, "checked")
     try:
         os.makedirs(d, exist_ok=True)
         probe = os.path.join(d, f".w{os.getpid()}")
@@ -75,7 +84,7 @@ def _build_dir() -> str:
         os.remove(probe)
         return d
     except OSError:
-        d = os.path.join(tempfile.gettempdir(), f"ri_b200_build_{os.getuid()}")
+        d = os.path.join(tempfile.gettempdir(), f"ri_b200_build_{os.getuid()}" + ("_checked" if CHECKED else ""))
         os.makedirs(d, exist_ok=True)
         return d
 
@@ -163,6 +172,11 @@ def load(module: str) -> ctypes.CDLL:
             lib.ri_last_error.restype = ctypes.c_char_p
             _loaded[module] = lib
         return lib
+
+
+def loaded_cuda_modules() -> list[str]:
+    """Names of the CUDA libraries loaded so far."""
+    return [m for m in _loaded if MODULES[m].endswith(".cu")]
 
 
 def build_all(verbose: bool = True) -> list[str]:

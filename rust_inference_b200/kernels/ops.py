@@ -56,13 +56,66 @@ def launch_count() -> int:
     return _launches
 
 
+_limits = None          # checked build: (vocabulary, slots, pages) for libraries still to be loaded
+_limited: set = set()   # libraries that have them
+
+
 def _call(module: str, fn: str, *args) -> None:
     global _launches
     lib = load(module)
+    if _limits is not None and module not in _limited:
+        _apply_limits(module, lib)
     rc = getattr(lib, fn)(*args)
     if rc != 0:
         raise KernelError(f"{fn}: {lib.ri_last_error().decode()}")
     _launches += 1
+
+
+# ----------------------------------------------------------------------------
+# The checked build (RI_B200_CHECK_BOUNDS=1)
+# ----------------------------------------------------------------------------
+BOUND_CHECKS = {1: "a token id outside the vocabulary", 2: "a cache slot that does not exist",
+                3: "a position beyond a sequence's page table", 4: "a page that does not exist"}
+
+
+def checked_build() -> bool:
+    from . import build
+    return build.CHECKED
+
+
+def _apply_limits(module: str, lib) -> None:
+    from . import build
+    if build.MODULES[module].endswith(".cu"):
+        if lib.ri_bounds_set_limits(c_int(_limits[0]), c_int(_limits[1]), c_int(_limits[2])) != 0:
+            raise KernelError(f"{module}: {lib.ri_last_error().decode()}")
+    _limited.add(module)
+
+
+def bounds_set_limits(vocab: int, slots: int, pages: int) -> None:
+    """Checked build only: the limits that kernels are not given as arguments (0: not checked), for
+    every CUDA library loaded so far and, at its first call, every one loaded later."""
+    global _limits
+    from . import build
+    _limits = (int(vocab), int(slots), int(pages))
+    _limited.clear()
+    for module in build.loaded_cuda_modules():
+        _apply_limits(module, load(module))
+
+
+def bounds_report() -> list:
+    """Checked build only: what the kernels recorded since the last call, per library:
+    (library, what was outside, the index, its limit, how many indices were outside).  Reads the
+    records back (synchronises the device) and clears them."""
+    from . import build
+    out = []
+    for module in build.loaded_cuda_modules():
+        lib = load(module)
+        rec = (c_int * 4)()
+        if lib.ri_bounds_report(rec) != 0:
+            raise KernelError(f"{module}: {lib.ri_last_error().decode()}")
+        if rec[3]:
+            out.append((module, BOUND_CHECKS.get(rec[0], f"check {rec[0]}"), rec[1], rec[2], rec[3]))
+    return out
 
 
 # ----------------------------------------------------------------------------
