@@ -353,3 +353,36 @@ def test_a_random_model_saved_and_loaded_again(dtype, tmp_path):
     folder = m.save_safetensors(str(tmp_path / "saved"))
     again = Model.load(folder, dtype=dtype, max_tokens_in_cache=512).logits(toks)
     assert rel_err(again, got) <= (1e-6 if dtype == "float32" else 2e-2)
+
+
+def test_bfloat16_generation_with_stop_ids(model_factory):
+    """bfloat16, greedy, stop ids, batches that shrink and follow one another: a run with stop ids is the
+    free run cut before each sequence's first stop id (model.rs:383-387), and every token of the free run
+    is within the bfloat16 bound of the plain implementation's maximum."""
+    from rust_inference_b200 import Model, SamplerConfig
+    model = model_factory("B", std=0.08)
+    vocab = model.cfg["vocab_size"]
+    prompts = [random_tokens(n, vocab, seed=300 + n) for n in (3, 41, 8, 1, 66, 17, 5)]
+    greedy = SamplerConfig.plain(0.0)
+    m = Model.load(model.folder, dtype="bfloat16", max_tokens_in_cache=1024, n_slots=4)
+    free = [r.tokens for r in m.generate(prompts, 14, greedy, stop_ids=())]
+    for p, toks in zip(prompts[:3], free[:3]):
+        seq = list(p)
+        for tok in toks:
+            ref = model.plain_logits(seq)[-1]
+            assert float((ref.max() - ref[tok]) / ref.abs().max()) <= 2 * TOL["bfloat16"]
+            seq.append(tok)
+    stops = (free[0][4], free[1][0], free[4][9], free[6][13])          # an early one, a first token, a late one, a last one
+    got = m.generate(prompts, 14, greedy, stop_ids=stops)
+    n_stopped = 0
+    for g, f in zip(got, free):
+        cut = next((i for i, t in enumerate(f) if t in stops), None)
+        if cut is None:
+            assert g.tokens == f and g.finish_reason == "length"
+        else:
+            assert g.tokens == f[:cut] and g.finish_reason == "stop"
+            n_stopped += 1
+    assert n_stopped >= 4
+    m.engine.cache.pager.audit()
+    assert m.engine.cache.pager.free_slot_count() == 4
+    m.engine.check_device_status()
