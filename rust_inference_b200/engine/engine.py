@@ -344,11 +344,13 @@ class Engine:
         self.cache.advance(slots, [1] * len(slots))
         return graph.ctx.token_ids, graph.last_tokens_host()
 
-    def decode_steps(self, slots: list, first_tokens: list, n_steps: int, sampler_config=None) -> torch.Tensor:
+    def decode_steps(self, slots: list, first_tokens: list, n_steps: int, sampler_config=None,
+                     on_step=None) -> torch.Tensor:
         """Device-resident decoding: n_steps steps of one token per sequence in which each
         sampled token is fed to the next step on the device, with no host round trip and no
         stop check in between.  Returns the sampled tokens, int32 [n_steps, B], on the device.
-        The first step is fed `first_tokens`."""
+        The first step is fed `first_tokens`.  `on_step(i)` is called on the host just before step i
+        is launched, everything it needs being in place (a benchmark records its event there)."""
         from ..sampling.params import SamplerConfig
         from .graphs import LOG_RING
         cfg = sampler_config or SamplerConfig.plain(temperature=0.0)
@@ -365,7 +367,8 @@ class Engine:
         pieces = []
         with torch.cuda.device(self.device):
             graph = self._graph_for(n, cfg)
-            first = torch.tensor(first_tokens, dtype=torch.int32).pin_memory().to(self.device, non_blocking=True)
+            first = self._ring.stage(np.asarray(first_tokens, dtype=np.int32), self.device)    # through the pinned ring: no allocation
+            self.h2d_bytes += 4 * n
             done = 0
             while done < n_steps:
                 run = min(LOG_RING, n_steps - done)
@@ -373,6 +376,8 @@ class Engine:
                     self._enter_decode(graph, slots, streams, [done + i] * n, cfg.seed)
                     if done + i == 0:
                         self._feed(graph, first)
+                    if on_step is not None:
+                        on_step(done + i)
                     graph.launch()
                     self.cache.advance(slots, [1] * n)
                 pieces.append(graph.logged_tokens(run))
