@@ -15,6 +15,9 @@ Added for a library that takes token ids and may run without a checkpoint:
   --random-prompts B:MIN:MAX                B prompts of seeded random ids, lengths uniform in MIN..MAX
   --slots N                                 sequences that may be live at once (larger batches run in waves)
   --print-logits-topk K                     the K largest logits after each prompt, before generating
+  --bench                                   after generating, one JSON line on standard error: steps, prompt and
+                                            generated tokens, seconds, tokens per second, bytes copied, the model's
+                                            bytes on the device
   --dump-layer-stats                        min / max / mean / first values of the hidden vector at position 0
                                             after every layer, as debug builds of the reference print them
                                             (transformer.rs:80-96)
@@ -51,6 +54,7 @@ Options:
   --slots            Sequences live at once (default: as many as the cache holds)
   --print-logits-topk  Print the K largest logits after each prompt
   --dump-layer-stats Print per-layer statistics of the hidden state at position 0
+  --bench            Print the run's counts, rates and the model's memory as one JSON line
   --help, -h         Show this help message
 """
 
@@ -72,7 +76,7 @@ def parse_args(argv: list) -> dict:
     a = {"model": None, "prompts": [], "max_tokens": 512, "temperature": 0.8, "top_k": 40, "top_p": 0.95,
          "repetition_penalty": 1.1, "seed": 12345, "max_seq_len": None, "stop_ids": None,
          "dtype": "bfloat16", "help": False, "random_config": None, "weights_seed": 0, "random_prompts": None,
-         "slots": None, "logits_topk": 0, "layer_stats": False}
+         "slots": None, "logits_topk": 0, "layer_stats": False, "bench": False}
     i = 0
 
     def value(flag):
@@ -143,6 +147,8 @@ def parse_args(argv: list) -> dict:
             a["logits_topk"] = number("--print-logits-topk", int)
         elif arg == "--dump-layer-stats":
             a["layer_stats"] = True
+        elif arg == "--bench":
+            a["bench"] = True
         elif arg in ("--help", "-h"):
             a["help"] = True
             return a
@@ -223,6 +229,10 @@ def main(argv=None) -> int:
     n = sum(len(r.tokens) for r in results)
     print(f"{n} tokens in {dt:.3f} s ({n / dt:.1f} tok/s), finish: "
           + ", ".join(r.finish_reason for r in results), file=sys.stderr)
+    if a["bench"]:
+        import json
+        stats = {k: v for k, v in model.last_stats.items() if k != "step_times"}
+        print(json.dumps({**stats, **model.memory()}), file=sys.stderr)
     return 0
 
 

@@ -46,8 +46,10 @@ CXX_FLAGS = ["-std=c++17", "-O2", "-shared", "-fPIC", "-fvisibility=hidden"]
 # compared with their limits, recorded and skipped when outside: `csrc/common.cuh`).  It is compiled into
 # and loaded from a folder of its own, beside the ordinary libraries.
 CHECKED = os.environ.get("RI_B200_CHECK_BOUNDS", "") == "1"
-if CHECKED:
-    NVCC_FLAGS = NVCC_FLAGS + ["-DRI_CHECK_BOUNDS"]
+
+
+def _nvcc_flags(checked: bool) -> list:
+    return NVCC_FLAGS + (["-DRI_CHECK_BOUNDS"] if checked else [])
 
 
 class KernelBuildError(RuntimeError):
@@ -72,9 +74,10 @@ def _cxx() -> str:
     raise KernelBuildError("no C++ compiler found: the host runtime cannot be compiled (set CXX or PATH)")
 
 
-def _build_dir() -> str:
+def _build_dir(checked: bool | None = None) -> str:
+    checked = CHECKED if checked is None else checked
     d = os.environ.get("RI_B200_BUILD_DIR") or os.path.join(CSRC, "_build")
-    if CHECKED:
+    if checked:
         d = os.path.join(d, "checked")
     try:
         os.makedirs(d, exist_ok=True)
@@ -84,14 +87,14 @@ def _build_dir() -> str:
         os.remove(probe)
         return d
     except OSError:
-        d = os.path.join(tempfile.gettempdir(), f"ri_b200_build_{os.getuid()}" + ("_checked" if CHECKED else ""))
+        d = os.path.join(tempfile.gettempdir(), f"ri_b200_build_{os.getuid()}" + ("_checked" if checked else ""))
         os.makedirs(d, exist_ok=True)
         return d
 
 
-def _source_digest(src: str) -> str:
+def _source_digest(src: str, checked: bool) -> str:
     h = hashlib.sha256()
-    h.update(" ".join(NVCC_FLAGS if src.endswith(".cu") else CXX_FLAGS).encode())
+    h.update(" ".join(_nvcc_flags(checked) if src.endswith(".cu") else CXX_FLAGS).encode())
     headers = sorted(f for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))) if src.endswith(".cu") else []
     for name in [src] + headers:
         with open(os.path.join(CSRC, name), "rb") as f:
@@ -104,21 +107,23 @@ def _say(msg: str) -> None:
     print(f"[rust_inference_b200] {msg}", file=sys.stderr, flush=True)
 
 
-def library_path(module: str) -> str:
-    return os.path.join(_build_dir(), f"libri_{module}.so")
+def library_path(module: str, checked: bool | None = None) -> str:
+    return os.path.join(_build_dir(checked), f"libri_{module}.so")
 
 
-def build(module: str, *, force: bool = False, verbose: bool = True) -> str:
-    """Compile one module if its library is missing or older than its sources."""
+def build(module: str, *, force: bool = False, verbose: bool = True, checked: bool | None = None) -> str:
+    """Compile one module if its library is missing or older than its sources (`checked`: the checked
+    build instead of the one this process loads)."""
+    checked = CHECKED if checked is None else checked
     if module not in MODULES:
         raise KernelBuildError(f"unknown kernel module {module!r}")
     src = MODULES[module]
     src_path = os.path.join(CSRC, src)
     if not os.path.isfile(src_path):
         raise KernelBuildError(f"kernel source {src_path} is missing")
-    out = library_path(module)
+    out = library_path(module, checked)
     stamp = out + ".sha256"
-    digest = _source_digest(src)
+    digest = _source_digest(src, checked)
     lock_path = os.path.join(os.path.dirname(out), f".{module}.lock")
     with open(lock_path, "w") as lock:
         fcntl.flock(lock, fcntl.LOCK_EX)
@@ -129,11 +134,12 @@ def build(module: str, *, force: bool = False, verbose: bool = True) -> str:
                         return out
             tmp = out + f".{os.getpid()}.tmp"
             if src.endswith(".cu"):
-                cmd = [_nvcc()] + NVCC_FLAGS + ["-I", CSRC, "-o", tmp, src_path]
+                cmd = [_nvcc()] + _nvcc_flags(checked) + ["-I", CSRC, "-o", tmp, src_path]
             else:
                 cmd = [_cxx()] + CXX_FLAGS + ["-o", tmp, src_path]
             if verbose:
-                _say(f"compiling {src}" + (" for sm_100a ..." if src.endswith(".cu") else " ..."))
+                _say(f"compiling {src}" + (" for sm_100a" + (" (checked build)" if checked else "") + " ..."
+                                            if src.endswith(".cu") else " ..."))
             t0 = time.time()
             proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
             last = t0
@@ -179,5 +185,6 @@ def loaded_cuda_modules() -> list[str]:
     return [m for m in _loaded if MODULES[m].endswith(".cu")]
 
 
-def build_all(verbose: bool = True) -> list[str]:
-    return [build(m, verbose=verbose) for m in MODULES if os.path.isfile(os.path.join(CSRC, MODULES[m]))]
+def build_all(verbose: bool = True, checked: bool | None = None) -> list[str]:
+    return [build(m, verbose=verbose, checked=checked) for m in MODULES
+            if os.path.isfile(os.path.join(CSRC, MODULES[m]))]

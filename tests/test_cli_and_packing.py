@@ -122,8 +122,8 @@ def test_flags_of_the_random_weights_mode(tmp_path):
     cfg = tmp_path / "config.json"
     cfg.write_text("{}")
     a = parse_args(["--random-config", str(cfg), "--weights-seed", "7", "--random-prompts", "3:5:9", "--slots", "2",
-                    "--print-logits-topk", "4", "--dump-layer-stats"])
-    assert a["random_config"] == str(cfg) and a["weights_seed"] == 7 and a["random_prompts"] == (3, 5, 9)
+                    "--print-logits-topk", "4", "--dump-layer-stats", "--bench"])
+    assert a["bench"] and a["random_config"] == str(cfg) and a["weights_seed"] == 7 and a["random_prompts"] == (3, 5, 9)
     assert a["slots"] == 2 and a["logits_topk"] == 4 and a["layer_stats"] and a["model"] is None
     for argv, word in [
         (["--random-config", str(cfg)], "--prompt is required"),

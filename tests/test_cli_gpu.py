@@ -65,10 +65,12 @@ def test_random_weights_mode_with_statistics(tmp_path):
     path.write_text(json.dumps(cfg))
     rc, out, err = _run("--random-config", path, "--weights-seed", 3, "--random-prompts", "3:2:9", "--slots", 2,
                         "-n", 4, "-t", 0, "--repetition-penalty", 1, "--print-logits-topk", 3, "--dump-layer-stats",
-                        "--dtype", "float32", "--stop-ids", "")
+                        "--dtype", "float32", "--stop-ids", "", "--bench")
     assert rc == 0, err[-2000:]
     lines = [l.split() for l in out.splitlines() if l.strip()]
     assert len(lines) == 3 and all(len(l) == 4 for l in lines)
+    stats = json.loads(err.strip().splitlines()[-1])
+    assert stats["generated_tokens"] == 12 and stats["tokens_per_second"] > 0 and stats["weight_bytes"] > 0
     # three prompts: for each the statistics of every layer and of the final norm, then the top logits
     assert err.count("[L0] min=") == 3 and err.count("[L2] min=") == 3 and err.count("[FNL] min=") == 3
     assert err.count("top logits") == 3
