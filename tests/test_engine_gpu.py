@@ -279,19 +279,21 @@ def test_the_order_of_layers_is_data(dtype, model_factory):
 
 def test_a_failed_decode_step_leaves_no_dirty_accumulator(model_factory, monkeypatch):
     """A bf16 decode step of a model this wide adds the pieces of its K-split q/k/v projection onto a
-    float32 accumulator that the rotary kernel consumes and zeroes again.  If a step fails between the
-    two, the accumulator must not keep the leftovers: the failure is injected on the host (the rotary
-    kernel's Python face raises before it launches), in each phase of a batch size's life: on the
-    engine's shared scratch, on the size's own scratch, during the capture, and in a replayed graph's
-    neighbour (an eager prefill step)."""
+    float32 accumulator that the rotary kernel consumes and zeroes again.  If a step fails between the two, the
+    accumulator must not keep the leftovers: the failure is injected on the host (the rotary kernel's
+    Python face raises before it launches), in each phase of a batch size's life: on the engine's
+    shared scratch, on the size's own scratch, during the capture, and in a replayed graph's neighbour
+    (an eager prefill step)."""
     from rust_inference_b200.kernels import ops, tcgen05
     model = model_factory("E", std=0.05)
     eng = _engine(model, "bfloat16")
-    assert tcgen05.plan(1, 8 * 64 + 2 * 2 * 64, 512, ops.EPI_RESIDUAL)[1] > 1     # the projection is split over K
-    toks = random_tokens(60, model.cfg["vocab_size"], seed=8)
-    want = model.plain_logits(toks)
-    s = eng.alloc_slot()
-    eng.step([s], [toks[:40]], "none")
+    assert tcgen05.plan(5, 8 * 64 + 2 * 2 * 64, 512, ops.EPI_RESIDUAL)[1] > 1     # the projection is split over K
+    n = 5
+    seqs = [random_tokens(60, model.cfg["vocab_size"], seed=8 + i) for i in range(n)]
+    want = [model.plain_logits(t) for t in seqs]
+    slots = [eng.alloc_slot() for _ in range(n)]
+    eng.step(slots, [t[:40 - i] for i, t in enumerate(seqs)], "none")
+    at = [40 - i for i in range(n)]
     real = ops.rope_cache_write_acc
     state = {"fail": False, "calls": 0}
 
@@ -302,30 +304,32 @@ def test_a_failed_decode_step_leaves_no_dirty_accumulator(model_factory, monkeyp
         return real(*a, **k)
 
     monkeypatch.setattr(ops, "rope_cache_write_acc", flaky)
-    pos = 40
+    step = lambda: eng.step(slots, [[seqs[i][at[i]]] for i in range(n)], "last")
     # decode steps of this batch size, in order: the 1st and 2nd run on the engine's shared scratch, the
     # 3rd on the size's own, the 4th is captured; after an abandoned capture the next step captures again
     for nth, outcome in enumerate(["fail", "ok", "fail", "fail", "ok", "ok", "ok"], start=1):
         if outcome == "fail":
             state["fail"] = True
             with pytest.raises(RuntimeError, match="injected"):
-                eng.step([s], [[toks[pos]]], "last")
+                step()
             state["fail"] = False
-            assert eng.cache.length(s) == pos                  # the failed step did not count
-            assert eng.decode_graph(1).graph is None
+            assert eng.cache.lengths(slots) == at              # the failed step did not count
+            assert eng.decode_graph(n).graph is None
             continue
-        got = eng.step([s], [[toks[pos]]], "last")[0]
-        assert rel_err(got, want[pos]) <= TOL["bfloat16"], nth
-        pos += 1
-    assert eng.decode_graph(1).graph is not None                    # the size did get its graph in the end
+        got = step().cpu()
+        for i in range(n):
+            assert rel_err(got[i], want[i][at[i]]) <= TOL["bfloat16"], (nth, i)
+            at[i] += 1
+    assert eng.decode_graph(n).graph is not None               # the size did get its graph in the end
     assert state["calls"] > 0                                  # the path under test did run
     # an eager step of several tokens that fails, then the same step again
+    s, pos, toks = slots[0], at[0], seqs[0]
     state["fail"] = True
     with pytest.raises(RuntimeError, match="injected"):
         eng.step([s], [toks[pos:pos + 5]], "all")
     state["fail"] = False
     got = eng.step([s], [toks[pos:pos + 5]], "all")
-    assert rel_err(got, want[pos:pos + 5]) <= TOL["bfloat16"]
+    assert rel_err(got, want[0][pos:pos + 5]) <= TOL["bfloat16"]
     eng.check_device_status()
 
 
