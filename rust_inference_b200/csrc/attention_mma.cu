@@ -90,6 +90,14 @@ template <int HD>
 __device__ __forceinline__ void qk_16keys(const uint32_t (*q)[4], uint32_t ktile, int kbase, float (*s)[4]) {
     const int lane = threadIdx.x & 31;
     const int mi = lane >> 3, rr = lane & 7;
+    // The k-steps go round four accumulators, so that an MMA waits for the one four steps before it and not
+    // for its neighbour: a decode step's CTAs have a page or two each and nothing else to fill the pipe with.
+    constexpr int CH = (HD / 16) < 4 ? (HD / 16) : 4;
+    float part[CH][2][4];
+#pragma unroll
+    for (int c = 0; c < CH; ++c)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) part[c][0][e] = part[c][1][e] = 0.f;
 #pragma unroll
     for (int ks = 0; ks < HD / 16; ++ks) {
         // matrices: (keys 0-7, k 0-7), (keys 0-7, k 8-15), (keys 8-15, k 0-7), (keys 8-15, k 8-15)
@@ -97,8 +105,19 @@ __device__ __forceinline__ void qk_16keys(const uint32_t (*q)[4], uint32_t ktile
         const int chunk = ks * 2 + (mi & 1);
         uint32_t b0, b1, b2, b3;
         ldmatrix_x4(ktile + tile_off<HD>(row, chunk), b0, b1, b2, b3);
-        mma_bf16(s[0], q[ks], b0, b1);
-        mma_bf16(s[1], q[ks], b2, b3);
+        mma_bf16(part[ks % CH][0], q[ks], b0, b1);
+        mma_bf16(part[ks % CH][1], q[ks], b2, b3);
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+        for (int c = 0; c < CH; ++c) {
+            a0 += part[c][0][e];
+            a1 += part[c][1][e];
+        }
+        s[0][e] += a0;
+        s[1][e] += a1;
     }
 }
 
@@ -149,6 +168,76 @@ __device__ __forceinline__ void softmax_update(float (*s)[4], float* m, float* l
         for (int t = 0; t < ONT; ++t) {
             o[t][2 * half] *= alpha;
             o[t][2 * half + 1] *= alpha;
+        }
+    }
+}
+
+// The merge of a CTA's four warps, each of which saw a quarter of the keys: `so` holds their unnormalised
+// outputs [4][16][HD + 4], `sml` their running maximum and sum per row [4][16][2].  Returns outputs d .. d+3 of
+// row r scaled to the row's maximum M over the warps, and M and the row's sum L.  Every thread works the
+// statistics of its row out itself (four loads and exponentials that overlap) instead of waiting at a barrier
+// for one thread per row.
+template <int HD>
+__device__ __forceinline__ float4 merge_warps(const float* so, const float* sml, int r, int d, float& M, float& L) {
+    constexpr int SO_LD = HD + 4;
+    float2 ml[4];
+#pragma unroll
+    for (int w = 0; w < 4; ++w) ml[w] = *reinterpret_cast<const float2*>(sml + ((w * 16 + r) << 1));
+    M = fmaxf(fmaxf(ml[0].x, ml[1].x), fmaxf(ml[2].x, ml[3].x));
+    L = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+        const float f = (M == -INFINITY) ? 0.f : expf(ml[w].x - M);
+        const float4 x = *reinterpret_cast<const float4*>(so + (w * 16 + r) * SO_LD + d);
+        L += f * ml[w].y;
+        acc.x += f * x.x;
+        acc.y += f * x.y;
+        acc.z += f * x.z;
+        acc.w += f * x.w;
+    }
+    return acc;
+}
+
+// four consecutive outputs as bfloat16: one 8-byte store where the row allows it
+__device__ __forceinline__ void store_bf16x4(__nv_bfloat16* p, float a, float b, float c, float d, bool wide) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    if (wide) {
+        uint2 v;
+        v.x = *reinterpret_cast<const uint32_t*>(&lo);
+        v.y = *reinterpret_cast<const uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(p) = v;
+    } else {                                              // rows that are only 4-byte aligned
+        *reinterpret_cast<__nv_bfloat162*>(p) = lo;
+        *reinterpret_cast<__nv_bfloat162*>(p + 2) = hi;
+    }
+}
+
+// What a CTA that merged its warps does with row r, outputs d .. d+3, when it is not part of a cluster: the
+// final result if it saw the whole sequence, else its partial result for the kernel that merges the splits.
+template <int HD>
+__device__ __forceinline__ void write_merged(const float* so, const float* sml, int r, int d, int b, int h, int token,
+                                             int n_heads, int n_splits, int split, float* __restrict__ part_o,
+                                             float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out, int out_ld) {
+    float M, L;
+    const float4 acc = merge_warps<HD>(so, sml, r, d, M, L);
+    if (n_splits == 1) {
+        const bool wide = ((reinterpret_cast<uintptr_t>(out) & 7) == 0) && ((out_ld & 3) == 0);
+        store_bf16x4(out + (size_t)token * out_ld + (size_t)h * HD + d, acc.x / L, acc.y / L, acc.z / L, acc.w / L, wide);
+    } else {
+        const size_t row = ((size_t)b * n_heads + h) * n_splits + split;
+        float* po = part_o + row * HD + d;
+        if ((reinterpret_cast<uintptr_t>(part_o) & 15) == 0) {
+            *reinterpret_cast<float4*>(po) = acc;
+        } else {
+            po[0] = acc.x;
+            po[1] = acc.y;
+            po[2] = acc.z;
+            po[3] = acc.w;
+        }
+        if (d == 0) {
+            part_ml[row * 2] = M;
+            part_ml[row * 2 + 1] = L;
         }
     }
 }
@@ -216,6 +305,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_ld, const __nv_bfl
         *reinterpret_cast<uint4*>(smem + 2 * NBUF * TILE + tile_off<HD>(r, c)) = v;
     }
     __syncthreads();                                      // Q tile written
+    RI_PHASE(0);
 
     uint32_t qf[HD / 16][4];
     {
@@ -262,12 +352,12 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_ld, const __nv_bfl
         __syncthreads();                                  // everyone is done with this buffer
     }
 
+    RI_PHASE(1);
+    RI_PHASE_LATEST(2);
     // ---- merge the 4 warps (each saw a quarter of the keys) through shared memory ----
     constexpr int SO_LD = HD + 4;                         // padded rows: the 8 rows a warp stores at once hit 8 bank groups
     float* so = reinterpret_cast<float*>(smem);           // [4][16][SO_LD]
     float* sml = so + 4 * 16 * SO_LD;                     // [4][16][2]
-    float* rowf = sml + 4 * 16 * 2;                       // [4][16]: exp(m_w - M) of each warp and row
-    float* rowML = rowf + 4 * 16;                         // [16][2]: the CTA's M and L of each row
 #pragma unroll
     for (int t = 0; t < HD / 8; ++t) {
         const int d = t * 8 + 2 * tq;
@@ -280,92 +370,72 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_ld, const __nv_bfl
         sml[((warp * 16 + g + 8) << 1)] = m[1];
         sml[((warp * 16 + g + 8) << 1) + 1] = l[1];
     }
-    __syncthreads();
-    // a row's statistics once (not once per output element): its maximum over the warps, each warp's factor, its sum
-    if ((int)threadIdx.x < n_rep) {
-        const int r = threadIdx.x;
-        float M = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < 4; ++w) M = fmaxf(M, sml[(w * 16 + r) << 1]);
-        float L = 0.f;
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {
-            const float f = (M == -INFINITY) ? 0.f : expf(sml[(w * 16 + r) << 1] - M);
-            rowf[w * 16 + r] = f;
-            L += f * sml[((w * 16 + r) << 1) + 1];
-        }
-        rowML[2 * r] = M;
-        rowML[2 * r + 1] = L;
-    }
-    // cluster form: what the peers send lies behind the Q tile, outside anything a CTA still works on
-    namespace cg = cooperative_groups;
-    cg::cluster_group cluster = cg::this_cluster();
-    const int chunk = (n_rep * HD + n_splits - 1) / n_splits;
-    float* recv_o = reinterpret_cast<float*>(smem + 2 * NBUF * TILE + 16 * HD * 2);   // [n_splits][chunk]
-    float* recv_ml = recv_o + 16 * HD + MAX_CLUSTER_SPLITS;                           // [n_splits][16][2]
-    float* comb = recv_ml + MAX_CLUSTER_SPLITS * 16 * 2;                              // [n_splits + 1][16]: factors, 1 / L
-    if (CLUSTER) {
+    __syncthreads();                                      // every warp's partial result is in shared memory
+    if constexpr (CLUSTER) {
+        // The splits of this (sequence, kv head) are the CTAs of one cluster (its z extent).  Every CTA merges its
+        // four warps and sends the result to the CTA that merges that part of the output over the splits (runs of
+        // `chunk` outputs, a multiple of 4, so that everything moves as float4): plain stores into the peers'
+        // shared memory, nothing is read remotely.  Each thread works out its row's maximum and factors itself
+        // (a few loads and exponentials that overlap) rather than wait at a barrier for one thread per row.
+        namespace cg = cooperative_groups;
+        cg::cluster_group cluster = cg::this_cluster();
+        const int total = n_rep * HD;
+        const int chunk = (((total + n_splits - 1) / n_splits) + 3) & ~3;
+        // what the peers send lies behind the Q tile, outside anything a CTA still works on
+        float* recv_o = reinterpret_cast<float*>(smem + 2 * NBUF * TILE + 16 * HD * 2);    // [n_splits][chunk]
+        float* recv_ml = recv_o + 16 * HD + 4 * MAX_CLUSTER_SPLITS;                        // [n_splits][16][2]
         // every CTA of the cluster has arrived at the barrier near its start by now: all of them exist, so
         // their shared memory may be written
         asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-    }
-    __syncthreads();                                      // row statistics written
-    if (CLUSTER && (int)threadIdx.x < n_rep) {
-        // this CTA's row statistics to every CTA of the cluster (plain stores into the peers' shared memory)
-        const int r = threadIdx.x;
-        for (int sp = 0; sp < n_splits; ++sp) {
-            float* ml = cluster.map_shared_rank(recv_ml, sp) + (split * 16 + r) * 2;
-            ml[0] = rowML[2 * r];
-            ml[1] = rowML[2 * r + 1];
+        for (int it = threadIdx.x; it < n_rep * (HD / 4); it += THREADS) {
+            const int r = it / (HD / 4), d = (it % (HD / 4)) * 4;
+            float M, L;
+            const float4 acc = merge_warps<HD>(so, sml, r, d, M, L);
+            const int idx = r * HD + d, owner = idx / chunk;
+            *reinterpret_cast<float4*>(cluster.map_shared_rank(recv_o, owner) + split * chunk + (idx - owner * chunk)) = acc;
+            // the row's statistics go with the first piece of the row that a CTA merges: to the CTAs that need them
+            if (d == 0 || idx == owner * chunk)
+                *reinterpret_cast<float2*>(cluster.map_shared_rank(recv_ml, owner) + (split * 16 + r) * 2) = make_float2(M, L);
         }
-    }
-    for (int idx = threadIdx.x; idx < n_rep * HD; idx += THREADS) {
-        const int r = idx / HD, d = idx % HD;
-        float acc = 0.f;
-#pragma unroll
-        for (int w = 0; w < 4; ++w) acc += rowf[w * 16 + r] * so[(w * 16 + r) * SO_LD + d];
-        const int h = kvh * n_rep + r;
-        if (CLUSTER) {
-            // The splits of this (sequence, kv head) are the CTAs of one cluster (its z extent).  Output idx is
-            // merged by CTA idx / chunk: every CTA sends its partial value there; nothing is read remotely.
-            const int owner = idx / chunk;
-            cluster.map_shared_rank(recv_o, owner)[split * chunk + (idx - owner * chunk)] = acc;
-        } else if (n_splits == 1) {
-            out[(size_t)token * out_ld + (size_t)h * HD + d] = __float2bfloat16_rn(acc / rowML[2 * r + 1]);
-        } else {
-            const size_t row = ((size_t)b * n_heads + h) * n_splits + split;
-            part_o[row * HD + d] = acc;
-            if (d == 0) {
-                part_ml[row * 2] = rowML[2 * r];
-                part_ml[row * 2 + 1] = rowML[2 * r + 1];
-            }
-        }
-    }
-    if (CLUSTER) {
+        RI_PHASE(3);
         cluster.sync();                                   // everything sent has arrived
-        if ((int)threadIdx.x < n_rep) {
-            // a row's merge over the splits once: its maximum, each split's factor, one over its sum
-            const int r = threadIdx.x;
-            float M = -INFINITY;
-            for (int sp = 0; sp < n_splits; ++sp) M = fmaxf(M, recv_ml[(sp * 16 + r) * 2]);
-            float L = 0.f;
-            for (int sp = 0; sp < n_splits; ++sp) {
-                const float ms = recv_ml[(sp * 16 + r) * 2];
-                const float f = (ms == -INFINITY) ? 0.f : expf(ms - M);
-                comb[sp * 16 + r] = f;
-                L += f * recv_ml[(sp * 16 + r) * 2 + 1];
-            }
-            comb[n_splits * 16 + r] = 1.0f / L;
-        }
-        __syncthreads();
-        const int lo = split * chunk, hi = min(n_rep * HD, lo + chunk);
-        for (int idx = lo + (int)threadIdx.x; idx < hi; idx += THREADS) {
+        RI_PHASE(4);
+        const int lo = split * chunk, hi = min(total, lo + chunk);
+        const bool wide = ((reinterpret_cast<uintptr_t>(out) & 7) == 0) && ((out_ld & 3) == 0);
+        for (int idx = lo + 4 * (int)threadIdx.x; idx < hi; idx += 4 * THREADS) {
             const int r = idx / HD, d = idx % HD;
-            float acc = 0.f;
-            for (int sp = 0; sp < n_splits; ++sp) acc += comb[sp * 16 + r] * recv_o[sp * chunk + (idx - lo)];
-            out[(size_t)token * out_ld + (size_t)(kvh * n_rep + r) * HD + d] = __float2bfloat16_rn(acc * comb[n_splits * 16 + r]);
+            float2 ml[MAX_CLUSTER_SPLITS];
+            float M = -INFINITY;
+#pragma unroll
+            for (int sp = 0; sp < MAX_CLUSTER_SPLITS; ++sp)
+                if (sp < n_splits) {
+                    ml[sp] = *reinterpret_cast<const float2*>(recv_ml + (sp * 16 + r) * 2);
+                    M = fmaxf(M, ml[sp].x);
+                }
+            float L = 0.f;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int sp = 0; sp < MAX_CLUSTER_SPLITS; ++sp)
+                if (sp < n_splits) {
+                    const float f = (ml[sp].x == -INFINITY) ? 0.f : expf(ml[sp].x - M);
+                    const float4 x = *reinterpret_cast<const float4*>(recv_o + sp * chunk + (idx - lo));
+                    L += f * ml[sp].y;
+                    acc.x += f * x.x;
+                    acc.y += f * x.y;
+                    acc.z += f * x.z;
+                    acc.w += f * x.w;
+                }
+            const float inv = 1.0f / L;
+            store_bf16x4(out + (size_t)token * out_ld + (size_t)(kvh * n_rep + r) * HD + d, acc.x * inv, acc.y * inv,
+                         acc.z * inv, acc.w * inv, wide);
         }
+        RI_PHASE_LATEST(5);
         // nobody reads or writes a peer's shared memory after that barrier: a CTA may leave when it is done
+        return;
+    }
+    for (int it = threadIdx.x; it < n_rep * (HD / 4); it += THREADS) {
+        const int r = it / (HD / 4), d = (it % (HD / 4)) * 4;
+        write_merged<HD>(so, sml, r, d, b, kvh * n_rep + r, token, n_heads, n_splits, split, part_o, part_ml, out, out_ld);
     }
 }
 
@@ -540,8 +610,6 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     constexpr int SO_LD = HD + 4;                         // padded rows: the 8 rows a warp stores at once hit 8 bank groups
     float* so = reinterpret_cast<float*>(smem);           // [4][16][SO_LD]
     float* sml = so + 4 * 16 * SO_LD;                     // [4][16][2]
-    float* rowf = sml + 4 * 16 * 2;                       // [4][16]: exp(m_w - M) of each warp and row
-    float* rowML = rowf + 4 * 16;                         // [16][2]: M and L of each row
     if (warp < 4) {
 #pragma unroll
         for (int t = 0; t < HD / 8; ++t) {
@@ -558,39 +626,9 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     }
     __syncthreads();
     if (abort_flag) return;
-    // a row's statistics once (not once per output element)
-    if ((int)threadIdx.x < n_rep) {
-        const int r = threadIdx.x;
-        float M = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < 4; ++w) M = fmaxf(M, sml[(w * 16 + r) << 1]);
-        float L = 0.f;
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {
-            const float f = (M == -INFINITY) ? 0.f : expf(sml[(w * 16 + r) << 1] - M);
-            rowf[w * 16 + r] = f;
-            L += f * sml[((w * 16 + r) << 1) + 1];
-        }
-        rowML[2 * r] = M;
-        rowML[2 * r + 1] = L;
-    }
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < n_rep * HD; idx += DECODE_TMA_THREADS) {
-        const int r = idx / HD, d = idx % HD;
-        float acc = 0.f;
-#pragma unroll
-        for (int w = 0; w < 4; ++w) acc += rowf[w * 16 + r] * so[(w * 16 + r) * SO_LD + d];
-        const int h = kvh * n_rep + r;
-        if (n_splits == 1) {
-            out[(size_t)token * out_ld + (size_t)h * HD + d] = __float2bfloat16_rn(acc / rowML[2 * r + 1]);
-        } else {
-            const size_t row = ((size_t)b * n_heads + h) * n_splits + split;
-            part_o[row * HD + d] = acc;
-            if (d == 0) {
-                part_ml[row * 2] = rowML[2 * r];
-                part_ml[row * 2 + 1] = rowML[2 * r + 1];
-            }
-        }
+    for (int it = threadIdx.x; it < n_rep * (HD / 4); it += DECODE_TMA_THREADS) {
+        const int r = it / (HD / 4), d = (it % (HD / 4)) * 4;
+        write_merged<HD>(so, sml, r, d, b, kvh * n_rep + r, token, n_heads, n_splits, split, part_o, part_ml, out, out_ld);
     }
 }
 
@@ -763,18 +801,49 @@ int launch_decode(const void* q, int q_ld, const void* kc, const void* vc, const
 
 // The splits of a (sequence, kv head) as one thread-block cluster that merges its own partial results.
 
+// page buffers (the warps' merge area lies over them), the Q tile, and what the peers send
+template <int HD>
+constexpr int cluster_smem_bytes() {
+    static_assert((4 * 16 * (HD + 4) + 4 * 16 * 2 + 4 * 16 + 16 * 2) * 4 <= 2 * NBUF * PAGE * HD * 2, "merge area must fit the page buffers");
+    return 2 * NBUF * PAGE * HD * 2 + 16 * HD * 2 + (16 * HD + 4 * MAX_CLUSTER_SPLITS + MAX_CLUSTER_SPLITS * 16 * 2) * 4;
+}
+
+template <int HD>
+PerDeviceOnce& cluster_configured() {      // per device: the attribute belongs to a device's copy of the kernel
+    static PerDeviceOnce once;
+    return once;
+}
+
+// How many clusters of n_splits CTAs of the kernel the device holds at once.
+template <int HD>
+int decode_cluster_capacity(int n_splits, int* clusters) {
+    constexpr int SMEM = cluster_smem_bytes<HD>();
+    auto kernel = attn_decode_kernel<HD, true>;
+    if (int rc = raise_dynamic_smem(kernel, SMEM, cluster_configured<HD>(), "attention")) return rc;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1, 1, n_splits);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = SMEM;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = (unsigned)n_splits;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaOccupancyMaxActiveClusters(clusters, kernel, &cfg);
+    if (e != cudaSuccess) return fail("attention_decode: cannot ask how many clusters fit: %s", cudaGetErrorString(e));
+    return 0;
+}
+
 template <int HD>
 int launch_decode_cluster(const void* q, int q_ld, const void* kc, const void* vc, const int* page_table, int max_pages,
                           const int* seq_slot, const int* seq_len, const int* cu_seqlens, int n_seqs, int n_heads,
                           int n_kv_heads, float scale, int window, int n_splits, void* out, int out_ld,
                           cudaStream_t stream) {
-    // page buffers (the warps' merge area lies over them), the Q tile, and what the peers send
-    constexpr int SMEM = 2 * NBUF * PAGE * HD * 2 + 16 * HD * 2 +
-                         (16 * HD + MAX_CLUSTER_SPLITS + MAX_CLUSTER_SPLITS * 16 * 2 + (MAX_CLUSTER_SPLITS + 1) * 16) * 4;
-    static_assert((4 * 16 * (HD + 4) + 4 * 16 * 2 + 4 * 16 + 16 * 2) * 4 <= 2 * NBUF * PAGE * HD * 2, "merge area must fit the page buffers");
+    constexpr int SMEM = cluster_smem_bytes<HD>();
     auto kernel = attn_decode_kernel<HD, true>;
-    static PerDeviceOnce configured;       // per device: the attribute belongs to a device's copy of the kernel
-    if (int rc = raise_dynamic_smem(kernel, SMEM, configured, "attention")) return rc;
+    if (int rc = raise_dynamic_smem(kernel, SMEM, cluster_configured<HD>(), "attention")) return rc;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(n_seqs, n_kv_heads, n_splits);
     cfg.blockDim = dim3(THREADS);
@@ -895,6 +964,15 @@ RI_API int ri_attention_decode_cluster(const void* q, int q_ld, const void* kcac
                                          n_seqs, n_heads, n_kv_heads, scale, window, n_splits, out, out_ld, stream);
     return launch_decode_cluster<128>(q, q_ld, kcache, vcache, page_table, max_pages, seq_slot, seq_len, cu_seqlens,
                                       n_seqs, n_heads, n_kv_heads, scale, window, n_splits, out, out_ld, stream);
+}
+
+// clusters[0] = how many clusters of n_splits CTAs of that kernel the current device holds at the same time:
+// a step with more (sequences x kv heads) than that runs them in turns.
+RI_API int ri_attention_decode_cluster_capacity(int hd, int n_splits, int* clusters) {
+    if (hd != 64 && hd != 128) return fail("attention_mma: head_dim %d is not 64 or 128", hd);
+    if (n_splits < 2 || n_splits > MAX_CLUSTER_SPLITS)
+        return fail("attention_decode: a cluster takes 2 to %d splits, not %d", MAX_CLUSTER_SPLITS, n_splits);
+    return hd == 64 ? decode_cluster_capacity<64>(n_splits, clusters) : decode_cluster_capacity<128>(n_splits, clusters);
 }
 
 // The same with the cache pages brought in by TMA.  map_k / map_v: tensor maps (128 bytes each) of the

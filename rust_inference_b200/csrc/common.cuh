@@ -109,9 +109,76 @@ __device__ __forceinline__ float silu_f32(float x) {
 // `let_next_kernel_start()` tells the scheduler that the next kernel may be brought onto the
 // SMs; its own wait still holds it until this kernel has finished and its writes are visible.
 // Setting RI_B200_NO_PDL=1 launches everything strictly one after another.
+//
+// The timeline build (-DRI_TIMELINE; `RI_B200_TIMELINE=1` makes the Python side compile and load it from
+// a folder of its own) makes these two calls keep a record per kernel launch, written by thread 0 of
+// block 0: the device-wide timer when the kernel came onto an SM, when its wait for the kernel before
+// ended, and at up to RI_TIMELINE_PHASES places a kernel marks with RI_PHASE(k), all with plain stores;
+// RI_PHASE_LATEST(k) keeps the latest time at which thread 0 of any block passed.
+// `ri_timeline_read` hands the records to the host, which sees a captured step kernel by kernel with
+// the overlap it really has.  In the ordinary build none of this exists.
 // ---------------------------------------------------------------------------------------
+#define RI_TIMELINE_PHASES 6
+#ifdef RI_TIMELINE
+#define RI_TIMELINE_CAP 4096
+#define RI_TIMELINE_WORDS (5 + RI_TIMELINE_PHASES)        // entry time, entry line, wait time, wait line, grid id, phases
+__device__ unsigned long long g_timeline[RI_TIMELINE_CAP * RI_TIMELINE_WORDS];
+__device__ unsigned int g_timeline_n;
+__device__ __forceinline__ unsigned long long global_timer() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// A launch's record is found by the launch's own number (%gridid, which the hardware gives every
+// launch), so that no mark has to wait for an atomic's answer and nothing is kept in shared memory
+// (several kernels lay out their shared memory to the byte).  The host sees two launches that fell on
+// one record by their count.
+__device__ __forceinline__ unsigned long long* timeline_record(unsigned long long& grid) {
+    asm volatile("mov.u64 %0, %%gridid;" : "=l"(grid));
+    return g_timeline + (size_t)(grid % RI_TIMELINE_CAP) * RI_TIMELINE_WORDS;
+}
+__device__ __forceinline__ bool timeline_writer() {
+    return (blockIdx.x | blockIdx.y | blockIdx.z) == 0 && (threadIdx.x | threadIdx.y | threadIdx.z) == 0;
+}
+__device__ __forceinline__ void timeline_entry(int line) {
+    if (!timeline_writer()) return;
+    unsigned long long grid;
+    unsigned long long* rec = timeline_record(grid);
+    rec[0] = global_timer();
+    rec[1] = (unsigned long long)line;
+    rec[4] = grid + 1;
+    atomicAdd(&g_timeline_n, 1u);                          // the answer is not used: nothing waits for it
+}
+__device__ __forceinline__ void timeline_mark(int word, int line) {
+    if (!timeline_writer()) return;
+    unsigned long long grid;
+    unsigned long long* rec = timeline_record(grid);
+    rec[word] = global_timer();
+    if (word == 2) rec[3] = (unsigned long long)line;
+}
+// the latest time at which thread 0 of ANY block passed this place (one fire-and-forget atomic per block)
+__device__ __forceinline__ void timeline_mark_latest(int word) {
+    if ((threadIdx.x | threadIdx.y | threadIdx.z) != 0) return;
+    unsigned long long grid;
+    unsigned long long* rec = timeline_record(grid);
+    atomicMax(rec + word, global_timer());
+}
+#define RI_PHASE(k) ri::timeline_mark(5 + (k), __LINE__)
+#define RI_PHASE_LATEST(k) ri::timeline_mark_latest(5 + (k))
+__device__ __forceinline__ void wait_for_previous_kernels(int line = __builtin_LINE()) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    timeline_mark(2, line);
+}
+__device__ __forceinline__ void let_next_kernel_start(int line = __builtin_LINE()) {
+    timeline_entry(line);
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+#else
+#define RI_PHASE(k) ((void)0)
+#define RI_PHASE_LATEST(k) ((void)0)
 __device__ __forceinline__ void wait_for_previous_kernels() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void let_next_kernel_start() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#endif
 
 inline bool pdl_enabled() {
     static int on = -1;
@@ -222,6 +289,32 @@ __device__ __forceinline__ bool in_range(long long i, long long limit, int check
     RI_API int ri_bounds_report(int*) { return ri::fail("this library is not a checked build"); }
 #endif
 
+#ifdef RI_TIMELINE
+#define RI_DEFINE_TIMELINE()                                                                                   \
+    /* Copies the table of RI_TIMELINE_CAP records (RI_TIMELINE_WORDS words each; a record whose first word  */ \
+    /* is 0 is empty) to `out`, clears it and returns how many launches were recorded since the last call    */ \
+    /* (-1: error).  Synchronises the device.                                                                */ \
+    RI_API int ri_timeline_read(unsigned long long* out, int cap) {                                            \
+        if (cap < RI_TIMELINE_CAP) return ri::fail("timeline: room for %d records needed", RI_TIMELINE_CAP), -1; \
+        unsigned int n = 0;                                                                                    \
+        const size_t bytes = sizeof(unsigned long long) * RI_TIMELINE_CAP * RI_TIMELINE_WORDS;                 \
+        cudaError_t e = cudaDeviceSynchronize();                                                               \
+        if (e == cudaSuccess) e = cudaMemcpyFromSymbol(&n, ri::g_timeline_n, sizeof(n));                       \
+        if (e == cudaSuccess) e = cudaMemcpyFromSymbol(out, ri::g_timeline, bytes);                            \
+        void* base = nullptr;                                                                                  \
+        if (e == cudaSuccess) e = cudaGetSymbolAddress(&base, ri::g_timeline);                                 \
+        if (e == cudaSuccess) e = cudaMemset(base, 0, bytes);                                                  \
+        const unsigned int zero = 0;                                                                           \
+        if (e == cudaSuccess) e = cudaMemcpyToSymbol(ri::g_timeline_n, &zero, sizeof(zero));                   \
+        if (e != cudaSuccess) return ri::fail("timeline: cannot read the records: %s", cudaGetErrorString(e)), -1; \
+        return (int)n;                                                                                         \
+    }
+#else
+#define RI_DEFINE_TIMELINE() \
+    RI_API int ri_timeline_read(unsigned long long*, int) { return ri::fail("this library is not a timeline build"), -1; }
+#endif
+
 #define RI_DEFINE_LAST_ERROR() \
     RI_DEFINE_BOUNDS()         \
+    RI_DEFINE_TIMELINE()       \
     RI_API const char* ri_last_error() { return ri::error_buffer(); }

@@ -112,6 +112,7 @@ rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ w, con
             store4<T>(o + 4 * i, xv[j].x * scale * wv[j].x, xv[j].y * scale * wv[j].y, xv[j].z * scale * wv[j].z,
                       xv[j].w * scale * wv[j].w);
     }
+    RI_PHASE_LATEST(5);
 }
 
 // Steps of many rows (prompts): one warp per row, the row in registers, no block-wide barrier; the
@@ -457,6 +458,13 @@ __global__ void rope_cache_write_acc_kernel(float* __restrict__ acc, int ld, con
     constants(threadIdx.x);
     wait_for_previous_kernels();          // the projections come from the previous kernel
 
+    // the first round of values goes out with the first round of pairs: one trip to memory, not two
+    float v_first[PER];
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+        const int idx = threadIdx.x + j * blockDim.x;
+        if (idx < kv_dim) v_first[j] = row[q_dim + kv_dim + idx];
+    }
     // rotary pairs of the q heads and then the k heads (same column order in the accumulator)
     for (int base = threadIdx.x; base < n_pairs; base += PER * blockDim.x) {
         if (base != (int)threadIdx.x) constants(base);
@@ -495,7 +503,7 @@ __global__ void rope_cache_write_acc_kernel(float* __restrict__ acc, int ld, con
         for (int j = 0; j < PER; ++j) {
             const int idx = base + j * blockDim.x;
             if (idx < kv_dim) {
-                v[j] = row[q_dim + kv_dim + idx];
+                v[j] = base == (int)threadIdx.x ? v_first[j] : row[q_dim + kv_dim + idx];
                 if (bias) v[j] += bias[q_dim + kv_dim + idx];
             }
         }
@@ -508,6 +516,7 @@ __global__ void rope_cache_write_acc_kernel(float* __restrict__ acc, int ld, con
             }
         }
     }
+    RI_PHASE_LATEST(5);
 }
 
 RI_API int ri_rope_cache_write_acc(float* acc, int ld, const float* bias, void* q_out, int dtype, const float* cos_t,

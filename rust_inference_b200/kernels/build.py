@@ -47,9 +47,14 @@ CXX_FLAGS = ["-std=c++17", "-O2", "-shared", "-fPIC", "-fvisibility=hidden"]
 # and loaded from a folder of its own, beside the ordinary libraries.
 CHECKED = os.environ.get("RI_B200_CHECK_BOUNDS", "") == "1"
 
+# RI_B200_TIMELINE=1: the timeline build (thread 0 of every launch's first block records when the kernel
+# came onto an SM and when its wait for the kernel before ended: `csrc/common.cuh`), likewise in a
+# folder of its own.  For looking at a step's kernels as they overlap; slightly slower than the ordinary one.
+TIMELINE = os.environ.get("RI_B200_TIMELINE", "") == "1"
 
-def _nvcc_flags(checked: bool) -> list:
-    return NVCC_FLAGS + (["-DRI_CHECK_BOUNDS"] if checked else [])
+
+def _nvcc_flags(checked: bool, timeline: bool) -> list:
+    return NVCC_FLAGS + (["-DRI_CHECK_BOUNDS"] if checked else []) + (["-DRI_TIMELINE"] if timeline else [])
 
 
 class KernelBuildError(RuntimeError):
@@ -74,11 +79,14 @@ def _cxx() -> str:
     raise KernelBuildError("no C++ compiler found: the host runtime cannot be compiled (set CXX or PATH)")
 
 
-def _build_dir(checked: bool | None = None) -> str:
+def _build_dir(checked: bool | None = None, timeline: bool | None = None) -> str:
     checked = CHECKED if checked is None else checked
+    timeline = TIMELINE if timeline is None else timeline
     d = os.environ.get("RI_B200_BUILD_DIR") or os.path.join(CSRC, "_build")
     if checked:
         d = os.path.join(d, "checked")
+    if timeline:
+        d = os.path.join(d, "timeline")
     try:
         os.makedirs(d, exist_ok=True)
         probe = os.path.join(d, f".w{os.getpid()}")
@@ -87,14 +95,15 @@ def _build_dir(checked: bool | None = None) -> str:
         os.remove(probe)
         return d
     except OSError:
-        d = os.path.join(tempfile.gettempdir(), f"ri_b200_build_{os.getuid()}" + ("_checked" if checked else ""))
+        d = os.path.join(tempfile.gettempdir(), f"ri_b200_build_{os.getuid()}" + ("_checked" if checked else "")
+                         + ("_timeline" if timeline else ""))
         os.makedirs(d, exist_ok=True)
         return d
 
 
-def _source_digest(src: str, checked: bool) -> str:
+def _source_digest(src: str, checked: bool, timeline: bool) -> str:
     h = hashlib.sha256()
-    h.update(" ".join(_nvcc_flags(checked) if src.endswith(".cu") else CXX_FLAGS).encode())
+    h.update(" ".join(_nvcc_flags(checked, timeline) if src.endswith(".cu") else CXX_FLAGS).encode())
     headers = sorted(f for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))) if src.endswith(".cu") else []
     for name in [src] + headers:
         with open(os.path.join(CSRC, name), "rb") as f:
@@ -107,23 +116,25 @@ def _say(msg: str) -> None:
     print(f"[rust_inference_b200] {msg}", file=sys.stderr, flush=True)
 
 
-def library_path(module: str, checked: bool | None = None) -> str:
-    return os.path.join(_build_dir(checked), f"libri_{module}.so")
+def library_path(module: str, checked: bool | None = None, timeline: bool | None = None) -> str:
+    return os.path.join(_build_dir(checked, timeline), f"libri_{module}.so")
 
 
-def build(module: str, *, force: bool = False, verbose: bool = True, checked: bool | None = None) -> str:
-    """Compile one module if its library is missing or older than its sources (`checked`: the checked
-    build instead of the one this process loads)."""
+def build(module: str, *, force: bool = False, verbose: bool = True, checked: bool | None = None,
+          timeline: bool | None = None) -> str:
+    """Compile one module if its library is missing or older than its sources (`checked`, `timeline`:
+    that build instead of the one this process loads)."""
     checked = CHECKED if checked is None else checked
+    timeline = TIMELINE if timeline is None else timeline
     if module not in MODULES:
         raise KernelBuildError(f"unknown kernel module {module!r}")
     src = MODULES[module]
     src_path = os.path.join(CSRC, src)
     if not os.path.isfile(src_path):
         raise KernelBuildError(f"kernel source {src_path} is missing")
-    out = library_path(module, checked)
+    out = library_path(module, checked, timeline)
     stamp = out + ".sha256"
-    digest = _source_digest(src, checked)
+    digest = _source_digest(src, checked, timeline)
     lock_path = os.path.join(os.path.dirname(out), f".{module}.lock")
     with open(lock_path, "w") as lock:
         fcntl.flock(lock, fcntl.LOCK_EX)
@@ -134,11 +145,12 @@ def build(module: str, *, force: bool = False, verbose: bool = True, checked: bo
                         return out
             tmp = out + f".{os.getpid()}.tmp"
             if src.endswith(".cu"):
-                cmd = [_nvcc()] + _nvcc_flags(checked) + ["-I", CSRC, "-o", tmp, src_path]
+                cmd = [_nvcc()] + _nvcc_flags(checked, timeline) + ["-I", CSRC, "-o", tmp, src_path]
             else:
                 cmd = [_cxx()] + CXX_FLAGS + ["-o", tmp, src_path]
             if verbose:
-                _say(f"compiling {src}" + (" for sm_100a" + (" (checked build)" if checked else "") + " ..."
+                _say(f"compiling {src}" + (" for sm_100a" + (" (checked build)" if checked else "")
+                                            + (" (timeline build)" if timeline else "") + " ..."
                                             if src.endswith(".cu") else " ..."))
             t0 = time.time()
             proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
@@ -185,6 +197,6 @@ def loaded_cuda_modules() -> list[str]:
     return [m for m in _loaded if MODULES[m].endswith(".cu")]
 
 
-def build_all(verbose: bool = True, checked: bool | None = None) -> list[str]:
-    return [build(m, verbose=verbose, checked=checked) for m in MODULES
+def build_all(verbose: bool = True, checked: bool | None = None, timeline: bool | None = None) -> list[str]:
+    return [build(m, verbose=verbose, checked=checked, timeline=timeline) for m in MODULES
             if os.path.isfile(os.path.join(CSRC, MODULES[m]))]

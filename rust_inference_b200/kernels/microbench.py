@@ -3,6 +3,7 @@
     python bench.py --kernel gate_up --tokens 8
     python bench.py --kernel attn_decode --tokens 64 --context 1024
     python bench.py --kernel step_parts --tokens 8      # what each kind of kernel costs INSIDE a decode step
+    RI_B200_TIMELINE=1 python bench.py --kernel step_timeline --tokens 8     # the step kernel by kernel, as it overlaps
 
 The operand that a step streams (weights, or the cache) is rotated over enough copies to
 exceed L2, and the launches are replayed from a CUDA graph so that host launch cost is
@@ -17,7 +18,7 @@ import math
 import torch
 
 KERNELS = ("qkv", "qkv_split", "o_proj", "gate_up", "down", "lm_head", "sample", "attn_decode", "attn_prefill",
-           "attn_prefill_mma", "rmsnorm", "rope", "step_parts")
+           "attn_prefill_mma", "rmsnorm", "rope", "step_parts", "step_timeline")
 
 
 def _graph_time(fn, launches_per_replay: int, reps: int = 10) -> float:
@@ -181,20 +182,13 @@ def run(kernel: str, model: dict, tokens: int, context: int = 1024, eager_only: 
     return out
 
 
-def step_parts(model: dict, batch: int, prompt_min: int = 128, prompt_max: int = 2048) -> dict:
-    """What each kind of kernel costs inside a decode step of `batch` sequences of the whole model: the
-    captured step (model, greedy sampler, move to the next position) is timed as it is and again with
-    one kind of kernel left out; the difference is that kind's share with everything that overlaps it
-    (programmatic dependent launch, tails and ramps) counted as it falls.  Results are microseconds
-    per step; the step without a kernel computes nothing meaningful and is only timed."""
+def _decode_step_setup(model: dict, batch: int, prompt_min: int, prompt_max: int, room: int = 64):
+    """The whole model with random weights, `batch` prompts of random lengths in its cache, and the
+    device arrays of the decode step that follows them (with room for `room` such steps)."""
     import random
     from ..api import Model
     from ..config.registry import config_from_dict
     from ..engine.context import pack_step
-    from ..engine.graphs import DecodeGraph
-    from ..parts import attention as attention_part
-    from ..sampling.params import SamplerConfig
-    from . import ops, tcgen05
 
     cfg = config_from_dict(dict(model))
     m = Model.random(cfg, seed=0, dtype="bfloat16", max_seq_len=8192, max_tokens_in_cache=batch * 2304 + 4096)
@@ -206,12 +200,144 @@ def step_parts(model: dict, batch: int, prompt_min: int = 128, prompt_max: int =
         eng.step(slots[i:i + 8], prompts[i:i + 8], "none")
     starts = eng.cache.lengths(slots)
     # every replay moves the step's positions on by one: room for all of them
-    eng.cache.reserve([(s, st + 64) for s, st in zip(slots, starts)])
+    eng.cache.reserve([(s, st + room) for s, st in zip(slots, starts)])
     meta, layout, _ = pack_step(starts, [[5]] * batch, [[0]] * batch)
     o, c = layout["seq_slot"]
     meta[o:o + c] = slots
     rows = torch.cat([torch.arange(batch, dtype=torch.int32), torch.zeros(batch + 2, dtype=torch.int32)])   # streams, draw counters, seed
     meta_dev = torch.cat([torch.from_numpy(meta), rows]).cuda()
+    return cfg, m, meta_dev
+
+
+def _kernel_of_line(module: str):
+    """line -> name of the `__global__` function of that module's source the line lies in."""
+    import bisect
+    import os
+    import re
+    from . import build
+    with open(os.path.join(build.CSRC, build.MODULES[module])) as f:
+        text = f.read()
+    starts, names = [], []
+    for mt in re.finditer(r"__global__\s+void\s+(?:__launch_bounds__\([^)]*\)\s*)?(\w+)\s*\(", text):
+        starts.append(text.count("\n", 0, mt.start()) + 1)
+        names.append(mt.group(1))
+
+    def name(line: int) -> str:
+        i = bisect.bisect_right(starts, line) - 1
+        return names[i] if i >= 0 else f"{module}:{line}"
+    return name
+
+
+def step_timeline(model: dict, batch: int, prompt_min: int = 128, prompt_max: int = 2048, reps: int = 20) -> dict:
+    """The captured decode step of `batch` sequences kernel by kernel, from the records the timeline
+    build keeps (RI_B200_TIMELINE=1): for every kernel of a layer, averaged over the layers and over
+    `reps` replays, `exclusive_us` (from the end of its wait for the kernel before to the end of the next
+    kernel's wait: what it adds to the step), `resident_before_us` (how long it sat on an SM before
+    the kernel before it finished: the prologue that programmatic dependent launch hides) and the
+    places it marked, in microseconds after its wait ended."""
+    from ..engine.graphs import DecodeGraph
+    from ..sampling.params import SamplerConfig
+    from . import ops, tcgen05
+
+    if not ops.timeline_build():
+        raise SystemExit("step_timeline needs the timeline build: run with RI_B200_TIMELINE=1")
+    cfg, m, meta_dev = _decode_step_setup(model, batch, prompt_min, prompt_max, room=reps + 16)
+    g = DecodeGraph(m.engine, batch, SamplerConfig.plain(0.0))
+    for _ in range(4):                                      # three steps kernel by kernel, then the capture
+        g.load_meta(meta_dev)
+        g.launch()
+    torch.cuda.synchronize()
+    g.load_meta(meta_dev)
+    for _ in range(3):
+        g.graph.replay()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(5):
+        g.graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    step_us = e0.elapsed_time(e1) * 1e3 / 5
+    ops.timeline_read(strict=False)                         # what ran so far is not looked at
+
+    names: dict = {}
+    runs = []
+    for _ in range(reps):
+        g.graph.replay()
+        recs = ops.timeline_read()
+        for r in recs:
+            if r["module"] not in names:
+                names[r["module"]] = _kernel_of_line(r["module"])
+            r["kernel"] = names[r["module"]](r["entry_line"])
+            r["start_ns"] = r["wait_ns"] or r["entry_ns"]
+        runs.append(recs)
+    tcgen05.check_status()
+    n = len(runs[0])
+    if any(len(r) != n for r in runs):
+        raise RuntimeError("the replays recorded different numbers of kernels")
+    seq = [r["kernel"] for r in runs[0]]
+    layers = cfg.num_hidden_layers
+    pre = period = None
+    for p0 in range(0, 8):
+        for k in range(2, 64):
+            if p0 + layers * k <= n and all(seq[p0 + j] == seq[p0 + j + k] for j in range((layers - 1) * k)):
+                pre, period = p0, k
+                break
+        if period:
+            break
+    if not period:
+        raise RuntimeError(f"no repeating run of {layers} layers among {n} kernels: {seq[:40]}")
+
+    def stats(index_sets):
+        """Averages over the given record indices of every replay."""
+        ex = res = 0.0
+        ph = [0.0] * ops.TIMELINE_PHASES
+        ph_n = [0] * ops.TIMELINE_PHASES
+        cnt = 0
+        for recs in runs:
+            for i in index_sets:
+                r = recs[i]
+                if i + 1 < n:
+                    ex += (recs[i + 1]["start_ns"] - r["start_ns"]) * 1e-3
+                res += (r["start_ns"] - r["entry_ns"]) * 1e-3
+                for k, t in enumerate(r["phases_ns"]):
+                    if t:
+                        ph[k] += (t - r["start_ns"]) * 1e-3
+                        ph_n[k] += 1
+                cnt += 1
+        return {"exclusive_us": round(ex / cnt, 3), "resident_before_us": round(res / cnt, 3),
+                "phases_us": [round(ph[k] / ph_n[k], 3) if ph_n[k] else None for k in range(ops.TIMELINE_PHASES)]}
+
+    out = {"kernel": "step_timeline", "tokens": batch, "layers": layers, "kernels_per_step": n,
+           "kernels_per_layer": period, "step_us_in_this_build": step_us,
+           "recorded_span_us": sum((r[-1]["start_ns"] - r[0]["start_ns"]) for r in runs) * 1e-3 / reps,
+           "before_layers": [], "layer": [], "after_layers": []}
+    for i in range(pre):
+        out["before_layers"].append({"kernel": seq[i], **stats([i])})
+    for j in range(period):
+        # the first layer follows the embedding and the last precedes the head: left out of the average
+        idx = [pre + l * period + j for l in range(1, layers - 1)] or [pre + j]
+        out["layer"].append({"kernel": seq[pre + j], "wait_line": runs[0][pre + j]["wait_line"], **stats(idx)})
+    for i in range(pre + layers * period, n):
+        out["after_layers"].append({"kernel": seq[i], **stats([i])})
+    out["layer_us"] = round(sum(k["exclusive_us"] for k in out["layer"]), 3)
+    stamps = sorted({r["start_ns"] for recs in runs for r in recs})
+    out["timer_step_ns"] = min((b - a for a, b in zip(stamps, stamps[1:])), default=0)
+    return out
+
+
+def step_parts(model: dict, batch: int, prompt_min: int = 128, prompt_max: int = 2048) -> dict:
+    """What each kind of kernel costs inside a decode step of `batch` sequences of the whole model: the
+    captured step (model, greedy sampler, move to the next position) is timed as it is and again with
+    one kind of kernel left out; the difference is that kind's share with everything that overlaps it
+    (programmatic dependent launch, tails and ramps) counted as it falls.  Results are microseconds
+    per step; the step without a kernel computes nothing meaningful and is only timed."""
+    from ..engine.graphs import DecodeGraph
+    from ..parts import attention as attention_part
+    from ..sampling.params import SamplerConfig
+    from . import ops, tcgen05
+
+    cfg, m, meta_dev = _decode_step_setup(model, batch, prompt_min, prompt_max)
+    eng = m.engine
     greedy = SamplerConfig.plain(0.0)
 
     def time_step(sampler=greedy, reps=30):
@@ -277,6 +403,9 @@ def main(kernel: str, model: dict, tokens: int, context: int, eager_only: bool =
         return 2
     if kernel == "step_parts":
         print(json.dumps(step_parts(model, tokens)))
+        return 0
+    if kernel == "step_timeline":
+        print(json.dumps(step_timeline(model, tokens)))
         return 0
     print(json.dumps(run(kernel, model, tokens, context, eager_only)))
     return 0

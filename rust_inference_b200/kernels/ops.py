@@ -119,6 +119,48 @@ def bounds_report() -> list:
 
 
 # ----------------------------------------------------------------------------
+# The timeline build (RI_B200_TIMELINE=1)
+# ----------------------------------------------------------------------------
+TIMELINE_PHASES = 6
+
+
+def timeline_build() -> bool:
+    from . import build
+    return build.TIMELINE
+
+
+def timeline_read(strict: bool = True) -> list:
+    """Timeline build only: one record per kernel launched since the last call, in the order the kernels
+    came onto the device: {"module", "entry_ns", "entry_line", "wait_ns", "wait_line", "phases_ns"} with
+    the device-wide timer's values (0: that mark was not passed) and the source lines of the kernel's
+    `let_next_kernel_start()` and `wait_for_previous_kernels()`.  Synchronises the device and clears
+    the records.  `strict`: raise when launches fell on the same record (thousands since the last read)."""
+    import ctypes
+    from . import build
+    words = 5 + TIMELINE_PHASES
+    cap = 4096
+    out = []
+    for module in build.loaded_cuda_modules():
+        lib = load(module)
+        buf = (ctypes.c_ulonglong * (cap * words))()
+        n = lib.ri_timeline_read(buf, c_int(cap))
+        if n < 0:
+            raise KernelError(f"{module}: {lib.ri_last_error().decode()}")
+        found = 0
+        for i in range(cap):
+            if buf[i * words]:
+                r = buf[i * words:(i + 1) * words]
+                out.append({"module": module, "entry_ns": r[0], "entry_line": r[1], "wait_ns": r[2], "wait_line": r[3],
+                            "grid": r[4] - 1, "phases_ns": list(r[5:])})
+                found += 1
+        if strict and found != n:
+            raise KernelError(f"{module}: {n} launches since the last read but {found} records: launches fell on "
+                              f"the same record (the timeline keeps {cap})")
+    out.sort(key=lambda r: r["entry_ns"])
+    return out
+
+
+# ----------------------------------------------------------------------------
 def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """out[t, :] = table[ids[t], :] widened to float32.  ids: int32 [T]; out: float32 [T, H]."""
     _need_cuda(table, ids, out)
@@ -362,6 +404,20 @@ def attention_decode_cluster(q: torch.Tensor, q_ld: int, kcache, vcache, page_ta
           c_int(n_seqs), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_int(page_size), c_float(scale),
           c_int(window), c_int(n_splits), _stream())
     return out
+
+
+_cluster_capacity: dict = {}
+
+
+def attention_decode_cluster_capacity(head_dim: int, n_splits: int) -> int:
+    """How many clusters of n_splits CTAs of the cluster decode kernel the current device holds at once
+    (asked once per device, head size and split count)."""
+    key = (torch.cuda.current_device(), head_dim, n_splits)
+    if key not in _cluster_capacity:
+        got = c_int(0)
+        _call("attention_mma", "ri_attention_decode_cluster_capacity", c_int(head_dim), c_int(n_splits), ctypes.byref(got))
+        _cluster_capacity[key] = int(got.value)
+    return _cluster_capacity[key]
 
 
 def attention_prefill(q: torch.Tensor, q_ld: int, kcache, vcache, page_table, seq_slot, seq_start, cu_seqlens,
