@@ -23,6 +23,33 @@ __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __re
         return;
     }
     const T* row = table + (size_t)id * hidden;
+    if (sizeof(T) == 2 && (hidden & 7) == 0 && (reinterpret_cast<uintptr_t>(table) & 15) == 0 &&
+        (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+        // 16 bytes (8 elements) per load, up to four loads of a thread on their way together: the row comes
+        // from memory in one trip, not in one trip per element
+        constexpr int AHEAD = 4;
+        const uint4* src = reinterpret_cast<const uint4*>(row);
+        const int n8 = hidden >> 3;
+        for (int base = threadIdx.x; base < n8; base += AHEAD * blockDim.x) {
+            uint4 v[AHEAD];
+#pragma unroll
+            for (int j = 0; j < AHEAD; ++j) {
+                const int i = base + j * blockDim.x;
+                if (i < n8) v[j] = src[i];
+            }
+#pragma unroll
+            for (int j = 0; j < AHEAD; ++j) {
+                const int i = base + j * blockDim.x;
+                if (i < n8) {
+                    const T* e = reinterpret_cast<const T*>(&v[j]);
+                    float4* dst = reinterpret_cast<float4*>(o + 8 * (size_t)i);
+                    dst[0] = make_float4(to_f32<T>(e[0]), to_f32<T>(e[1]), to_f32<T>(e[2]), to_f32<T>(e[3]));
+                    dst[1] = make_float4(to_f32<T>(e[4]), to_f32<T>(e[5]), to_f32<T>(e[6]), to_f32<T>(e[7]));
+                }
+            }
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_f32<T>(row[i]);
 }
 
@@ -91,9 +118,10 @@ rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ w, con
         const int i = threadIdx.x + j * blockDim.x;
         wv[j] = i < n4 ? reinterpret_cast<const float4*>(w)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
     }
+    const int in_row = rows ? rows[r] : r;                // the wanted rows are fixed before the step's first kernel
     let_next_kernel_start();
     wait_for_previous_kernels();
-    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * n);
+    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)in_row * n);
     float ss = 0.f;
 #pragma unroll
     for (int j = 0; j < PER; ++j) {
@@ -456,10 +484,15 @@ __global__ void rope_cache_write_acc_kernel(float* __restrict__ acc, int ld, con
         }
     };
     constants(threadIdx.x);
+    float v_first[PER], vb_first[PER];    // the first round of values and their bias
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+        const int idx = threadIdx.x + j * blockDim.x;
+        vb_first[j] = (bias != nullptr && idx < kv_dim) ? bias[q_dim + kv_dim + idx] : 0.f;
+    }
     wait_for_previous_kernels();          // the projections come from the previous kernel
 
     // the first round of values goes out with the first round of pairs: one trip to memory, not two
-    float v_first[PER];
 #pragma unroll
     for (int j = 0; j < PER; ++j) {
         const int idx = threadIdx.x + j * blockDim.x;
@@ -503,8 +536,12 @@ __global__ void rope_cache_write_acc_kernel(float* __restrict__ acc, int ld, con
         for (int j = 0; j < PER; ++j) {
             const int idx = base + j * blockDim.x;
             if (idx < kv_dim) {
-                v[j] = base == (int)threadIdx.x ? v_first[j] : row[q_dim + kv_dim + idx];
-                if (bias) v[j] += bias[q_dim + kv_dim + idx];
+                if (base == (int)threadIdx.x) {
+                    v[j] = v_first[j] + vb_first[j];
+                } else {
+                    v[j] = row[q_dim + kv_dim + idx];
+                    if (bias) v[j] += bias[q_dim + kv_dim + idx];
+                }
             }
         }
 #pragma unroll
