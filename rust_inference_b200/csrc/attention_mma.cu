@@ -5,8 +5,8 @@
 // the maximum subtracted (math.rs:104-118), weighted sum of the values; all statistics
 // and accumulators in float32, here with an online softmax over pages of 64 keys.
 //
-// Two kernels share the building blocks (cp.async into XOR-swizzled shared tiles,
-// ldmatrix, mma.sync m16n8k16 with float32 accumulation):
+// The kernels share the building blocks (XOR-swizzled shared tiles, ldmatrix, mma.sync
+// m16n8k16 with float32 accumulation):
 //
 //  attn_decode   one token per sequence.  A CTA serves one (sequence, kv head, split): the
 //                n_rep (<= 16) query heads that share the kv head are the 16 rows of the
@@ -14,11 +14,15 @@
 //                sequence are cut into `n_splits` runs of pages so that a small batch still
 //                fills the GPU; inside a CTA the 4 warps take 16 keys of each page each.
 //                Every split writes an un-normalised partial result and its (max, sum) to
-//                scratch memory; attn_combine merges them by log-sum-exp.  With up to 8
-//                splits the CTAs of one (sequence, kv head) can instead form a thread-block
-//                cluster: each keeps its partial result in shared memory, and after a
-//                cluster barrier every CTA merges a slice of the outputs from its peers'
-//                shared memory and writes the final rows: no scratch, no second kernel.
+//                scratch memory; attn_combine merges them by log-sum-exp.  Pages come in by
+//                cp.async.
+//  attn_decode_tma  the same computation with the pages brought in by TMA through a ring of
+//                stages (one elected thread issues the copies, the compute warps never meet
+//                at a block-wide barrier in the loop).  With 2 to 8 splits the CTAs of one
+//                (sequence, kv head) can form a thread-block cluster: each keeps its partial
+//                result in shared memory and sends it to the CTA that merges that slice of
+//                the outputs; after a cluster barrier every CTA writes its slice of the final
+//                rows: no scratch, no second kernel.  This is what decode steps take.
 //  attn_prefill  any number of new tokens per sequence (whole prompts, or a continuation).
 //                A CTA serves 64 consecutive query tokens of one head; the warps take 16
 //                query rows each and walk the key pages up to the causal limit: the token
@@ -172,6 +176,8 @@ __device__ __forceinline__ void softmax_update(float (*s)[4], float* m, float* l
     }
 }
 
+constexpr int MAX_CLUSTER_SPLITS = 8;                          // the portable cluster size
+
 // The merge of a CTA's four warps, each of which saw a quarter of the keys: `so` holds their unnormalised
 // outputs [4][16][HD + 4], `sml` their running maximum and sum per row [4][16][2].  Returns outputs d .. d+3 of
 // row r scaled to the row's maximum M over the warps, and M and the row's sum L.  Every thread works the
@@ -213,6 +219,80 @@ __device__ __forceinline__ void store_bf16x4(__nv_bfloat16* p, float a, float b,
     }
 }
 
+// floats of shared memory a CTA keeps for what its cluster sends it (see cluster_merge)
+template <int HD>
+constexpr int CLUSTER_RECV_FLOATS = 16 * HD + 4 * MAX_CLUSTER_SPLITS + MAX_CLUSTER_SPLITS * 16 * 2;
+
+// The splits of a (sequence, kv head) as the CTAs of one thread-block cluster (its z extent): what every CTA
+// does once its four warps' partial results lie in `so` / `sml`.  Every CTA merges its warps and sends the
+// result to the CTA that merges that part of the output over the splits (runs of `chunk` outputs, a
+// multiple of 4, so that everything moves as float4): plain stores into the peers' shared memory, nothing is
+// read remotely.  `recv` is this CTA's area for what the peers send ([n_splits][chunk] outputs, then
+// [n_splits][16][2] statistics: CLUSTER_RECV_FLOATS<HD> floats, at the same place in every CTA and outside
+// anything a CTA still works on).  All NT threads of the CTA call; the CTA has arrived at the cluster's
+// barrier once, near its start.  `ok` false: the CTA gave up on its pages; it sends and stores nothing but
+// still meets its cluster at the barriers.
+template <int HD, int NT>
+__device__ __forceinline__ void cluster_merge(const float* so, const float* sml, float* recv, int n_rep, int n_splits,
+                                              int split, int token, int kvh, __nv_bfloat16* __restrict__ out,
+                                              int out_ld, bool ok) {
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    const int total = n_rep * HD;
+    const int chunk = (((total + n_splits - 1) / n_splits) + 3) & ~3;
+    float* recv_o = recv;                                                   // [n_splits][chunk]
+    float* recv_ml = recv + 16 * HD + 4 * MAX_CLUSTER_SPLITS;               // [n_splits][16][2]
+    // every CTA of the cluster has arrived at the barrier near its start by now: all of them exist, so
+    // their shared memory may be written
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (ok)
+        for (int it = threadIdx.x; it < n_rep * (HD / 4); it += NT) {
+            const int r = it / (HD / 4), d = (it % (HD / 4)) * 4;
+            float M, L;
+            const float4 acc = merge_warps<HD>(so, sml, r, d, M, L);
+            const int idx = r * HD + d, owner = idx / chunk;
+            *reinterpret_cast<float4*>(cluster.map_shared_rank(recv_o, owner) + split * chunk + (idx - owner * chunk)) = acc;
+            // the row's statistics go with the first piece of the row that a CTA merges: to the CTAs that need them
+            if (d == 0 || idx == owner * chunk)
+                *reinterpret_cast<float2*>(cluster.map_shared_rank(recv_ml, owner) + (split * 16 + r) * 2) = make_float2(M, L);
+        }
+    RI_PHASE(3);
+    cluster.sync();                                       // everything sent has arrived
+    RI_PHASE(4);
+    const int lo = split * chunk, hi = min(total, lo + chunk);
+    const bool wide = ((reinterpret_cast<uintptr_t>(out) & 7) == 0) && ((out_ld & 3) == 0);
+    if (ok)
+        for (int idx = lo + 4 * (int)threadIdx.x; idx < hi; idx += 4 * NT) {
+            const int r = idx / HD, d = idx % HD;
+            float2 ml[MAX_CLUSTER_SPLITS];
+            float M = -INFINITY;
+#pragma unroll
+            for (int sp = 0; sp < MAX_CLUSTER_SPLITS; ++sp)
+                if (sp < n_splits) {
+                    ml[sp] = *reinterpret_cast<const float2*>(recv_ml + (sp * 16 + r) * 2);
+                    M = fmaxf(M, ml[sp].x);
+                }
+            float L = 0.f;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int sp = 0; sp < MAX_CLUSTER_SPLITS; ++sp)
+                if (sp < n_splits) {
+                    const float f = (ml[sp].x == -INFINITY) ? 0.f : expf(ml[sp].x - M);
+                    const float4 x = *reinterpret_cast<const float4*>(recv_o + sp * chunk + (idx - lo));
+                    L += f * ml[sp].y;
+                    acc.x += f * x.x;
+                    acc.y += f * x.y;
+                    acc.z += f * x.z;
+                    acc.w += f * x.w;
+                }
+            const float inv = 1.0f / L;
+            store_bf16x4(out + (size_t)token * out_ld + (size_t)(kvh * n_rep + r) * HD + d, acc.x * inv, acc.y * inv,
+                         acc.z * inv, acc.w * inv, wide);
+        }
+    RI_PHASE_LATEST(5);
+    // nobody reads or writes a peer's shared memory after that barrier: a CTA may leave when it is done
+}
+
 // What a CTA that merged its warps does with row r, outputs d .. d+3, when it is not part of a cluster: the
 // final result if it saw the whole sequence, else its partial result for the kernel that merges the splits.
 template <int HD>
@@ -245,11 +325,10 @@ __device__ __forceinline__ void write_merged(const float* so, const float* sml, 
 // ---------------------------------------------------------------------------------------------
 // decode: one token per sequence, split over runs of pages
 // ---------------------------------------------------------------------------------------------
-constexpr int MAX_CLUSTER_SPLITS = 8;                          // the portable cluster size
 constexpr int NBUF = 3;             // page buffers of the cp.async decode kernel: with three, a run of three pages is in
                                     // flight before the kernel has even waited for its predecessor
 
-template <int HD, bool CLUSTER>
+template <int HD>
 __global__ void __launch_bounds__(THREADS)
 attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_ld, const __nv_bfloat16* __restrict__ kcache,
                    const __nv_bfloat16* __restrict__ vcache, const int* __restrict__ page_table, int max_pages,
@@ -259,13 +338,12 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_ld, const __nv_bfl
                    __nv_bfloat16* __restrict__ out, int out_ld) {
     constexpr int TILE = PAGE * HD * 2;                 // bytes of one K or V page tile
     extern __shared__ __align__(128) uint8_t smem[];
-    // [NBUF buffers][K tile, V tile], then the Q tile [16][HD], then (cluster form) what the peers send
+    // [NBUF buffers][K tile, V tile], then the Q tile [16][HD]
     const uint32_t kv_base = smem_u32(smem);
     const uint32_t q_tile = kv_base + 2 * NBUF * TILE;
 
     const int b = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
     let_next_kernel_start();
-    if (CLUSTER) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");   // "this CTA runs": waited for before the merge
     // What the step fixed before its first kernel (lengths, slots, the page table) and the pages that
     // hold only older positions are written by no kernel of this step: they are read, and the first
     // page's copy is started, while the kernel before this one still runs.
@@ -305,7 +383,6 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_ld, const __nv_bfl
         *reinterpret_cast<uint4*>(smem + 2 * NBUF * TILE + tile_off<HD>(r, c)) = v;
     }
     __syncthreads();                                      // Q tile written
-    RI_PHASE(0);
 
     uint32_t qf[HD / 16][4];
     {
@@ -352,8 +429,6 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_ld, const __nv_bfl
         __syncthreads();                                  // everyone is done with this buffer
     }
 
-    RI_PHASE(1);
-    RI_PHASE_LATEST(2);
     // ---- merge the 4 warps (each saw a quarter of the keys) through shared memory ----
     constexpr int SO_LD = HD + 4;                         // padded rows: the 8 rows a warp stores at once hit 8 bank groups
     float* so = reinterpret_cast<float*>(smem);           // [4][16][SO_LD]
@@ -371,68 +446,6 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_ld, const __nv_bfl
         sml[((warp * 16 + g + 8) << 1) + 1] = l[1];
     }
     __syncthreads();                                      // every warp's partial result is in shared memory
-    if constexpr (CLUSTER) {
-        // The splits of this (sequence, kv head) are the CTAs of one cluster (its z extent).  Every CTA merges its
-        // four warps and sends the result to the CTA that merges that part of the output over the splits (runs of
-        // `chunk` outputs, a multiple of 4, so that everything moves as float4): plain stores into the peers'
-        // shared memory, nothing is read remotely.  Each thread works out its row's maximum and factors itself
-        // (a few loads and exponentials that overlap) rather than wait at a barrier for one thread per row.
-        namespace cg = cooperative_groups;
-        cg::cluster_group cluster = cg::this_cluster();
-        const int total = n_rep * HD;
-        const int chunk = (((total + n_splits - 1) / n_splits) + 3) & ~3;
-        // what the peers send lies behind the Q tile, outside anything a CTA still works on
-        float* recv_o = reinterpret_cast<float*>(smem + 2 * NBUF * TILE + 16 * HD * 2);    // [n_splits][chunk]
-        float* recv_ml = recv_o + 16 * HD + 4 * MAX_CLUSTER_SPLITS;                        // [n_splits][16][2]
-        // every CTA of the cluster has arrived at the barrier near its start by now: all of them exist, so
-        // their shared memory may be written
-        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-        for (int it = threadIdx.x; it < n_rep * (HD / 4); it += THREADS) {
-            const int r = it / (HD / 4), d = (it % (HD / 4)) * 4;
-            float M, L;
-            const float4 acc = merge_warps<HD>(so, sml, r, d, M, L);
-            const int idx = r * HD + d, owner = idx / chunk;
-            *reinterpret_cast<float4*>(cluster.map_shared_rank(recv_o, owner) + split * chunk + (idx - owner * chunk)) = acc;
-            // the row's statistics go with the first piece of the row that a CTA merges: to the CTAs that need them
-            if (d == 0 || idx == owner * chunk)
-                *reinterpret_cast<float2*>(cluster.map_shared_rank(recv_ml, owner) + (split * 16 + r) * 2) = make_float2(M, L);
-        }
-        RI_PHASE(3);
-        cluster.sync();                                   // everything sent has arrived
-        RI_PHASE(4);
-        const int lo = split * chunk, hi = min(total, lo + chunk);
-        const bool wide = ((reinterpret_cast<uintptr_t>(out) & 7) == 0) && ((out_ld & 3) == 0);
-        for (int idx = lo + 4 * (int)threadIdx.x; idx < hi; idx += 4 * THREADS) {
-            const int r = idx / HD, d = idx % HD;
-            float2 ml[MAX_CLUSTER_SPLITS];
-            float M = -INFINITY;
-#pragma unroll
-            for (int sp = 0; sp < MAX_CLUSTER_SPLITS; ++sp)
-                if (sp < n_splits) {
-                    ml[sp] = *reinterpret_cast<const float2*>(recv_ml + (sp * 16 + r) * 2);
-                    M = fmaxf(M, ml[sp].x);
-                }
-            float L = 0.f;
-            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-            for (int sp = 0; sp < MAX_CLUSTER_SPLITS; ++sp)
-                if (sp < n_splits) {
-                    const float f = (ml[sp].x == -INFINITY) ? 0.f : expf(ml[sp].x - M);
-                    const float4 x = *reinterpret_cast<const float4*>(recv_o + sp * chunk + (idx - lo));
-                    L += f * ml[sp].y;
-                    acc.x += f * x.x;
-                    acc.y += f * x.y;
-                    acc.z += f * x.z;
-                    acc.w += f * x.w;
-                }
-            const float inv = 1.0f / L;
-            store_bf16x4(out + (size_t)token * out_ld + (size_t)(kvh * n_rep + r) * HD + d, acc.x * inv, acc.y * inv,
-                         acc.z * inv, acc.w * inv, wide);
-        }
-        RI_PHASE_LATEST(5);
-        // nobody reads or writes a peer's shared memory after that barrier: a CTA may leave when it is done
-        return;
-    }
     for (int it = threadIdx.x; it < n_rep * (HD / 4); it += THREADS) {
         const int r = it / (HD / 4), d = (it % (HD / 4)) * 4;
         write_merged<HD>(so, sml, r, d, b, kvh * n_rep + r, token, n_heads, n_splits, split, part_o, part_ml, out, out_ld);
@@ -484,7 +497,7 @@ __device__ __forceinline__ void pv_16keys_atoms(const uint32_t* p, uint32_t vtil
     }
 }
 
-template <int HD>
+template <int HD, bool CLUSTER>
 __global__ void __launch_bounds__(DECODE_TMA_THREADS)
 attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                        const __nv_bfloat16* __restrict__ q, int q_ld, const int* __restrict__ page_table,
@@ -514,6 +527,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     }
     __syncthreads();
     let_next_kernel_start();
+    if (CLUSTER) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");   // "this CTA runs": waited for before the merge
     // Lengths, slots and the page table were fixed before the step's first kernel, and pages that hold
     // only older positions are written by no kernel of this step: the producer starts on them while
     // the kernel before this one still runs.  q and the sequence's last page wait for it.
@@ -569,6 +583,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             *reinterpret_cast<uint4*>(smem + 2 * RING * TILE + tile_off<HD>(r, c)) = v;
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");          // the four compute warps: Q tile written
+        RI_PHASE(0);
         uint32_t qf[HD / 16][4];
         {
             const int row = lane & 15, half = lane >> 4;
@@ -604,7 +619,9 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             if (lane == 0) tc::mbar_arrive(smem_u32(&empty_bar[s]));       // this warp is done with the stage
         }
     }
+    RI_PHASE(1);
     __syncthreads();                      // every page consumed, every copy landed: the ring is free
+    RI_PHASE_LATEST(2);
 
     // ---- merge the 4 compute warps (each saw a quarter of the keys) through shared memory ----
     constexpr int SO_LD = HD + 4;                         // padded rows: the 8 rows a warp stores at once hit 8 bank groups
@@ -625,6 +642,12 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         }
     }
     __syncthreads();
+    if constexpr (CLUSTER) {
+        // the splits of this (sequence, kv head) are the CTAs of one cluster: merged here, no scratch, no second kernel
+        float* recv = reinterpret_cast<float*>(smem + 2 * RING * TILE + 16 * HD * 2);
+        cluster_merge<HD, DECODE_TMA_THREADS>(so, sml, recv, n_rep, n_splits, split, token, kvh, out, out_ld, !abort_flag);
+        return;
+    }
     if (abort_flag) return;
     for (int it = threadIdx.x; it < n_rep * (HD / 4); it += DECODE_TMA_THREADS) {
         const int r = it / (HD / 4), d = (it % (HD / 4)) * 4;
@@ -783,10 +806,10 @@ int launch_decode(const void* q, int q_ld, const void* kc, const void* vc, const
     constexpr int SMEM = 2 * NBUF * PAGE * HD * 2 + 16 * HD * 2;      // the merge area lies over the page buffers
     static_assert((4 * 16 * (HD + 4) + 4 * 16 * 2 + 4 * 16 + 16 * 2) * 4 <= SMEM, "merge area must fit");
     static PerDeviceOnce configured;       // per device: the attribute belongs to a device's copy of the kernel
-    if (int rc = raise_dynamic_smem(attn_decode_kernel<HD, false>, SMEM, configured, "attention")) return rc;
+    if (int rc = raise_dynamic_smem(attn_decode_kernel<HD>, SMEM, configured, "attention")) return rc;
     dim3 grid(n_seqs, n_kv_heads, n_splits);
     cudaError_t e = launch_dependent(
-        attn_decode_kernel<HD, false>, grid, dim3(THREADS), (size_t)SMEM, stream, (const __nv_bfloat16*)q, q_ld,
+        attn_decode_kernel<HD>, grid, dim3(THREADS), (size_t)SMEM, stream, (const __nv_bfloat16*)q, q_ld,
         (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, page_table, max_pages, seq_slot, seq_len, cu_seqlens,
         n_heads, n_kv_heads, scale, window, n_splits, part_o, part_ml, (__nv_bfloat16*)out, out_ld);
     if (int rc = check_launch(e, "attn_decode")) return rc;
@@ -799,72 +822,6 @@ int launch_decode(const void* q, int q_ld, const void* kc, const void* vc, const
     return 0;
 }
 
-// The splits of a (sequence, kv head) as one thread-block cluster that merges its own partial results.
-
-// page buffers (the warps' merge area lies over them), the Q tile, and what the peers send
-template <int HD>
-constexpr int cluster_smem_bytes() {
-    static_assert((4 * 16 * (HD + 4) + 4 * 16 * 2 + 4 * 16 + 16 * 2) * 4 <= 2 * NBUF * PAGE * HD * 2, "merge area must fit the page buffers");
-    return 2 * NBUF * PAGE * HD * 2 + 16 * HD * 2 + (16 * HD + 4 * MAX_CLUSTER_SPLITS + MAX_CLUSTER_SPLITS * 16 * 2) * 4;
-}
-
-template <int HD>
-PerDeviceOnce& cluster_configured() {      // per device: the attribute belongs to a device's copy of the kernel
-    static PerDeviceOnce once;
-    return once;
-}
-
-// How many clusters of n_splits CTAs of the kernel the device holds at once.
-template <int HD>
-int decode_cluster_capacity(int n_splits, int* clusters) {
-    constexpr int SMEM = cluster_smem_bytes<HD>();
-    auto kernel = attn_decode_kernel<HD, true>;
-    if (int rc = raise_dynamic_smem(kernel, SMEM, cluster_configured<HD>(), "attention")) return rc;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(1, 1, n_splits);
-    cfg.blockDim = dim3(THREADS);
-    cfg.dynamicSmemBytes = SMEM;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 1;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = (unsigned)n_splits;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    cudaError_t e = cudaOccupancyMaxActiveClusters(clusters, kernel, &cfg);
-    if (e != cudaSuccess) return fail("attention_decode: cannot ask how many clusters fit: %s", cudaGetErrorString(e));
-    return 0;
-}
-
-template <int HD>
-int launch_decode_cluster(const void* q, int q_ld, const void* kc, const void* vc, const int* page_table, int max_pages,
-                          const int* seq_slot, const int* seq_len, const int* cu_seqlens, int n_seqs, int n_heads,
-                          int n_kv_heads, float scale, int window, int n_splits, void* out, int out_ld,
-                          cudaStream_t stream) {
-    constexpr int SMEM = cluster_smem_bytes<HD>();
-    auto kernel = attn_decode_kernel<HD, true>;
-    if (int rc = raise_dynamic_smem(kernel, SMEM, cluster_configured<HD>(), "attention")) return rc;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(n_seqs, n_kv_heads, n_splits);
-    cfg.blockDim = dim3(THREADS);
-    cfg.dynamicSmemBytes = SMEM;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[2];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 1;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = (unsigned)n_splits;
-    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[1].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = pdl_enabled() ? 2 : 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, (const __nv_bfloat16*)q, q_ld, (const __nv_bfloat16*)kc,
-                                       (const __nv_bfloat16*)vc, page_table, max_pages, seq_slot, seq_len, cu_seqlens,
-                                       n_heads, n_kv_heads, scale, window, n_splits, (float*)nullptr, (float*)nullptr,
-                                       (__nv_bfloat16*)out, out_ld);
-    return check_launch(e, "attn_decode (cluster)");
-}
-
 template <int HD>
 int launch_decode_tma(const CUtensorMap& mk, const CUtensorMap& mv, const void* q, int q_ld, const int* page_table,
                       int max_pages, const int* seq_slot, const int* seq_len, const int* cu_seqlens, int n_seqs,
@@ -873,10 +830,10 @@ int launch_decode_tma(const CUtensorMap& mk, const CUtensorMap& mv, const void* 
     constexpr int SMEM = 2 * RING * PAGE * HD * 2 + 16 * HD * 2 + 1024;
     static_assert((4 * 16 * (HD + 4) + 4 * 16 * 2 + 4 * 16 + 16 * 2) * 4 <= 2 * RING * PAGE * HD * 2, "merge area must fit the ring");
     static PerDeviceOnce configured;       // per device: the attribute belongs to a device's copy of the kernel
-    if (int rc = raise_dynamic_smem(attn_decode_tma_kernel<HD>, SMEM, configured, "attention")) return rc;
+    if (int rc = raise_dynamic_smem(attn_decode_tma_kernel<HD, false>, SMEM, configured, "attention")) return rc;
     dim3 grid(n_seqs, n_kv_heads, n_splits);
     cudaError_t e = launch_dependent(
-        attn_decode_tma_kernel<HD>, grid, dim3(DECODE_TMA_THREADS), (size_t)SMEM, stream, mk, mv, (const __nv_bfloat16*)q,
+        attn_decode_tma_kernel<HD, false>, grid, dim3(DECODE_TMA_THREADS), (size_t)SMEM, stream, mk, mv, (const __nv_bfloat16*)q,
         q_ld, page_table, max_pages, seq_slot, seq_len, cu_seqlens, n_heads, n_kv_heads, scale, window, n_splits, part_o,
         part_ml, (__nv_bfloat16*)out, out_ld, status);
     if (int rc = check_launch(e, "attn_decode_tma")) return rc;
@@ -886,6 +843,66 @@ int launch_decode_tma(const CUtensorMap& mk, const CUtensorMap& mv, const void* 
                              (__nv_bfloat16*)out, out_ld);
         return check_launch(e, "attn_combine");
     }
+    return 0;
+}
+
+// The TMA-fed kernel with the splits of a (sequence, kv head) as one cluster.
+template <int HD>
+constexpr int tma_cluster_smem_bytes() {
+    return 2 * RING * PAGE * HD * 2 + 16 * HD * 2 + CLUSTER_RECV_FLOATS<HD> * 4 + 1024;
+}
+
+template <int HD>
+PerDeviceOnce& tma_cluster_configured() {
+    static PerDeviceOnce once;
+    return once;
+}
+
+template <int HD>
+void tma_cluster_config(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, int n_seqs, int n_kv_heads, int n_splits,
+                        cudaStream_t stream) {
+    cfg = {};
+    cfg.gridDim = dim3(n_seqs, n_kv_heads, n_splits);
+    cfg.blockDim = dim3(DECODE_TMA_THREADS);
+    cfg.dynamicSmemBytes = tma_cluster_smem_bytes<HD>();
+    cfg.stream = stream;
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = (unsigned)n_splits;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
+}
+
+template <int HD>
+int launch_decode_tma_cluster(const CUtensorMap& mk, const CUtensorMap& mv, const void* q, int q_ld, const int* page_table,
+                              int max_pages, const int* seq_slot, const int* seq_len, const int* cu_seqlens, int n_seqs,
+                              int n_heads, int n_kv_heads, float scale, int window, int n_splits, void* out, int out_ld,
+                              int* status, cudaStream_t stream) {
+    auto kernel = attn_decode_tma_kernel<HD, true>;
+    if (int rc = raise_dynamic_smem(kernel, tma_cluster_smem_bytes<HD>(), tma_cluster_configured<HD>(), "attention")) return rc;
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute attr[2];
+    tma_cluster_config<HD>(cfg, attr, n_seqs, n_kv_heads, n_splits, stream);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, mk, mv, (const __nv_bfloat16*)q, q_ld, page_table, max_pages, seq_slot,
+                                       seq_len, cu_seqlens, n_heads, n_kv_heads, scale, window, n_splits, (float*)nullptr,
+                                       (float*)nullptr, (__nv_bfloat16*)out, out_ld, status);
+    return check_launch(e, "attn_decode_tma_cluster");
+}
+
+// How many clusters of n_splits CTAs of that kernel the device holds at once.
+template <int HD>
+int decode_tma_cluster_capacity(int n_splits, int* clusters) {
+    auto kernel = attn_decode_tma_kernel<HD, true>;
+    if (int rc = raise_dynamic_smem(kernel, tma_cluster_smem_bytes<HD>(), tma_cluster_configured<HD>(), "attention")) return rc;
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute attr[2];
+    tma_cluster_config<HD>(cfg, attr, 1, 1, n_splits, nullptr);
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaOccupancyMaxActiveClusters(clusters, kernel, &cfg);
+    if (e != cudaSuccess) return fail("attention_decode: cannot ask how many clusters fit: %s", cudaGetErrorString(e));
     return 0;
 }
 
@@ -945,36 +962,6 @@ RI_API int ri_attention_decode(const void* q, int q_ld, const void* kcache, cons
                               n_heads, n_kv_heads, scale, window, n_splits, part_o, part_ml, out, out_ld, stream);
 }
 
-// The same with the splits of a (sequence, kv head) as one thread-block cluster, 2 <= n_splits <= 8: the
-// partial results are merged through distributed shared memory inside the kernel, so there is no
-// scratch and no second kernel.
-RI_API int ri_attention_decode_cluster(const void* q, int q_ld, const void* kcache, const void* vcache,
-                                       const int* page_table, int max_pages, const int* seq_slot, const int* seq_len,
-                                       const int* cu_seqlens, void* out, int out_ld, int n_seqs, int n_heads,
-                                       int n_kv_heads, int hd, int page_size, float scale, int window, int n_splits,
-                                       cudaStream_t stream) {
-    if (n_seqs <= 0) return 0;
-    if (int rc = check_common(hd, page_size, n_heads, n_kv_heads, q_ld, out_ld, q, out)) return rc;
-    if (n_heads / n_kv_heads > 16) return fail("attention_decode: %d query heads per kv head exceed 16", n_heads / n_kv_heads);
-    if (n_splits < 2 || n_splits > MAX_CLUSTER_SPLITS)
-        return fail("attention_decode: a cluster takes 2 to %d splits, not %d", MAX_CLUSTER_SPLITS, n_splits);
-    if (n_kv_heads > 65535) return fail("attention_decode: %d kv heads exceed the grid limit", n_kv_heads);
-    if (hd == 64)
-        return launch_decode_cluster<64>(q, q_ld, kcache, vcache, page_table, max_pages, seq_slot, seq_len, cu_seqlens,
-                                         n_seqs, n_heads, n_kv_heads, scale, window, n_splits, out, out_ld, stream);
-    return launch_decode_cluster<128>(q, q_ld, kcache, vcache, page_table, max_pages, seq_slot, seq_len, cu_seqlens,
-                                      n_seqs, n_heads, n_kv_heads, scale, window, n_splits, out, out_ld, stream);
-}
-
-// clusters[0] = how many clusters of n_splits CTAs of that kernel the current device holds at the same time:
-// a step with more (sequences x kv heads) than that runs them in turns.
-RI_API int ri_attention_decode_cluster_capacity(int hd, int n_splits, int* clusters) {
-    if (hd != 64 && hd != 128) return fail("attention_mma: head_dim %d is not 64 or 128", hd);
-    if (n_splits < 2 || n_splits > MAX_CLUSTER_SPLITS)
-        return fail("attention_decode: a cluster takes 2 to %d splits, not %d", MAX_CLUSTER_SPLITS, n_splits);
-    return hd == 64 ? decode_cluster_capacity<64>(n_splits, clusters) : decode_cluster_capacity<128>(n_splits, clusters);
-}
-
 // The same with the cache pages brought in by TMA.  map_k / map_v: tensor maps (128 bytes each) of the
 // layer's K and V viewed as [pages * kv heads * 64, head_dim] with a {64, 64} box and 128-byte swizzle.
 // `status` (may be null) is a host-visible int that receives a code if a bounded wait ran out.
@@ -996,6 +983,36 @@ RI_API int ri_attention_decode_tma(const void* map_k, const void* map_v, const v
                                      n_kv_heads, scale, window, n_splits, part_o, part_ml, out, out_ld, status, stream);
     return launch_decode_tma<128>(mk, mv, q, q_ld, page_table, max_pages, seq_slot, seq_len, cu_seqlens, n_seqs, n_heads,
                                   n_kv_heads, scale, window, n_splits, part_o, part_ml, out, out_ld, status, stream);
+}
+
+// The same with the 2..8 splits of a (sequence, kv head) as one thread-block cluster that merges its own partial
+// results through distributed shared memory: no scratch and no second kernel.
+RI_API int ri_attention_decode_tma_cluster(const void* map_k, const void* map_v, const void* q, int q_ld,
+                                           const int* page_table, int max_pages, const int* seq_slot,
+                                           const int* seq_len, const int* cu_seqlens, void* out, int out_ld, int n_seqs,
+                                           int n_heads, int n_kv_heads, int hd, int page_size, float scale, int window,
+                                           int n_splits, int* status, cudaStream_t stream) {
+    if (n_seqs <= 0) return 0;
+    if (int rc = check_common(hd, page_size, n_heads, n_kv_heads, q_ld, out_ld, q, out)) return rc;
+    if (n_heads / n_kv_heads > 16) return fail("attention_decode: %d query heads per kv head exceed 16", n_heads / n_kv_heads);
+    if (n_splits < 2 || n_splits > MAX_CLUSTER_SPLITS)
+        return fail("attention_decode: a cluster takes 2 to %d splits, not %d", MAX_CLUSTER_SPLITS, n_splits);
+    if (n_kv_heads > 65535) return fail("attention_decode: %d kv heads exceed the grid limit", n_kv_heads);
+    const CUtensorMap& mk = *reinterpret_cast<const CUtensorMap*>(map_k);
+    const CUtensorMap& mv = *reinterpret_cast<const CUtensorMap*>(map_v);
+    if (hd == 64)
+        return launch_decode_tma_cluster<64>(mk, mv, q, q_ld, page_table, max_pages, seq_slot, seq_len, cu_seqlens, n_seqs,
+                                             n_heads, n_kv_heads, scale, window, n_splits, out, out_ld, status, stream);
+    return launch_decode_tma_cluster<128>(mk, mv, q, q_ld, page_table, max_pages, seq_slot, seq_len, cu_seqlens, n_seqs,
+                                          n_heads, n_kv_heads, scale, window, n_splits, out, out_ld, status, stream);
+}
+
+// clusters[0] = how many clusters of n_splits CTAs of that kernel the current device holds at the same time
+RI_API int ri_attention_decode_tma_cluster_capacity(int hd, int n_splits, int* clusters) {
+    if (hd != 64 && hd != 128) return fail("attention_mma: head_dim %d is not 64 or 128", hd);
+    if (n_splits < 2 || n_splits > MAX_CLUSTER_SPLITS)
+        return fail("attention_decode: a cluster takes 2 to %d splits, not %d", MAX_CLUSTER_SPLITS, n_splits);
+    return hd == 64 ? decode_tma_cluster_capacity<64>(n_splits, clusters) : decode_tma_cluster_capacity<128>(n_splits, clusters);
 }
 
 RI_API int ri_attention_prefill(const void* q, int q_ld, const void* kcache, const void* vcache, const int* page_table,

@@ -39,22 +39,25 @@ def decode_splits(n_seqs: int, n_kv_heads: int, max_seq_len: int, page_size: int
     return max(1, min(want, limit, -(-max_seq_len // page_size)))
 
 
-def decode_plan(n_seqs: int, n_kv_heads: int, max_seq_len: int, page_size: int):
+def decode_plan(n_seqs: int, n_kv_heads: int, max_seq_len: int, page_size: int, head_dim: int | None = None):
     """Which decode kernel a step of n_seqs sequences takes, and into how many runs of pages it
     cuts a sequence: ("cluster" | "tma" | "cp_async", splits).  Left to itself it answers "cluster"
-    (2..8 runs) while a step's sequences x kv heads leave SMs idle, and "tma" with one run per
-    sequence beyond; "cp_async" (runs merged through scratch by a second kernel) is only taken when
-    RI_B200_DECODE_ATTENTION asks for it: it is the kernel of the allocation-free entry point and
-    the comparison for the other two.
+    (the TMA-fed kernel with the 2..8 runs of a sequence as one thread-block cluster) while a step's
+    sequences x kv heads leave SMs idle, and "tma" (the same kernel, one run per sequence) beyond;
+    "cp_async" (pages by cp.async, runs merged through scratch by a second kernel) is only taken
+    when RI_B200_DECODE_ATTENTION asks for it: it is the kernel of the allocation-free entry point
+    and the comparison for the other two.
 
     Split runs are merged inside the kernel when the splits of a (sequence, kv head) fit a
-    thread-block cluster: no scratch round trip and no second kernel.  Large batches are not
-    split and stream many pages per CTA: there the TMA ring keeps more of them in flight (batch
-    64, 1,024 positions: 26.7 us against 40.9 us with cp.async)."""
+    thread-block cluster: no scratch round trip and no second kernel.  With `head_dim` given the
+    device is asked how many such clusters it holds at once, and the runs are made fewer until the
+    whole step is resident together."""
     if _DECODE in ("auto", "cluster"):
         splits = decode_splits(n_seqs, n_kv_heads, max_seq_len, page_size, CLUSTER_SPLITS)
-        # measured at 1,024 positions: 1 sequence 5.3 us against 7.9 us with the merge kernel, 4: 6.3
-        # against 11.1, 8: 8.4 against 9.6, 16 (four splits): 10.9 against 10.7, 32 (two): 16.3 against 16.4
+        if head_dim is not None:
+            from . import attention_tc
+            while splits >= 2 and attention_tc.decode_cluster_capacity(head_dim, splits) < n_seqs * n_kv_heads:
+                splits -= 1
         if splits >= 2:
             return "cluster", splits
     splits = decode_splits(n_seqs, n_kv_heads, max_seq_len, page_size)
@@ -65,7 +68,8 @@ def decode_plan(n_seqs: int, n_kv_heads: int, max_seq_len: int, page_size: int):
 
 def decode_kernel(name: str):
     if name == "cluster":
-        return ops.attention_decode_cluster
+        from . import attention_tc
+        return attention_tc.decode_cluster
     if name == "tma":
         from . import attention_tc
         return attention_tc.decode
@@ -81,7 +85,7 @@ def attention(qkv, cache_layer, out, ctx, *, n_heads, n_kv_heads, head_dim, scal
         if ops.attention_mma_supports(head_dim, ctx.page_size, n_heads, n_kv_heads, decode):
             if decode:
                 max_len = ctx.page_table.shape[1] * ctx.page_size
-                name, splits = decode_plan(ctx.n_seqs, n_kv_heads, max_len, ctx.page_size)
+                name, splits = decode_plan(ctx.n_seqs, n_kv_heads, max_len, ctx.page_size, head_dim)
                 part_o = part_ml = None
                 if splits > 1 and name != "cluster":
                     part_o = ctx.buffer("attn_part_o", (ctx.n_seqs * n_heads * splits * head_dim,), torch.float32)

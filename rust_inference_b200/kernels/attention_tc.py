@@ -76,3 +76,38 @@ def decode(q: torch.Tensor, q_ld: int, kcache: torch.Tensor, vcache: torch.Tenso
           c_int(out.shape[1]), c_int(n_seqs), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_int(page_size),
           c_float(scale), c_int(window), c_int(n_splits), _p(part_o), _p(part_ml), c_void_p(st.data_ptr()), _stream())
     return out
+
+
+def decode_cluster(q: torch.Tensor, q_ld: int, kcache: torch.Tensor, vcache: torch.Tensor, page_table, seq_slot, seq_len,
+                   cu_seqlens, out: torch.Tensor, *, n_seqs: int, n_heads: int, n_kv_heads: int, head_dim: int,
+                   page_size: int, scale: float, window: int, n_splits: int, part_o=None, part_ml=None) -> torch.Tensor:
+    """The same kernel with the 2..8 splits of a (sequence, kv head) as one thread-block cluster that merges
+    its partial results through distributed shared memory: no scratch (`part_o`, `part_ml` are not
+    used), one kernel."""
+    _need_cuda(q, kcache, vcache, page_table, seq_slot, seq_len, cu_seqlens, out)
+    _need(q.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+          and kcache.is_contiguous() and vcache.is_contiguous(), "attention_decode: bf16 contiguous tensors only")
+    rows = kcache.shape[0] * kcache.shape[1] * kcache.shape[2]
+    mk = _map(1, kcache, rows, head_dim, head_dim)
+    mv = _map(1, vcache, rows, head_dim, head_dim)
+    st = status_word()
+    _call("attention_mma", "ri_attention_decode_tma_cluster", c_void_p(mk.data_ptr()), c_void_p(mv.data_ptr()), _p(q),
+          c_int(q_ld), _p(page_table), c_int(page_table.shape[1]), _p(seq_slot), _p(seq_len), _p(cu_seqlens), _p(out),
+          c_int(out.shape[1]), c_int(n_seqs), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_int(page_size),
+          c_float(scale), c_int(window), c_int(n_splits), c_void_p(st.data_ptr()), _stream())
+    return out
+
+
+_capacity: dict = {}
+
+
+def decode_cluster_capacity(head_dim: int, n_splits: int) -> int:
+    """How many clusters of n_splits CTAs of `decode_cluster`'s kernel the current device holds at once
+    (asked once per device, head size and split count)."""
+    import ctypes
+    key = (torch.cuda.current_device(), head_dim, n_splits)
+    if key not in _capacity:
+        got = c_int(0)
+        _call("attention_mma", "ri_attention_decode_tma_cluster_capacity", c_int(head_dim), c_int(n_splits), ctypes.byref(got))
+        _capacity[key] = int(got.value)
+    return _capacity[key]

@@ -391,35 +391,6 @@ def attention_decode(q: torch.Tensor, q_ld: int, kcache, vcache, page_table, seq
     return out
 
 
-def attention_decode_cluster(q: torch.Tensor, q_ld: int, kcache, vcache, page_table, seq_slot, seq_len, cu_seqlens,
-                             out: torch.Tensor, *, n_seqs: int, n_heads: int, n_kv_heads: int, head_dim: int,
-                             page_size: int, scale: float, window: int, n_splits: int, part_o=None, part_ml=None):
-    """The same with the 2..8 splits of a (sequence, kv head) as one thread-block cluster that
-    merges its partial results through distributed shared memory: no scratch, one kernel."""
-    _need_cuda(q, kcache, vcache, page_table, seq_slot, seq_len, cu_seqlens, out)
-    _need(q.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16,
-          "attention_decode: bf16 only")
-    _call("attention_mma", "ri_attention_decode_cluster", _p(q), c_int(q_ld), _p(kcache), _p(vcache), _p(page_table),
-          c_int(page_table.shape[1]), _p(seq_slot), _p(seq_len), _p(cu_seqlens), _p(out), c_int(out.shape[1]),
-          c_int(n_seqs), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_int(page_size), c_float(scale),
-          c_int(window), c_int(n_splits), _stream())
-    return out
-
-
-_cluster_capacity: dict = {}
-
-
-def attention_decode_cluster_capacity(head_dim: int, n_splits: int) -> int:
-    """How many clusters of n_splits CTAs of the cluster decode kernel the current device holds at once
-    (asked once per device, head size and split count)."""
-    key = (torch.cuda.current_device(), head_dim, n_splits)
-    if key not in _cluster_capacity:
-        got = c_int(0)
-        _call("attention_mma", "ri_attention_decode_cluster_capacity", c_int(head_dim), c_int(n_splits), ctypes.byref(got))
-        _cluster_capacity[key] = int(got.value)
-    return _cluster_capacity[key]
-
-
 def attention_prefill(q: torch.Tensor, q_ld: int, kcache, vcache, page_table, seq_slot, seq_start, cu_seqlens,
                       out: torch.Tensor, *, n_seqs: int, max_new: int, n_heads: int, n_kv_heads: int,
                       head_dim: int, page_size: int, scale: float, window: int):

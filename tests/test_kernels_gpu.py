@@ -463,17 +463,22 @@ DECODE_CASES = [
 def test_decode_attention_as_a_cluster(nh, nkv, hd, starts, window):
     """The runs of a (sequence, kv head) as one thread-block cluster that merges its own partial results."""
     ops = _ops()
+    from rust_inference_b200.kernels import attention_tc, tcgen05
+    kernel = attention_tc.decode_cluster
     c = _attention_case(nh, nkv, hd, [1] * len(starts), starts, torch.bfloat16, window=window)
     for splits in (2, 3, 5, 8):
         out = torch.zeros(c["T"], nh * hd, device=DEV, dtype=torch.bfloat16)
-        ops.attention_decode_cluster(c["q"], c["q"].shape[1], c["kc"], c["vc"], c["table"], c["slot"], c["length"],
-                                     c["cu"], out, n_seqs=c["B"], n_heads=nh, n_kv_heads=nkv, head_dim=hd,
-                                     page_size=64, scale=c["scale"], window=window, n_splits=splits)
+        kernel(c["q"], c["q"].shape[1], c["kc"], c["vc"], c["table"], c["slot"], c["length"],
+               c["cu"], out, n_seqs=c["B"], n_heads=nh, n_kv_heads=nkv, head_dim=hd,
+               page_size=64, scale=c["scale"], window=window, n_splits=splits)
+        torch.cuda.synchronize()
+        tcgen05.check_status()
         assert (out.float().cpu() - c["ref"]).abs().max().item() <= 2e-2 * c["ref"].abs().max().item(), splits
     with pytest.raises(ops.KernelError, match="2 to 8 splits"):
-        ops.attention_decode_cluster(c["q"], c["q"].shape[1], c["kc"], c["vc"], c["table"], c["slot"], c["length"],
-                                     c["cu"], out, n_seqs=c["B"], n_heads=nh, n_kv_heads=nkv, head_dim=hd,
-                                     page_size=64, scale=c["scale"], window=window, n_splits=9)
+        kernel(c["q"], c["q"].shape[1], c["kc"], c["vc"], c["table"], c["slot"], c["length"],
+               c["cu"], out, n_seqs=c["B"], n_heads=nh, n_kv_heads=nkv, head_dim=hd,
+               page_size=64, scale=c["scale"], window=window, n_splits=9)
+    assert attention_tc.decode_cluster_capacity(hd, 8) >= 1
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
