@@ -311,8 +311,11 @@ def main() -> int:
         + 3 * cfg.intermediate_size * cfg.hidden_size
     flops = 2.0 * t * per_layer * n_layers + n_layers * 4.0 * t * t * cfg.q_dim / 2.0 \
         + 2.0 * cfg.vocab_size * cfg.hidden_size
+    # frac: of the burst figure (a product timed alone).  The step is timed after the decode runs and three
+    # untimed prefills, at the power cap; frac_of_sustained divides by the library's throughput in that state.
     prefill = {"value": t / (pre * 1e-3), "tokens": t, "ms": pre,
-               "frac": flops / (pre * 1e-3) / (peaks["bf16_tflops"] * 1e12)}
+               "frac": flops / (pre * 1e-3) / (peaks["bf16_tflops"] * 1e12),
+               "frac_of_sustained": flops / (pre * 1e-3) / (peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"]) * 1e12)}
 
     points, points_detail = {}, {}
     if not args.skip_points:

@@ -4,6 +4,7 @@
     python bench.py --kernel attn_decode --tokens 64 --context 1024
     python bench.py --kernel step_parts --tokens 8      # what each kind of kernel costs INSIDE a decode step
     RI_B200_TIMELINE=1 python bench.py --kernel step_timeline --tokens 8     # the step kernel by kernel, as it overlaps
+    python bench.py --kernel prefill_step --tokens 2048   # a prompt's step of the whole model, twelve times in a row
 
 The operand that a step streams (weights, or the cache) is rotated over enough copies to
 exceed L2, and the launches are replayed from a CUDA graph so that host launch cost is
@@ -18,7 +19,7 @@ import math
 import torch
 
 KERNELS = ("qkv", "qkv_split", "o_proj", "gate_up", "down", "lm_head", "sample", "attn_decode", "attn_prefill",
-           "attn_prefill_mma", "rmsnorm", "rope", "step_parts", "step_timeline")
+           "attn_prefill_mma", "rmsnorm", "rope", "step_parts", "step_timeline", "prefill_step")
 
 
 def _graph_time(fn, launches_per_replay: int, reps: int = 10) -> float:
@@ -325,6 +326,37 @@ def step_timeline(model: dict, batch: int, prompt_min: int = 128, prompt_max: in
     return out
 
 
+def prefill_step(model: dict, tokens: int, reps: int = 12) -> dict:
+    """One prompt of `tokens` tokens through the whole model, `reps` times in a row in a process that has
+    run nothing else: the first steps find the GPU idle and cool, the later ones run at its power cap."""
+    import random
+    from ..api import Model
+    from ..config.registry import config_from_dict
+
+    cfg = config_from_dict(dict(model))
+    m = Model.random(cfg, seed=0, dtype="bfloat16", max_seq_len=max(8192, tokens), max_tokens_in_cache=tokens + 4096)
+    eng = m.engine
+    rng = random.Random(7)
+    prompt = [rng.randrange(cfg.vocab_size) for _ in range(tokens)]
+    times = []
+    for _ in range(reps):
+        slot = eng.alloc_slot()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        eng.step([slot], [prompt], "last")
+        e1.record()
+        torch.cuda.synchronize()
+        eng.free_slot(slot)
+        times.append(round(e0.elapsed_time(e1), 3))
+    eng.check_device_status()
+    per_layer = (cfg.q_dim + 2 * cfg.kv_dim) * cfg.hidden_size + cfg.hidden_size * cfg.q_dim \
+        + 3 * cfg.intermediate_size * cfg.hidden_size
+    flops = 2.0 * tokens * per_layer * cfg.num_hidden_layers + cfg.num_hidden_layers * 4.0 * tokens * tokens * cfg.q_dim / 2.0 \
+        + 2.0 * cfg.vocab_size * cfg.hidden_size
+    return {"kernel": "prefill_step", "tokens": tokens, "ms": times, "flops": flops,
+            "tflop_per_s": [round(flops / (t * 1e-3) * 1e-12, 1) for t in times]}
+
+
 def step_parts(model: dict, batch: int, prompt_min: int = 128, prompt_max: int = 2048) -> dict:
     """What each kind of kernel costs inside a decode step of `batch` sequences of the whole model: the
     captured step (model, greedy sampler, move to the next position) is timed as it is and again with
@@ -406,6 +438,9 @@ def main(kernel: str, model: dict, tokens: int, context: int, eager_only: bool =
         return 0
     if kernel == "step_timeline":
         print(json.dumps(step_timeline(model, tokens)))
+        return 0
+    if kernel == "prefill_step":
+        print(json.dumps(prefill_step(model, tokens)))
         return 0
     print(json.dumps(run(kernel, model, tokens, context, eager_only)))
     return 0
