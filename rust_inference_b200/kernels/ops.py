@@ -365,6 +365,13 @@ def sample_cluster_min_vocab(vocab: int) -> None:
     load("sampling").ri_sample_set_cluster_min_vocab(c_int(vocab))
 
 
+def sample_cluster_any_rows(on: bool) -> None:
+    """Whether such rows are sampled by clusters however many rows a call brings (the library's default:
+    only while the clusters are few enough to run together; more rows take a block each).  For
+    comparisons and tests."""
+    load("sampling").ri_sample_set_cluster_any_rows(c_int(1 if on else 0))
+
+
 def attention_mma_supports(head_dim: int, page_size: int, n_heads: int, n_kv_heads: int, decode: bool) -> bool:
     lib = load("attention_mma")
     return bool(lib.ri_attention_mma_supports(c_int(head_dim), c_int(page_size), c_int(n_heads),

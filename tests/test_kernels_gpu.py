@@ -514,8 +514,10 @@ def sampling_kernel(request):
     that gives it to a cluster of eight wherever the options allow it (whatever the size of the vocabulary)."""
     ops = _ops()
     ops.sample_cluster_min_vocab(0 if request.param == "a block per row" else 1)
+    ops.sample_cluster_any_rows(True)
     yield request.param
     ops.sample_cluster_min_vocab(32768)
+    ops.sample_cluster_any_rows(False)
 
 
 def _sample(logits, **kw):
