@@ -60,10 +60,10 @@ def decode_plan(n_seqs: int, n_kv_heads: int, max_seq_len: int, page_size: int, 
                 splits -= 1
         if splits >= 2:
             return "cluster", splits
+    # no clusters (one run per sequence is enough, or the device holds too few): the same kernel, its runs,
+    # if any, merged through scratch by a second kernel
     splits = decode_splits(n_seqs, n_kv_heads, max_seq_len, page_size)
-    if _DECODE == "tma" or (_DECODE in ("auto", "cluster") and splits == 1):
-        return "tma", splits
-    return "cp_async", splits
+    return ("cp_async" if _DECODE == "cp_async" else "tma"), splits
 
 
 def decode_kernel(name: str):
