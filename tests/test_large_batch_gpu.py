@@ -29,7 +29,7 @@ def test_eighty_sequences_decode_together(name, dtype, model_factory):
     eng = Engine.from_pretrained(model.folder, dtype=dtype, max_tokens=N_SEQS * 192)
     if dtype == "bfloat16":
         plan = attn.decode_plan(N_SEQS, model.cfg["num_key_value_heads"], eng.cache.page_table.shape[1] * 64, 64)
-        assert plan == ("tma", 1)
+        assert plan == ("tma", 1) or attn._DECODE != "auto"          # unless the environment forces a kernel
     slots = [eng.alloc_slot() for _ in seqs]
     for g in range(0, N_SEQS, 16):                                      # prompts in unequal groups of 16
         got = eng.step(slots[g:g + 16], [s[:n] for s, n in zip(seqs[g:g + 16], lens[g:g + 16])], "last").cpu()
