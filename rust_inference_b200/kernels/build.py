@@ -197,6 +197,11 @@ def loaded_cuda_modules() -> list[str]:
     return [m for m in _loaded if MODULES[m].endswith(".cu")]
 
 
-def build_all(verbose: bool = True, checked: bool | None = None, timeline: bool | None = None) -> list[str]:
-    return [build(m, verbose=verbose, checked=checked, timeline=timeline) for m in MODULES
-            if os.path.isfile(os.path.join(CSRC, MODULES[m]))]
+def build_all(verbose: bool = True, checked: bool | None = None, timeline: bool | None = None,
+              jobs: int | None = None) -> list[str]:
+    """Every module of one build, several compilers at a time (`jobs`; default: the machine's cores, 8 at most)."""
+    from concurrent.futures import ThreadPoolExecutor
+    names = [m for m in MODULES if os.path.isfile(os.path.join(CSRC, MODULES[m]))]
+    jobs = jobs or max(1, min(8, os.cpu_count() or 1))
+    with ThreadPoolExecutor(max_workers=jobs) as pool:
+        return list(pool.map(lambda m: build(m, verbose=verbose, checked=checked, timeline=timeline), names))
