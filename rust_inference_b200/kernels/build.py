@@ -89,7 +89,7 @@ def _build_dir(checked: bool | None = None, timeline: bool | None = None) -> str
         d = os.path.join(d, "timeline")
     try:
         os.makedirs(d, exist_ok=True)
-        probe = os.path.join(d, f".w{os.getpid()}")
+        probe = os.path.join(d, f".w{os.getpid()}_{threading.get_ident()}")      # several threads may ask at once
         with open(probe, "w"):
             pass
         os.remove(probe)
